@@ -1,0 +1,106 @@
+// Fused multi-tensor Adam step. Replaces the ~14 array expressions per parameter tensor of
+// Adam.step (endia/optim/adam.mojo:47-65) with one launch over all tensors; the operation order
+// inside an element follows the reference so that fp32 results agree to rounding.
+#include "common.cuh"
+
+namespace eb {
+
+constexpr int ADAM_MAX_TENSORS = 48;  // per launch; longer lists are issued in groups
+constexpr int ADAM_CHUNK = 256 * 4 * 8;  // elements per CTA work item
+
+struct AdamArgs {
+  float *p[ADAM_MAX_TENSORS];
+  const float *g[ADAM_MAX_TENSORS];
+  float *m[ADAM_MAX_TENSORS];
+  float *v[ADAM_MAX_TENSORS];
+  int64_t chunk_start[ADAM_MAX_TENSORS + 1];  // prefix sum of chunks per tensor
+  int64_t numel[ADAM_MAX_TENSORS];
+  int n;
+  float lr, b1, b2, eps, omb1, omb2, c1, c2, gscale;
+};
+
+__device__ __forceinline__ void adam_one(float &p, float g, float &m, float &v, const AdamArgs &a) {
+  g *= a.gscale;
+  m = a.b1 * m + a.omb1 * g;           // adam.mojo:49-51
+  v = a.b2 * v + (a.omb2 * g) * g;     // adam.mojo:52-56, (1-b2)*g*g left to right
+  const float mhat = m / a.c1;         // adam.mojo:57-58
+  const float vhat = v / a.c2;
+  p = p - (a.lr * mhat) / (sqrtf(vhat) + a.eps);  // adam.mojo:61-63
+}
+
+__global__ void __launch_bounds__(256) adam_kernel(const __grid_constant__ AdamArgs a) {
+  const int64_t total = a.chunk_start[a.n];
+  for (int64_t c = blockIdx.x; c < total; c += gridDim.x) {
+    int t = 0;
+    while (t + 1 < a.n && a.chunk_start[t + 1] <= c) ++t;
+    const int64_t n = a.numel[t];
+    const int64_t e0 = (c - a.chunk_start[t]) * ADAM_CHUNK;
+    int64_t e1 = e0 + ADAM_CHUNK;
+    if (e1 > n) e1 = n;
+    float *p = a.p[t]; const float *g = a.g[t]; float *m = a.m[t]; float *v = a.v[t];
+    const bool vec = ((reinterpret_cast<uintptr_t>(p) | reinterpret_cast<uintptr_t>(g) |
+                       reinterpret_cast<uintptr_t>(m) | reinterpret_cast<uintptr_t>(v)) & 15) == 0;
+    if (vec) {
+      const int64_t v1 = e1 & ~int64_t(3);
+      for (int64_t i = e0 + threadIdx.x * 4; i < v1; i += 256 * 4) {
+        float4 pp = *reinterpret_cast<float4 *>(p + i);
+        float4 gg = __ldg(reinterpret_cast<const float4 *>(g + i));
+        float4 mm = *reinterpret_cast<float4 *>(m + i);
+        float4 vv = *reinterpret_cast<float4 *>(v + i);
+        adam_one(pp.x, gg.x, mm.x, vv.x, a); adam_one(pp.y, gg.y, mm.y, vv.y, a);
+        adam_one(pp.z, gg.z, mm.z, vv.z, a); adam_one(pp.w, gg.w, mm.w, vv.w, a);
+        *reinterpret_cast<float4 *>(p + i) = pp;
+        *reinterpret_cast<float4 *>(m + i) = mm;
+        *reinterpret_cast<float4 *>(v + i) = vv;
+      }
+      for (int64_t i = v1 + threadIdx.x; i < e1; i += 256) adam_one(p[i], g[i], m[i], v[i], a);
+    } else {
+      for (int64_t i = e0 + threadIdx.x; i < e1; i += 256) adam_one(p[i], g[i], m[i], v[i], a);
+    }
+  }
+}
+
+}  // namespace eb
+
+using namespace eb;
+
+extern "C" int endia_b200_adam_step_multi(int32_t n_tensors, float *const *params,
+                                          const float *const *grads, float *const *m,
+                                          float *const *v, const int64_t *numel, float lr,
+                                          float beta1, float beta2, float eps, float t,
+                                          float grad_scale, void *stream) {
+  int st = require_device();
+  if (st) return st;
+  EB_REQUIRE(n_tensors >= 0, ENDIA_B200_EINVAL, "adam: negative tensor count");
+  if (n_tensors == 0) return ENDIA_B200_OK;
+  EB_REQUIRE(params && grads && m && v && numel, ENDIA_B200_EINVAL, "adam: NULL argument array");
+  EB_REQUIRE(t >= 1.f, ENDIA_B200_EINVAL, "adam: step count t starts at 1 (adam.mojo:40)");
+  for (int i0 = 0; i0 < n_tensors; i0 += ADAM_MAX_TENSORS) {
+    AdamArgs a{};
+    a.n = 0;
+    a.chunk_start[0] = 0;
+    for (int i = i0; i < n_tensors && a.n < ADAM_MAX_TENSORS; ++i) {
+      EB_REQUIRE(numel[i] >= 0, ENDIA_B200_EINVAL, "adam: negative numel for tensor %d", i);
+      if (numel[i] == 0) continue;
+      EB_REQUIRE(params[i] && grads[i] && m[i] && v[i], ENDIA_B200_EINVAL,
+                 "adam: NULL pointer for tensor %d", i);
+      a.p[a.n] = params[i]; a.g[a.n] = grads[i]; a.m[a.n] = m[i]; a.v[a.n] = v[i];
+      a.numel[a.n] = numel[i];
+      a.chunk_start[a.n + 1] = a.chunk_start[a.n] + ceil_div(numel[i], ADAM_CHUNK);
+      ++a.n;
+    }
+    if (a.n == 0) continue;
+    a.lr = lr; a.b1 = beta1; a.b2 = beta2; a.eps = eps; a.gscale = grad_scale;
+    // fp32 scalars exactly as the reference forms them (adam.mojo:50, 54, 57-58).
+    a.omb1 = 1.f - beta1;
+    a.omb2 = 1.f - beta2;
+    a.c1 = 1.f - powf(beta1, t);
+    a.c2 = 1.f - powf(beta2, t);
+    int64_t total = a.chunk_start[a.n];
+    int64_t cap = (int64_t)(sm_count() > 0 ? sm_count() : 148) * 8;
+    int grid = (int)(total < cap ? total : cap);
+    adam_kernel<<<grid, 256, 0, as_stream(stream)>>>(a);
+    EB_LAUNCH_CHECK();
+  }
+  return ENDIA_B200_OK;
+}

@@ -1,0 +1,429 @@
+// Complex64 FFT: shared-memory Stockham kernels (radix 16/8/4/2 butterflies in registers),
+// tiled over lines so that strided axes are read and written in contiguous segments, and a
+// four-step split (two passes with a twiddle in between) for lengths that do not fit in shared
+// memory. Replaces the float64 radix-2 Cooley-Tukey core and the per-axis transposing gathers of
+// fft_cooley_tukey_parallel (endia/functional/fft_ops/fft_cooley_tukey.mojo:133-176, 241-297).
+// The inverse direction is conj -> forward -> conj, as IFFTN and FFTN.vjp state it
+// (ifftn_op.mojo:60-77, fftn_op.mojo:43-49), fused into the first load and the last store.
+#include "common.cuh"
+#include <map>
+#include <mutex>
+#include <vector>
+#include <math.h>
+
+namespace eb {
+
+constexpr int FFT_E = 16;            // complex elements held by one thread
+constexpr int FFT_MAX_SMEM_N = 4096; // longest line transformed inside one CTA
+constexpr int FFT_MAX_STAGES = 6;
+
+struct FftParams {
+  const float2 *in;
+  float2 *out;
+  int N;
+  int T, logT;                   // lines per tile (power of two)
+  int n_stages;
+  int radix[FFT_MAX_STAGES];
+  int64_t n_tiles, lines_per_outer, tiles_per_outer;
+  int64_t in_outer_stride, in_line_stride, in_elem_stride;
+  int64_t out_outer_stride, out_line_stride, out_elem_stride;
+  const float2 *tw;              // W_N^q, q in [0, N)
+  int conj_in, conj_out;
+  float scale;
+  // Four-step twiddle applied at the store: element j of line l is multiplied by
+  // W_big^(j*l) = tw_hi[(j*l) >> lo_bits] * tw_lo[(j*l) & mask].
+  const float2 *tw_hi, *tw_lo;
+  int lo_bits;
+};
+
+__device__ __forceinline__ float2 cmul(float2 a, float2 b) {
+  return make_float2(a.x * b.x - a.y * b.y, a.x * b.y + a.y * b.x);
+}
+__device__ __forceinline__ float2 cadd(float2 a, float2 b) { return make_float2(a.x + b.x, a.y + b.y); }
+__device__ __forceinline__ float2 csub(float2 a, float2 b) { return make_float2(a.x - b.x, a.y - b.y); }
+// multiply by -i
+__device__ __forceinline__ float2 mul_mi(float2 a) { return make_float2(a.y, -a.x); }
+
+template <int R>
+__device__ __forceinline__ void dft(float2 *u);
+
+template <>
+__device__ __forceinline__ void dft<2>(float2 *u) {
+  float2 a = u[0], b = u[1];
+  u[0] = cadd(a, b);
+  u[1] = csub(a, b);
+}
+template <>
+__device__ __forceinline__ void dft<4>(float2 *u) {
+  float2 a = cadd(u[0], u[2]), b = csub(u[0], u[2]);
+  float2 c = cadd(u[1], u[3]), d = mul_mi(csub(u[1], u[3]));
+  u[0] = cadd(a, c); u[1] = cadd(b, d); u[2] = csub(a, c); u[3] = csub(b, d);
+}
+template <>
+__device__ __forceinline__ void dft<8>(float2 *u) {
+  float2 e[4] = {u[0], u[2], u[4], u[6]};
+  float2 o[4] = {u[1], u[3], u[5], u[7]};
+  dft<4>(e);
+  dft<4>(o);
+  const float h = 0.70710678118654752440f;
+  o[1] = make_float2(h * (o[1].x + o[1].y), h * (o[1].y - o[1].x));   // * (1 - i)/sqrt2
+  o[2] = mul_mi(o[2]);
+  o[3] = make_float2(h * (o[3].y - o[3].x), -h * (o[3].x + o[3].y));  // * (-1 - i)/sqrt2
+#pragma unroll
+  for (int k = 0; k < 4; ++k) { u[k] = cadd(e[k], o[k]); u[k + 4] = csub(e[k], o[k]); }
+}
+template <>
+__device__ __forceinline__ void dft<16>(float2 *u) {
+  // 4 x 4 decomposition: DFT-4 over m of u[j + 4m], twiddle W16^(j q), DFT-4 over j.
+  float2 a[4][4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+#pragma unroll
+    for (int m = 0; m < 4; ++m) a[j][m] = u[j + 4 * m];
+    dft<4>(a[j]);
+  }
+  const float c1 = 0.92387953251128675613f, s1 = 0.38268343236508977173f;  // cos, sin(pi/8)
+  const float h = 0.70710678118654752440f;
+  const float2 w[10] = {
+      make_float2(1.f, 0.f),  make_float2(c1, -s1), make_float2(h, -h),  make_float2(s1, -c1),
+      make_float2(0.f, -1.f), make_float2(-s1, -c1), make_float2(-h, -h), make_float2(-c1, -s1),
+      make_float2(-1.f, 0.f), make_float2(-c1, s1)};
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    float2 b[4];
+    b[0] = a[0][q];
+#pragma unroll
+    for (int j = 1; j < 4; ++j) b[j] = (q == 0) ? a[j][q] : cmul(a[j][q], w[j * q]);
+    dft<4>(b);
+#pragma unroll
+    for (int s = 0; s < 4; ++s) u[q + 4 * s] = b[s];
+  }
+}
+
+// One Stockham stage of radix R over every line of the tile. `p` is the product of the radices
+// of the earlier stages. Every thread owns FFT_E/R butterflies; all reads of the stage happen
+// before the barrier and all writes after it, so the stage runs in place.
+template <int R>
+__device__ __forceinline__ void stage(float2 *sm, const FftParams &P, int p, int tid) {
+  constexpr int ITEMS = FFT_E / R;
+  const int T = P.T, LS = T + 1;
+  const int per_line = P.N / R;        // butterflies per line
+  const int tw_step = P.N / (p * R);
+  float2 u[ITEMS][R];
+  int jout[ITEMS];
+#pragma unroll
+  for (int it = 0; it < ITEMS; ++it) {
+    const int w = tid + it * blockDim.x;  // t fastest
+    const int t = w & (T - 1), i = w >> P.logT;
+    const int k = i & (p - 1);
+#pragma unroll
+    for (int r = 0; r < R; ++r) u[it][r] = sm[(i + r * per_line) * LS + t];
+    if (p > 1) {
+#pragma unroll
+      for (int r = 1; r < R; ++r) u[it][r] = cmul(u[it][r], __ldg(P.tw + r * k * tw_step));
+    }
+    dft<R>(u[it]);
+    jout[it] = ((i - k) * R + k) * LS + t;
+  }
+  __syncthreads();
+#pragma unroll
+  for (int it = 0; it < ITEMS; ++it) {
+#pragma unroll
+    for (int r = 0; r < R; ++r) sm[jout[it] + r * p * LS] = u[it][r];
+  }
+  __syncthreads();
+}
+
+__global__ void __launch_bounds__(1024, 1) fft_tile_kernel(const __grid_constant__ FftParams P) {
+  extern __shared__ float2 sm[];
+  const int tid = threadIdx.x, nthr = blockDim.x;
+  const int T = P.T, LS = T + 1, N = P.N;
+  const int total = T * N;
+  for (int64_t tile = blockIdx.x; tile < P.n_tiles; tile += gridDim.x) {
+    const int64_t o = tile / P.tiles_per_outer;
+    const int64_t line0 = (tile - o * P.tiles_per_outer) * T;
+    int64_t nl64 = P.lines_per_outer - line0;
+    const int nl = nl64 < T ? (int)nl64 : T;
+    // ---- load
+    const float2 *src = P.in + o * P.in_outer_stride + line0 * P.in_line_stride;
+    if (P.in_elem_stride == 1) {
+      for (int w = tid; w < total; w += nthr) {
+        const int t = w / N, j = w - t * N;
+        float2 v = make_float2(0.f, 0.f);
+        if (t < nl) v = src[(int64_t)t * P.in_line_stride + j];
+        if (P.conj_in) v.y = -v.y;
+        sm[j * LS + t] = v;
+      }
+    } else {
+      for (int w = tid; w < total; w += nthr) {
+        const int t = w & (T - 1), j = w >> P.logT;
+        float2 v = make_float2(0.f, 0.f);
+        if (t < nl) v = src[(int64_t)t * P.in_line_stride + (int64_t)j * P.in_elem_stride];
+        if (P.conj_in) v.y = -v.y;
+        sm[j * LS + t] = v;
+      }
+    }
+    __syncthreads();
+    // ---- stages
+    int p = 1;
+    for (int s = 0; s < P.n_stages; ++s) {
+      const int R = P.radix[s];
+      if (R == 16) stage<16>(sm, P, p, tid);
+      else if (R == 8) stage<8>(sm, P, p, tid);
+      else if (R == 4) stage<4>(sm, P, p, tid);
+      else stage<2>(sm, P, p, tid);
+      p *= R;
+    }
+    // ---- store
+    float2 *dst = P.out + o * P.out_outer_stride + line0 * P.out_line_stride;
+    const bool t_fast = P.out_elem_stride != 1;
+    for (int w = tid; w < total; w += nthr) {
+      int t, j;
+      if (t_fast) { t = w & (T - 1); j = w >> P.logT; }
+      else { t = w / N; j = w - t * N; }
+      if (t >= nl) continue;
+      float2 v = sm[j * LS + t];
+      if (P.tw_hi) {
+        const int64_t q = (int64_t)j * (line0 + t);
+        v = cmul(v, cmul(__ldg(P.tw_hi + (q >> P.lo_bits)),
+                         __ldg(P.tw_lo + (q & ((int64_t(1) << P.lo_bits) - 1)))));
+      }
+      v.x *= P.scale; v.y *= P.scale;
+      if (P.conj_out) v.y = -v.y;
+      dst[(int64_t)t * P.out_line_stride + (int64_t)j * P.out_elem_stride] = v;
+    }
+    __syncthreads();
+  }
+}
+
+// ------------------------------------------------------------------ host side
+static std::mutex g_tw_mutex;
+static std::map<std::pair<int, int64_t>, float2 *> g_tw_cache;  // (device, key) -> table
+
+// Table of `count` entries: entry q = exp(-2*pi*i * q * mult / n), evaluated in float64.
+static int twiddle_table(int64_t n, int64_t mult, int64_t count, int kind, const float2 **out) {
+  int dev = 0;
+  EB_CUDA(cudaGetDevice(&dev));
+  const int64_t key = (n << 8) | (int64_t)kind;
+  std::lock_guard<std::mutex> lock(g_tw_mutex);
+  auto it = g_tw_cache.find({dev, key});
+  if (it != g_tw_cache.end()) { *out = it->second; return ENDIA_B200_OK; }
+  std::vector<float2> host((size_t)count);
+  const long double two_pi = 6.283185307179586476925286766559L;
+  for (int64_t q = 0; q < count; ++q) {
+    // Reduce the angle to an exact fraction of the circle before the float64 evaluation.
+    const int64_t num = (q * mult) % n;
+    const long double ang = -two_pi * (long double)num / (long double)n;
+    host[(size_t)q] = make_float2((float)cosl(ang), (float)sinl(ang));
+  }
+  float2 *dev_ptr = nullptr;
+  cudaError_t e = cudaMalloc(&dev_ptr, sizeof(float2) * (size_t)count);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    set_error("fft: twiddle table allocation failed");
+    return ENDIA_B200_ENOMEM;
+  }
+  EB_CUDA(cudaMemcpy(dev_ptr, host.data(), sizeof(float2) * (size_t)count, cudaMemcpyHostToDevice));
+  g_tw_cache[{dev, key}] = dev_ptr;
+  *out = dev_ptr;
+  return ENDIA_B200_OK;
+}
+
+static void plan_radices(int N, FftParams &P) {
+  int L = ilog2(N);
+  P.n_stages = 0;
+  while (L > 0) {
+    int l = L >= 4 ? 4 : L;
+    if (L == 5) l = 3;  // 8 * 4 rather than 16 * 2
+    P.radix[P.n_stages++] = 1 << l;
+    L -= l;
+  }
+}
+
+// Lines per tile for a line length N: at least 2048 elements per CTA (128 threads), 16 lines
+// (128-byte segments on strided axes) where shared memory allows.
+static int pick_T(int N) {
+  int T = 16;
+  while (T * N < 2048) T *= 2;
+  while (T > 1 && (size_t)N * (T + 1) * sizeof(float2) > 200 * 1024) T /= 2;
+  if (N == 1024) T = 8;  // 3 CTAs per SM instead of 1
+  return T;
+}
+
+struct Pass {
+  int N;
+  int64_t n_outer, lines_per_outer;
+  int64_t in_outer, in_line, in_elem, out_outer, out_line, out_elem;
+  int conj_in, conj_out;
+  float scale;
+  int64_t big_n;  // > 0: four-step twiddle W_big^(j*line) at the store
+};
+
+static int launch_pass(const Pass &ps, const float2 *in, float2 *out, cudaStream_t s) {
+  FftParams P{};
+  P.in = in; P.out = out; P.N = ps.N;
+  P.T = pick_T(ps.N); P.logT = ilog2(P.T);
+  plan_radices(ps.N, P);
+  P.lines_per_outer = ps.lines_per_outer;
+  P.tiles_per_outer = ceil_div(ps.lines_per_outer, P.T);
+  P.n_tiles = P.tiles_per_outer * ps.n_outer;
+  P.in_outer_stride = ps.in_outer; P.in_line_stride = ps.in_line; P.in_elem_stride = ps.in_elem;
+  P.out_outer_stride = ps.out_outer; P.out_line_stride = ps.out_line; P.out_elem_stride = ps.out_elem;
+  P.conj_in = ps.conj_in; P.conj_out = ps.conj_out; P.scale = ps.scale;
+  if (P.n_tiles == 0) return ENDIA_B200_OK;
+  int st = twiddle_table(ps.N, 1, ps.N, 0, &P.tw);
+  if (st) return st;
+  if (ps.big_n > 0) {
+    const int lb = ilog2(ps.big_n);
+    P.lo_bits = (lb + 1) / 2;
+    if ((st = twiddle_table(ps.big_n, 1, int64_t(1) << P.lo_bits, 1, &P.tw_lo))) return st;
+    if ((st = twiddle_table(ps.big_n, int64_t(1) << P.lo_bits, int64_t(1) << (lb - P.lo_bits), 2,
+                            &P.tw_hi))) return st;
+  }
+  int threads = P.T * ps.N / FFT_E;
+  if (threads < 32) threads = 32;  // short tiles: surplus threads own no butterfly
+  const size_t smem = sizeof(float2) * (size_t)ps.N * (P.T + 1);
+  static bool attr_set = false;
+  if (!attr_set) {
+    EB_CUDA(cudaFuncSetAttribute(fft_tile_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 227 * 1024));
+    attr_set = true;
+  }
+  int64_t cap = (int64_t)(sm_count() > 0 ? sm_count() : 148) * 4;
+  int grid = (int)(P.n_tiles < cap ? P.n_tiles : cap);
+  fft_tile_kernel<<<grid, threads, smem, s>>>(P);
+  EB_LAUNCH_CHECK();
+  return ENDIA_B200_OK;
+}
+
+// Splits a long line length into N1 * N2 with both factors <= FFT_MAX_SMEM_N.
+static bool split_len(int64_t N, int &N1, int &N2) {
+  const int L = ilog2(N);
+  const int l1 = (L + 1) / 2;
+  N1 = 1 << l1; N2 = 1 << (L - l1);
+  return N1 <= FFT_MAX_SMEM_N && N2 <= FFT_MAX_SMEM_N;
+}
+
+struct AxisInfo { int64_t outer, n, inner; };
+
+static int collect_axes(const endia_b200_tensor *in, const int32_t *dims, int32_t n_dims,
+                        std::vector<AxisInfo> &axes, bool &need_scratch) {
+  need_scratch = false;
+  uint32_t seen = 0;
+  for (int a = 0; a < n_dims; ++a) {
+    int d = dims[a] < 0 ? dims[a] + in->ndim : dims[a];
+    EB_REQUIRE(d >= 0 && d < in->ndim, ENDIA_B200_EINVAL, "fft: dim %d out of range for rank %d",
+               dims[a], in->ndim);
+    EB_REQUIRE(!((seen >> d) & 1u), ENDIA_B200_EINVAL, "fft: dim %d listed twice", dims[a]);
+    seen |= 1u << d;
+    const int64_t n = in->shape[d];
+    // fft_cooley_tukey.mojo:227-235 raises for lengths that are not powers of two.
+    EB_REQUIRE(is_pow2(n), ENDIA_B200_EPOW2, "fft: length %lld of dim %d is not a power of two",
+               (long long)n, d);
+    AxisInfo ai{1, n, 1};
+    for (int e = 0; e < d; ++e) ai.outer *= in->shape[e];
+    for (int e = d + 1; e < in->ndim; ++e) ai.inner *= in->shape[e];
+    if (n > FFT_MAX_SMEM_N) {
+      int n1, n2;
+      EB_REQUIRE(split_len(n, n1, n2), ENDIA_B200_ELIMIT, "fft: length %lld exceeds the limit %lld",
+                 (long long)n, (long long)FFT_MAX_SMEM_N * FFT_MAX_SMEM_N);
+      EB_REQUIRE(ai.inner == 1, ENDIA_B200_ELIMIT,
+                 "fft: lengths above %d are supported on the innermost axis only", FFT_MAX_SMEM_N);
+      need_scratch = true;
+    }
+    if (n > 1) axes.push_back(ai);
+  }
+  return ENDIA_B200_OK;
+}
+
+}  // namespace eb
+
+using namespace eb;
+
+extern "C" {
+
+size_t endia_b200_fft_scratch_bytes(const endia_b200_tensor *in, const int32_t *dims,
+                                    int32_t n_dims) {
+  if (!in || (n_dims > 0 && !dims)) return 0;
+  std::vector<AxisInfo> axes;
+  bool need = false;
+  if (collect_axes(in, dims, n_dims, axes, need)) return 0;
+  return need ? sizeof(float2) * (size_t)numel(in) : 0;
+}
+
+int endia_b200_fft_c2c(const endia_b200_tensor *in, const endia_b200_tensor *out,
+                       const int32_t *dims, int32_t n_dims, int inverse, float scale, void *scratch,
+                       void *stream) {
+  int st = require_device();
+  if (st) return st;
+  if ((st = check_tensor(in, "fft: in"))) return st;
+  if ((st = check_tensor(out, "fft: out"))) return st;
+  EB_REQUIRE(in->is_complex && out->is_complex, ENDIA_B200_EINVAL, "fft: in and out must be complex");
+  EB_REQUIRE(n_dims >= 0 && n_dims <= ENDIA_B200_MAX_DIMS && (n_dims == 0 || dims), ENDIA_B200_EINVAL,
+             "fft: bad dims list");
+  EB_REQUIRE(in->ndim == out->ndim, ENDIA_B200_ESHAPE, "fft: rank mismatch");
+  for (int d = 0; d < in->ndim; ++d)
+    EB_REQUIRE(in->shape[d] == out->shape[d], ENDIA_B200_ESHAPE, "fft: shape mismatch in dim %d", d);
+  EB_REQUIRE(is_contiguous(out), ENDIA_B200_EINVAL, "fft: out must be contiguous");
+  std::vector<AxisInfo> axes;
+  bool need_scratch = false;
+  if ((st = collect_axes(in, dims, n_dims, axes, need_scratch))) return st;
+  EB_REQUIRE(!need_scratch || scratch, ENDIA_B200_EINVAL,
+             "fft: scratch of endia_b200_fft_scratch_bytes() bytes is required");
+  const int64_t total = numel(in);
+  if (total == 0) return ENDIA_B200_OK;
+  cudaStream_t s = as_stream(stream);
+  const float2 *src = reinterpret_cast<const float2 *>(in->data) + in->offset;
+  float2 *dst = reinterpret_cast<float2 *>(out->data) + out->offset;
+  if (!is_contiguous(in)) {
+    // Gather the strided view once; the transform then runs in place on `out`.
+    if ((st = endia_b200_ew_unary(ENDIA_B200_UN_COPY, in, out, stream))) return st;
+    src = dst;
+  }
+  if (axes.empty()) {
+    // Nothing to transform: out = scale * in (the inverse of a length-1 transform is itself).
+    Pass ps{1, 1, total, 0, 1, 1, 0, 1, 1, 0, 0, scale, 0};
+    return launch_pass(ps, src, dst, s);
+  }
+  // Innermost axis first: its pass reads `in` in long contiguous runs.
+  for (size_t a = axes.size(); a-- > 0;) {
+    const AxisInfo &ai = axes[a];
+    const bool first = (a + 1 == axes.size()), last = (a == 0);
+    const int cin = (inverse && first) ? 1 : 0, cout = (inverse && last) ? 1 : 0;
+    const float sc = last ? scale : 1.f;
+    if (ai.n <= FFT_MAX_SMEM_N) {
+      Pass ps{};
+      ps.N = (int)ai.n; ps.conj_in = cin; ps.conj_out = cout; ps.scale = sc; ps.big_n = 0;
+      if (ai.inner == 1) {
+        ps.n_outer = 1; ps.lines_per_outer = ai.outer;
+        ps.in_outer = ps.out_outer = 0; ps.in_line = ps.out_line = ai.n; ps.in_elem = ps.out_elem = 1;
+      } else {
+        ps.n_outer = ai.outer; ps.lines_per_outer = ai.inner;
+        ps.in_outer = ps.out_outer = ai.n * ai.inner; ps.in_line = ps.out_line = 1;
+        ps.in_elem = ps.out_elem = ai.inner;
+      }
+      if ((st = launch_pass(ps, src, dst, s))) return st;
+    } else {
+      int n1, n2;
+      split_len(ai.n, n1, n2);
+      float2 *tmp = reinterpret_cast<float2 *>(scratch);
+      // Pass A: for every n2, transform over n1 (stride n2), then multiply by W_n^(k1*n2).
+      Pass pa{};
+      pa.N = n1; pa.n_outer = ai.outer; pa.lines_per_outer = n2;
+      pa.in_outer = pa.out_outer = ai.n; pa.in_line = pa.out_line = 1; pa.in_elem = pa.out_elem = n2;
+      pa.conj_in = cin; pa.conj_out = 0; pa.scale = 1.f; pa.big_n = ai.n;
+      if ((st = launch_pass(pa, src, tmp, s))) return st;
+      // Pass B: for every k1, transform the contiguous row over n2; X[k1 + n1*k2] = row[k2].
+      Pass pb{};
+      pb.N = n2; pb.n_outer = ai.outer; pb.lines_per_outer = n1;
+      pb.in_outer = pb.out_outer = ai.n; pb.in_line = n2; pb.in_elem = 1;
+      pb.out_line = 1; pb.out_elem = n1;
+      pb.conj_in = 0; pb.conj_out = cout; pb.scale = sc; pb.big_n = 0;
+      if ((st = launch_pass(pb, tmp, dst, s))) return st;
+    }
+    src = dst;
+  }
+  return ENDIA_B200_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,61 @@
+// Parameters shared by the GEMM kernels and the epilogue they all apply.
+#pragma once
+#include "common.cuh"
+
+namespace eb {
+
+struct EpiParams {
+  float alpha, beta;
+  const float *bias;
+  int act, dact;
+  const float *dact_src;
+  int64_t ld_dact;
+  float *colsum_partial;  // [row tiles (x batch), N] partial column sums, or NULL
+};
+
+struct GemmParams {
+  const float *A, *B;
+  float *C;
+  int64_t M, N, K, lda, ldb, ldc;
+  int64_t stride_a, stride_b, stride_c;
+  bool vec_a, vec_b, vec_c;  // 16-byte aligned base, leading dimension and batch stride
+  EpiParams epi;
+};
+
+__device__ __forceinline__ float act_fwd(int act, float v) {
+  switch (act) {
+    case ENDIA_B200_ACT_RELU: return fmaxf(v, 0.f);                 // relu_op.mojo:115
+    case ENDIA_B200_ACT_TANH: return tanhf(v);                      // tanh_op.mojo:112-115
+    case ENDIA_B200_ACT_SIGMOID: return 1.f / (1.f + expf(-v));     // sigmoid_op.mojo:118-121
+    default: return v;
+  }
+}
+// Derivative factor from the saved tensor (see endia_b200_epilogue in the public header).
+__device__ __forceinline__ float act_bwd(int dact, float s) {
+  switch (dact) {
+    case ENDIA_B200_ACT_RELU: return s > 0.f ? 1.f : 0.f;           // relu_op.mojo:95
+    case ENDIA_B200_ACT_TANH: return 1.f - s * s;                   // tanh_op.mojo:92
+    case ENDIA_B200_ACT_SIGMOID: return s * (1.f - s);              // sigmoid_op.mojo:98
+    default: return 1.f;
+  }
+}
+
+// v = acc after the fused steps, for output element (m, n); `c_old` points at C[m,n].
+__device__ __forceinline__ float apply_epilogue(const EpiParams &e, float acc, int64_t m, int64_t n,
+                                                const float *c_old) {
+  float v = e.alpha * acc;
+  if (e.bias) v += __ldg(e.bias + n);
+  if (e.act) v = act_fwd(e.act, v);
+  if (e.dact) v *= act_bwd(e.dact, __ldg(e.dact_src + m * e.ld_dact + n));
+  if (e.beta != 0.f) v += e.beta * (*c_old);
+  return v;
+}
+
+int launch_gemm_ffma(const GemmParams &p, int trans_a, int trans_b, int64_t batch, cudaStream_t s);
+int launch_colsum_finish(const float *partial, float *out, int64_t N, int tiles, int64_t batch,
+                         cudaStream_t s);
+// tcgen05 3xTF32 path: true when the shape/alignment is one it handles.
+bool tc_gemm_supported(const GemmParams &p, int trans_a, int trans_b, int64_t batch);
+int launch_gemm_tc(const GemmParams &p, int trans_a, int trans_b, cudaStream_t s);
+
+}  // namespace eb

@@ -1,0 +1,425 @@
+// Sum reductions with a fixed (deterministic) summation tree, and the fused MSE loss.
+// Replaces ReduceAdd.__call__ (endia/functional/reduce_ops/reduce_add_op.mojo:65-210), which
+// accumulates sequentially in fp32, and the op chain of mse (loss_ops/mse_op.mojo:18-20).
+#include "common.cuh"
+
+namespace eb {
+
+constexpr int RD = ENDIA_B200_MAX_DIMS + 1;  // +1: complex arrays get an inner (re, im) dim
+
+struct RedParams {
+  const float *in;
+  float *dst;           // partials [n_out, splits] (or the output itself when splits == 1)
+  int nk, nr;
+  int64_t kshape[RD], kstride[RD];
+  int64_t rshape[RD], rstride[RD];
+  int64_t n_out, n_red;
+  int splits;
+  int64_t red_per_split;
+};
+
+__device__ __forceinline__ int64_t offs(const int64_t *shape, const int64_t *stride, int n,
+                                        int64_t i) {
+  int64_t o = 0;
+  for (int d = n - 1; d >= 0; --d) {
+    int64_t q = i / shape[d];
+    o += (i - q * shape[d]) * stride[d];
+    i = q;
+  }
+  return o;
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+// Sum of `v` over the CTA (blockDim.x a multiple of 32, at most 1024); valid in thread 0.
+__device__ __forceinline__ float block_sum(float v) {
+  __shared__ float warp_part[32];
+  v = warp_sum(v);
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  __syncthreads();
+  if (lane == 0) warp_part[w] = v;
+  __syncthreads();
+  float r = 0.f;
+  if (w == 0) {
+    r = lane < (int)(blockDim.x >> 5) ? warp_part[lane] : 0.f;
+    r = warp_sum(r);
+  }
+  return r;
+}
+
+// GROUP threads cooperate on one (output element, split): GROUP = 256 (a CTA), 32 (a warp) or 1.
+template <int GROUP>
+__global__ void __launch_bounds__(256) reduce_generic_kernel(RedParams p) {
+  const int64_t n_groups = p.n_out * p.splits;
+  const int groups_per_cta = 256 / GROUP;
+  const int g_in_cta = threadIdx.x / GROUP;
+  const int t_in_g = threadIdx.x % GROUP;
+  for (int64_t gbase = (int64_t)blockIdx.x * groups_per_cta; gbase < n_groups;
+       gbase += (int64_t)gridDim.x * groups_per_cta) {
+    const int64_t g = gbase + g_in_cta;
+    float acc = 0.f;
+    if (g < n_groups) {
+      const int64_t o = g / p.splits;
+      const int s = (int)(g - o * p.splits);
+      const int64_t base = offs(p.kshape, p.kstride, p.nk, o);
+      const int64_t r0 = (int64_t)s * p.red_per_split;
+      int64_t r1 = r0 + p.red_per_split;
+      if (r1 > p.n_red) r1 = p.n_red;
+      for (int64_t r = r0 + t_in_g; r < r1; r += GROUP)
+        acc += p.in[base + offs(p.rshape, p.rstride, p.nr, r)];
+    }
+    if constexpr (GROUP == 256) {
+      acc = block_sum(acc);
+      if (threadIdx.x == 0 && g < n_groups) p.dst[g] = acc;
+    } else if constexpr (GROUP == 32) {
+      acc = warp_sum(acc);
+      if (t_in_g == 0 && g < n_groups) p.dst[g] = acc;
+    } else {
+      if (g < n_groups) p.dst[g] = acc;
+    }
+  }
+}
+
+// out[o] = sum_s partial[o*splits + s], sequential in s.
+__global__ void __launch_bounds__(256)
+reduce_finish_kernel(const float *partial, float *out, int64_t n_out, int splits, float scale) {
+  const int64_t step = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t o = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; o < n_out; o += step) {
+    float acc = 0.f;
+    for (int s = 0; s < splits; ++s) acc += partial[o * splits + s];
+    out[o] = acc * scale;
+  }
+}
+
+// Layout [A, R, C] with C contiguous: dst[(a*chunks + chunk)*C + c] = sum over the chunk's rows.
+__global__ void __launch_bounds__(256)
+colsum_partial_kernel(const float *in, float *dst, int64_t R, int64_t C, int64_t a_stride,
+                      int64_t r_stride, int64_t rows_per_chunk) {
+  const int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  const int64_t chunk = blockIdx.y, a = blockIdx.z;
+  const int64_t r0 = chunk * rows_per_chunk;
+  int64_t r1 = r0 + rows_per_chunk;
+  if (r1 > R) r1 = R;
+  const float *src = in + a * a_stride + c;
+  float acc0 = 0.f, acc1 = 0.f, acc2 = 0.f, acc3 = 0.f;
+  int64_t r = r0;
+  for (; r + 3 < r1; r += 4) {
+    acc0 += src[(r + 0) * r_stride];
+    acc1 += src[(r + 1) * r_stride];
+    acc2 += src[(r + 2) * r_stride];
+    acc3 += src[(r + 3) * r_stride];
+  }
+  for (; r < r1; ++r) acc0 += src[r * r_stride];
+  dst[(a * gridDim.y + chunk) * C + c] = (acc0 + acc1) + (acc2 + acc3);
+}
+// out[a*C + c] = sum over chunks, sequential.
+__global__ void __launch_bounds__(256)
+colsum_finish_kernel(const float *partial, float *out, int64_t A, int64_t C, int chunks) {
+  const int64_t step = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < A * C; i += step) {
+    const int64_t a = i / C, c = i - a * C;
+    float acc = 0.f;
+    for (int k = 0; k < chunks; ++k) acc += partial[(a * chunks + k) * C + c];
+    out[i] = acc;
+  }
+}
+
+// Per-CTA partial of sum((p-t)^2); optionally writes dpred = g2n*(p-t).
+__global__ void __launch_bounds__(256)
+mse_partial_kernel(const float *pred, const float *target, int64_t n, float g2n, float *dpred,
+                   float *partial) {
+  float acc = 0.f;
+  const int64_t step = (int64_t)gridDim.x * blockDim.x;
+  const int64_t n4 = ((reinterpret_cast<uintptr_t>(pred) | reinterpret_cast<uintptr_t>(target) |
+                       reinterpret_cast<uintptr_t>(dpred)) & 15) == 0 ? n / 4 : 0;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += step) {
+    float4 p = reinterpret_cast<const float4 *>(pred)[i];
+    float4 t = reinterpret_cast<const float4 *>(target)[i];
+    float4 d = make_float4(p.x - t.x, p.y - t.y, p.z - t.z, p.w - t.w);
+    acc += (d.x * d.x + d.y * d.y) + (d.z * d.z + d.w * d.w);
+    if (dpred)
+      reinterpret_cast<float4 *>(dpred)[i] = make_float4(g2n * d.x, g2n * d.y, g2n * d.z, g2n * d.w);
+  }
+  for (int64_t i = n4 * 4 + (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += step) {
+    float d = pred[i] - target[i];
+    acc += d * d;
+    if (dpred) dpred[i] = g2n * d;
+  }
+  acc = block_sum(acc);
+  if (threadIdx.x == 0) partial[blockIdx.x] = acc;
+}
+
+
+// Fused activation backward + bias gradient over a contiguous [M, N] layer output:
+//   dS[m,n] = grad[m,n] * act'(a[m,n]);  partial[chunk][n] = sum over the chunk's rows of dS.
+// One thread owns 4 adjacent columns (VEC) or 1 and walks its chunk of rows.
+template <int VEC>
+__global__ void __launch_bounds__(256)
+act_bwd_colsum_kernel(int act, const float *a, const float *grad, float *ds, float *partial,
+                      int64_t M, int64_t N, int64_t rows_per_chunk) {
+  const int64_t c = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * VEC;
+  if (c >= N) return;
+  const int64_t r0 = (int64_t)blockIdx.y * rows_per_chunk;
+  int64_t r1 = r0 + rows_per_chunk;
+  if (r1 > M) r1 = M;
+  float acc[VEC];
+#pragma unroll
+  for (int j = 0; j < VEC; ++j) acc[j] = 0.f;
+  for (int64_t r = r0; r < r1; ++r) {
+    float g[VEC], s[VEC];
+    if constexpr (VEC == 4) {
+      *reinterpret_cast<float4 *>(g) = __ldg(reinterpret_cast<const float4 *>(grad + r * N + c));
+      if (act) *reinterpret_cast<float4 *>(s) = __ldg(reinterpret_cast<const float4 *>(a + r * N + c));
+    } else {
+      g[0] = grad[r * N + c];
+      if (act) s[0] = a[r * N + c];
+    }
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) {
+      float f = 1.f;
+      if (act == ENDIA_B200_ACT_RELU) f = s[j] > 0.f ? 1.f : 0.f;          // relu_op.mojo:95
+      else if (act == ENDIA_B200_ACT_TANH) f = 1.f - s[j] * s[j];          // tanh_op.mojo:92
+      else if (act == ENDIA_B200_ACT_SIGMOID) f = s[j] * (1.f - s[j]);     // sigmoid_op.mojo:98
+      g[j] *= f;
+      acc[j] += g[j];
+    }
+    if (ds) {
+      if constexpr (VEC == 4) *reinterpret_cast<float4 *>(ds + r * N + c) = *reinterpret_cast<float4 *>(g);
+      else ds[r * N + c] = g[0];
+    }
+  }
+  if (partial) {
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) partial[(int64_t)blockIdx.y * N + c + j] = acc[j];
+  }
+}
+
+static int act_bwd_chunks(int64_t M, int64_t N) {
+  const int64_t ctas_x = ceil_div(ceil_div(N, 4), 256);
+  int64_t want = ceil_div((int64_t)4 * 148, ctas_x);
+  const int64_t max_chunks = ceil_div(M, 8);
+  if (want > max_chunks) want = max_chunks;
+  if (want < 1) want = 1;
+  if (want > 4096) want = 4096;
+  const int64_t rows = ceil_div(M, want);
+  return (int)ceil_div(M, rows);
+}
+
+struct RedPlan {
+  RedParams p;
+  bool colsum;       // [A, R, C] fast path
+  int64_t A, R, C, a_stride, r_stride;
+  int chunks;
+  int64_t rows_per_chunk;
+  int group;
+  size_t scratch_bytes;
+};
+
+static int make_plan(const endia_b200_tensor *in, uint32_t axes_mask, RedPlan &pl) {
+  int st = check_tensor(in, "reduce_add: in");
+  if (st) return st;
+  // Float view of the input: complex arrays get an extra kept (re, im) dim.
+  int nd = 0;
+  int64_t shape[RD], stride[RD];
+  bool red[RD];
+  const int w = in->is_complex ? 2 : 1;
+  for (int d = 0; d < in->ndim; ++d) {
+    shape[nd] = in->shape[d]; stride[nd] = in->stride[d] * w;
+    red[nd] = (axes_mask >> d) & 1u; ++nd;
+  }
+  if (in->is_complex) { shape[nd] = 2; stride[nd] = 1; red[nd] = false; ++nd; }
+  RedParams &p = pl.p;
+  p = RedParams{};
+  p.in = static_cast<const float *>(in->data) + in->offset * w;
+  p.n_out = 1; p.n_red = 1;
+  // Kept and reduced dims, each collapsed where adjacent dims form one longer dim.
+  for (int d = 0; d < nd; ++d) {
+    if (shape[d] == 1) continue;
+    if (red[d]) {
+      if (p.nr > 0 && p.rstride[p.nr - 1] == stride[d] * shape[d] && d > 0 && red[d - 1]) {
+        p.rshape[p.nr - 1] *= shape[d]; p.rstride[p.nr - 1] = stride[d];
+      } else { p.rshape[p.nr] = shape[d]; p.rstride[p.nr] = stride[d]; ++p.nr; }
+      p.n_red *= shape[d];
+    } else {
+      if (p.nk > 0 && p.kstride[p.nk - 1] == stride[d] * shape[d] && d > 0 && !red[d - 1]) {
+        p.kshape[p.nk - 1] *= shape[d]; p.kstride[p.nk - 1] = stride[d];
+      } else { p.kshape[p.nk] = shape[d]; p.kstride[p.nk] = stride[d]; ++p.nk; }
+      p.n_out *= shape[d];
+    }
+  }
+  for (int d = 0; d < nd; ++d)
+    if (shape[d] == 0) { p.n_out = red[d] ? p.n_out : 0; p.n_red = red[d] ? 0 : p.n_red; }
+  pl.colsum = false;
+  pl.scratch_bytes = 0;
+  // Column-sum fast path: one reduced dim, innermost kept dim contiguous and inside it.
+  if (p.nr == 1 && p.nk >= 1 && p.nk <= 2 && p.kstride[p.nk - 1] == 1 && p.kshape[p.nk - 1] >= 32 &&
+      p.n_red > 1) {
+    pl.C = p.kshape[p.nk - 1];
+    pl.R = p.rshape[0]; pl.r_stride = p.rstride[0];
+    pl.A = p.nk == 2 ? p.kshape[0] : 1;
+    pl.a_stride = p.nk == 2 ? p.kstride[0] : 0;
+    const int64_t ctas_x = ceil_div(pl.C, 256) * pl.A;
+    int64_t want = ceil_div((int64_t)4 * 148, ctas_x);
+    int64_t max_chunks = ceil_div(pl.R, 16);
+    if (want > max_chunks) want = max_chunks;
+    if (want < 1) want = 1;
+    if (want > 65535) want = 65535;
+    pl.rows_per_chunk = ceil_div(pl.R, want);
+    pl.chunks = (int)ceil_div(pl.R, pl.rows_per_chunk);
+    if (pl.A <= 65535) {
+      pl.colsum = true;
+      pl.scratch_bytes = pl.chunks > 1 ? sizeof(float) * pl.A * pl.chunks * pl.C : 0;
+      return ENDIA_B200_OK;
+    }
+  }
+  // Generic path: pick the group size from the amount of work per output element.
+  pl.group = p.n_red >= 2048 ? 256 : (p.n_red >= 64 ? 32 : 1);
+  p.splits = 1;
+  if (pl.group == 256) {
+    const int64_t target = 4 * 148;
+    if (p.n_out < target) {
+      int64_t s = target / (p.n_out > 0 ? p.n_out : 1);
+      int64_t max_s = ceil_div(p.n_red, 4096);
+      if (s > max_s) s = max_s;
+      if (s < 1) s = 1;
+      if (s > 4096) s = 4096;
+      p.splits = (int)s;
+    }
+  }
+  p.red_per_split = ceil_div(p.n_red > 0 ? p.n_red : 1, p.splits);
+  p.splits = (int)ceil_div(p.n_red > 0 ? p.n_red : 1, p.red_per_split);
+  pl.scratch_bytes = p.splits > 1 ? sizeof(float) * p.n_out * p.splits : 0;
+  return ENDIA_B200_OK;
+}
+
+static int mse_ctas(int64_t n) {
+  int64_t c = ceil_div(n, 256 * 16);
+  if (c > 1024) c = 1024;
+  if (c < 1) c = 1;
+  return (int)c;
+}
+
+}  // namespace eb
+
+using namespace eb;
+
+extern "C" {
+
+size_t endia_b200_reduce_scratch_bytes(const endia_b200_tensor *in, uint32_t axes_mask) {
+  RedPlan pl;
+  if (make_plan(in, axes_mask, pl)) return 0;
+  return pl.scratch_bytes;
+}
+
+int endia_b200_reduce_add(const endia_b200_tensor *in, uint32_t axes_mask, float *out, void *scratch,
+                          void *stream) {
+  int st = require_device();
+  if (st) return st;
+  RedPlan pl;
+  if ((st = make_plan(in, axes_mask, pl))) return st;
+  if (pl.p.n_out == 0) return ENDIA_B200_OK;
+  EB_REQUIRE(out != nullptr, ENDIA_B200_EINVAL, "reduce_add: out is NULL");
+  EB_REQUIRE(pl.scratch_bytes == 0 || scratch != nullptr, ENDIA_B200_EINVAL,
+             "reduce_add: %zu bytes of scratch are required", pl.scratch_bytes);
+  cudaStream_t s = as_stream(stream);
+  if (pl.p.n_red == 0) {
+    EB_CUDA(cudaMemsetAsync(out, 0, sizeof(float) * pl.p.n_out, s));
+    return ENDIA_B200_OK;
+  }
+  if (pl.colsum) {
+    dim3 grid((unsigned)ceil_div(pl.C, 256), (unsigned)pl.chunks, (unsigned)pl.A);
+    float *dst = pl.chunks > 1 ? static_cast<float *>(scratch) : out;
+    colsum_partial_kernel<<<grid, 256, 0, s>>>(pl.p.in, dst, pl.R, pl.C, pl.a_stride, pl.r_stride,
+                                               pl.rows_per_chunk);
+    EB_LAUNCH_CHECK();
+    if (pl.chunks > 1) {
+      colsum_finish_kernel<<<grid_for(pl.A * pl.C, 256), 256, 0, s>>>(
+          static_cast<const float *>(scratch), out, pl.A, pl.C, pl.chunks);
+      EB_LAUNCH_CHECK();
+    }
+    return ENDIA_B200_OK;
+  }
+  RedParams p = pl.p;
+  p.dst = p.splits > 1 ? static_cast<float *>(scratch) : out;
+  const int64_t n_groups = p.n_out * p.splits;
+  if (pl.group == 256) {
+    int64_t g = n_groups < (int64_t)148 * 16 ? n_groups : (int64_t)148 * 16;
+    reduce_generic_kernel<256><<<(unsigned)g, 256, 0, s>>>(p);
+  } else if (pl.group == 32) {
+    reduce_generic_kernel<32><<<grid_for(n_groups * 32, 256), 256, 0, s>>>(p);
+  } else {
+    reduce_generic_kernel<1><<<grid_for(n_groups, 256), 256, 0, s>>>(p);
+  }
+  EB_LAUNCH_CHECK();
+  if (p.splits > 1) {
+    reduce_finish_kernel<<<grid_for(p.n_out, 256), 256, 0, s>>>(static_cast<const float *>(scratch),
+                                                                out, p.n_out, p.splits, 1.f);
+    EB_LAUNCH_CHECK();
+  }
+  return ENDIA_B200_OK;
+}
+
+size_t endia_b200_mse_scratch_bytes(int64_t n) { return sizeof(float) * (size_t)mse_ctas(n); }
+
+int endia_b200_mse_fwd_bwd(const float *pred, const float *target, int64_t n, float gscale,
+                           float *loss, float *dpred, void *scratch, void *stream) {
+  int st = require_device();
+  if (st) return st;
+  EB_REQUIRE(n > 0, ENDIA_B200_EINVAL, "mse: n must be positive");
+  EB_REQUIRE(pred && target && loss && scratch, ENDIA_B200_EINVAL, "mse: NULL pointer");
+  cudaStream_t s = as_stream(stream);
+  const int ctas = mse_ctas(n);
+  // 2/n as the reference forms it: two products d*g with g = 1/n, added (mul_op.mojo:125-128,
+  // autograd/functional.mojo:55-57).
+  const float inv_n = 1.f / (float)n;
+  const float g2n = gscale * (inv_n + inv_n);
+  mse_partial_kernel<<<ctas, 256, 0, s>>>(pred, target, n, g2n, dpred, static_cast<float *>(scratch));
+  EB_LAUNCH_CHECK();
+  reduce_finish_kernel<<<1, 32, 0, s>>>(static_cast<const float *>(scratch), loss, 1, ctas, inv_n);
+  EB_LAUNCH_CHECK();
+  return ENDIA_B200_OK;
+}
+
+size_t endia_b200_act_bwd_colsum_scratch_bytes(int64_t M, int64_t N) {
+  if (M <= 0 || N <= 0) return 0;
+  return sizeof(float) * (size_t)act_bwd_chunks(M, N) * (size_t)N;
+}
+
+int endia_b200_act_bwd_colsum(int act, const float *act_out, const float *grad, float *ds,
+                              float *colsum, int64_t M, int64_t N, void *scratch, void *stream) {
+  int st = require_device();
+  if (st) return st;
+  EB_REQUIRE(M >= 0 && N >= 0, ENDIA_B200_EINVAL, "act_bwd_colsum: negative size");
+  EB_REQUIRE(act >= 0 && act <= ENDIA_B200_ACT_SIGMOID, ENDIA_B200_EINVAL,
+             "act_bwd_colsum: unknown activation %d", act);
+  if (M == 0 || N == 0) return ENDIA_B200_OK;
+  EB_REQUIRE(grad != nullptr && (act == 0 || (act_out && ds)), ENDIA_B200_EINVAL,
+             "act_bwd_colsum: NULL pointer");
+  EB_REQUIRE(!colsum || scratch, ENDIA_B200_EINVAL, "act_bwd_colsum: colsum needs scratch");
+  cudaStream_t s = as_stream(stream);
+  const int chunks = act_bwd_chunks(M, N);
+  const int64_t rows = ceil_div(M, chunks);
+  float *partial = colsum ? static_cast<float *>(scratch) : nullptr;
+  const bool vec = N % 4 == 0 && ((reinterpret_cast<uintptr_t>(grad) | reinterpret_cast<uintptr_t>(act_out) |
+                                   reinterpret_cast<uintptr_t>(ds)) & 15) == 0;
+  if (vec) {
+    dim3 grid((unsigned)ceil_div(N / 4, 256), (unsigned)chunks);
+    act_bwd_colsum_kernel<4><<<grid, 256, 0, s>>>(act, act_out, grad, act ? ds : nullptr, partial, M, N, rows);
+  } else {
+    dim3 grid((unsigned)ceil_div(N, 256), (unsigned)chunks);
+    act_bwd_colsum_kernel<1><<<grid, 256, 0, s>>>(act, act_out, grad, act ? ds : nullptr, partial, M, N, rows);
+  }
+  EB_LAUNCH_CHECK();
+  if (colsum) {
+    colsum_finish_kernel<<<grid_for(N, 256), 256, 0, s>>>(partial, colsum, 1, N, chunks);
+    EB_LAUNCH_CHECK();
+  }
+  return ENDIA_B200_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,193 @@
+"""Binary elementwise ops with numpy broadcasting and matmul
+(endia/functional/binary_ops/). Forward passes enqueue one vectorised kernel that reads
+broadcast operands through stride-0 dims; VJPs are compositions of these same ops, so gradients
+of gradients work (create_graph=True). When no graph of the gradient is wanted the VJPs switch to
+fused single-pass kernels."""
+from .. import _lib
+from .._array import Array, ArrayShape, alloc, stream
+from ..autograd import state as _state
+from ._utils import (op_array, setup_shape_and_data, broadcast_shapes, launch_binary, contiguous)
+from .view_ops import expand
+
+
+def _binary_call(opcode):
+    def call(curr, args):
+        setup_shape_and_data(curr)
+        if curr.size():
+            launch_binary(opcode, args[0], args[1], curr)
+    return call
+
+
+def binary_op_array(arg0, arg1, name, opcode, vjp):
+    """Expand both args to the broadcast shape (views), then register the op on the expanded
+    args (binary_ops/_utils.mojo:57-90)."""
+    shape = broadcast_shapes(arg0.shape(), arg1.shape())
+    a0, a1 = expand(arg0, shape), expand(arg1, shape)
+    return op_array(ArrayShape(shape), [a0, a1], name, _binary_call(opcode), vjp=vjp)
+
+
+def _zero():
+    return Array(0)
+
+
+def _add_vjp(primals, grad, out):  # add_op.mojo:107-110
+    return [grad if primals[0].requires_grad() else _zero(),
+            grad if primals[1].requires_grad() else _zero()]
+
+
+def _sub_vjp(primals, grad, out):  # sub_op.mojo:109-112
+    from .unary_ops import neg
+    return [grad if primals[0].requires_grad() else _zero(),
+            neg(grad) if primals[1].requires_grad() else _zero()]
+
+
+def _mul_vjp(primals, grad, out):  # mul_op.mojo:125-128 (no conjugation)
+    return [mul(grad, primals[1]) if primals[0].requires_grad() else _zero(),
+            mul(grad, primals[0]) if primals[1].requires_grad() else _zero()]
+
+
+def _div_vjp(primals, grad, out):  # div_op.mojo:108-114
+    from .unary_ops import neg
+    lhs = div(grad, primals[1]) if primals[0].requires_grad() else _zero()
+    rhs = div(mul(neg(grad), primals[0]), mul(primals[1], primals[1])) if primals[1].requires_grad() else _zero()
+    return [lhs, rhs]
+
+
+def _pow_vjp(primals, grad, out):  # pow_op.mojo:109-115
+    from .unary_ops import log
+    lhs = mul(mul(grad, primals[1]), div(out, primals[0])) if primals[0].requires_grad() else _zero()
+    rhs = mul(mul(grad, out), log(primals[0])) if primals[1].requires_grad() else _zero()
+    return [lhs, rhs]
+
+
+def add(arg0, arg1):
+    return binary_op_array(arg0, arg1, "add", _lib.BIN_ADD, _add_vjp)
+
+
+def sub(arg0, arg1):
+    return binary_op_array(arg0, arg1, "sub", _lib.BIN_SUB, _sub_vjp)
+
+
+def mul(arg0, arg1):
+    return binary_op_array(arg0, arg1, "mul", _lib.BIN_MUL, _mul_vjp)
+
+
+def div(arg0, arg1):
+    return binary_op_array(arg0, arg1, "div", _lib.BIN_DIV, _div_vjp)
+
+
+def pow_to(arg0, arg1):
+    return binary_op_array(arg0, arg1, "pow_to", _lib.BIN_POW, _pow_vjp)
+
+
+pow = pow_to
+
+
+def fused_binary(opcode, a, b):
+    """Gradient-free single-pass kernel for the fused VJP forms (ENDIA_B200_BIN_*_BWD)."""
+    shape = broadcast_shapes(a.shape(), b.shape())
+    a0, a1 = expand(a, shape), expand(b, shape)
+    out = Array(ArrayShape(shape))
+    setup_shape_and_data(out)
+    if out.size():
+        launch_binary(opcode, a0, a1, out)
+    return out
+
+
+# ------------------------------------------------------------------------------ matmul
+def _matmul_shape(s0, s1):
+    """Result shape of a batched product (binary_ops/matmul_op.mojo:36-90)."""
+    if len(s0) < 2 or len(s1) < 2:
+        raise _lib.EndiaError(_lib.ESHAPE, "Error: matmul needs arrays of at least 2 dims")
+    if s0[-1] != s1[-2]:
+        raise _lib.EndiaError(_lib.ESHAPE, "Error: matmul shapes are incompatible: %s @ %s" % (s0, s1))
+    batch = broadcast_shapes(s0[:-2], s1[:-2])
+    return batch, batch + [s0[-2], s1[-1]]
+
+
+def _matrix_layout(a):
+    """(transposed, leading dimension) when the last two dims of `a` can feed the GEMM without a
+    copy: row-major [r, c] (stride (ld, 1)) or its transposed view (stride (1, ld))."""
+    r, c = a.shape()[-2], a.shape()[-1]
+    sr, sc = a.stride()[-2], a.stride()[-1]
+    if (sc == 1 or c == 1) and (sr >= c or r == 1) and sr != 0:
+        return 0, (sr if r > 1 else max(c, 1))
+    if (sr == 1 or r == 1) and (sc >= r or c == 1) and sc != 0:
+        return 1, (sc if c > 1 else max(r, 1))
+    return None
+
+
+def _batch_stride(a, batch):
+    """Single element stride between consecutive batch matrices, or None if not expressible."""
+    nb = len(batch)
+    if nb == 0:
+        return 0
+    lead_shape, lead_stride = a.shape()[:-2], a.stride()[:-2]
+    total = 1
+    for s in batch:
+        total *= s
+    if total == 1:
+        return 0
+    if all(st == 0 for st, e in zip(lead_stride, lead_shape) if e != 1):
+        return 0
+    expect = None
+    for e, st in zip(reversed(lead_shape), reversed(lead_stride)):
+        if e == 1:
+            continue
+        if expect is None:
+            expect = st * e
+            base = st
+        else:
+            if st != expect:
+                return None
+            expect = st * e
+    return base
+
+
+def gemm_arrays(a, b, out, epi=None, algo=None):
+    """out = a @ b over the last two dims; a and b are already expanded over the batch dims.
+    Transposed views are passed as such (no materialised copy, unlike matmul_op.mojo:107-136)."""
+    batch = out.shape()[:-2]
+    nbatch = 1
+    for s in batch:
+        nbatch *= s
+    M, N, K = out.shape()[-2], out.shape()[-1], a.shape()[-1]
+    la, lb = _matrix_layout(a), _matrix_layout(b)
+    sa, sb = _batch_stride(a, batch), _batch_stride(b, batch)
+    if la is None or sa is None:
+        a = contiguous(a)
+        la, sa = _matrix_layout(a), _batch_stride(a, batch)
+    if lb is None or sb is None:
+        b = contiguous(b)
+        lb, sb = _matrix_layout(b), _batch_stride(b, batch)
+    if algo is None:
+        algo = _state.gemm_algo
+    if out.is_complex():
+        if not (a.is_complex() and b.is_complex()):
+            raise _lib.EndiaError(_lib.EINVAL, "matmul of a complex and a real array is not supported")
+        _lib.call("endia_b200_gemm_complex", la[0], lb[0], M, N, K, a.data_ptr(), la[1], b.data_ptr(),
+                  lb[1], out.data_ptr(), N, nbatch, sa, sb, M * N, stream())
+        return
+    _lib.call("endia_b200_gemm", la[0], lb[0], M, N, K, a.data_ptr(), la[1], b.data_ptr(), lb[1],
+              out.data_ptr(), N, nbatch, sa, sb, M * N, epi, algo, stream())
+
+
+def _matmul_call(curr, args):
+    setup_shape_and_data(curr)
+    if curr.size():
+        gemm_arrays(args[0], args[1], curr)
+
+
+def _matmul_vjp(primals, grad, out):
+    # dX = g @ W.T, dW = X.T @ g, each a new differentiable matmul on a transposed view
+    # (matmul_op.mojo:278-284). The product with a square W is the mathematically correct one.
+    lhs = matmul(grad, primals[1].T()) if primals[0].requires_grad() else _zero()
+    rhs = matmul(primals[0].T(), grad) if primals[1].requires_grad() else _zero()
+    return [lhs, rhs]
+
+
+def matmul(arg0, arg1):
+    batch, shape = _matmul_shape(arg0.shape(), arg1.shape())
+    a0 = expand(arg0, batch + arg0.shape()[-2:], ignore_axes=(-2, -1))
+    a1 = expand(arg1, batch + arg1.shape()[-2:], ignore_axes=(-2, -1))
+    return op_array(ArrayShape(shape), [a0, a1], "matmul", _matmul_call, vjp=_matmul_vjp)

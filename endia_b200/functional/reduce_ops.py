@@ -1,0 +1,46 @@
+"""Sum reductions (endia/functional/reduce_ops/): reduce_add keeps reduced dims as 1; sum and
+mean squeeze afterwards, so a full reduction has shape [1]."""
+from .. import _lib
+from .._array import ArrayShape, alloc, stream
+from ._utils import op_array, setup_shape_and_data
+from .view_ops import expand, squeeze
+
+
+def reduce_add(arg0, axis):
+    """Sum over `axis`, reduced dims kept with extent 1 (reduce_add_op.mojo:39-62); the vjp
+    expands the gradient back to the primal's shape (:234)."""
+    nd = arg0.ndim()
+    axes = sorted(set(a + nd if a < 0 else a for a in axis))
+    shape = [1 if i in axes else s for i, s in enumerate(arg0.shape())]
+    mask = 0
+    for a in axes:
+        mask |= 1 << a
+
+    def call(curr, args):
+        setup_shape_and_data(curr)
+        if curr.size() == 0:
+            return
+        d = args[0].desc()
+        nbytes = _lib.lib.endia_b200_reduce_scratch_bytes(d, mask)
+        scratch = alloc((nbytes + 3) // 4) if nbytes else None
+        _lib.call("endia_b200_reduce_add", d, mask, curr.data_ptr(),
+                  scratch.data_ptr() if scratch is not None else None, stream())
+
+    def vjp(primals, grad, out):
+        return [expand(grad, primals[0].array_shape())]
+    return op_array(ArrayShape(shape), [arg0], "reduce_add", call, vjp=vjp)
+
+
+def sum(arg0):
+    """Sum over all axes; shape [1] (sum_op.mojo:35-62, squeeze keeps the last dim)."""
+    return squeeze(reduce_add(arg0, list(range(arg0.ndim()))))
+
+
+def mean(arg0, axes=None, keepdims=False):
+    """reduce_add / (size_in / size_out) (mean_op.mojo:35-65)."""
+    if axes is None:
+        axes = list(range(arg0.ndim()))
+    res = reduce_add(arg0, axes)
+    divisor = float(arg0.size() / res.size())
+    out = res / divisor
+    return out if keepdims else squeeze(out)

@@ -1,0 +1,123 @@
+"""Unary elementwise ops (endia/functional/unary_ops/); VJPs are compositions of ops."""
+from .. import _lib
+from .._array import Array, ArrayShape
+from ..autograd import state as _state
+from ._utils import op_array, setup_shape_and_data, launch_unary
+
+
+def _unary_call(opcode):
+    def call(curr, args):
+        setup_shape_and_data(curr)
+        if curr.size():
+            launch_unary(opcode, args[0], curr)
+    return call
+
+
+def unary_op_array(arg0, name, opcode, vjp):
+    return op_array(ArrayShape(arg0.shape()), [arg0], name, _unary_call(opcode), vjp=vjp)
+
+
+def _fused(opcode, a, b):
+    from .binary_ops import fused_binary
+    return fused_binary(opcode, a, b)
+
+
+def neg(arg0):
+    return unary_op_array(arg0, "neg", _lib.UN_NEG, lambda p, g, o: [neg(g)])  # neg_op.mojo:91
+
+
+def _relu_vjp(primals, grad, out):
+    # greater(x, 0) * grad, strict > (relu_op.mojo:95)
+    if not _state.create_graph:
+        return [_fused(_lib.BIN_RELU_BWD, primals[0], grad)]
+    from .comparison_ops import greater
+    from .binary_ops import mul
+    return [mul(greater(primals[0], Array([primals[0].shape()[-1]])), grad)]
+
+
+def relu(arg0):
+    if arg0.is_complex():
+        raise _lib.EndiaError(_lib.EINVAL, "Warning: Relu does not support complex numbers")  # relu_op.mojo:51-52
+    return unary_op_array(arg0, "relu", _lib.UN_RELU, _relu_vjp)
+
+
+def _tanh_vjp(primals, grad, out):
+    # (1 - square(tanh(x))) * grad, tanh recomputed from the primal (tanh_op.mojo:92)
+    if not _state.create_graph and not primals[0].is_complex():
+        return [_fused(_lib.BIN_TANH_BWD, primals[0], grad)]
+    from .binary_ops import mul
+    return [mul(1.0 - square(tanh(primals[0])), grad)]
+
+
+def tanh(arg0):
+    return unary_op_array(arg0, "tanh", _lib.UN_TANH, _tanh_vjp)
+
+
+def _sigmoid_vjp(primals, grad, out):
+    # out * (1 - out) * grad (sigmoid_op.mojo:98)
+    if not _state.create_graph:
+        return [_fused(_lib.BIN_SIGMOID_BWD, out, grad)]
+    from .binary_ops import mul
+    return [mul(mul(out, 1.0 - out), grad)]
+
+
+def sigmoid(arg0):
+    if arg0.is_complex():
+        raise _lib.EndiaError(_lib.EINVAL, "Warning: Sigmoid does not support complex numbers")  # sigmoid_op.mojo:49-50
+    return unary_op_array(arg0, "sigmoid", _lib.UN_SIGMOID, _sigmoid_vjp)
+
+
+def square(arg0):
+    from .binary_ops import mul
+    return unary_op_array(arg0, "square", _lib.UN_SQUARE, lambda p, g, o: [mul(2.0 * p[0], g)])  # square_op.mojo:96
+
+
+def sqrt(arg0):
+    from .binary_ops import div
+    return unary_op_array(arg0, "sqrt", _lib.UN_SQRT, lambda p, g, o: [div(g, 2.0 * sqrt(p[0]))])  # sqrt_op.mojo:91
+
+
+def conj(arg0):
+    return unary_op_array(arg0, "conj", _lib.UN_CONJ, lambda p, g, o: [conj(g)])  # conj_op.mojo
+
+
+def sign(arg0):
+    from ._utils import default_vjp
+    return unary_op_array(arg0, "sign", _lib.UN_SIGN, default_vjp)  # sign_op.mojo: default vjp
+
+
+def abs(arg0):
+    from .binary_ops import mul
+    return unary_op_array(arg0, "abs", _lib.UN_ABS, lambda p, g, o: [mul(sign(p[0]), g)])  # abs_op.mojo:93
+
+
+def to_abs(arg0):
+    """abs as a real array (abs_op.mojo:157)."""
+    from .view_ops import real
+    return real(abs(arg0))
+
+
+def exp(arg0):
+    from .binary_ops import mul
+    return unary_op_array(arg0, "exp", _lib.UN_EXP, lambda p, g, o: [mul(exp(p[0]), g)])
+
+
+def log(arg0):
+    from .binary_ops import div
+    return unary_op_array(arg0, "log", _lib.UN_LOG, lambda p, g, o: [div(g, p[0])])  # log_op.mojo:91
+
+
+def sin(arg0):
+    from .binary_ops import mul
+    return unary_op_array(arg0, "sin", _lib.UN_SIN, lambda p, g, o: [mul(cos(p[0]), g)])
+
+
+def cos(arg0):
+    from .binary_ops import mul
+    return unary_op_array(arg0, "cos", _lib.UN_COS, lambda p, g, o: [mul(neg(sin(p[0])), g)])
+
+
+def reciprocal(arg0):
+    from .binary_ops import div
+    return unary_op_array(arg0, "reciprocal", _lib.UN_RECIPROCAL,
+                          lambda p, g, o: [div(neg(g), square(p[0]))])

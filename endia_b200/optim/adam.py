@@ -1,0 +1,42 @@
+"""Adam (endia/optim/adam.mojo:17-65) as one fused multi-tensor kernel per step."""
+import ctypes as C
+
+from .. import _lib
+from .._array import Array, ArrayShape, stream
+from ..functional._utils import contiguous, broadcast_shapes
+
+
+class Adam:
+    def __init__(self, params, lr=0.001, beta1=0.9, beta2=0.999, eps=1e-8):
+        self.params = list(params)
+        self.lr, self.beta1, self.beta2, self.eps = lr, beta1, beta2, eps
+        self.t = 1.0  # the step count starts at 1 (adam.mojo:40)
+        self.m = [Array(p.shape()) for p in self.params]
+        self.v = [Array(p.shape()) for p in self.params]
+        self.grad_scale = 1.0  # folded into the gradient read (1/world_size under data parallelism)
+
+    def step(self):
+        n = len(self.params)
+        grads = []
+        for p in self.params:
+            if not p.is_contiguous():
+                raise _lib.EndiaError(_lib.EINVAL, "Adam: parameters must be contiguous arrays")
+            grads.append(contiguous(p.grad()))  # zeros when no gradient is stored (_array.mojo:695-698)
+        P = (C.c_void_p * n)(*[p.data_ptr() for p in self.params])
+        G = (C.c_void_p * n)(*[g.data_ptr() for g in grads])
+        M = (C.c_void_p * n)(*[m.data_ptr() for m in self.m])
+        V = (C.c_void_p * n)(*[v.data_ptr() for v in self.v])
+        numel = (C.c_int64 * n)(*[p.size() for p in self.params])
+        for p, g in zip(self.params, grads):
+            if g.size() != p.size():
+                raise _lib.EndiaError(_lib.ESHAPE, "Adam: gradient %s does not match parameter %s" % (
+                    g.shape(), p.shape()))
+        _lib.call("endia_b200_adam_step_multi", n, P, G, M, V, numel, self.lr, self.beta1, self.beta2,
+                  self.eps, self.t, self.grad_scale, stream())
+        # m and v take the broadcast shape of (state, grad): a bias gradient is (1, N), so the
+        # moments become (1, N) while the parameter keeps (N) (adam.mojo:49-56, expand_op.mojo:121-126).
+        for i, g in enumerate(grads):
+            shp = broadcast_shapes(self.m[i].shape(), g.shape())
+            self.m[i].array_shape_ = ArrayShape(shp)
+            self.v[i].array_shape_ = ArrayShape(shp)
+        self.t += 1.0

@@ -1,0 +1,259 @@
+/*
+ * endia_b200.h — C ABI of the B200 (sm_100a) device path for Endia's reverse-mode
+ * hot path: the ops of an MLP training step (matmul and its VJPs, elementwise and
+ * reduction VJPs, fused Adam) and the complex FFT family with its VJPs.
+ *
+ * Conventions
+ *   - Every entry point returns 0 on success and a negative ENDIA_B200_E* code on
+ *     failure; endia_b200_last_error() then returns a thread-local message. Nothing
+ *     throws across this boundary (Endia's ops `raise "string"`; the binding turns a
+ *     non-zero status into such a raise).
+ *   - All data pointers are DEVICE pointers to float32 storage. A complex element is
+ *     an interleaved (re, im) float pair (endia/_array/_array.mojo:126-128, 528-536).
+ *   - Every launch takes an explicit `stream` (a cudaStream_t passed as void*;
+ *     NULL = the legacy default stream). Calls are asynchronous unless stated.
+ *   - A tensor descriptor carries Endia's ArrayShape semantics: shape, stride and
+ *     storage offset counted in ELEMENTS (one complex element counts 1),
+ *     row-major default strides (endia/utils/_array_shape.mojo:24-30).
+ *   - There is no CPU fallback: without a usable sm_100 device every compute entry
+ *     point fails with ENDIA_B200_ENODEV.
+ */
+#ifndef ENDIA_B200_H
+#define ENDIA_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define ENDIA_B200_MAX_DIMS 8
+
+enum {
+  ENDIA_B200_OK = 0,
+  ENDIA_B200_EINVAL = -1,   /* bad shape / stride / NULL pointer / unsupported flag  */
+  ENDIA_B200_ECUDA = -2,    /* a CUDA runtime call failed                            */
+  ENDIA_B200_ENODEV = -3,   /* no CUDA device / not an sm_100 part                   */
+  ENDIA_B200_ENOMEM = -4,   /* device allocation failed                              */
+  ENDIA_B200_ESHAPE = -5,   /* operand shapes are not compatible                     */
+  ENDIA_B200_EPOW2 = -6,    /* FFT length is not a power of two
+                               (endia/functional/fft_ops/fft_cooley_tukey.mojo:227-235) */
+  ENDIA_B200_ETIMEOUT = -7, /* a bounded device-side wait gave up                    */
+  ENDIA_B200_ELIMIT = -8    /* size beyond a documented fixed limit                  */
+};
+
+/* Strided view of device storage. Replaces Array/ArrayShape as seen by an op's
+ * `fwd` callable (endia/_array/_array.mojo:56-113; endia/utils/_array_shape.mojo:85-250). */
+typedef struct endia_b200_tensor {
+  void *data;                           /* base of the float32 buffer              */
+  int64_t shape[ENDIA_B200_MAX_DIMS];
+  int64_t stride[ENDIA_B200_MAX_DIMS];  /* in elements; 0 = broadcast dimension    */
+  int64_t offset;                       /* storage offset in elements              */
+  int32_t ndim;
+  int32_t is_complex;                   /* 1: elements are (re, im) float pairs    */
+} endia_b200_tensor;
+
+/* ---------------------------------------------------------------- runtime ---- */
+
+/* Select `device`, verify compute capability 10.x, create the per-device state.
+ * Replaces nothing in the reference (its arrays live in host memory); it is the hook the
+ * device-resident Node storage needs (endia/_array/_array.mojo:125-131). */
+int endia_b200_init(int device);
+int endia_b200_shutdown(void);
+const char *endia_b200_last_error(void);
+/* ABI version (major*1000 + minor). */
+int endia_b200_version(void);
+/* 1 when the library was built with the tcgen05 GEMM and the device accepts it. */
+int endia_b200_has_tcgen05(void);
+
+/* Stream-ordered device memory. Replaces UnsafePointer.alloc/free + memset_zero in
+ * Node.__init__/__del__ (endia/_array/_array.mojo:127-128, 177-179) and
+ * setup_shape_and_data (endia/functional/_utils.mojo:319-326). */
+int endia_b200_malloc(void **ptr, size_t bytes, void *stream);
+int endia_b200_free(void *ptr, void *stream);
+int endia_b200_memset0(void *ptr, size_t bytes, void *stream);
+int endia_b200_h2d(void *dst_dev, const void *src_host, size_t bytes, void *stream);
+int endia_b200_d2h(void *dst_host, const void *src_dev, size_t bytes, void *stream);
+int endia_b200_d2d(void *dst_dev, const void *src_dev, size_t bytes, void *stream);
+
+int endia_b200_stream_create(void **stream);
+int endia_b200_stream_destroy(void *stream);
+int endia_b200_stream_sync(void *stream);
+int endia_b200_event_create(void **event);
+int endia_b200_event_destroy(void *event);
+int endia_b200_event_record(void *event, void *stream);
+int endia_b200_stream_wait_event(void *stream, void *event);
+/* Milliseconds between two recorded events (both must have completed). */
+int endia_b200_event_elapsed_ms(void *start, void *stop, float *ms);
+
+/* ------------------------------------------------------------------ GEMM ---- */
+
+enum { ENDIA_B200_ACT_NONE = 0, ENDIA_B200_ACT_RELU = 1, ENDIA_B200_ACT_TANH = 2,
+       ENDIA_B200_ACT_SIGMOID = 3 };
+
+enum { ENDIA_B200_GEMM_AUTO = 0,   /* tcgen05 3xTF32 when the shape allows, else FFMA */
+       ENDIA_B200_GEMM_FFMA = 1,   /* fp32 FFMA tiles                                 */
+       ENDIA_B200_GEMM_3XTF32 = 2  /* tcgen05 tf32 MMAs, hi/lo split, fp32 accumulate */ };
+
+/* Work fused into the GEMM's store, applied in this order to acc = op(A)·op(B):
+ *   v = alpha*acc
+ *   v += bias[n]                           (bias != NULL)          Add after matmul,
+ *                                           endia/nn/modules/_mlp.mojo:50-51
+ *   v  = act(v)                            (act != NONE)           relu_op.mojo:115,
+ *                                           tanh_op.mojo:112-115, sigmoid_op.mojo:118-121
+ *   v *= act'(dact_src[m,n])               (dact != NONE)          the VJP masks:
+ *        RELU:    dact_src = pre-activation s, factor (s > 0)      relu_op.mojo:95
+ *        TANH:    dact_src = activation   a, factor 1 - a*a        tanh_op.mojo:92
+ *        SIGMOID: dact_src = activation   a, factor a*(1-a)        sigmoid_op.mojo:98
+ *   v += beta*C[m,n]                       (beta != 0; gradient accumulation,
+ *                                           endia/autograd/functional.mojo:55-57)
+ *   C[m,n] = v
+ *   colsum[n] = sum_m v                    (colsum != NULL; the bias gradient that
+ *                                           Expand.vjp reduces, expand_op.mojo:121-126)
+ * colsum is reduced deterministically: per-row-tile partials go to `colsum_scratch`
+ * (at least endia_b200_gemm_colsum_scratch_bytes(M, N) bytes) and a second small kernel
+ * adds them in a fixed order. */
+typedef struct endia_b200_epilogue {
+  float alpha;
+  float beta;
+  const float *bias;
+  int32_t act;
+  int32_t dact;
+  const float *dact_src;
+  int64_t ld_dact;
+  float *colsum;
+  float *colsum_scratch;
+} endia_b200_epilogue;
+
+size_t endia_b200_gemm_colsum_scratch_bytes(int64_t M, int64_t N);
+
+/* C[M,N] = epilogue(op(A)[M,K] · op(B)[K,N]), fp32, row-major storage.
+ *   trans_a = 0: A is stored [M,K] with leading dimension lda >= K
+ *   trans_a = 1: A is stored [K,M] with leading dimension lda >= M   (Xᵀ·dY without a copy)
+ *   trans_b = 0: B is stored [K,N], ldb >= N;  trans_b = 1: B is stored [N,K], ldb >= K (dY·Wᵀ)
+ * `batch` independent products with element strides stride_a/b/c between them
+ * (a stride of 0 broadcasts that operand over the batch).
+ * Replaces matmul_fwd (endia/functional/binary_ops/matmul_op.mojo:93-254) and the
+ * transposing copies it makes of `.T()` operands (matmul_op.mojo:107-136), so that the
+ * two products of matmul_vjp (matmul_op.mojo:278-284) need no materialised transpose.
+ * `epi` may be NULL (alpha = 1, nothing fused). `algo` is one of ENDIA_B200_GEMM_*. */
+int endia_b200_gemm(int trans_a, int trans_b, int64_t M, int64_t N, int64_t K,
+                    const float *A, int64_t lda, const float *B, int64_t ldb,
+                    float *C, int64_t ldc, int64_t batch, int64_t stride_a,
+                    int64_t stride_b, int64_t stride_c, const endia_b200_epilogue *epi,
+                    int algo, void *stream);
+
+/* Complex (interleaved) matmul, same storage conventions, no epilogue.
+ * Replaces the complex branch of matmul_fwd (matmul_op.mojo:200-238). */
+int endia_b200_gemm_complex(int trans_a, int trans_b, int64_t M, int64_t N, int64_t K,
+                            const float *A, int64_t lda, const float *B, int64_t ldb,
+                            float *C, int64_t ldc, int64_t batch, int64_t stride_a,
+                            int64_t stride_b, int64_t stride_c, void *stream);
+
+/* ------------------------------------------------------------ elementwise ---- */
+
+enum {
+  ENDIA_B200_UN_COPY = 0,   /* strided gather → `out` (contiguous(), functional/_utils.mojo:79-205) */
+  ENDIA_B200_UN_NEG, ENDIA_B200_UN_RELU, ENDIA_B200_UN_TANH, ENDIA_B200_UN_SIGMOID,
+  ENDIA_B200_UN_SQUARE, ENDIA_B200_UN_SQRT, ENDIA_B200_UN_ABS, ENDIA_B200_UN_SIGN,
+  ENDIA_B200_UN_CONJ, ENDIA_B200_UN_EXP, ENDIA_B200_UN_LOG, ENDIA_B200_UN_SIN,
+  ENDIA_B200_UN_COS, ENDIA_B200_UN_RECIPROCAL,
+  ENDIA_B200_UN_COUNT
+};
+enum {
+  ENDIA_B200_BIN_ADD = 0, ENDIA_B200_BIN_SUB, ENDIA_B200_BIN_MUL, ENDIA_B200_BIN_DIV,
+  ENDIA_B200_BIN_POW, ENDIA_B200_BIN_GREATER,
+  /* fused VJP forms (one pass instead of the reference's op chains):           */
+  ENDIA_B200_BIN_RELU_BWD,     /* out = (a > 0) * b          a = pre-activation, b = grad */
+  ENDIA_B200_BIN_TANH_BWD,     /* out = (1 - tanh(a)^2) * b  a = pre-activation           */
+  ENDIA_B200_BIN_SIGMOID_BWD,  /* out = a*(1-a) * b          a = sigmoid output           */
+  ENDIA_B200_BIN_COMPLEX,      /* out = a + i*b, a and b real, out complex (`complex(re, im)`,
+                                  init_ops.mojo:419-433)                                      */
+  ENDIA_B200_BIN_COUNT
+};
+
+/* out[i] = f(in[i]) over in's logical shape; `out` must have the same shape. `in` may be any
+ * strided view (broadcast strides included); complex inputs use the complex formulas of the
+ * op files under endia/functional/unary_ops/. Replaces execute_unary_op
+ * (endia/functional/unary_ops/_utils.mojo:77-134) and execute_copy_raw
+ * (endia/functional/_utils.mojo:79-163). */
+int endia_b200_ew_unary(int op, const endia_b200_tensor *in, const endia_b200_tensor *out,
+                        void *stream);
+
+/* out = a (op) b. a and b must already be expanded to out's shape (stride 0 on stretched
+ * dims, as Endia's `expand` view produces, expand_op.mojo:62-84); nothing is materialised.
+ * Replaces execute_binary_op (endia/functional/binary_ops/_utils.mojo:93-177). */
+int endia_b200_ew_binary(int op, const endia_b200_tensor *a, const endia_b200_tensor *b,
+                         const endia_b200_tensor *out, void *stream);
+
+/* Fill a contiguous float buffer with a constant (endia `full`/`ones`/`zeros`,
+ * init_ops.mojo:85-205). For complex buffers pass re/im. */
+int endia_b200_fill(float *dst, int64_t n_elements, int is_complex, float re, float im,
+                    void *stream);
+/* n×n identity (init_ops.mojo `eye`), used as the Jacobian seed of non-scalar outputs
+ * (endia/autograd/functional.mojo:34-38). */
+int endia_b200_eye(float *dst, int64_t n, void *stream);
+
+/* -------------------------------------------------------------- reductions ---- */
+
+/* out = sum of `in` over the axes set in `axes_mask` (bit d = reduce dim d); `out` is a
+ * contiguous buffer with the reduced dims kept as 1. Deterministic (fixed tree order).
+ * `scratch` must hold endia_b200_reduce_scratch_bytes(in, axes_mask) bytes (may be NULL when
+ * that is 0). Replaces ReduceAdd.__call__ (endia/functional/reduce_ops/reduce_add_op.mojo:65-210). */
+size_t endia_b200_reduce_scratch_bytes(const endia_b200_tensor *in, uint32_t axes_mask);
+int endia_b200_reduce_add(const endia_b200_tensor *in, uint32_t axes_mask, float *out,
+                          void *scratch, void *stream);
+
+/* Fused mean-squared-error forward and backward on contiguous [n] buffers:
+ *   loss[0] = sum((p-t)^2) / n ;  dpred[i] = gscale * 2 (p[i]-t[i]) / n   (dpred may be NULL)
+ * `scratch` >= endia_b200_mse_scratch_bytes(n). Replaces the op chain of mse
+ * (endia/functional/loss_ops/mse_op.mojo:18-20) and its five VJP passes. */
+size_t endia_b200_mse_scratch_bytes(int64_t n);
+int endia_b200_mse_fwd_bwd(const float *pred, const float *target, int64_t n, float gscale,
+                           float *loss, float *dpred, void *scratch, void *stream);
+
+/* Fused activation backward and bias gradient of one layer, on contiguous [M, N] buffers:
+ *   ds[m,n] = grad[m,n] * act'(act_out[m,n])   (factors as in endia_b200_epilogue; act = NONE
+ *                                               leaves ds untouched and only sums grad)
+ *   colsum[n] = sum_m ds[m,n]                   (colsum may be NULL)
+ * `scratch` >= endia_b200_act_bwd_colsum_scratch_bytes(M, N) when colsum is given. Replaces the
+ * VJP chains of relu/tanh/sigmoid (relu_op.mojo:95, tanh_op.mojo:92, sigmoid_op.mojo:98) followed by
+ * Expand.vjp's reduce_add for the bias (expand_op.mojo:121-126). */
+size_t endia_b200_act_bwd_colsum_scratch_bytes(int64_t M, int64_t N);
+int endia_b200_act_bwd_colsum(int act, const float *act_out, const float *grad, float *ds,
+                              float *colsum, int64_t M, int64_t N, void *scratch, void *stream);
+
+/* --------------------------------------------------------------- optimizer ---- */
+
+/* One fused Adam step over n_tensors parameter tensors (device pointers passed in HOST arrays):
+ *   g' = grad_scale*g; m = b1*m + (1-b1)*g'; v = b2*v + ((1-b2)*g')*g';
+ *   p -= (lr * (m/(1-b1^t))) / (sqrt(v/(1-b2^t)) + eps)
+ * with every scalar evaluated in fp32 and t an fp32 step count that starts at 1
+ * (endia/optim/adam.mojo:40, 47-65). Replaces ~14 array passes per tensor. */
+int endia_b200_adam_step_multi(int32_t n_tensors, float *const *params, const float *const *grads,
+                               float *const *m, float *const *v, const int64_t *numel, float lr,
+                               float beta1, float beta2, float eps, float t, float grad_scale,
+                               void *stream);
+
+/* --------------------------------------------------------------------- FFT ---- */
+
+/* Complex-to-complex FFT over the listed dims of `in` (contiguous or strided, complex) into
+ * `out` (contiguous, same shape):
+ *   inverse = 0: sign -  (forward DFT),  inverse = 1: sign +  (conjugate-direction transform,
+ *   i.e. conj(fft(conj(x))), which is both FFTN.vjp and the core of ifftn)
+ *   every output element is multiplied by `scale`.
+ * Each transformed length must be a power of two (ENDIA_B200_EPOW2 otherwise).
+ * `scratch` must hold endia_b200_fft_scratch_bytes(...) bytes (NULL when that is 0).
+ * Replaces fft_cooley_tukey_parallel (endia/functional/fft_ops/fft_cooley_tukey.mojo:179-313)
+ * as called by FFTN/IFFTN and their VJPs (fftn_op.mojo:43-60, ifftn_op.mojo:42-77). */
+size_t endia_b200_fft_scratch_bytes(const endia_b200_tensor *in, const int32_t *dims,
+                                    int32_t n_dims);
+int endia_b200_fft_c2c(const endia_b200_tensor *in, const endia_b200_tensor *out,
+                       const int32_t *dims, int32_t n_dims, int inverse, float scale,
+                       void *scratch, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ENDIA_B200_H */

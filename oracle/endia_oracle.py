@@ -1,0 +1,732 @@
+"""CPU restatement of Endia's reference algorithms for the reverse-mode hot path: Array metadata,
+the eager ops with their VJP compositions, the reverse walk (with create_graph), nn.MLP, Adam and
+the float64 radix-2 FFT family.
+
+THIS IS TEST INFRASTRUCTURE, NOT A PRODUCT PATH. Only tests/, __graft_entry__.smoke() and the
+cpu_baseline / reference legs of bench.py may import it; nothing under endia_b200/ does.
+
+Parity status: the reference (Mojo 24.5) cannot be compiled or run on this machine and its tests
+hold no golden vectors - they compare against PyTorch at mean relative error 1e-4 (1e-5 for FFT
+forwards). This restatement is therefore pinned against (a) the reference's in-tree known answers
+(README.md:74-76, 106-108; examples/custom_ops_examples/custom_mul.mojo:64-71) and (b) PyTorch CPU on
+the reference's own test shapes, which is the reference's oracle. Values no reference test checks
+(FFT VJPs, mse, nn.MLP, Adam, second-order results) are "parity unpinned" by the reference itself;
+for those this file follows the cited source lines and is cross-checked against torch autograd.
+
+Each function cites the reference file:line it follows (paths relative to the reference repo).
+Arithmetic is float32 numpy, evaluated op by op with the reference's formulas; matmul, reduce_add
+and the FFT core run in kernels.c (compiled by build()).
+"""
+import ast
+import ctypes as C
+import math
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB = os.path.join(_HERE, "_build", "liboracle.so")
+
+config = {
+    "mode": "faithful",       # "faithful": reference loop order, fp32, 1 thread. "fast": f64 accumulation, all cores
+    "nelts": 16,              # SIMD width of the matmul/reduce partial sums: simdwidthof[float32]*2 on AVX2
+                              # (endia/utils/aliases.mojo:20-21)
+    "square_T_quirk": False,  # True reproduces matmul_fwd's handling of a transposed view of a SQUARE
+                              # matrix (matmul_op.mojo:111-129): `g @ W.T()` is then evaluated as `g @ W`
+    "fft_threads": 1,
+}
+
+
+def build(force=False):
+    """Compile kernels.c with gcc (no -march=native: the library must run on another host)."""
+    src = os.path.join(_HERE, "kernels.c")
+    os.makedirs(os.path.dirname(_LIB), exist_ok=True)
+    if not force and os.path.exists(_LIB) and os.path.getmtime(_LIB) >= os.path.getmtime(src):
+        return _LIB
+    subprocess.check_call(["gcc", "-O3", "-ffp-contract=off", "-fopenmp", "-shared", "-fPIC", src,
+                           "-o", _LIB, "-lm"])
+    return _LIB
+
+
+_lib = None
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        if not os.path.exists(_LIB) or os.path.getmtime(_LIB) < os.path.getmtime(os.path.join(_HERE, "kernels.c")):
+            build()
+        _lib = C.CDLL(_LIB)
+        fp, i64 = C.c_void_p, C.c_int64
+        _lib.oracle_matmul_f32.argtypes = [fp, fp, fp, i64, i64, i64, C.c_int]
+        _lib.oracle_matmul_fast.argtypes = [fp, fp, fp, i64, i64, i64]
+        _lib.oracle_matmul_c64.argtypes = [fp, fp, fp, i64, i64, i64, C.c_int]
+        _lib.oracle_reduce_add.argtypes = [fp, fp, C.c_int, fp, fp, C.c_int, C.c_int]
+        _lib.oracle_fft_rows_f64.argtypes = [fp, i64, i64, C.c_int]
+    return _lib
+
+
+def _ptr(a):
+    return a.ctypes.data_as(C.c_void_p)
+
+
+f32 = np.float32
+
+
+# ------------------------------------------------------------------------------------- Array
+class Array:
+    """Graph node + storage (endia/_array/_array.mojo:56-180). `v` is a numpy array or view of
+    dtype float32 / complex64; numpy's strides carry Endia's element strides."""
+
+    def __init__(self, data, requires_grad=False, is_complex=False):
+        if isinstance(data, str):
+            data = np.asarray(ast.literal_eval(data.strip()), dtype=np.float32)
+        elif isinstance(data, (list, tuple)) and all(isinstance(d, (int, np.integer)) for d in data):
+            data = np.zeros(tuple(data), dtype=np.complex64 if is_complex else np.float32)
+        elif isinstance(data, (int, np.integer)):
+            data = np.zeros((int(data),), dtype=np.float32)
+        data = np.asarray(data)
+        if np.iscomplexobj(data):
+            data = data.astype(np.complex64, copy=False)
+        else:
+            data = data.astype(np.float32, copy=False)
+        if data.ndim == 0:
+            data = data.reshape(1)
+        self.v = data
+        self.requires_grad_flag = bool(requires_grad)
+        self.args_ = []
+        self.vjp_ = None
+        self.name = "arg"
+        self.grad_node = None
+        self.meta_data = []
+
+    # metadata -------------------------------------------------------------------------------
+    def shape(self):
+        return list(self.v.shape)
+
+    def stride(self):
+        return [s // self.v.itemsize for s in self.v.strides]
+
+    def storage_offset(self):
+        base = self.v
+        while base.base is not None and isinstance(base.base, np.ndarray):
+            base = base.base
+        return (self.v.__array_interface__["data"][0] - base.__array_interface__["data"][0]) // self.v.itemsize
+
+    def ndim(self):
+        return self.v.ndim
+
+    def size(self):
+        return int(self.v.size)
+
+    def is_complex(self):
+        return np.iscomplexobj(self.v)
+
+    def requires_grad(self):
+        return self.requires_grad_flag
+
+    def requires_grad_(self, flag=True):
+        self.requires_grad_flag = bool(flag)
+        return self
+
+    def args(self):
+        return self.args_
+
+    def has_grad(self):
+        return self.grad_node is not None
+
+    def grad(self):
+        if self.grad_node is None:  # _array.mojo:695-698
+            return Array(np.zeros(self.v.shape, dtype=self.v.dtype))
+        return self.grad_node
+
+    def grad_(self, g):
+        self.grad_node = g
+
+    def remove_grad(self):
+        self.grad_node = None
+
+    def clear_args(self):
+        self.args_ = []
+        self.vjp_ = None
+
+    def backward(self, create_graph=False):
+        backward(self, create_graph)
+
+    def zero_grad(self):
+        remove_grad_rec(self)
+
+    def T(self):  # _array.mojo:797-800
+        if self.ndim() == 1:
+            return self
+        return permute(self, [-1, -2])
+
+    def to_numpy(self):
+        return np.ascontiguousarray(self.v)
+
+    # operator sugar: a scalar becomes full([last_dim], scalar) (_array.mojo:957-1099) ----------
+    def _coerce(self, other):
+        if isinstance(other, Array):
+            return other
+        return full([self.shape()[-1]], other)
+
+    def __add__(self, o): return add(self, self._coerce(o))
+    def __radd__(self, o): return add(self._coerce(o), self)
+    def __sub__(self, o): return sub(self, self._coerce(o))
+    def __rsub__(self, o): return sub(self._coerce(o), self)
+    def __mul__(self, o): return mul(self, self._coerce(o))
+    def __rmul__(self, o): return mul(self._coerce(o), self)
+    def __truediv__(self, o): return div(self, self._coerce(o))
+    def __rtruediv__(self, o): return div(self._coerce(o), self)
+    def __pow__(self, o): return pow_to(self, self._coerce(o))
+    def __matmul__(self, o): return matmul(self, o)
+    def __neg__(self): return neg(self)
+
+    def __isub__(self, o):  # sub, then flat copy into this storage (_array.mojo:998-1006)
+        res = self.__sub__(o)
+        self.v.reshape(-1)[...] = np.ascontiguousarray(res.v).reshape(-1)
+        return self
+
+    def __iadd__(self, o):
+        res = self.__add__(o)
+        self.v.reshape(-1)[...] = np.ascontiguousarray(res.v).reshape(-1)
+        return self
+
+
+def op_array(value, args, name, vjp=None, meta_data=None):
+    """Result node of an op (endia/functional/_utils.mojo:208-316): requires_grad is the OR over
+    the args; edges and the vjp are stored only then (:262-272)."""
+    res = Array(value)
+    res.name = name
+    res.meta_data = list(meta_data) if meta_data else []
+    res.requires_grad_flag = any(a.requires_grad() for a in args)
+    if res.requires_grad_flag:
+        res.args_ = list(args)
+        res.vjp_ = vjp
+    return res
+
+
+def contiguous(a):  # functional/_utils.mojo:179-205
+    return np.ascontiguousarray(a.v)
+
+
+# ---------------------------------------------------------------------------------- init ops
+def full(shape, value):  # init_ops.mojo:196-205
+    return Array(np.full(tuple(shape), value, dtype=np.float32))
+
+
+def zeros(shape):
+    return Array(np.zeros(tuple(shape), dtype=np.float32))
+
+
+def ones(shape):
+    return Array(np.ones(tuple(shape), dtype=np.float32))
+
+
+def eye(n):
+    return Array(np.eye(n, dtype=np.float32))
+
+
+def complex(re, im):  # init_ops.mojo:419-433: a fresh leaf, no graph
+    return Array((contiguous(re) + 1j * contiguous(im)).astype(np.complex64))
+
+
+# ---------------------------------------------------------------------------------- view ops
+def broadcast_shapes(s0, s1):  # utils/_array_shape.mojo:366-411
+    return list(np.broadcast_shapes(tuple(s0), tuple(s1)))
+
+
+def expand(a, shape, ignore_axes=()):
+    """Stride-0 broadcast view (view_ops/expand_op.mojo:36-199); returns `a` itself when rank and
+    non-ignored extents already match (:161-172). vjp: reduce_add over the stretched axes, dims
+    kept (:121-126)."""
+    shape = list(shape)
+    nd = a.ndim()
+    ignore = [i + nd if i < 0 else i for i in ignore_axes]
+    if nd == len(shape) and all(i in ignore or s == t for i, (s, t) in enumerate(zip(a.shape(), shape))):
+        return a
+    diff = len(shape) - nd
+    tgt = list(shape[:diff]) + [a.shape()[i] if i in ignore else shape[i + diff] for i in range(nd)]
+    view = np.broadcast_to(a.v, tuple(tgt))
+
+    def vjp(primals, grad, out):
+        axes = [i for i, st in enumerate(out.stride()) if st == 0]
+        return [reduce_add(grad, axes)]
+    return op_array(view, [a], "brdcst", vjp)
+
+
+def _perm_axes(axis, ndim):  # permute_op.mojo:48-60: `axis` orders the trailing len(axis) dims
+    perm = list(range(ndim))
+    for i, ax in enumerate(axis):
+        perm[ndim - len(axis) + i] = ax + ndim if ax < 0 else ax
+    return perm
+
+
+def permute(a, axis):
+    perm = _perm_axes(list(axis), a.ndim())
+    ax = list(axis)
+    return op_array(np.transpose(a.v, perm), [a], "permute", lambda p, g, o: [permute_inv(g, ax)])
+
+
+def permute_inv(a, axis):  # permute_op.mojo:239-357
+    perm = _perm_axes(list(axis), a.ndim())
+    inv = [0] * len(perm)
+    for i, p in enumerate(perm):
+        inv[p] = i
+    ax = list(axis)
+    return op_array(np.transpose(a.v, inv), [a], "permute_inv", lambda p, g, o: [permute(g, ax)])
+
+
+def _squeezable(shape):  # squeeze_op.mojo:34-43
+    axes = [i for i, s in enumerate(shape) if s == 1]
+    if len(axes) == len(shape) and axes:
+        axes.pop()
+    return axes
+
+
+def squeeze(a):
+    axes = _squeezable(a.shape())
+    keep = tuple(slice(None) if i not in axes else 0 for i in range(a.ndim()))
+    return op_array(a.v[keep], [a], "squeeze", lambda p, g, o: [unsqueeze(g, axes)])
+
+
+def unsqueeze(a, axis):  # unsqueeze_op.mojo:42-74
+    axis = list(axis)
+    if not axis:
+        view = a.v
+    else:
+        shape = [-1] * (axis[-1] + 1)
+        for x in axis:
+            shape[x] = 1
+        src = a.shape()
+        idx = 0
+        for i in range(len(shape)):
+            if shape[i] == -1:
+                shape[i] = src[idx]
+                idx += 1
+        shape += src[idx:]
+        view = a.v.reshape(shape) if a.v.flags.c_contiguous else np.expand_dims(a.v, tuple(axis))
+    return op_array(view, [a], "unsqueeze", lambda p, g, o: [squeeze(g)])
+
+
+def reshape(a, shape):  # view_op.mojo:62-107
+    prim = a.shape()
+    return op_array(np.ascontiguousarray(a.v).reshape(tuple(shape)), [a], "reshape",
+                    lambda p, g, o: [reshape(g, prim)])
+
+
+def real(a):  # real_op.mojo:43-52, 75-77
+    if not a.is_complex():
+        return a
+    return op_array(a.v.real, [a], "real", lambda p, g, o: [complex(g, zeros(g.shape()))])
+
+
+# ----------------------------------------------------------------------------- elementwise ops
+def _binary(a, b, name, fn_real, fn_cplx, vjp):
+    """binary_op_array + execute_binary_op (binary_ops/_utils.mojo:57-177): both args are expanded
+    to the broadcast shape (views), made contiguous (materialised), then combined elementwise."""
+    shape = broadcast_shapes(a.shape(), b.shape())
+    a0, a1 = expand(a, shape), expand(b, shape)
+    x, y = contiguous(a0), contiguous(a1)
+    if np.iscomplexobj(x) or np.iscomplexobj(y):
+        x, y = x.astype(np.complex64), y.astype(np.complex64)
+        re, im = fn_cplx(x.real, y.real, x.imag, y.imag)
+        val = (re + 1j * im).astype(np.complex64)
+    else:
+        val = fn_real(x, y).astype(np.float32)
+    return op_array(val, [a0, a1], name, vjp)
+
+
+def _z():
+    return Array(0)
+
+
+def add(a, b):  # add_op.mojo:107-110
+    return _binary(a, b, "add", lambda x, y: x + y, lambda xr, yr, xi, yi: (xr + yr, xi + yi),
+                   lambda p, g, o: [g if p[0].requires_grad() else _z(), g if p[1].requires_grad() else _z()])
+
+
+def sub(a, b):  # sub_op.mojo:109-112
+    return _binary(a, b, "sub", lambda x, y: x - y, lambda xr, yr, xi, yi: (xr - yr, xi - yi),
+                   lambda p, g, o: [g if p[0].requires_grad() else _z(), neg(g) if p[1].requires_grad() else _z()])
+
+
+def mul(a, b):  # mul_op.mojo:125-128, 152-155 (no conjugation in the vjp)
+    return _binary(a, b, "mul", lambda x, y: x * y,
+                   lambda xr, yr, xi, yi: (xr * yr - xi * yi, xr * yi + xi * yr),
+                   lambda p, g, o: [mul(g, p[1]) if p[0].requires_grad() else _z(),
+                                    mul(g, p[0]) if p[1].requires_grad() else _z()])
+
+
+def div(a, b):  # div_op.mojo:108-114, 138-142: the real lane of the complex quotient
+    def vjp(p, g, o):
+        lhs = div(g, p[1]) if p[0].requires_grad() else _z()
+        rhs = div(mul(neg(g), p[0]), mul(p[1], p[1])) if p[1].requires_grad() else _z()
+        return [lhs, rhs]
+    with np.errstate(all="ignore"):
+        return _binary(a, b, "div", lambda x, y: (x * y) / (y * y),
+                       lambda xr, yr, xi, yi: ((xr * yr + xi * yi) / (yr * yr + yi * yi),
+                                               (xi * yr - xr * yi) / (yr * yr + yi * yi)), vjp)
+
+
+def pow_to(a, b):  # pow_op.mojo:109-115, 139-147: polar form, also for reals
+    def cplx(xr, yr, xi, yi):
+        with np.errstate(all="ignore"):
+            log_mag = np.log(np.sqrt(xr * xr + xi * xi))
+            arg = np.arctan2(xi, xr)
+            u = np.exp(log_mag * yr - arg * yi)
+            v = log_mag * yi + arg * yr
+            return u * np.cos(v), u * np.sin(v)
+
+    def realf(x, y):
+        z = np.zeros_like(x)
+        return cplx(x, y, z, z)[0]
+
+    def vjp(p, g, o):
+        lhs = mul(mul(g, p[1]), div(o, p[0])) if p[0].requires_grad() else _z()
+        rhs = mul(mul(g, o), log(p[0])) if p[1].requires_grad() else _z()
+        return [lhs, rhs]
+    return _binary(a, b, "pow_to", realf, cplx, vjp)
+
+
+def greater(a, b):  # comparison_ops/greater_op.mojo:46-60: 1.0 / 0.0, no gradient
+    shape = broadcast_shapes(a.shape(), b.shape())
+    x, y = contiguous(expand(a, shape)), contiguous(expand(b, shape))
+    return Array((x > y).astype(np.float32))
+
+
+def _unary(a, name, fn_real, fn_cplx, vjp):  # unary_ops/_utils.mojo:52-134
+    x = contiguous(a)
+    with np.errstate(all="ignore"):
+        if np.iscomplexobj(x):
+            re, im = fn_cplx(x.real, x.imag)
+            val = (re + 1j * im).astype(np.complex64)
+        else:
+            val = fn_real(x).astype(np.float32)
+    return op_array(val, [a], name, vjp)
+
+
+def neg(a):  # neg_op.mojo:91
+    return _unary(a, "neg", lambda x: -x, lambda r, i: (-r, -i), lambda p, g, o: [neg(g)])
+
+
+def relu(a):  # relu_op.mojo:51-52, 95, 115
+    if a.is_complex():
+        raise ValueError("Warning: Relu does not support complex numbers")
+    return _unary(a, "relu", lambda x: np.maximum(x, f32(0)), None,
+                  lambda p, g, o: [mul(greater(p[0], zeros([p[0].shape()[-1]])), g)])
+
+
+def tanh(a):  # tanh_op.mojo:92, 112-115: sinh(2x) / (cosh(2x) + cos(2 im)); NaN for |x| > ~44
+    def cplx(r, i):
+        d = np.cosh(2 * r) + np.cos(2 * i)
+        return np.sinh(2 * r) / d, np.sin(2 * i) / d
+    return _unary(a, "tanh", lambda x: np.sinh(f32(2) * x) / (np.cosh(f32(2) * x) + f32(1)), cplx,
+                  lambda p, g, o: [mul(1 - square(tanh(p[0])), g)])
+
+
+def sigmoid(a):  # sigmoid_op.mojo:49-50, 98, 118-121
+    if a.is_complex():
+        raise ValueError("Warning: Sigmoid does not support complex numbers")
+    return _unary(a, "sigmoid", lambda x: f32(1) / (f32(1) + np.exp(-x)), None,
+                  lambda p, g, o: [mul(mul(o, 1 - o), g)])
+
+
+def square(a):  # square_op.mojo:96, 117-119
+    return _unary(a, "square", lambda x: x * x, lambda r, i: (r * r - i * i, 2 * r * i),
+                  lambda p, g, o: [mul(2 * p[0], g)])
+
+
+def sqrt(a):  # sqrt_op.mojo:91, 111-114: the real lane of the complex root
+    def cplx(r, i):
+        m = np.sqrt(r * r + i * i)
+        return np.sqrt((m + r) / 2), np.copysign(np.sqrt((m - r) / 2), i)
+    return _unary(a, "sqrt", lambda x: np.sqrt((np.sqrt(x * x) + x) / f32(2)), cplx,
+                  lambda p, g, o: [div(g, 2 * sqrt(p[0]))])
+
+
+def log(a):  # log_op.mojo:91, 111-115
+    return _unary(a, "log", lambda x: np.log(np.sqrt(x * x)),
+                  lambda r, i: (np.log(np.sqrt(r * r + i * i)), np.arctan2(i, r)),
+                  lambda p, g, o: [div(g, p[0])])
+
+
+def exp(a):
+    return _unary(a, "exp", lambda x: np.exp(x), lambda r, i: (np.exp(r) * np.cos(i), np.exp(r) * np.sin(i)),
+                  lambda p, g, o: [mul(exp(p[0]), g)])
+
+
+def conj(a):  # conj_op.mojo:29-63
+    return _unary(a, "conj", lambda x: x, lambda r, i: (r, -i), lambda p, g, o: [conj(g)])
+
+
+def sign(a):  # sign_op.mojo:78-81; default (pass-through) vjp
+    def cplx(r, i):
+        n = np.sqrt(r * r + i * i)
+        return r / n, i / n
+    return _unary(a, "sign", lambda x: x / np.sqrt(x * x), cplx, lambda p, g, o: [g])
+
+
+def abs(a):  # abs_op.mojo:93, 114-115: complex layout kept, imaginary part zero
+    return _unary(a, "abs", lambda x: np.sqrt(x * x), lambda r, i: (np.sqrt(r * r + i * i), np.zeros_like(r)),
+                  lambda p, g, o: [mul(sign(p[0]), g)])
+
+
+def to_abs(a):  # abs_op.mojo:157
+    return real(abs(a))
+
+
+# ------------------------------------------------------------------------------- reductions
+def reduce_add(a, axis):  # reduce_ops/reduce_add_op.mojo:39-274
+    nd = a.ndim()
+    axes = sorted(set(x + nd if x < 0 else x for x in axis))
+    x = contiguous(a)
+    shape = [1 if i in axes else s for i, s in enumerate(x.shape)]
+    if config["mode"] == "fast":
+        val = x.astype(np.complex128 if np.iscomplexobj(x) else np.float64).sum(
+            axis=tuple(axes), keepdims=True).astype(x.dtype) if axes else x.copy()
+    else:
+        out = np.zeros(shape, dtype=x.dtype)
+        shp = (C.c_int64 * nd)(*x.shape)
+        red = (C.c_int32 * nd)(*[1 if i in axes else 0 for i in range(nd)])
+        lib().oracle_reduce_add(_ptr(x), _ptr(out), nd, shp, red, 2 if np.iscomplexobj(x) else 1,
+                                config["nelts"])
+        val = out
+    return op_array(val, [a], "reduce_add", lambda p, g, o: [expand(g, p[0].shape())])
+
+
+def sum(a):  # sum_op.mojo:35-62 -> shape [1]
+    return squeeze(reduce_add(a, list(range(a.ndim()))))
+
+
+def mean(a, axes=None, keepdims=False):  # mean_op.mojo:35-65
+    if axes is None:
+        axes = list(range(a.ndim()))
+    res = reduce_add(a, axes)
+    divisor = float(np.float32(a.size() / res.size()))
+    out = res / divisor
+    return out if keepdims else squeeze(out)
+
+
+def mse(pred, target):  # loss_ops/mse_op.mojo:18-20
+    diff = sub(pred, target)
+    return sum(mul(diff, diff)) / float(pred.size())
+
+
+# ----------------------------------------------------------------------------------- matmul
+def _rhs_transposed(b):
+    """The transposed-contiguous rhs that matmul_fwd builds (matmul_op.mojo:111-136). With the
+    quirk switch on, a transposed view of a contiguous SQUARE matrix is taken as already being in
+    that form and its storage is used as is."""
+    bt = np.swapaxes(b.v, -1, -2)
+    if config["square_T_quirk"] and b.v.shape[-1] == b.v.shape[-2] and b.v.shape[-1] > 1:
+        expect = [s // b.v.itemsize for s in np.empty(b.v.shape, dtype=b.v.dtype).strides]
+        swapped = list(b.stride())
+        swapped[-1], swapped[-2] = swapped[-2], swapped[-1]
+        if swapped == expect:
+            # arg1 = args[1] keeps the view's strides, and the dot-product loop then reads element
+            # (n, k) of the VIEW, i.e. the product uses the view itself as if it were its transpose.
+            return np.ascontiguousarray(b.v)
+    return np.ascontiguousarray(bt)
+
+
+def matmul(a, b):  # matmul_op.mojo:36-90 (shape), 93-254 (fwd), 257-284 (vjp)
+    if a.ndim() < 2 or b.ndim() < 2 or a.shape()[-1] != b.shape()[-2]:
+        raise ValueError("Error: matmul shapes are incompatible: %s @ %s" % (a.shape(), b.shape()))
+    batch = broadcast_shapes(a.shape()[:-2], b.shape()[:-2])
+    a0 = expand(a, batch + a.shape()[-2:], ignore_axes=(-2, -1))
+    a1 = expand(b, batch + b.shape()[-2:], ignore_axes=(-2, -1))
+    x = contiguous(a0)
+    bt = _rhs_transposed(a1)
+    M, K, N = x.shape[-2], x.shape[-1], a1.shape()[-1]
+    cplx = np.iscomplexobj(x) or np.iscomplexobj(bt)
+    if cplx:
+        x, bt = x.astype(np.complex64), bt.astype(np.complex64)
+    out = np.zeros(tuple(batch) + (M, N), dtype=x.dtype)
+    xb, bb, ob = x.reshape(-1, M, K), bt.reshape(-1, N, K), out.reshape(-1, M, N)
+    for i in range(ob.shape[0]):
+        if cplx:
+            lib().oracle_matmul_c64(_ptr(xb[i]), _ptr(bb[i]), _ptr(ob[i]), M, N, K, config["nelts"])
+        elif config["mode"] == "fast":
+            lib().oracle_matmul_fast(_ptr(xb[i]), _ptr(bb[i]), _ptr(ob[i]), M, N, K)
+        else:
+            lib().oracle_matmul_f32(_ptr(xb[i]), _ptr(bb[i]), _ptr(ob[i]), M, N, K, config["nelts"])
+
+    def vjp(p, g, o):
+        lhs = matmul(g, p[1].T()) if p[0].requires_grad() else _z()
+        rhs = matmul(p[0].T(), g) if p[1].requires_grad() else _z()
+        return [lhs, rhs]
+    return op_array(out, [a0, a1], "matmul", vjp)
+
+
+# -------------------------------------------------------------------------------------- FFT
+def _fft_core(x, dims, conj_in, conj_out, divisor):
+    """fft_cooley_tukey_parallel (fft_ops/fft_cooley_tukey.mojo:179-313): float64 working copy
+    (conjugated for the inverse), then per transformed dim the axis is made innermost and every row
+    goes through the radix-2 kernel; finally cast back to float32 (conjugate and divide for the
+    inverse). The transform is the standard one for every `dims` (the reference's result layout is
+    only correct when the last transformed dim is the last axis, :294-310)."""
+    work = x.astype(np.complex128)
+    if conj_in:
+        work = np.conj(work)
+    for d in dims:
+        n = work.shape[d]
+        if n & (n - 1):
+            raise ValueError("Dimension must be a power of two")  # :232-235
+        moved = np.ascontiguousarray(np.moveaxis(work, d, -1))
+        rows = moved.size // n if n else 0
+        if rows and n > 1:
+            lib().oracle_fft_rows_f64(_ptr(moved), rows, n, config["fft_threads"])
+        work = np.moveaxis(moved, -1, d)
+    if conj_out:
+        work = np.conj(work)
+    return (work / divisor).astype(np.complex64)
+
+
+def _norm_dims(x, dims):
+    nd = x.ndim()
+    if not dims:
+        return list(range(nd))
+    return [d + nd if d < 0 else d for d in dims]
+
+
+def fftn(x, dims=None, norm="backward"):  # fftn_op.mojo:25-79
+    d = _norm_dims(x, list(dims) if dims else [])
+    xin = contiguous(x) if x.is_complex() else contiguous(x).astype(np.complex64)
+    val = _fft_core(xin, d, False, False, 1.0)
+    dl = list(dims) if dims else []
+    return op_array(val, [x], "fftn", lambda p, g, o: [conj(fftn(conj(g), dl, norm))])
+
+
+def ifftn(x, dims=None, norm="backward"):  # ifftn_op.mojo:24-96: conj, forward kernel, conj, / prod(n)
+    d = _norm_dims(x, list(dims) if dims else [])
+    xin = contiguous(x) if x.is_complex() else contiguous(x).astype(np.complex64)
+    n = 1
+    for a in d:
+        n *= xin.shape[a]
+    val = _fft_core(xin, d, True, True, float(np.float32(n)))
+    dl = list(dims) if dims else []
+    return op_array(val, [x], "ifftn", lambda p, g, o: [conj(ifftn(conj(g), dl, norm))])
+
+
+def fft(x, dim=-1, norm="backward"):
+    return fftn(x, [dim], norm)
+
+
+def ifft(x, dim=-1, norm="backward"):
+    return ifftn(x, [dim], norm)
+
+
+def fft2(x, dims=(-2, -1), norm="backward"):
+    return fftn(x, list(dims), norm)
+
+
+def ifft2(x, dims=(-2, -1), norm="backward"):
+    return ifftn(x, list(dims), norm)
+
+
+# --------------------------------------------------------------------------------- autograd
+def top_order(out):  # utils/general.mojo:26-32
+    trace, seen, stack = [], {id(out)}, [(out, 0)]
+    while stack:
+        node, i = stack.pop()
+        if i < len(node.args_):
+            stack.append((node, i + 1))
+            a = node.args_[i]
+            if id(a) not in seen:
+                seen.add(id(a))
+                stack.append((a, 0))
+        else:
+            trace.append(node)
+    return trace
+
+
+def remove_grad_rec(out):  # utils/general.mojo:59-62
+    for n in top_order(out):
+        n.remove_grad()
+
+
+def backward(arg, create_graph=False):
+    """jacrev (autograd/functional.mojo:26-67)."""
+    out = arg
+    trace = top_order(out)
+    last = out.shape()[-1]
+    if out.ndim() != 1 or last != 1:
+        seed = reshape(eye(out.size()), out.shape() + out.shape())
+    else:
+        seed = ones([last])
+    out.grad_(seed)
+    for curr in reversed(trace):
+        primals = curr.args_
+        if not primals:
+            continue
+        grads = curr.vjp_(primals, curr.grad(), curr)
+        for primal, g in zip(primals, grads):
+            if not primal.requires_grad():
+                continue
+            if primal.has_grad():
+                g = add(g, primal.grad())
+            primal.grad_(g)
+            if not create_graph:
+                g.clear_args()
+
+
+def grad(outs, inputs, retain_grads=True, create_graph=False):  # autograd/functional.mojo:70-97
+    for o in outs:
+        remove_grad_rec(o)
+    for i in inputs:
+        remove_grad_rec(i)
+    for o in outs:
+        o.backward(create_graph=create_graph)
+    final = []
+    for i in inputs:
+        g = i.grad()
+        if not create_graph:
+            g.clear_args()
+            g.remove_grad()
+        if not retain_grads:
+            i.remove_grad()
+        final.append(g)
+    return final
+
+
+# ------------------------------------------------------------------------------- nn / optim
+ACTIVATIONS = {"relu": relu, "tanh": tanh, "sigmoid": sigmoid}
+
+
+def mlp_forward(x, weights, biases, activation="relu"):
+    """nn.MLP.forward (nn/modules/_mlp.mojo:47-53): pred @ W + b, activation on all but the last
+    layer (the reference hard-codes relu)."""
+    pred = x
+    act = ACTIVATIONS[activation]
+    for i, (w, b) in enumerate(zip(weights, biases)):
+        pred = pred @ w + b
+        if i < len(weights) - 1:
+            pred = act(pred)
+    return pred
+
+
+class Adam:
+    """optim/adam.mojo:17-65, written with the same array expressions; t starts at float32 1."""
+
+    def __init__(self, params, lr=0.001, beta1=0.9, beta2=0.999, eps=1e-8):
+        self.params = list(params)
+        self.lr, self.beta1, self.beta2, self.eps = f32(lr), f32(beta1), f32(beta2), f32(eps)
+        self.t = f32(1)
+        self.m = [Array(p.shape()) for p in self.params]
+        self.v = [Array(p.shape()) for p in self.params]
+
+    def step(self):
+        one = f32(1)
+        for i, p in enumerate(self.params):
+            g = p.grad()
+            self.m[i] = float(self.beta1) * self.m[i] + float(one - self.beta1) * g
+            self.m[i].clear_args()
+            self.v[i] = float(self.beta2) * self.v[i] + float(one - self.beta2) * g * g
+            self.v[i].clear_args()
+            m_hat = self.m[i] / float(one - np.power(self.beta1, self.t, dtype=np.float32))
+            v_hat = self.v[i] / float(one - np.power(self.beta2, self.t, dtype=np.float32))
+            p -= float(self.lr) * m_hat / (sqrt(v_hat) + float(self.eps))
+            p.clear_args()
+        self.t = f32(self.t + one)
