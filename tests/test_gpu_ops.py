@@ -1,0 +1,273 @@
+"""GPU parity of single ops and their VJPs against the CPU oracle, on the reference's test shapes
+and on ragged / edge shapes. Every program is written once against the shared Endia API and run
+through both implementations on the same seeded inputs."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+from conftest import rng, rel_l2, max_rel
+
+pytestmark = pytest.mark.gpu
+
+TOL = 1e-4  # max relative error (floor = 1e-3 of the tensor's max), fp32 ops
+
+
+def both(nd, eo, prog, *inputs):
+    """Run prog(lib, *arrays) with both libraries; return lists of numpy results."""
+    out_g = prog(nd, *[nd.Array(x, requires_grad=True) for x in inputs])
+    out_o = prog(eo, *[eo.Array(x.copy(), requires_grad=True) for x in inputs])
+    return [(g.to_numpy(), o.to_numpy(), g.shape(), o.shape()) for g, o in zip(out_g, out_o)]
+
+
+def check(results, tol=TOL):
+    for g, o, sg, so in results:
+        assert sg == so, "shape metadata differs: %s vs %s" % (sg, so)
+        if np.iscomplexobj(o):
+            assert rel_l2(g, o) < tol
+        else:
+            assert max_rel(g, o) < tol, max_rel(g, o)
+
+
+UNARY = ["neg", "relu", "tanh", "sigmoid", "square", "exp", "conj"]
+
+
+@pytest.mark.parametrize("name", UNARY)
+def test_unary_fwd_grad(nd, oracle, name):
+    x = rng(1).standard_normal((2, 30, 40)).astype(np.float32)
+
+    def prog(L, X):
+        y = getattr(L, name)(X)
+        L.sum(y).backward()
+        return [y, X.grad()]
+    check(both(nd, oracle, prog, x))
+
+
+@pytest.mark.parametrize("name", ["sqrt", "abs", "log", "sign"])
+def test_unary_positive_inputs(nd, oracle, name):
+    x = (np.abs(rng(2).standard_normal((40, 50))) + 0.1).astype(np.float32)
+
+    def prog(L, X):
+        y = getattr(L, name)(X)
+        L.sum(y * y).backward()
+        return [y, X.grad()]
+    check(both(nd, oracle, prog, x))
+
+
+@pytest.mark.parametrize("name", ["neg", "square", "conj", "abs", "sign", "sqrt", "exp", "log", "tanh"])
+def test_unary_complex(nd, oracle, name):
+    r = rng(3)
+    z = (r.standard_normal((6, 33)) + 1j * r.standard_normal((6, 33))).astype(np.complex64)
+
+    def prog(L, Z):
+        return [getattr(L, name)(Z)]
+    check(both(nd, oracle, prog, z), tol=2e-5)
+
+
+def test_relu_sigmoid_reject_complex(nd):
+    z = nd.Array(np.ones((4,), np.complex64))
+    with pytest.raises(nd.EndiaError):
+        nd.relu(z)
+    with pytest.raises(nd.EndiaError):
+        nd.sigmoid(z)
+
+
+@pytest.mark.parametrize("name", ["add", "sub", "mul", "div"])
+@pytest.mark.parametrize("shapes", [((2, 30, 40), (30, 40)), ((128, 32), (32,)), ((7, 1, 5), (3, 1)),
+                                    ((1,), (9, 13)), ((64, 64), (64, 64))])
+def test_binary_broadcast_fwd_grad(nd, oracle, name, shapes):
+    r = rng(4)
+    a = r.standard_normal(shapes[0]).astype(np.float32)
+    b = (r.standard_normal(shapes[1]) + 3.0).astype(np.float32)
+
+    def prog(L, A, B):
+        y = getattr(L, name)(A, B)
+        L.sum(y * y).backward()
+        return [y, A.grad(), B.grad()]
+    check(both(nd, oracle, prog, a, b))
+
+
+def test_binary_complex_and_pow(nd, oracle):
+    r = rng(5)
+    a = (r.standard_normal((5, 17)) + 1j * r.standard_normal((5, 17))).astype(np.complex64)
+    b = (r.standard_normal((17,)) + 1j * r.standard_normal((17,)) + 2).astype(np.complex64)
+    p = (np.abs(r.standard_normal((5, 17))) + 0.5).astype(np.float32)
+
+    def prog(L, A, B):
+        return [L.mul(A, B), L.div(A, B), L.add(A, B), L.sub(A, B)]
+    check(both(nd, oracle, prog, a, b), tol=2e-5)
+
+    def prog2(L, P):
+        y = P ** 3.0
+        L.sum(y).backward()
+        return [y, P.grad(), (-P) ** 2.0]
+    check(both(nd, oracle, prog2, p))
+
+
+def test_scalar_operator_sugar(nd, oracle):
+    x = rng(6).standard_normal((12, 20)).astype(np.float32)
+
+    def prog(L, X):
+        y = (1.0 - 2.0 * X) / 4.0 + X * X - 0.5
+        L.sum(y).backward()
+        return [y, X.grad()]
+    check(both(nd, oracle, prog, x))
+
+
+@pytest.mark.parametrize("shape,axes", [((2, 30, 40), [1]), ((2, 30, 40), [0, 2]), ((128, 32), [0]),
+                                        ((8192, 64), [0]), ((3, 5000), [1]), ((70000,), [0]),
+                                        ((4, 3, 2, 5), [1, 3]), ((1, 1), [0, 1])])
+def test_reduce_add_mean_sum(nd, oracle, shape, axes):
+    x = rng(7).standard_normal(shape).astype(np.float32)
+
+    def prog(L, X):
+        red = L.reduce_add(X, axes)
+        m = L.mean(X, axes)
+        s = L.sum(X * X)
+        s.backward()
+        return [red, m, s, X.grad()]
+    # sums of many terms: the CPU order is sequential, the GPU order a tree -> 1e-4 on the result
+    check(both(nd, oracle, prog, x), tol=2e-4)
+
+
+def test_reduce_complex(nd, oracle):
+    r = rng(8)
+    z = (r.standard_normal((6, 40)) + 1j * r.standard_normal((6, 40))).astype(np.complex64)
+
+    def prog(L, Z):
+        return [L.reduce_add(Z, [0]), L.reduce_add(Z, [1]), L.sum(Z)]
+    check(both(nd, oracle, prog, z), tol=2e-5)
+
+
+def test_view_ops_metadata_and_grads(nd, oracle):
+    x = rng(9).standard_normal((2, 30, 40)).astype(np.float32)
+
+    def prog(L, X):
+        p = L.permute(X, [2, 0, 1])
+        e = L.expand(L.reduce_add(X, [0]), [2, 30, 40])
+        u = L.unsqueeze(L.squeeze(L.reduce_add(X, [0, 1])), [0, 2])
+        rsh = L.reshape(p, [40, 60])
+        y = L.sum(rsh * 2.0) + L.sum(e * X) + L.sum(u)
+        y.backward()
+        return [p, e, u, rsh, y, X.grad()]
+    res = both(nd, oracle, prog, x)
+    check(res, tol=2e-4)
+    # strides and offsets of the views must agree exactly
+    X = nd.Array(x)
+    O = oracle.Array(x)
+    for fn in (lambda L, A: L.permute(A, [2, 0, 1]), lambda L, A: A.T(),
+               lambda L, A: L.expand(L.reduce_add(A, [0]), [2, 30, 40]),
+               lambda L, A: L.squeeze(L.reduce_add(A, [0, 1])),
+               lambda L, A: L.unsqueeze(L.squeeze(L.reduce_add(A, [0, 1])), [0, 2])):
+        g, o = fn(nd, X), fn(oracle, O)
+        assert g.shape() == o.shape()
+        assert [s for s, e in zip(g.stride(), g.shape()) if e > 1] == \
+               [s for s, e in zip(o.stride(), o.shape()) if e > 1]
+        assert g.storage_offset() == o.storage_offset()
+
+
+MM_SHAPES = [((2, 30, 40), (40, 50)), ((128, 1), (1, 32)), ((128, 32), (32, 32)), ((128, 32), (32, 1)),
+             ((1, 1), (1, 1)), ((33, 7), (7, 129)), ((257, 130), (130, 65)), ((3, 2, 9, 5), (2, 5, 4)),
+             ((512, 300), (300, 260))]
+
+
+@pytest.mark.parametrize("shapes", MM_SHAPES)
+def test_matmul_fwd_and_vjp(nd, oracle, shapes):
+    r = rng(10)
+    a = r.standard_normal(shapes[0]).astype(np.float32)
+    b = r.standard_normal(shapes[1]).astype(np.float32)
+
+    def prog(L, A, B):
+        y = L.matmul(A, B)
+        L.sum(y * y).backward()
+        return [y, A.grad(), B.grad()]
+    oracle.config["mode"] = "fast"
+    try:
+        check(both(nd, oracle, prog, a, b))
+    finally:
+        oracle.config["mode"] = "faithful"
+
+
+def test_matmul_square_weight_is_mathematically_correct(nd):
+    r = rng(11)
+    g = r.standard_normal((5, 4)).astype(np.float32)
+    w = r.standard_normal((4, 4)).astype(np.float32)
+    out = nd.matmul(nd.Array(g), nd.Array(w).T()).to_numpy()
+    assert np.allclose(out, g @ w.T, atol=1e-5)
+
+
+def test_matmul_complex(nd, oracle):
+    r = rng(12)
+    a = (r.standard_normal((9, 20)) + 1j * r.standard_normal((9, 20))).astype(np.complex64)
+    b = (r.standard_normal((20, 11)) + 1j * r.standard_normal((20, 11))).astype(np.complex64)
+
+    def prog(L, A, B):
+        return [L.matmul(A, B), L.matmul(A, B.T().T())]
+    check(both(nd, oracle, prog, a, b), tol=2e-5)
+
+
+def test_matmul_rejects_bad_shapes(nd):
+    with pytest.raises(nd.EndiaError):
+        nd.matmul(nd.Array(np.ones((3, 4), np.float32)), nd.Array(np.ones((5, 6), np.float32)))
+
+
+def _dev(nd, a):
+    arr = nd.Array(np.ascontiguousarray(a))
+    return arr
+
+
+@pytest.mark.parametrize("algo", [1])
+@pytest.mark.parametrize("ta,tb", [(0, 0), (0, 1), (1, 0), (1, 1)])
+@pytest.mark.parametrize("M,N,K", [(128, 128, 64), (200, 136, 72), (1, 5, 3), (130, 257, 33)])
+def test_gemm_c_abi_all_layouts_with_epilogue(nd, ta, tb, M, N, K, algo):
+    """endia_b200_gemm called directly: transposed operands, bias + activation, derivative mask,
+    accumulation (beta) and the fused column sum."""
+    from endia_b200 import _lib
+    from endia_b200._array import stream, alloc
+    r = rng(13)
+    a = r.standard_normal((K, M) if ta else (M, K)).astype(np.float32)
+    b = r.standard_normal((N, K) if tb else (K, N)).astype(np.float32)
+    bias = r.standard_normal(N).astype(np.float32)
+    saved = r.standard_normal((M, N)).astype(np.float32)
+    c0 = r.standard_normal((M, N)).astype(np.float32)
+    A, B, BIAS, SAVED, Cd = _dev(nd, a), _dev(nd, b), _dev(nd, bias), _dev(nd, saved), _dev(nd, c0)
+    colsum = nd.Array([N])
+    scratch = alloc(_lib.lib.endia_b200_gemm_colsum_scratch_bytes(M, N) // 4 + 1)
+    epi = _lib.Epilogue()
+    epi.alpha, epi.beta = 0.5, 2.0
+    epi.bias = BIAS.data_ptr()
+    epi.act, epi.dact = _lib.ACT_TANH, _lib.ACT_SIGMOID
+    epi.dact_src, epi.ld_dact = SAVED.data_ptr(), N
+    epi.colsum, epi.colsum_scratch = colsum.data_ptr(), scratch.data_ptr()
+    _lib.call("endia_b200_gemm", ta, tb, M, N, K, A.data_ptr(), a.shape[1], B.data_ptr(), b.shape[1],
+              Cd.data_ptr(), N, 1, 0, 0, 0, C.byref(epi), algo, stream())
+    am = (a.T if ta else a).astype(np.float64)
+    bm = (b.T if tb else b).astype(np.float64)
+    v = np.tanh(0.5 * (am @ bm) + bias) * (saved.astype(np.float64) * (1 - saved)) + 2.0 * c0
+    assert max_rel(Cd.to_numpy(), v) < TOL
+    assert max_rel(colsum.to_numpy(), v.sum(0)) < 2e-4
+
+
+def test_c_abi_error_codes(nd):
+    from endia_b200 import _lib
+    from endia_b200._array import stream
+    x = nd.Array(np.ones((4, 6), np.complex64))
+    y = nd.Array([4, 6], is_complex=True)
+    dims = (C.c_int32 * 1)(1)
+    st = _lib.lib.endia_b200_fft_c2c(x.desc(), y.desc(), dims, 1, 0, 1.0, None, stream())
+    assert st == _lib.EPOW2 and b"power of two" in _lib.lib.endia_b200_last_error()
+    st = _lib.lib.endia_b200_gemm(0, 0, 4, 4, 4, x.data_ptr(), 2, x.data_ptr(), 4, y.data_ptr(), 4, 1, 0,
+                                  0, 0, None, 0, stream())
+    assert st == _lib.EINVAL
+    st = _lib.lib.endia_b200_ew_unary(99, x.desc(), y.desc(), stream())
+    assert st == _lib.EINVAL
+    st = _lib.lib.endia_b200_adam_step_multi(1, None, None, None, None, None, 1e-3, .9, .999, 1e-8, 1., 1., None)
+    assert st == _lib.EINVAL
+
+
+def test_empty_arrays(nd):
+    e = nd.Array([0, 5])
+    assert nd.add(e, e).shape() == [0, 5]
+    assert nd.relu(e).to_numpy().shape == (0, 5)
+    m = nd.matmul(nd.Array([0, 3]), nd.Array([3, 4]))
+    assert m.shape() == [0, 4]

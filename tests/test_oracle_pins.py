@@ -276,3 +276,25 @@ def test_second_order_gradient_penalty_vs_torch(oracle):
     for a, b in zip(grads, tg):
         bn = b.numpy()
         assert np.abs(a.v.reshape(bn.shape) - bn).max() <= 1e-4 * max(np.abs(bn).max(), 1e-6)
+
+
+def test_oracle_reproduces_golden_fixtures(oracle):
+    """The committed fixtures (tests/golden/make_golden.py) pin the oracle against regressions."""
+    import os
+    from test_gpu_mlp import make_mlp_inputs, train_step, fwd_unfused
+    eo = oracle
+    here = os.path.join(os.path.dirname(__file__), "golden")
+    gold = np.load(os.path.join(here, "c1_mlp_step.npz"))
+    Ws, bs, x, y = make_mlp_inputs([1, 32, 32, 32, 1], 128, 0, x_dist="uniform")
+    res = train_step(eo, fwd_unfused("relu"), Ws, bs, x, y, steps=1)
+    assert np.array_equal(res["loss"], gold["loss"])
+    for i in range(8):
+        assert np.array_equal(res["grads"][i], gold["grad_%d" % i])
+        assert np.array_equal(res["params"][i], gold["param_%d" % i])
+    f = np.load(os.path.join(here, "fft_256.npz"))
+    Z = eo.Array(f["x"], requires_grad=True)
+    Y = eo.fft(Z)
+    loss = eo.sum(eo.square(eo.to_abs(Y))) * (1.0 / 256)
+    loss.backward()
+    assert np.array_equal(Y.to_numpy(), f["y"]) and np.array_equal(Z.grad().to_numpy(), f["grad"])
+    assert rel_l2(f["grad"], 2 * f["x"]) < 1e-6
