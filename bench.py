@@ -1,0 +1,352 @@
+"""Benchmark of the training-step hot path: fp32 MLP 1024->4096->4096->4096->1024 (tanh hidden,
+zero bias, Kaiming-uniform weights), global batch 8192, MSE loss, one Adam step per iteration;
+synthetic N(0,1) inputs and targets (seeded). One step = forward + backward + Adam over one batch.
+
+  python bench.py --gpus 1 --steps 10 --warmup 3          # this implementation (B200)
+  python bench.py --impl reference --steps 1 --warmup 0   # Endia's CPU algorithm (oracle port)
+
+Under torchrun (--gpus N > 1) the global batch is split over the ranks (strong scaling), the
+gradients are all-reduced over NCCL while the backward pass is still running, and the mean over
+ranks is folded into Adam's gradient scale. Rank 0 prints one JSON line.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+DIMS = [1024, 4096, 4096, 4096, 1024]
+GLOBAL_BATCH = 8192
+METRIC = "train-step samples/s (MLP fwd+bwd+Adam)"
+UNIT = "samples/s"
+
+
+def gemm_flops(batch, dims=DIMS):
+    """Sum of 2*M*N*K over the GEMMs of one step: forward, dW for every layer, dX for every layer
+    but the first (x needs no gradient)."""
+    fwd = sum(2.0 * batch * dims[i] * dims[i + 1] for i in range(len(dims) - 1))
+    return fwd + fwd + sum(2.0 * batch * dims[i] * dims[i + 1] for i in range(1, len(dims) - 1))
+
+
+def make_weights(seed=0, dims=DIMS):
+    r = np.random.Generator(np.random.PCG64(seed))
+    Ws = []
+    for i in range(len(dims) - 1):
+        lim = np.sqrt(6.0 / dims[i])
+        Ws.append(r.uniform(-lim, lim, (dims[i], dims[i + 1])).astype(np.float32))
+    return r, Ws
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as fh:
+            d = json.load(fh)
+        return {"hbm_gbs": d["hbm_gbs"], "bf16_tflops": d["bf16_tflops"],
+                "bf16_tflops_sustained": d["bf16_tflops_sustained"], "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu = gpu_index
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.gpu), "--query-gpu=" + self.QUERY,
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.proc is None:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, reasons, smax = [], set(), None
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        try:
+            for line in open(self.path):
+                f = [x.strip() for x in line.split(",")]
+                if len(f) < 9:
+                    continue
+                try:
+                    sm.append(float(f[1]))
+                    smax = float(f[2])
+                except ValueError:
+                    continue
+                for name, val in zip(names, f[5:9]):
+                    if val.lower().startswith("active"):
+                        reasons.add(name)
+            os.unlink(self.path)
+        except OSError:
+            pass
+        if sm:
+            # the busiest half of the samples: the region under load
+            top = sorted(sm)[len(sm) // 2:]
+            out.update(sm_mhz=float(np.median(top)) if len(sm) < 4 else float(np.median(sm)),
+                       sm_max_mhz=smax, reasons=sorted(reasons), samples=len(sm))
+        return out
+
+
+class GemmTimer:
+    """Brackets every GEMM launch with CUDA events on the launching stream."""
+
+    def __init__(self, torch):
+        self.torch = torch
+        self.records = []
+        self._cur = None
+
+    def start(self, flops):
+        e0 = self.torch.cuda.Event(enable_timing=True)
+        e0.record()
+        self._cur = (flops, e0)
+
+    def stop(self):
+        e1 = self.torch.cuda.Event(enable_timing=True)
+        e1.record()
+        self.records.append((self._cur[0], self._cur[1], e1))
+
+    def summary(self):
+        ms = sum(a.elapsed_time(b) for _, a, b in self.records)
+        fl = sum(f for f, _, _ in self.records)
+        return len(self.records), fl, ms
+
+
+class TrainStep:
+    """The step a user of the library writes: nn.mlp + mse + backward + Adam.step + zero_grad."""
+
+    def __init__(self, nd, torch, rank, world, seed=0):
+        from endia_b200 import dist as ndist
+        self.nd, self.torch, self.rank, self.world = nd, torch, rank, world
+        self.local_batch = GLOBAL_BATCH // world
+        r, Ws = make_weights(seed)
+        x = r.standard_normal((GLOBAL_BATCH, DIMS[0])).astype(np.float32)
+        y = r.standard_normal((GLOBAL_BATCH, DIMS[-1])).astype(np.float32)
+        lo, hi = rank * self.local_batch, (rank + 1) * self.local_batch
+        self.x_host = torch.from_numpy(np.ascontiguousarray(x[lo:hi])).pin_memory()
+        self.y_host = torch.from_numpy(np.ascontiguousarray(y[lo:hi])).pin_memory()
+        self.loss_host = torch.empty(1, dtype=torch.float32).pin_memory()
+        self.W = [nd.Array(w, requires_grad=True) for w in Ws]
+        self.B = [nd.Array([DIMS[i + 1]], requires_grad=True) for i in range(len(DIMS) - 1)]
+        self.params = [p for wb in zip(self.W, self.B) for p in wb]
+        self.X = nd.Array(x[lo:hi])
+        self.Y = nd.Array(y[lo:hi])
+        self.opt = nd.optim.Adam(self.params, lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8)
+        self.reducer = None
+        if world > 1:
+            self.reducer = ndist.GradAllReducer(self.params)
+            self.opt.grad_scale = 1.0 / world   # global-mean loss = mean of the ranks' local means
+        self.flat = ndist.flat_tensor
+
+    def step(self, host_io=False):
+        nd = self.nd
+        if host_io:
+            self.flat(self.X).copy_(self.x_host.reshape(-1), non_blocking=True)
+            self.flat(self.Y).copy_(self.y_host.reshape(-1), non_blocking=True)
+        pred = nd.nn.mlp([self.X, None] + self.params, activation="tanh")
+        loss = nd.mse(pred, self.Y)
+        loss.backward()
+        if self.reducer is not None:
+            self.reducer.wait()
+        self.opt.step()
+        loss.zero_grad()
+        if host_io:
+            self.loss_host.copy_(self.flat(loss), non_blocking=True)
+            self.torch.cuda.current_stream().synchronize()
+            return float(self.loss_host[0])
+        return loss
+
+
+def cpu_baseline(sample_rows=48, threads_note=True):
+    """Endia's CPU algorithm (the oracle port, faithful mode: single-threaded dot-product matmul,
+    one temporary per op, Adam as array expressions) on a bounded sample of the same workload:
+    `sample_rows` rows of the batch through the full-size network. Forward+backward scales linearly
+    with the batch and the Adam step does not depend on it, so the full-batch time is
+    rows-time * (8192 / sample_rows) + Adam-time."""
+    from oracle import endia_oracle as eo
+    eo.build()
+    eo.config["mode"] = "faithful"
+    r, Ws = make_weights(0)
+    x = r.standard_normal((sample_rows, DIMS[0])).astype(np.float32)
+    y = r.standard_normal((sample_rows, DIMS[-1])).astype(np.float32)
+    W = [eo.Array(w, requires_grad=True) for w in Ws]
+    B = [eo.Array(np.zeros(DIMS[i + 1], np.float32), requires_grad=True) for i in range(len(DIMS) - 1)]
+    params = [p for wb in zip(W, B) for p in wb]
+    opt = eo.Adam(params)
+    t0 = time.perf_counter()
+    loss = eo.mse(eo.mlp_forward(eo.Array(x), W, B, "tanh"), eo.Array(y))
+    loss.backward()
+    t1 = time.perf_counter()
+    opt.step()
+    t2 = time.perf_counter()
+    full = (t1 - t0) * (GLOBAL_BATCH / sample_rows) + (t2 - t1)
+    return {"value": GLOBAL_BATCH / full, "unit": UNIT, "cores": 1, "kind": "port",
+            "sample": "%d of 8192 batch rows through the full 1024-4096-4096-4096-1024 network "
+                      "(fwd+bwd %.2f s, scaled x%.1f) + one full Adam step (%.2f s); the reference's "
+                      "matmul is single-threaded (matmul_op.mojo:168-169)" % (
+                          sample_rows, t1 - t0, GLOBAL_BATCH / sample_rows, t2 - t1),
+            "host_cores_available": os.cpu_count(), "seconds": t2 - t0}
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    vals, last = [], None
+    for i in range(args.warmup + args.steps):
+        last = cpu_baseline(sample_rows=args.cpu_rows)
+        if i >= args.warmup:
+            vals.append(last["value"])
+    value = float(np.mean(vals)) if vals else last["value"]
+    last["value"] = value
+    line = {"impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1000.0 * GLOBAL_BATCH / value,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
+            "data": "synthetic",
+            "config": {"workload": "c2: MLP 1024-4096-4096-4096-1024 tanh, global batch 8192, MSE+Adam",
+                       "global_batch": GLOBAL_BATCH},
+            "cpu_baseline": last,
+            "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="endia_b200", choices=["endia_b200", "reference"])
+    ap.add_argument("--cpu-rows", type=int, default=48)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--gemm", default="auto", choices=["auto", "ffma", "3xtf32"])
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+        return
+    if args.warmup < 3:
+        args.warmup = 3
+
+    import torch
+    import endia_b200 as nd
+    from endia_b200 import _lib, dist as ndist
+    import torch.distributed as tdist
+
+    rank, world = ndist.init_process_group()
+    nd._array.device()
+    nd.config.gemm_algo = {"auto": _lib.GEMM_AUTO, "ffma": _lib.GEMM_FFMA, "3xtf32": _lib.GEMM_3XTF32}[args.gemm]
+    work = TrainStep(nd, torch, rank, world)
+
+    def barrier():
+        if world > 1:
+            tdist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        work.step()
+    barrier()
+
+    # ---- device-resident timing (value) with per-GEMM events
+    sampler = ClockSampler(torch.cuda.current_device())
+    timer = GemmTimer(torch)
+    nd.config.gemm_timer = timer
+    launches0 = _lib.lib.endia_b200_launch_count()
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        work.step()
+    e1.record()
+    barrier()
+    clocks = sampler.stop()
+    nd.config.gemm_timer = None
+    launches = _lib.lib.endia_b200_launch_count() - launches0
+    ms_total = e0.elapsed_time(e1)
+    n_gemm, gemm_fl, gemm_ms = timer.summary()
+
+    # ---- end-to-end timing through the public API with host buffers
+    for _ in range(2):
+        work.step(host_io=True)
+    barrier()
+    e2, e3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e2.record()
+    for _ in range(args.steps):
+        work.step(host_io=True)
+    e3.record()
+    barrier()
+    ms_e2e = e2.elapsed_time(e3)
+
+    times = torch.tensor([ms_total, ms_e2e, gemm_ms], dtype=torch.float64, device="cuda")
+    if world > 1:
+        tdist.all_reduce(times, op=tdist.ReduceOp.MAX)
+    ms_total, ms_e2e, gemm_ms = [float(t) for t in times.cpu()]
+    if rank != 0:
+        if world > 1:
+            tdist.destroy_process_group()
+        return
+
+    pk = peaks()
+    ms_step = ms_total / args.steps
+    value = GLOBAL_BATCH / (ms_step / 1000.0)
+    tflops = gemm_fl / (gemm_ms / 1000.0) / 1e12 if gemm_ms > 0 else 0.0
+    tc = bool(_lib.lib.endia_b200_has_tcgen05()) and args.gemm != "ffma"
+    # 3xTF32 issues three tf32 MMAs per logical product and tf32 runs at half the bf16 rate, so the
+    # ceiling for logical flops is the measured bf16 throughput / 6.
+    peak = pk["bf16_tflops_sustained"] / 6.0
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "c2: MLP 1024-4096-4096-4096-1024 tanh, global batch 8192, MSE+Adam",
+                   "global_batch": GLOBAL_BATCH, "per_gpu_batch": GLOBAL_BATCH // world,
+                   "parallelism": "dp%d" % world,
+                   "gemm": "tcgen05 3xTF32 (fp32 accumulate)" if tc else "fp32 FFMA",
+                   "l2": "activations and weights (>= 32 MiB each, 1.3 GB per step) exceed the 126 MB L2; no flush"},
+        "clocks": {"sm_mhz": clocks["sm_mhz"], "sm_max_mhz": clocks["sm_max_mhz"],
+                   "reasons": clocks["reasons"], "samples": clocks["samples"]},
+        "e2e": {"value": GLOBAL_BATCH / (ms_e2e / args.steps / 1000.0), "unit": UNIT,
+                "h2d_bytes_per_step": int(work.x_host.numel() * 4 + work.y_host.numel() * 4) * world,
+                "d2h_bytes_per_step": 4 * world},
+        "gpu_launches": int(launches),
+        "roofline": {"bound": "tensor", "achieved": tflops, "peak": peak, "unit": "TFLOP/s",
+                     "frac": tflops / peak if peak else None, "traffic": None,
+                     "kernel": "gemm (%d launches, %.1f%% of the step)" % (
+                         n_gemm, 100.0 * gemm_ms / ms_total if ms_total else 0.0),
+                     "peak_note": "%s bf16_tflops_sustained %.1f / 2 (tf32 rate) / 3 (MMAs per 3xTF32 product)" % (
+                         pk["source"], pk["bf16_tflops_sustained"]),
+                     "frac_of_bf16_%s" % pk["source"]: tflops / pk["bf16_tflops_sustained"],
+                     "algorithmic_gflop_per_step": gemm_flops(GLOBAL_BATCH) / 1e9 / world},
+    }
+    if world == 1 and not args.no_cpu_baseline:
+        line["cpu_baseline"] = cpu_baseline(sample_rows=args.cpu_rows)
+    print(json.dumps(line))
+    if world > 1:
+        tdist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

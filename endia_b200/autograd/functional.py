@@ -28,6 +28,12 @@ def jacrev(arg, create_graph=False):
     else:
         seed = ones([last_dim])
     out.grad_(seed)
+    # Number of graph edges into every node, so that a leaf's hook fires once its last
+    # contribution has been accumulated.
+    pending = {}
+    for node in trace:
+        for a in node.args_:
+            pending[id(a)] = pending.get(id(a), 0) + 1
     prev = _state.create_graph
     _state.create_graph = bool(create_graph)
     try:
@@ -44,6 +50,10 @@ def jacrev(arg, create_graph=False):
                 primal.grad_(g)
                 if not create_graph:
                     g.clear_args()
+                hook = getattr(primal, "grad_hook", None)
+                if hook is not None and not primal.args_ and pending[id(primal)] == 1:
+                    hook(primal, g)      # a leaf's gradient is complete: e.g. start its all-reduce
+                pending[id(primal)] -= 1
     finally:
         _state.create_graph = prev
         reset_node_id_recursive(out)

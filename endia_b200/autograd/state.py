@@ -6,3 +6,6 @@ from .. import _lib
 create_graph = False
 # GEMM algorithm handed to endia_b200_gemm (AUTO = tcgen05 3xTF32 when the shape allows).
 gemm_algo = _lib.GEMM_AUTO
+# Optional object with start(flops) / stop() called around every GEMM launch (benchmarks bracket
+# the launches with events on the launching stream).
+gemm_timer = None

@@ -15,6 +15,8 @@ int sm_count();
 bool device_ready();
 // Checks that init() succeeded; sets the error and returns a status otherwise.
 int require_device();
+// Every kernel launch of this library is counted (endia_b200_launch_count).
+void count_launch();
 
 inline cudaStream_t as_stream(void *s) { return reinterpret_cast<cudaStream_t>(s); }
 
@@ -30,6 +32,7 @@ inline cudaStream_t as_stream(void *s) { return reinterpret_cast<cudaStream_t>(s
 
 #define EB_LAUNCH_CHECK()                                                           \
   do {                                                                              \
+    eb::count_launch();                                                             \
     cudaError_t _e = cudaGetLastError();                                            \
     if (_e != cudaSuccess) {                                                        \
       eb::set_error("kernel launch failed: %s (%s:%d)", cudaGetErrorString(_e),     \

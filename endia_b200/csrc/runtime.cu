@@ -3,6 +3,7 @@
 // entry points are what a device-resident Node needs instead.
 #include "common.cuh"
 #include <string.h>
+#include <atomic>
 
 namespace eb {
 
@@ -10,6 +11,9 @@ static thread_local char g_err[512] = "";
 static int g_sm_count = 0;
 static int g_device = -1;
 static bool g_ready = false;
+static std::atomic<uint64_t> g_launches{0};
+void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
+uint64_t launches() { return g_launches.load(std::memory_order_relaxed); }
 
 void set_error(const char *fmt, ...) {
   va_list ap;
@@ -87,6 +91,7 @@ int endia_b200_shutdown(void) {
 
 const char *endia_b200_last_error(void) { return g_err; }
 int endia_b200_version(void) { return 1000; }
+uint64_t endia_b200_launch_count(void) { return eb::launches(); }
 
 int endia_b200_malloc(void **ptr, size_t bytes, void *stream) {
   EB_REQUIRE(ptr != nullptr, ENDIA_B200_EINVAL, "malloc: ptr is NULL");

@@ -168,8 +168,13 @@ def gemm_arrays(a, b, out, epi=None, algo=None):
         _lib.call("endia_b200_gemm_complex", la[0], lb[0], M, N, K, a.data_ptr(), la[1], b.data_ptr(),
                   lb[1], out.data_ptr(), N, nbatch, sa, sb, M * N, stream())
         return
+    timer = _state.gemm_timer
+    if timer is not None:
+        timer.start(2.0 * M * N * K * nbatch)
     _lib.call("endia_b200_gemm", la[0], lb[0], M, N, K, a.data_ptr(), la[1], b.data_ptr(), lb[1],
               out.data_ptr(), N, nbatch, sa, sb, M * N, epi, algo, stream())
+    if timer is not None:
+        timer.stop()
 
 
 def _matmul_call(curr, args):

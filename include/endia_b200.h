@@ -64,6 +64,9 @@ int endia_b200_shutdown(void);
 const char *endia_b200_last_error(void);
 /* ABI version (major*1000 + minor). */
 int endia_b200_version(void);
+/* Number of kernels this library has launched in this process (all threads); a benchmark
+ * reads it before and after its timed region. */
+uint64_t endia_b200_launch_count(void);
 /* 1 when the library was built with the tcgen05 GEMM and the device accepts it. */
 int endia_b200_has_tcgen05(void);
 
