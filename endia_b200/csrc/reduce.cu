@@ -2,6 +2,7 @@
 // Replaces ReduceAdd.__call__ (endia/functional/reduce_ops/reduce_add_op.mojo:65-210), which
 // accumulates sequentially in fp32, and the op chain of mse (loss_ops/mse_op.mojo:18-20).
 #include "common.cuh"
+#include <mutex>
 
 namespace eb {
 
@@ -419,6 +420,54 @@ int endia_b200_act_bwd_colsum(int act, const float *act_out, const float *grad, 
     colsum_finish_kernel<<<grid_for(N, 256), 256, 0, s>>>(partial, colsum, 1, N, chunks);
     EB_LAUNCH_CHECK();
   }
+  return ENDIA_B200_OK;
+}
+
+// ---- allocation-free MSE --------------------------------------------------------------------
+// Partial sums of the allocation-free variant live in this fixed device array instead of a
+// caller-provided buffer. One partial per 4096 elements, so the array bounds the problem size.
+#define EB_MSE_NOALLOC_MAX_PARTIALS 4096
+#define EB_MSE_NOALLOC_ELEMS_PER_PARTIAL 4096
+static __device__ __align__(256) float g_mse_noalloc_scratch[EB_MSE_NOALLOC_MAX_PARTIALS];
+// Device address of the array above, looked up once per device (indexed by device ordinal).
+static float *g_mse_noalloc_addr[64] = {nullptr};
+static std::mutex g_mse_noalloc_mutex;
+
+int endia_b200_mse_fwd_bwd_noalloc(const float *pred, const float *target, int64_t n, float gscale,
+                                   float *loss, float *dpred, void *stream) {
+  int st = require_device();
+  if (st) return st;
+  EB_REQUIRE(n > 0, ENDIA_B200_EINVAL, "mse_noalloc: n must be positive");
+  EB_REQUIRE(pred && target && loss, ENDIA_B200_EINVAL, "mse_noalloc: NULL pointer");
+  const int64_t max_n = (int64_t)EB_MSE_NOALLOC_MAX_PARTIALS * EB_MSE_NOALLOC_ELEMS_PER_PARTIAL;
+  EB_REQUIRE(n <= max_n, ENDIA_B200_ELIMIT,
+             "mse_noalloc: n = %lld exceeds the fixed scratch of this entry point (at most %lld "
+             "elements); use endia_b200_mse_fwd_bwd with caller-provided scratch",
+             (long long)n, (long long)max_n);
+  int dev = 0;
+  EB_CUDA(cudaGetDevice(&dev));
+  EB_REQUIRE(dev >= 0 && dev < 64, ENDIA_B200_ELIMIT, "mse_noalloc: device ordinal %d not supported", dev);
+  float *scratch = nullptr;
+  {
+    // Set-up on the first call per device: the array's name is only a host-side handle, the
+    // kernels need its device address.
+    std::lock_guard<std::mutex> lock(g_mse_noalloc_mutex);
+    if (!g_mse_noalloc_addr[dev]) {
+      void *addr = nullptr;
+      EB_CUDA(cudaGetSymbolAddress(&addr, g_mse_noalloc_scratch));
+      g_mse_noalloc_addr[dev] = static_cast<float *>(addr);
+    }
+    scratch = g_mse_noalloc_addr[dev];
+  }
+  cudaStream_t s = as_stream(stream);
+  const int ctas = (int)ceil_div(n, EB_MSE_NOALLOC_ELEMS_PER_PARTIAL);
+  const float inv_n = 1.f / (float)n;
+  const float g2n = gscale * (inv_n + inv_n);
+  // Every partial slot in [0, ctas) is overwritten by this call, so nothing has to be cleared.
+  mse_partial_kernel<<<ctas, 256, 0, s>>>(pred, target, n, g2n, dpred, scratch);
+  EB_LAUNCH_CHECK();
+  reduce_finish_kernel<<<1, 32, 0, s>>>(scratch, loss, 1, ctas, inv_n);
+  EB_LAUNCH_CHECK();
   return ENDIA_B200_OK;
 }
 

@@ -216,6 +216,21 @@ size_t endia_b200_mse_scratch_bytes(int64_t n);
 int endia_b200_mse_fwd_bwd(const float *pred, const float *target, int64_t n, float gscale,
                            float *loss, float *dpred, void *scratch, void *stream);
 
+/* Allocation-free form of endia_b200_mse_fwd_bwd. It has no counterpart in the reference.
+ * It exists for hosts that must not allocate device memory around a call: a runtime that owns
+ * the whole device heap and hands out no more of it, or a caller inside a section where
+ * cudaMalloc is forbidden. Same results as endia_b200_mse_fwd_bwd, but the per-block partial sums
+ * go to a fixed 16 KiB array inside the library (held by every GPU that loads the library until the
+ * process exits) instead of caller-provided scratch, and the call allocates nothing.
+ *   - Limit: n <= 16,777,216 elements (4096 partials of 4096 elements); larger n returns
+ *     ENDIA_B200_ELIMIT and the message names the limit.
+ *   - The first call on each device looks up the array's device address; make that first call
+ *     before any stream capture begins.
+ *   - All calls share the one array (its old contents are simply overwritten), so two calls that
+ *     may run on the GPU at the same time (different streams) race: order them on one stream. */
+int endia_b200_mse_fwd_bwd_noalloc(const float *pred, const float *target, int64_t n,
+                                   float gscale, float *loss, float *dpred, void *stream);
+
 /* Fused activation backward and bias gradient of one layer, on contiguous [M, N] buffers:
  *   ds[m,n] = grad[m,n] * act'(act_out[m,n])   (factors as in endia_b200_epilogue; act = NONE
  *                                               leaves ds untouched and only sums grad)
