@@ -67,6 +67,7 @@ SIGNATURES = {
     "endia_b200_version": (C.c_int, []),
     "endia_b200_has_tcgen05": (C.c_int, []),
     "endia_b200_launch_count": (C.c_uint64, []),
+    "endia_b200_device_status": (C.c_int, [_vp]),
     "endia_b200_malloc": (C.c_int, [C.POINTER(_vp), _sz, _vp]),
     "endia_b200_free": (C.c_int, [_vp, _vp]),
     "endia_b200_memset0": (C.c_int, [_vp, _sz, _vp]),

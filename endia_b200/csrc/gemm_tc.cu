@@ -1,11 +1,430 @@
-// Placeholder for the tcgen05 3xTF32 GEMM (filled in by gemm_tc.cu proper).
+// fp32 GEMM on the 5th-generation tensor cores (tcgen05) with the 3xTF32 split:
+//   a = a_hi + a_lo,  a_hi = a with the 13 low mantissa bits cleared (exactly a tf32 value),
+//   a*b ~= a_hi*b_hi + a_hi*b_lo + a_lo*b_hi        (fp32 accumulation in tensor memory)
+// which keeps ~21 bits of each product, so gradients stay within 1e-4 of the fp32 result.
+//
+// Structure of one CTA (192 threads, one 128 x BN output tile):
+//   warp 0   : producer - one lane issues TMA tile loads (hi and lo tiles of A and B, 128-byte
+//              swizzle) into a ring of shared-memory stages, signalled through mbarriers
+//   warp 1   : allocates tensor memory; one lane issues tcgen05.mma (kind::tf32, M = 128, N = BN,
+//              K = 8) three times per k-step and commits each stage back to the producer
+//   warps 2-5: epilogue - tcgen05.ld of the accumulator (one row per thread), the fused epilogue
+//              of endia_b200_epilogue, 128-bit stores
+// Operands are consumed in the layout they have in global memory: a row-major [rows, K] operand
+// is K-major, a stored-transposed one ([K, rows]) is MN-major, selected in the instruction and
+// shared-memory descriptors, so dX = dY*W^T and dW = X^T*dY need no transposed copies
+// (endia/functional/binary_ops/matmul_op.mojo:107-136, 278-284).
+// Every wait on an mbarrier is bounded; a wait that gives up records a code in a device flag
+// (endia_b200_device_status) and the CTA drains and returns.
 #include "common.cuh"
 #include "gemm.cuh"
+#include <cuda.h>
+
 namespace eb {
-bool tc_gemm_supported(const GemmParams &, int, int, int64_t) { return false; }
-int launch_gemm_tc(const GemmParams &, int, int, cudaStream_t) {
-  set_error("tcgen05 GEMM not built");
-  return ENDIA_B200_EINVAL;
+
+constexpr int TC_BM = 128;
+constexpr int TC_BK = 32;                 // 32 floats = one 128-byte swizzle row
+constexpr uint32_t TC_WAIT_LIMIT = 1u << 24;
+
+static __device__ int g_tc_status = 0;    // 0 ok, else the code of the first wait that gave up
+
+// ------------------------------------------------------------------------------- PTX helpers
+__device__ __forceinline__ uint32_t smem_u32(const void *p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
 }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0;
+}
+// Bounded wait: false (and the status flag set) when the phase never completes.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int code) {
+  for (uint32_t it = 0; it < TC_WAIT_LIMIT; ++it)
+    if (mbar_try_wait(bar, parity)) return true;
+  atomicCAS(&g_tc_status, 0, code);
+  return false;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, uint32_t bar,
+                                            int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_mma_tf32(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                            uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]),
+        "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]),
+        "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]),
+        "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor (descriptor version 1): start address, leading and stride byte
+// offsets in 16-byte units, and the swizzle mode: 2 = 128-byte swizzle in 16-byte units (K-major
+// tiles), 1 = 128-byte swizzle in 32-byte units, the only mode MN-major 32-bit operands accept.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes,
+                                              uint32_t layout_type) {
+  uint64_t d = 0;
+  d |= (uint64_t)((addr & 0x3FFFFu) >> 4);
+  d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16;
+  d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)layout_type << 61;
+  return d;
+}
+// K-major tile: rows of 128 bytes, 8-row groups 1024 bytes apart. MN-major tile: boxes of
+// [32 k][32 rows] (4096 bytes apart), inside a box groups of 4 k-rows 512 bytes apart.
+template <bool MN_MAJOR>
+__device__ __forceinline__ uint64_t tile_desc(uint32_t addr) {
+  return MN_MAJOR ? smem_desc(addr, 4096, 512, 1) : smem_desc(addr, 16, 1024, 2);
+}
+
+struct TcMaps {
+  CUtensorMap a_hi, a_lo, b_hi, b_lo;
+};
+
+// ------------------------------------------------------------------------------------ kernel
+// A_MN / B_MN: the operand is MN-major in global memory (stored [K, rows]); its tile then arrives
+// as rows/32 boxes of [32 k][32 rows], 4096 bytes each.
+template <int BN, int STAGES, bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(192, 1)
+gemm_tc_kernel(const __grid_constant__ TcMaps maps, const GemmParams p, int tiles_m) {
+  extern __shared__ __align__(1024) uint8_t smem[];
+  constexpr uint32_t A_BYTES = TC_BM * TC_BK * 4;   // 16 KiB
+  constexpr uint32_t B_BYTES = BN * TC_BK * 4;
+  constexpr uint32_t STAGE_BYTES = 2 * A_BYTES + 2 * B_BYTES;
+  const uint32_t smem_base = (smem_u32(smem) + 1023u) & ~1023u;
+  const uint32_t bars = smem_base + STAGES * STAGE_BYTES;   // full[STAGES], empty[STAGES], acc
+  __shared__ uint32_t tmem_slot;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tile_m = blockIdx.x % tiles_m, tile_n = blockIdx.x / tiles_m;
+  const int m0 = tile_m * TC_BM, n0 = tile_n * BN;
+  const int nkb = (int)((p.K + TC_BK - 1) / TC_BK);
+  auto full_bar = [&](int s) { return bars + 8u * s; };
+  auto empty_bar = [&](int s) { return bars + 8u * (STAGES + s); };
+  const uint32_t acc_bar = bars + 8u * (2 * STAGES);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+    mbar_init(acc_bar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                 ::"r"(smem_u32(&tmem_slot)), "r"((uint32_t)BN) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_slot;
+
+  if (warp == 0) {
+    // ---------------------------------------------------------------- TMA producer
+    if (lane == 0) {
+      int issued = 0;
+      bool ok = true;
+      for (int kb = 0; kb < nkb && ok; ++kb) {
+        const int s = kb % STAGES;
+        if (kb >= STAGES) ok = mbar_wait(empty_bar(s), ((kb / STAGES) - 1) & 1, 1);
+        if (!ok) break;
+        const uint32_t st = smem_base + s * STAGE_BYTES;
+        const uint32_t fb = full_bar(s);
+        mbar_expect_tx(fb, STAGE_BYTES);
+        const int k0 = kb * TC_BK;
+        if constexpr (A_MN) {
+#pragma unroll
+          for (int j = 0; j < TC_BM / 32; ++j) {
+            tma_load_2d(st + j * 4096, &maps.a_hi, fb, m0 + 32 * j, k0);
+            tma_load_2d(st + A_BYTES + j * 4096, &maps.a_lo, fb, m0 + 32 * j, k0);
+          }
+        } else {
+          tma_load_2d(st, &maps.a_hi, fb, k0, m0);
+          tma_load_2d(st + A_BYTES, &maps.a_lo, fb, k0, m0);
+        }
+        const uint32_t sb = st + 2 * A_BYTES;
+        if constexpr (B_MN) {
+#pragma unroll
+          for (int j = 0; j < BN / 32; ++j) {
+            tma_load_2d(sb + j * 4096, &maps.b_hi, fb, n0 + 32 * j, k0);
+            tma_load_2d(sb + B_BYTES + j * 4096, &maps.b_lo, fb, n0 + 32 * j, k0);
+          }
+        } else {
+          tma_load_2d(sb, &maps.b_hi, fb, k0, n0);
+          tma_load_2d(sb + B_BYTES, &maps.b_lo, fb, k0, n0);
+        }
+        ++issued;
+      }
+      if (!ok) {
+        // Give copies already in flight a bounded chance to land before the CTA exits.
+        for (int kb = (issued > STAGES ? issued - STAGES : 0); kb < issued; ++kb)
+          mbar_wait(full_bar(kb % STAGES), (kb / STAGES) & 1, 2);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      // Instruction descriptor: fp32 accumulator, tf32 A and B, majors, N >> 3, M >> 4.
+      const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((A_MN ? 1u : 0u) << 15) |
+                             ((B_MN ? 1u : 0u) << 16) | ((uint32_t)(BN >> 3) << 17) |
+                             ((uint32_t)(TC_BM >> 4) << 24);
+      bool ok = true;
+      for (int kb = 0; kb < nkb; ++kb) {
+        const int s = kb % STAGES;
+        ok = mbar_wait(full_bar(s), (kb / STAGES) & 1, 3);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t st = smem_base + s * STAGE_BYTES;
+        const uint64_t a_hi = tile_desc<A_MN>(st), a_lo = tile_desc<A_MN>(st + A_BYTES);
+        const uint32_t sb = st + 2 * A_BYTES;
+        const uint64_t b_hi = tile_desc<B_MN>(sb), b_lo = tile_desc<B_MN>(sb + B_BYTES);
+        // One k-step (K = 8 floats) further: 32 bytes along a K-major row, one 8-row (1024-byte)
+        // block of an MN-major tile; in 16-byte descriptor units.
+        constexpr uint64_t A_STEP = A_MN ? 64 : 2, B_STEP = B_MN ? 64 : 2;
+#pragma unroll
+        for (int ks = 0; ks < TC_BK / 8; ++ks) {
+          const uint64_t ah = a_hi + ks * A_STEP, al = a_lo + ks * A_STEP;
+          const uint64_t bh = b_hi + ks * B_STEP, bl = b_lo + ks * B_STEP;
+          tc_mma_tf32(tmem_base, al, bh, idesc, (kb | ks) ? 1u : 0u);   // small terms first
+          tc_mma_tf32(tmem_base, ah, bl, idesc, 1u);
+          tc_mma_tf32(tmem_base, ah, bh, idesc, 1u);
+        }
+        tc_commit(empty_bar(s));   // frees the stage once these MMAs have read it
+      }
+      tc_commit(acc_bar);          // accumulator complete (also on the give-up path)
+    }
+  } else {
+    // --------------------------------------------------------------------- epilogue
+    const int q = warp & 3;        // tensor-memory lane quarter this warp may read
+    const bool ok = mbar_wait(acc_bar, 0, 4);
+    tc_fence_after();
+    const int64_t m = (int64_t)m0 + q * 32 + lane;
+    if (ok && nkb > 0) {
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tc_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(c * 32), r);
+        tc_wait_ld();
+        const int64_t nb = (int64_t)n0 + c * 32;
+        if (m < p.M && nb < p.N) {
+          float *crow = p.C + m * p.ldc + nb;
+          if (p.vec_c && nb + 32 <= p.N) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) {
+              float4 o;
+              o.x = apply_epilogue(p.epi, __uint_as_float(r[j + 0]), m, nb + j + 0, crow + j + 0);
+              o.y = apply_epilogue(p.epi, __uint_as_float(r[j + 1]), m, nb + j + 1, crow + j + 1);
+              o.z = apply_epilogue(p.epi, __uint_as_float(r[j + 2]), m, nb + j + 2, crow + j + 2);
+              o.w = apply_epilogue(p.epi, __uint_as_float(r[j + 3]), m, nb + j + 3, crow + j + 3);
+              *reinterpret_cast<float4 *>(crow + j) = o;
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (nb + j < p.N)
+                crow[j] = apply_epilogue(p.epi, __uint_as_float(r[j]), m, nb + j, crow + j);
+          }
+        }
+      }
+    } else if (ok && m < p.M) {
+      // K == 0: the product is empty, the epilogue applies to zeros.
+      for (int64_t n = n0; n < n0 + BN && n < p.N; ++n)
+        p.C[m * p.ldc + n] = apply_epilogue(p.epi, 0.f, m, n, p.C + m * p.ldc + n);
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)BN) : "memory");
+  }
+}
+
+// lo = x - hi with hi = x truncated to tf32 (13 low mantissa bits cleared); exact in fp32.
+// Optionally also writes hi. Rows of `cols` floats, leading dimensions ld_in / ld_out.
+__global__ void __launch_bounds__(256)
+tf32_split_kernel(const float *__restrict__ x, float *__restrict__ lo, float *__restrict__ hi,
+                  int64_t rows, int64_t cols4, int64_t ld_in, int64_t ld_out) {
+  const int64_t total = rows * cols4;
+  const int64_t step = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += step) {
+    const int64_t r = i / cols4, c = (i - r * cols4) * 4;
+    const float4 v = __ldg(reinterpret_cast<const float4 *>(x + r * ld_in + c));
+    float4 h, l;
+    h.x = __uint_as_float(__float_as_uint(v.x) & 0xFFFFE000u); l.x = v.x - h.x;
+    h.y = __uint_as_float(__float_as_uint(v.y) & 0xFFFFE000u); l.y = v.y - h.y;
+    h.z = __uint_as_float(__float_as_uint(v.z) & 0xFFFFE000u); l.z = v.z - h.z;
+    h.w = __uint_as_float(__float_as_uint(v.w) & 0xFFFFE000u); l.w = v.w - h.w;
+    *reinterpret_cast<float4 *>(lo + r * ld_out + c) = l;
+    if (hi) *reinterpret_cast<float4 *>(hi + r * ld_out + c) = h;
+  }
+}
+
+// ---------------------------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
+                                  const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
+                                  const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void *sym = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(sym);
+    else
+      cudaGetLastError();
+  }
+  return fn;
+}
+
+// Tensor map over a row-major [outer, inner] float array with leading dimension ld; the box is
+// [box_outer, 32] floats (128-byte rows, 128-byte swizzle); out-of-range elements read as zero.
+static int make_map(CUtensorMap *map, const float *base, int64_t inner, int64_t outer, int64_t ld,
+                    int box_outer, bool mn_major) {
+  cuuint64_t dims[2] = {(cuuint64_t)inner, (cuuint64_t)outer};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * sizeof(float)};
+  cuuint32_t box[2] = {32u, (cuuint32_t)box_outer};
+  cuuint32_t estr[2] = {1u, 1u};
+  CUresult r = encode_fn()(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float *>(base), dims,
+                           strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                           mn_major ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+                           CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_error("gemm: cuTensorMapEncodeTiled failed with code %d", (int)r);
+    return ENDIA_B200_ECUDA;
+  }
+  return ENDIA_B200_OK;
+}
+
+static bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+bool tc_gemm_supported(const GemmParams &p, int trans_a, int trans_b, int64_t batch) {
+  (void)trans_a; (void)trans_b;
+  if (batch != 1 || p.epi.colsum_partial) return false;
+  if (!encode_fn()) return false;
+  if (p.M < 128 || p.N < 128 || p.K < 32) return false;      // small products stay on the FFMA kernel
+  if (p.M > (int64_t)1 << 30 || p.N > (int64_t)1 << 30 || p.K > (int64_t)1 << 30) return false;
+  if (!aligned16(p.A) || !aligned16(p.B) || p.lda % 4 || p.ldb % 4) return false;
+  return true;
+}
+
+template <int BN, int STAGES>
+static int launch_variant(const TcMaps &maps, const GemmParams &p, int trans_a, int trans_b,
+                          cudaStream_t s) {
+  constexpr size_t SMEM = (size_t)STAGES * (2 * TC_BM * TC_BK * 4 + 2 * BN * TC_BK * 4) + 1024 + 256;
+  const int tiles_m = (int)ceil_div(p.M, TC_BM), tiles_n = (int)ceil_div(p.N, BN);
+  const dim3 grid((unsigned)(tiles_m * tiles_n));
+#define EB_TC_LAUNCH(AM, BM_)                                                                     \
+  do {                                                                                            \
+    auto kern = gemm_tc_kernel<BN, STAGES, AM, BM_>;                                              \
+    static bool attr = false;                                                                     \
+    if (!attr) {                                                                                  \
+      EB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM)); \
+      attr = true;                                                                                \
+    }                                                                                             \
+    kern<<<grid, 192, SMEM, s>>>(maps, p, tiles_m);                                               \
+  } while (0)
+  if (trans_a && !trans_b) EB_TC_LAUNCH(true, true);
+  else if (trans_a && trans_b) EB_TC_LAUNCH(true, false);
+  else if (!trans_a && !trans_b) EB_TC_LAUNCH(false, true);
+  else EB_TC_LAUNCH(false, false);
+#undef EB_TC_LAUNCH
+  EB_LAUNCH_CHECK();
+  return ENDIA_B200_OK;
+}
+
+int launch_gemm_tc(const GemmParams &p, int trans_a, int trans_b, cudaStream_t s) {
+  // Operand geometry in memory: A is [M, K] (K-major) or [K, M] (MN-major); B is [K, N] (MN-major,
+  // the row-major weight of `x @ W`) or [N, K] (K-major).
+  const int64_t a_rows = trans_a ? p.K : p.M, a_cols = trans_a ? p.M : p.K;
+  const int64_t b_rows = trans_b ? p.N : p.K, b_cols = trans_b ? p.K : p.N;
+  const int64_t a_ld = (a_cols + 3) / 4 * 4, b_ld = (b_cols + 3) / 4 * 4;
+  float *a_lo = nullptr, *b_lo = nullptr;
+  EB_CUDA(cudaMallocAsync(&a_lo, sizeof(float) * a_rows * a_ld, s));
+  EB_CUDA(cudaMallocAsync(&b_lo, sizeof(float) * b_rows * b_ld, s));
+  tf32_split_kernel<<<grid_for(a_rows * (a_ld / 4), 256), 256, 0, s>>>(p.A, a_lo, nullptr, a_rows,
+                                                                       a_ld / 4, p.lda, a_ld);
+  EB_LAUNCH_CHECK();
+  tf32_split_kernel<<<grid_for(b_rows * (b_ld / 4), 256), 256, 0, s>>>(p.B, b_lo, nullptr, b_rows,
+                                                                       b_ld / 4, p.ldb, b_ld);
+  EB_LAUNCH_CHECK();
+  const int bn = p.N >= 256 ? 256 : 128;
+  TcMaps maps;
+  int st;
+  // K-major operand: box [rows of the tile][32 k]; MN-major operand: box [32 k][32 rows].
+  const int a_box = trans_a ? 32 : TC_BM, b_box = trans_b ? bn : 32;
+  if ((st = make_map(&maps.a_hi, p.A, a_cols, a_rows, p.lda, a_box, trans_a != 0))) return st;
+  if ((st = make_map(&maps.a_lo, a_lo, a_cols, a_rows, a_ld, a_box, trans_a != 0))) return st;
+  if ((st = make_map(&maps.b_hi, p.B, b_cols, b_rows, p.ldb, b_box, trans_b == 0))) return st;
+  if ((st = make_map(&maps.b_lo, b_lo, b_cols, b_rows, b_ld, b_box, trans_b == 0))) return st;
+  if (bn == 256) st = launch_variant<256, 2>(maps, p, trans_a, trans_b, s);
+  else st = launch_variant<128, 3>(maps, p, trans_a, trans_b, s);
+  EB_CUDA(cudaFreeAsync(a_lo, s));
+  EB_CUDA(cudaFreeAsync(b_lo, s));
+  return st;
+}
+
+int tc_status_and_clear(cudaStream_t s) {
+  int h = 0;
+  if (cudaStreamSynchronize(s) != cudaSuccess) return -1;
+  if (cudaMemcpyFromSymbol(&h, g_tc_status, sizeof(int)) != cudaSuccess) return -1;
+  if (h) {
+    int z = 0;
+    cudaMemcpyToSymbol(g_tc_status, &z, sizeof(int));
+  }
+  return h;
+}
+
 }  // namespace eb
-extern "C" int endia_b200_has_tcgen05(void) { return 0; }
+
+extern "C" int endia_b200_has_tcgen05(void) { return eb::encode_fn() != nullptr ? 1 : 0; }
+
+extern "C" int endia_b200_device_status(void *stream) {
+  int st = eb::require_device();
+  if (st) return st;
+  int code = eb::tc_status_and_clear(eb::as_stream(stream));
+  if (code < 0) {
+    eb::set_error("device_status: synchronising the stream failed: %s", cudaGetErrorString(cudaGetLastError()));
+    return ENDIA_B200_ECUDA;
+  }
+  if (code > 0) {
+    eb::set_error("a bounded device-side wait gave up (tcgen05 GEMM, wait code %d)", code);
+    return ENDIA_B200_ETIMEOUT;
+  }
+  return ENDIA_B200_OK;
+}

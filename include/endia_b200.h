@@ -70,6 +70,12 @@ uint64_t endia_b200_launch_count(void);
 /* 1 when the library was built with the tcgen05 GEMM and the device accepts it. */
 int endia_b200_has_tcgen05(void);
 
+/* Synchronises `stream` and reports whether any kernel of this library gave up a bounded
+ * device-side wait since the last call (ENDIA_B200_ETIMEOUT, flag cleared), else 0. Kernels that
+ * wait on barriers never spin without a limit; a wait that runs out records a code, lets the
+ * kernel drain and return, and is reported here. */
+int endia_b200_device_status(void *stream);
+
 /* Stream-ordered device memory. Replaces UnsafePointer.alloc/free + memset_zero in
  * Node.__init__/__del__ (endia/_array/_array.mojo:127-128, 177-179) and
  * setup_shape_and_data (endia/functional/_utils.mojo:319-326). */

@@ -1,0 +1,97 @@
+"""The tcgen05 3xTF32 GEMM through the C ABI: all four operand layouts, ragged sizes and the fused
+epilogue, against float64 products. 3xTF32 keeps ~21 mantissa bits per product, so the error bound
+is a few 1e-6 of the natural scale of each dot product (|a|.|b|)."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+from conftest import rng, max_rel
+
+pytestmark = pytest.mark.gpu
+
+
+def run_gemm(nd, a, b, ta, tb, algo, epi=None, c0=None):
+    from endia_b200 import _lib
+    from endia_b200._array import stream
+    M = a.shape[1] if ta else a.shape[0]
+    K = a.shape[0] if ta else a.shape[1]
+    N = b.shape[0] if tb else b.shape[1]
+    A, B = nd.Array(a), nd.Array(b)
+    Cd = nd.Array(c0) if c0 is not None else nd.Array([M, N])
+    _lib.call("endia_b200_gemm", ta, tb, M, N, K, A.data_ptr(), a.shape[1], B.data_ptr(), b.shape[1],
+              Cd.data_ptr(), N, 1, 0, 0, 0, C.byref(epi) if epi is not None else None, algo, stream())
+    _lib.call("endia_b200_device_status", stream())
+    return Cd.to_numpy()
+
+
+def dot_scale(am, bm):
+    """|a_i|.|b_j| for every output element: the scale float32 dot products are accurate to."""
+    return np.abs(am).astype(np.float64) @ np.abs(bm).astype(np.float64)
+
+
+@pytest.mark.parametrize("ta,tb", [(0, 0), (0, 1), (1, 0), (1, 1)])
+@pytest.mark.parametrize("M,N,K", [(128, 128, 32), (256, 256, 64), (384, 512, 256), (200, 328, 100),
+                                   (1024, 1024, 1024), (136, 260, 36)])
+def test_3xtf32_all_layouts(nd, ta, tb, M, N, K):
+    from endia_b200 import _lib
+    if not _lib.lib.endia_b200_has_tcgen05():
+        pytest.fail("library built without the tcgen05 GEMM")
+    r = rng(M + N + K)
+    a = r.standard_normal((K, M) if ta else (M, K)).astype(np.float32)
+    b = r.standard_normal((N, K) if tb else (K, N)).astype(np.float32)
+    out = run_gemm(nd, a, b, ta, tb, _lib.GEMM_3XTF32)
+    am = (a.T if ta else a).astype(np.float64)
+    bm = (b.T if tb else b).astype(np.float64)
+    ref = am @ bm
+    err = np.abs(out - ref) / dot_scale(am, bm)
+    assert err.max() < 5e-6, err.max()          # plain tf32 would be ~1e-3
+    ffma = run_gemm(nd, a, b, ta, tb, _lib.GEMM_FFMA)
+    assert max_rel(out, ffma) < 1e-4
+
+
+def test_3xtf32_fused_epilogue(nd):
+    from endia_b200 import _lib
+    r = rng(5)
+    M, N, K = 256, 384, 160
+    a = r.standard_normal((M, K)).astype(np.float32)
+    b = r.standard_normal((K, N)).astype(np.float32) * np.float32(0.1)
+    bias = r.standard_normal(N).astype(np.float32)
+    saved = r.uniform(0.1, 0.9, (M, N)).astype(np.float32)
+    c0 = r.standard_normal((M, N)).astype(np.float32)
+    BIAS, SAVED = nd.Array(bias), nd.Array(saved)
+    epi = _lib.Epilogue()
+    epi.alpha, epi.beta = 0.5, 2.0
+    epi.bias = BIAS.data_ptr()
+    epi.act, epi.dact = _lib.ACT_TANH, _lib.ACT_SIGMOID
+    epi.dact_src, epi.ld_dact = SAVED.data_ptr(), N
+    out = run_gemm(nd, a, b, 0, 0, _lib.GEMM_3XTF32, epi=epi, c0=c0)
+    v = np.tanh(0.5 * (a.astype(np.float64) @ b) + bias) * (saved.astype(np.float64) * (1 - saved)) + 2.0 * c0
+    assert max_rel(out, v) < 1e-4
+
+
+def test_3xtf32_long_k_error_growth(nd):
+    """dW reduces over the batch: K = 8192 must still meet the gradient tolerance."""
+    from endia_b200 import _lib
+    r = rng(6)
+    M, N, K = 256, 256, 8192
+    a = r.standard_normal((K, M)).astype(np.float32)
+    b = r.standard_normal((K, N)).astype(np.float32)
+    out = run_gemm(nd, a, b, 1, 0, _lib.GEMM_3XTF32)
+    ref = a.T.astype(np.float64) @ b.astype(np.float64)
+    assert max_rel(out, ref) < 1e-4
+    assert (np.abs(out - ref) / dot_scale(a.T, b)).max() < 5e-6
+
+
+def test_auto_falls_back_to_ffma_for_unaligned_or_small(nd):
+    from endia_b200 import _lib
+    r = rng(7)
+    a = r.standard_normal((130, 33)).astype(np.float32)       # lda = 33: not 16-byte aligned rows
+    b = r.standard_normal((33, 257)).astype(np.float32)
+    out = run_gemm(nd, a, b, 0, 0, _lib.GEMM_AUTO)
+    assert max_rel(out, a.astype(np.float64) @ b) < 1e-4
+    from endia_b200._array import stream
+    A, B, Cd = nd.Array(a), nd.Array(b), nd.Array([130, 257])
+    st = _lib.lib.endia_b200_gemm(0, 0, 130, 257, 33, A.data_ptr(), 33, B.data_ptr(), 257, Cd.data_ptr(),
+                                  257, 1, 0, 0, 0, None, _lib.GEMM_3XTF32, stream())
+    assert st == _lib.EINVAL
