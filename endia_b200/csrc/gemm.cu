@@ -60,7 +60,7 @@ int endia_b200_gemm(int trans_a, int trans_b, int64_t M, int64_t N, int64_t K, c
   cudaStream_t s = as_stream(stream);
   bool use_tc = false;
   if (algo != ENDIA_B200_GEMM_FFMA) {
-    use_tc = tc_gemm_supported(p, trans_a, trans_b, batch);
+    use_tc = tc_gemm_supported(p, trans_a, trans_b, batch, algo == ENDIA_B200_GEMM_3XTF32);
     EB_REQUIRE(use_tc || algo == ENDIA_B200_GEMM_AUTO, ENDIA_B200_EINVAL,
                "gemm: the 3xTF32 tcgen05 kernel does not take this shape/alignment "
                "(M %lld N %lld K %lld batch %lld)", (long long)M, (long long)N, (long long)K,

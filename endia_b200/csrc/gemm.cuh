@@ -55,7 +55,8 @@ int launch_gemm_ffma(const GemmParams &p, int trans_a, int trans_b, int64_t batc
 int launch_colsum_finish(const float *partial, float *out, int64_t N, int tiles, int64_t batch,
                          cudaStream_t s);
 // tcgen05 3xTF32 path: true when the shape/alignment is one it handles.
-bool tc_gemm_supported(const GemmParams &p, int trans_a, int trans_b, int64_t batch);
+bool tc_gemm_supported(const GemmParams &p, int trans_a, int trans_b, int64_t batch,
+                       bool explicit_request);
 int launch_gemm_tc(const GemmParams &p, int trans_a, int trans_b, cudaStream_t s);
 
 }  // namespace eb

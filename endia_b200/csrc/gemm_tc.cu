@@ -6,8 +6,9 @@
 // Structure of one CTA (192 threads, one 128 x BN output tile):
 //   warp 0   : producer - one lane issues TMA tile loads (hi and lo tiles of A and B, 128-byte
 //              swizzle) into a ring of shared-memory stages, signalled through mbarriers
-//   warp 1   : allocates tensor memory; one lane issues tcgen05.mma (kind::tf32, M = 128, N = BN,
-//              K = 8) three times per k-step and commits each stage back to the producer
+//   warp 1   : allocates tensor memory (two accumulators of BN columns: the hi*hi sum and the
+//              sum of the two correction products); one lane issues tcgen05.mma (kind::tf32,
+//              M = 128, N = BN, K = 8) three times per k-step and commits each stage back
 //   warps 2-5: epilogue - tcgen05.ld of the accumulator (one row per thread), the fused epilogue
 //              of endia_b200_epilogue, 128-bit stores
 // Operands are consumed in the layout they have in global memory: a row-major [rows, K] operand
@@ -19,11 +20,11 @@
 #include "common.cuh"
 #include "gemm.cuh"
 #include <cuda.h>
+#include <stdlib.h>
 
 namespace eb {
 
 constexpr int TC_BM = 128;
-constexpr int TC_BK = 32;                 // 32 floats = one 128-byte swizzle row
 constexpr uint32_t TC_WAIT_LIMIT = 1u << 24;
 
 static __device__ int g_tc_status = 0;    // 0 ok, else the code of the first wait that gave up
@@ -100,11 +101,13 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes,
   d |= (uint64_t)layout_type << 61;
   return d;
 }
-// K-major tile: rows of 128 bytes, 8-row groups 1024 bytes apart. MN-major tile: boxes of
-// [32 k][32 rows] (4096 bytes apart), inside a box groups of 4 k-rows 512 bytes apart.
-template <bool MN_MAJOR>
+// K-major tile: rows of BK floats (128 bytes with the 128-byte swizzle, 64 with the 64-byte one),
+// 8-row groups contiguous. MN-major tile: boxes of [BK k][32 rows] (BK*128 bytes apart), inside
+// a box groups of 4 k-rows 512 bytes apart.
+template <bool MN_MAJOR, int BK>
 __device__ __forceinline__ uint64_t tile_desc(uint32_t addr) {
-  return MN_MAJOR ? smem_desc(addr, 4096, 512, 1) : smem_desc(addr, 16, 1024, 2);
+  return MN_MAJOR ? smem_desc(addr, BK * 128, 512, 1)
+                  : smem_desc(addr, 16, 8 * BK * 4, BK == 32 ? 2 : 4);
 }
 
 struct TcMaps {
@@ -113,13 +116,14 @@ struct TcMaps {
 
 // ------------------------------------------------------------------------------------ kernel
 // A_MN / B_MN: the operand is MN-major in global memory (stored [K, rows]); its tile then arrives
-// as rows/32 boxes of [32 k][32 rows], 4096 bytes each.
-template <int BN, int STAGES, bool A_MN, bool B_MN>
+// as rows/32 boxes of [BK k][32 rows].
+template <int BN, int BK, int STAGES, bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(192, 1)
 gemm_tc_kernel(const __grid_constant__ TcMaps maps, const GemmParams p, int tiles_m) {
   extern __shared__ __align__(1024) uint8_t smem[];
-  constexpr uint32_t A_BYTES = TC_BM * TC_BK * 4;   // 16 KiB
-  constexpr uint32_t B_BYTES = BN * TC_BK * 4;
+  constexpr uint32_t A_BYTES = TC_BM * BK * 4;
+  constexpr uint32_t B_BYTES = BN * BK * 4;
+  constexpr uint32_t BOX_BYTES = BK * 128;          // one [BK k][32 rows] box of an MN-major tile
   constexpr uint32_t STAGE_BYTES = 2 * A_BYTES + 2 * B_BYTES;
   const uint32_t smem_base = (smem_u32(smem) + 1023u) & ~1023u;
   const uint32_t bars = smem_base + STAGES * STAGE_BYTES;   // full[STAGES], empty[STAGES], acc
@@ -128,7 +132,7 @@ gemm_tc_kernel(const __grid_constant__ TcMaps maps, const GemmParams p, int tile
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tile_m = blockIdx.x % tiles_m, tile_n = blockIdx.x / tiles_m;
   const int m0 = tile_m * TC_BM, n0 = tile_n * BN;
-  const int nkb = (int)((p.K + TC_BK - 1) / TC_BK);
+  const int nkb = (int)((p.K + BK - 1) / BK);
   auto full_bar = [&](int s) { return bars + 8u * s; };
   auto empty_bar = [&](int s) { return bars + 8u * (STAGES + s); };
   const uint32_t acc_bar = bars + 8u * (2 * STAGES);
@@ -140,7 +144,7 @@ gemm_tc_kernel(const __grid_constant__ TcMaps maps, const GemmParams p, int tile
   }
   if (warp == 1) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
-                 ::"r"(smem_u32(&tmem_slot)), "r"((uint32_t)BN) : "memory");
+                 ::"r"(smem_u32(&tmem_slot)), "r"((uint32_t)(2 * BN)) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   tc_fence_before();
@@ -160,12 +164,12 @@ gemm_tc_kernel(const __grid_constant__ TcMaps maps, const GemmParams p, int tile
         const uint32_t st = smem_base + s * STAGE_BYTES;
         const uint32_t fb = full_bar(s);
         mbar_expect_tx(fb, STAGE_BYTES);
-        const int k0 = kb * TC_BK;
+        const int k0 = kb * BK;
         if constexpr (A_MN) {
 #pragma unroll
           for (int j = 0; j < TC_BM / 32; ++j) {
-            tma_load_2d(st + j * 4096, &maps.a_hi, fb, m0 + 32 * j, k0);
-            tma_load_2d(st + A_BYTES + j * 4096, &maps.a_lo, fb, m0 + 32 * j, k0);
+            tma_load_2d(st + j * BOX_BYTES, &maps.a_hi, fb, m0 + 32 * j, k0);
+            tma_load_2d(st + A_BYTES + j * BOX_BYTES, &maps.a_lo, fb, m0 + 32 * j, k0);
           }
         } else {
           tma_load_2d(st, &maps.a_hi, fb, k0, m0);
@@ -175,8 +179,8 @@ gemm_tc_kernel(const __grid_constant__ TcMaps maps, const GemmParams p, int tile
         if constexpr (B_MN) {
 #pragma unroll
           for (int j = 0; j < BN / 32; ++j) {
-            tma_load_2d(sb + j * 4096, &maps.b_hi, fb, n0 + 32 * j, k0);
-            tma_load_2d(sb + B_BYTES + j * 4096, &maps.b_lo, fb, n0 + 32 * j, k0);
+            tma_load_2d(sb + j * BOX_BYTES, &maps.b_hi, fb, n0 + 32 * j, k0);
+            tma_load_2d(sb + B_BYTES + j * BOX_BYTES, &maps.b_lo, fb, n0 + 32 * j, k0);
           }
         } else {
           tma_load_2d(sb, &maps.b_hi, fb, k0, n0);
@@ -204,19 +208,23 @@ gemm_tc_kernel(const __grid_constant__ TcMaps maps, const GemmParams p, int tile
         if (!ok) break;
         tc_fence_after();
         const uint32_t st = smem_base + s * STAGE_BYTES;
-        const uint64_t a_hi = tile_desc<A_MN>(st), a_lo = tile_desc<A_MN>(st + A_BYTES);
+        const uint64_t a_hi = tile_desc<A_MN, BK>(st), a_lo = tile_desc<A_MN, BK>(st + A_BYTES);
         const uint32_t sb = st + 2 * A_BYTES;
-        const uint64_t b_hi = tile_desc<B_MN>(sb), b_lo = tile_desc<B_MN>(sb + B_BYTES);
+        const uint64_t b_hi = tile_desc<B_MN, BK>(sb), b_lo = tile_desc<B_MN, BK>(sb + B_BYTES);
         // One k-step (K = 8 floats) further: 32 bytes along a K-major row, one 8-row (1024-byte)
         // block of an MN-major tile; in 16-byte descriptor units.
         constexpr uint64_t A_STEP = A_MN ? 64 : 2, B_STEP = B_MN ? 64 : 2;
 #pragma unroll
-        for (int ks = 0; ks < TC_BK / 8; ++ks) {
+        for (int ks = 0; ks < BK / 8; ++ks) {
           const uint64_t ah = a_hi + ks * A_STEP, al = a_lo + ks * A_STEP;
           const uint64_t bh = b_hi + ks * B_STEP, bl = b_lo + ks * B_STEP;
-          tc_mma_tf32(tmem_base, al, bh, idesc, (kb | ks) ? 1u : 0u);   // small terms first
-          tc_mma_tf32(tmem_base, ah, bl, idesc, 1u);
-          tc_mma_tf32(tmem_base, ah, bh, idesc, 1u);
+          // The two correction products accumulate in their own tensor-memory columns: the
+          // accumulator adds round toward zero, so every add into the large sum costs up to one
+          // ulp of it, and keeping the small terms apart leaves one such add per k-step.
+          const uint32_t acc = (kb | ks) ? 1u : 0u;
+          tc_mma_tf32(tmem_base + BN, al, bh, idesc, acc);
+          tc_mma_tf32(tmem_base + BN, ah, bl, idesc, 1u);
+          tc_mma_tf32(tmem_base, ah, bh, idesc, acc);
         }
         tc_commit(empty_bar(s));   // frees the stage once these MMAs have read it
       }
@@ -231,9 +239,12 @@ gemm_tc_kernel(const __grid_constant__ TcMaps maps, const GemmParams p, int tile
     if (ok && nkb > 0) {
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
-        uint32_t r[32];
+        uint32_t r[32], r2[32];
         tc_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(c * 32), r);
+        tc_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(BN + c * 32), r2);
         tc_wait_ld();
+#pragma unroll
+        for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) + __uint_as_float(r2[j]));
         const int64_t nb = (int64_t)n0 + c * 32;
         if (m < p.M && nb < p.N) {
           float *crow = p.C + m * p.ldc + nb;
@@ -265,7 +276,7 @@ gemm_tc_kernel(const __grid_constant__ TcMaps maps, const GemmParams p, int tile
   __syncthreads();
   if (warp == 1) {
     tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)BN) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)(2 * BN)) : "memory");
   }
 }
 
@@ -312,16 +323,18 @@ static EncodeTiledFn encode_fn() {
 }
 
 // Tensor map over a row-major [outer, inner] float array with leading dimension ld; the box is
-// [box_outer, 32] floats (128-byte rows, 128-byte swizzle); out-of-range elements read as zero.
+// [box_outer, box_inner] floats; out-of-range elements read as zero. MN-major tiles (32 floats
+// wide) use the 128-byte swizzle in 32-byte units, K-major tiles the swizzle as wide as a row.
 static int make_map(CUtensorMap *map, const float *base, int64_t inner, int64_t outer, int64_t ld,
-                    int box_outer, bool mn_major) {
+                    int box_inner, int box_outer, bool mn_major) {
   cuuint64_t dims[2] = {(cuuint64_t)inner, (cuuint64_t)outer};
   cuuint64_t strides[1] = {(cuuint64_t)ld * sizeof(float)};
-  cuuint32_t box[2] = {32u, (cuuint32_t)box_outer};
+  cuuint32_t box[2] = {(cuuint32_t)box_inner, (cuuint32_t)box_outer};
   cuuint32_t estr[2] = {1u, 1u};
   CUresult r = encode_fn()(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float *>(base), dims,
                            strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                           mn_major ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+                           mn_major ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B
+                                    : (box_inner == 32 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B),
                            CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
@@ -333,9 +346,13 @@ static int make_map(CUtensorMap *map, const float *base, int64_t inner, int64_t 
 
 static bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
-bool tc_gemm_supported(const GemmParams &p, int trans_a, int trans_b, int64_t batch) {
+bool tc_gemm_supported(const GemmParams &p, int trans_a, int trans_b, int64_t batch, bool explicit_request) {
   (void)trans_a; (void)trans_b;
   if (batch != 1 || p.epi.colsum_partial) return false;
+  // The tensor-core accumulator rounds toward zero on every add, a bias that grows linearly
+  // with K (measured: -1.7e-5 of the result at K = 8192, -6.7e-5 at K = 32768). Longer
+  // reductions stay on the FFMA kernel unless the caller asks for this one by name.
+  if (p.K > 8192 && !explicit_request) return false;
   if (!encode_fn()) return false;
   if (p.M < 128 || p.N < 128 || p.K < 32) return false;      // small products stay on the FFMA kernel
   if (p.M > (int64_t)1 << 30 || p.N > (int64_t)1 << 30 || p.K > (int64_t)1 << 30) return false;
@@ -343,15 +360,15 @@ bool tc_gemm_supported(const GemmParams &p, int trans_a, int trans_b, int64_t ba
   return true;
 }
 
-template <int BN, int STAGES>
+template <int BN, int BK, int STAGES>
 static int launch_variant(const TcMaps &maps, const GemmParams &p, int trans_a, int trans_b,
                           cudaStream_t s) {
-  constexpr size_t SMEM = (size_t)STAGES * (2 * TC_BM * TC_BK * 4 + 2 * BN * TC_BK * 4) + 1024 + 256;
+  constexpr size_t SMEM = (size_t)STAGES * (2 * TC_BM * BK * 4 + 2 * BN * BK * 4) + 1024 + 256;
   const int tiles_m = (int)ceil_div(p.M, TC_BM), tiles_n = (int)ceil_div(p.N, BN);
   const dim3 grid((unsigned)(tiles_m * tiles_n));
 #define EB_TC_LAUNCH(AM, BM_)                                                                     \
   do {                                                                                            \
-    auto kern = gemm_tc_kernel<BN, STAGES, AM, BM_>;                                              \
+    auto kern = gemm_tc_kernel<BN, BK, STAGES, AM, BM_>;                                              \
     static bool attr = false;                                                                     \
     if (!attr) {                                                                                  \
       EB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM)); \
@@ -384,16 +401,25 @@ int launch_gemm_tc(const GemmParams &p, int trans_a, int trans_b, cudaStream_t s
                                                                        b_ld / 4, p.ldb, b_ld);
   EB_LAUNCH_CHECK();
   const int bn = p.N >= 256 ? 256 : 128;
+  // k-block depth: 16 floats per stage with a 4- or 6-deep ring hides the tile-load latency
+  // better than 32 floats with 2 or 3 stages in the same shared memory.
+  static const int bk = []() {
+    const char *e = getenv("ENDIA_B200_TC_BK");
+    return (e && atoi(e) == 32) ? 32 : 16;
+  }();
   TcMaps maps;
   int st;
-  // K-major operand: box [rows of the tile][32 k]; MN-major operand: box [32 k][32 rows].
-  const int a_box = trans_a ? 32 : TC_BM, b_box = trans_b ? bn : 32;
-  if ((st = make_map(&maps.a_hi, p.A, a_cols, a_rows, p.lda, a_box, trans_a != 0))) return st;
-  if ((st = make_map(&maps.a_lo, a_lo, a_cols, a_rows, a_ld, a_box, trans_a != 0))) return st;
-  if ((st = make_map(&maps.b_hi, p.B, b_cols, b_rows, p.ldb, b_box, trans_b == 0))) return st;
-  if ((st = make_map(&maps.b_lo, b_lo, b_cols, b_rows, b_ld, b_box, trans_b == 0))) return st;
-  if (bn == 256) st = launch_variant<256, 2>(maps, p, trans_a, trans_b, s);
-  else st = launch_variant<128, 3>(maps, p, trans_a, trans_b, s);
+  // K-major operand: box [rows of the tile][bk k]; MN-major operand: box [bk k][32 rows].
+  const int a_bi = trans_a ? 32 : bk, a_bo = trans_a ? bk : TC_BM;
+  const int b_bi = trans_b ? bk : 32, b_bo = trans_b ? bn : bk;
+  if ((st = make_map(&maps.a_hi, p.A, a_cols, a_rows, p.lda, a_bi, a_bo, trans_a != 0))) return st;
+  if ((st = make_map(&maps.a_lo, a_lo, a_cols, a_rows, a_ld, a_bi, a_bo, trans_a != 0))) return st;
+  if ((st = make_map(&maps.b_hi, p.B, b_cols, b_rows, p.ldb, b_bi, b_bo, trans_b == 0))) return st;
+  if ((st = make_map(&maps.b_lo, b_lo, b_cols, b_rows, b_ld, b_bi, b_bo, trans_b == 0))) return st;
+  if (bn == 256 && bk == 16) st = launch_variant<256, 16, 4>(maps, p, trans_a, trans_b, s);
+  else if (bn == 256) st = launch_variant<256, 32, 2>(maps, p, trans_a, trans_b, s);
+  else if (bk == 16) st = launch_variant<128, 16, 6>(maps, p, trans_a, trans_b, s);
+  else st = launch_variant<128, 32, 3>(maps, p, trans_a, trans_b, s);
   EB_CUDA(cudaFreeAsync(a_lo, s));
   EB_CUDA(cudaFreeAsync(b_lo, s));
   return st;

@@ -76,6 +76,15 @@ int endia_b200_init(int device) {
     return ENDIA_B200_ENODEV;
   }
   EB_CUDA(cudaSetDevice(device));
+  // Stream-ordered allocations (endia_b200_malloc, GEMM work buffers) come from the device's
+  // default pool; keep freed blocks cached across synchronisation points instead of returning
+  // them to the driver, which would make the next allocation cost milliseconds.
+  cudaMemPool_t pool;
+  if (cudaDeviceGetDefaultMemPool(&pool, device) == cudaSuccess) {
+    uint64_t keep = UINT64_MAX;
+    cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep);
+  }
+  cudaGetLastError();
   g_sm_count = prop.multiProcessorCount;
   g_device = device;
   g_ready = true;

@@ -81,6 +81,11 @@ def test_3xtf32_long_k_error_growth(nd):
     ref = a.T.astype(np.float64) @ b.astype(np.float64)
     assert max_rel(out, ref) < 1e-4
     assert (np.abs(out - ref) / dot_scale(a.T, b)).max() < 5e-6
+    # Beyond K = 8192 the default algorithm choice goes back to exact fp32 accumulation.
+    a2 = r.standard_normal((16384, 128)).astype(np.float32)
+    b2 = r.standard_normal((16384, 128)).astype(np.float32)
+    out2 = run_gemm(nd, a2, b2, 1, 0, _lib.GEMM_AUTO)
+    assert max_rel(out2, a2.T.astype(np.float64) @ b2.astype(np.float64)) < 2e-5
 
 
 def test_auto_falls_back_to_ffma_for_unaligned_or_small(nd):
