@@ -16,6 +16,7 @@ INCLUDE = os.path.join(os.path.dirname(HERE), "include")
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+    "-Wno-deprecated-gpu-targets",
     "-Xcompiler", "-fPIC", "-Xcompiler", "-O3",
 ]
 
@@ -37,7 +38,7 @@ def _digest():
         os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith(".cuh"))
     files.append(os.path.join(INCLUDE, "endia_b200.h"))
     for f in files:
-        h.update(f.encode())
+        h.update(os.path.basename(f).encode())  # not the absolute path: the tree may be relocated
         with open(f, "rb") as fh:
             h.update(fh.read())
     h.update(" ".join(NVCC_FLAGS).encode())
@@ -49,10 +50,28 @@ def build(force=False, verbose=False):
     os.makedirs(LIBDIR, exist_ok=True)
     stamp = os.path.join(LIBDIR, "build.stamp")
     digest = _digest()
-    if not force and os.path.exists(LIBPATH) and os.path.exists(stamp):
-        with open(stamp) as fh:
-            if fh.read().strip() == digest:
-                return LIBPATH
+
+    def fresh():
+        if not force and os.path.exists(LIBPATH) and os.path.exists(stamp):
+            with open(stamp) as fh:
+                return fh.read().strip() == digest
+        return False
+    if fresh():
+        return LIBPATH
+    # Several ranks may import the package at once: only one of them compiles.
+    import fcntl
+    lock = open(os.path.join(LIBDIR, "build.lock"), "w")
+    fcntl.flock(lock, fcntl.LOCK_EX)
+    try:
+        if fresh():
+            return LIBPATH
+        return _compile(digest, stamp, verbose)
+    finally:
+        fcntl.flock(lock, fcntl.LOCK_UN)
+        lock.close()
+
+
+def _compile(digest, stamp, verbose):
     nvcc = _nvcc()
     objs = []
     procs = []
@@ -74,7 +93,7 @@ def build(force=False, verbose=False):
             sys.stderr.write("nvcc failed on %s\n" % src)
     if failed:
         raise RuntimeError("building libendia_b200.so failed")
-    link = [nvcc, "-shared", "-o", LIBPATH] + objs + ["-lcudart", "-lcuda"]
+    link = [nvcc, "-shared", "-o", LIBPATH] + objs + ["-lcudart"]
     subprocess.check_call(link)
     with open(stamp, "w") as fh:
         fh.write(digest)
