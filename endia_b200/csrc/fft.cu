@@ -10,6 +10,7 @@
 #include <mutex>
 #include <vector>
 #include <math.h>
+#include <stdlib.h>
 
 namespace eb {
 
@@ -196,6 +197,154 @@ __global__ void __launch_bounds__(1024, 1) fft_tile_kernel(const __grid_constant
   }
 }
 
+// ------------------------------------------------------------------- fast path
+// Lines of 256 / 512 / 1024 / 2048 points, 8 lines per tile, sizes known at compile time, plan
+// 16 x 16 x (N/256). Thread (t, i) owns 16 points of line t. The first radix-16 stage reads its
+// inputs straight from global memory and the last stage writes its outputs straight back, so only
+// the two exchanges between stages go through shared memory. Two thread mappings:
+//   COL (strided axis; the 8 lines are adjacent in memory): lanes run over the lines first, so a
+//       warp touches 64-byte segments; shared layout [point][line] with an XOR swizzle that keeps
+//       both line-major and point-major accesses free of bank conflicts;
+//   ROW (contiguous axis): lanes run over the points of one line, so a warp touches 256 contiguous
+//       bytes; shared layout [line][point] with the low 4 bits of the point index XORed by the
+//       next 4 (the Stockham write patterns of this plan then never collide).
+// COL with STAGE_IN reads contiguous lines through shared memory (coalesced) and writes strided:
+// the transposing second pass of the four-step split.
+// Twiddles W_N^q sit in shared memory for the lifetime of the (persistent) CTA.
+struct FastParams {
+  const float2 *in;
+  float2 *out;
+  int64_t n_tiles, tiles_per_outer;
+  int64_t in_outer, in_line, in_elem;
+  int64_t out_outer, out_line, out_elem;
+  const float2 *tw, *tw_hi, *tw_lo;
+  int lo_bits;
+  int conj_in, conj_out;
+  float scale;
+};
+
+enum { FAST_COL = 0, FAST_ROW = 1, FAST_COL_STAGED_IN = 2 };
+
+template <int LOGN, int MODE, int T>
+__device__ __forceinline__ int fast_phys(int j, int t) {
+  if constexpr (MODE == FAST_ROW) {
+    return (t << LOGN) + (j ^ ((j >> 4) & 15));
+  } else if constexpr (T == 16) {
+    // one row = one 128-byte bank line; rotating the slot by the row index keeps point-major
+    // accesses (same line, consecutive points) conflict-free too
+    return (j << 4) + (t ^ (j & 15));
+  } else {
+    // rows 2m and 2m+1 share a 128-byte bank line: which half is flipped by bit 4 of the row,
+    // and the slot inside the half is rotated by the line-pair index
+    const int m = j >> 1;
+    return (m << 4) + (((j ^ (j >> 4)) & 1) << 3) + (t ^ (m & 7));
+  }
+}
+
+// Four-step twiddle W_big^q from the two small tables.
+__device__ __forceinline__ float2 fast_bigtw(const FastParams &P, int q) {
+  return cmul(__ldg(P.tw_hi + (q >> P.lo_bits)), __ldg(P.tw_lo + (q & ((1 << P.lo_bits) - 1))));
+}
+__device__ __forceinline__ void fast_store(const FastParams &P, float2 *dst, int j, float2 v) {
+  v.x *= P.scale; v.y *= P.scale;
+  if (P.conj_out) v.y = -v.y;
+  dst[(int64_t)j * P.out_elem] = v;
+}
+
+template <int LOGN, int MODE, bool TW, int T>
+__global__ void __launch_bounds__((T << LOGN) / 16, 16384 / (T << LOGN))
+fft_fast_kernel(const __grid_constant__ FastParams P) {
+  constexpr int N = 1 << LOGN, NT = T * N / 16, Q = N / 16, R3 = N / 256;
+  constexpr int LOGT = T == 16 ? 4 : 3;
+  extern __shared__ float2 sm[];
+  float2 *tws = sm + N * T;
+  const int tid = threadIdx.x;
+  const int t = MODE == FAST_ROW ? tid / Q : (tid & (T - 1));
+  const int i0 = MODE == FAST_ROW ? tid % Q : (tid >> LOGT);
+  for (int q = tid; q < N; q += NT) tws[q] = __ldg(P.tw + q);
+  __syncthreads();
+  for (int64_t tile = blockIdx.x; tile < P.n_tiles; tile += gridDim.x) {
+    const int64_t o = tile / P.tiles_per_outer;
+    const int line0 = (int)(tile - o * P.tiles_per_outer) * T;
+    const int line = line0 + t;
+    float2 *dst = P.out + o * P.out_outer + (int64_t)line * P.out_line;
+    float2 u[16];
+    if constexpr (MODE == FAST_COL_STAGED_IN) {
+      // contiguous lines: a warp reads 32 consecutive points of one line, the swizzle makes the
+      // point-major shared store conflict-free as well
+      const float2 *src = P.in + o * P.in_outer + (int64_t)line0 * P.in_line;
+#pragma unroll
+      for (int e = 0; e < 16; ++e) {
+        const int w = tid + e * NT, j = w & (N - 1), tt = w >> LOGN;
+        float2 v = src[(int64_t)tt * P.in_line + j];
+        if (P.conj_in) v.y = -v.y;
+        sm[fast_phys<LOGN, MODE, T>(j, tt)] = v;
+      }
+      __syncthreads();
+#pragma unroll
+      for (int r = 0; r < 16; ++r) u[r] = sm[fast_phys<LOGN, MODE, T>(i0 + r * Q, t)];
+      __syncthreads();
+    } else {
+      const float2 *src = P.in + o * P.in_outer + (int64_t)line * P.in_line;
+#pragma unroll
+      for (int r = 0; r < 16; ++r) u[r] = src[(int64_t)(i0 + r * Q) * P.in_elem];
+      if (P.conj_in) {
+#pragma unroll
+        for (int r = 0; r < 16; ++r) u[r].y = -u[r].y;
+      }
+    }
+    // stage 1: radix 16 on inputs i0 + r*N/16
+    dft<16>(u);
+#pragma unroll
+    for (int r = 0; r < 16; ++r) sm[fast_phys<LOGN, MODE, T>(i0 * 16 + r, t)] = u[r];
+    __syncthreads();
+    // stage 2: radix 16, p = 16
+#pragma unroll
+    for (int r = 0; r < 16; ++r) u[r] = sm[fast_phys<LOGN, MODE, T>(i0 + r * Q, t)];
+    const int k = i0 & 15;
+#pragma unroll
+    for (int r = 1; r < 16; ++r) u[r] = cmul(u[r], tws[r * k * R3]);
+    dft<16>(u);
+    if constexpr (R3 == 1) {
+      // last stage: output point i0 + 16 r; its four-step twiddle is base * step^r
+      if constexpr (TW) {
+        float2 w = fast_bigtw(P, i0 * line);
+        const float2 step = fast_bigtw(P, 16 * line);
+#pragma unroll
+        for (int r = 0; r < 16; ++r) { u[r] = cmul(u[r], w); w = cmul(w, step); }
+      }
+#pragma unroll
+      for (int r = 0; r < 16; ++r) fast_store(P, dst, i0 + 16 * r, u[r]);
+    } else {
+      __syncthreads();
+#pragma unroll
+      for (int r = 0; r < 16; ++r) sm[fast_phys<LOGN, MODE, T>((i0 - k) * 16 + k + 16 * r, t)] = u[r];
+      __syncthreads();
+      // stage 3: radix R3, p = 256; 16/R3 butterflies per thread, outputs straight to global
+      float2 step = make_float2(1.f, 0.f);
+      if constexpr (TW) step = fast_bigtw(P, 256 * line);
+#pragma unroll
+      for (int it = 0; it < 16 / R3; ++it) {
+        const int i = i0 + it * Q;
+        float2 v[R3];
+#pragma unroll
+        for (int r = 0; r < R3; ++r) v[r] = sm[fast_phys<LOGN, MODE, T>(i + r * 256, t)];
+#pragma unroll
+        for (int r = 1; r < R3; ++r) v[r] = cmul(v[r], tws[r * i]);
+        dft<R3>(v);
+        if constexpr (TW) {
+          float2 w = fast_bigtw(P, i * line);
+#pragma unroll
+          for (int r = 0; r < R3; ++r) { v[r] = cmul(v[r], w); w = cmul(w, step); }
+        }
+#pragma unroll
+        for (int r = 0; r < R3; ++r) fast_store(P, dst, i + r * 256, v[r]);
+      }
+    }
+    __syncthreads();
+  }
+}
+
 // ------------------------------------------------------------------ host side
 static std::mutex g_tw_mutex;
 static std::map<std::pair<int, int64_t>, float2 *> g_tw_cache;  // (device, key) -> table
@@ -250,6 +399,62 @@ static int pick_T(int N) {
   return T;
 }
 
+template <int LOGN, int MODE, bool TW, int T>
+static int launch_fast_variant(FastParams F, int64_t lines_per_outer, int64_t n_outer, cudaStream_t s) {
+  constexpr int N = 1 << LOGN;
+  constexpr size_t SMEM = sizeof(float2) * (size_t)N * (T + 1);   // T lines of data + the twiddle table
+  F.tiles_per_outer = lines_per_outer / T;
+  F.n_tiles = F.tiles_per_outer * n_outer;
+  auto kern = fft_fast_kernel<LOGN, MODE, TW, T>;
+  static bool attr = false;
+  if (!attr) {
+    EB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM));
+    attr = true;
+  }
+  const int per_sm = 16384 / (T * N);   // 1024 threads (16 points each) per SM
+  const int64_t cap = (int64_t)(sm_count() > 0 ? sm_count() : 148) * per_sm;
+  const int grid = (int)(F.n_tiles < cap ? F.n_tiles : cap);
+  kern<<<grid, T * N / 16, SMEM, s>>>(F);
+  EB_LAUNCH_CHECK();
+  return ENDIA_B200_OK;
+}
+
+template <int LOGN>
+static int launch_fast_n(const FastParams &F, bool tw, int64_t lpo, int64_t no, cudaStream_t s) {
+  const bool row_in = F.in_elem == 1, row_out = F.out_elem == 1;
+  if (row_in && row_out) return launch_fast_variant<LOGN, FAST_ROW, false, 8>(F, lpo, no, s);
+  // 16 lines per tile give 128-byte segments on the strided side; they fit next to 2 CTAs per SM
+  // for lines up to 512 points (and, with one 1024-thread CTA per SM, for 1024 points).
+  static const int wide_max = []() { const char *e = getenv("ENDIA_B200_FFT_WIDE_MAX"); return e ? atoi(e) : 1024; }();
+  if constexpr (LOGN <= 10) {
+    if ((1 << LOGN) <= wide_max && lpo % 16 == 0) {
+      if (row_in) return launch_fast_variant<LOGN, FAST_COL_STAGED_IN, false, 16>(F, lpo, no, s);
+      return tw ? launch_fast_variant<LOGN, FAST_COL, true, 16>(F, lpo, no, s)
+                : launch_fast_variant<LOGN, FAST_COL, false, 16>(F, lpo, no, s);
+    }
+  }
+  if (row_in) return launch_fast_variant<LOGN, FAST_COL_STAGED_IN, false, 8>(F, lpo, no, s);
+  return tw ? launch_fast_variant<LOGN, FAST_COL, true, 8>(F, lpo, no, s)
+            : launch_fast_variant<LOGN, FAST_COL, false, 8>(F, lpo, no, s);
+}
+
+// Supported combinations: strided in and out (optionally with the four-step twiddle), contiguous
+// in and out, contiguous in with strided out.
+static bool fast_supported(int64_t in_elem, int64_t out_elem, bool tw) {
+  const bool row_in = in_elem == 1, row_out = out_elem == 1;
+  if (row_in) return !tw;
+  return !row_out;
+}
+
+static int launch_fast(const FastParams &F, int N, bool tw, int64_t lpo, int64_t no, cudaStream_t s) {
+  switch (N) {
+    case 256: return launch_fast_n<8>(F, tw, lpo, no, s);
+    case 512: return launch_fast_n<9>(F, tw, lpo, no, s);
+    case 1024: return launch_fast_n<10>(F, tw, lpo, no, s);
+    default: return launch_fast_n<11>(F, tw, lpo, no, s);
+  }
+}
+
 struct Pass {
   int N;
   int64_t n_outer, lines_per_outer;
@@ -273,6 +478,24 @@ static int launch_pass(const Pass &ps, const float2 *in, float2 *out, cudaStream
   if (P.n_tiles == 0) return ENDIA_B200_OK;
   int st = twiddle_table(ps.N, 1, ps.N, 0, &P.tw);
   if (st) return st;
+  if (ps.N >= 256 && ps.N <= 2048 && ps.lines_per_outer % 8 == 0 && ps.big_n < ((int64_t)1 << 23) &&
+      fast_supported(ps.in_elem, ps.out_elem, ps.big_n > 0)) {
+    FastParams F{};
+    F.in = in; F.out = out;
+    F.tiles_per_outer = ps.lines_per_outer / 8;
+    F.n_tiles = F.tiles_per_outer * ps.n_outer;
+    F.in_outer = ps.in_outer; F.in_line = ps.in_line; F.in_elem = ps.in_elem;
+    F.out_outer = ps.out_outer; F.out_line = ps.out_line; F.out_elem = ps.out_elem;
+    F.tw = P.tw; F.conj_in = ps.conj_in; F.conj_out = ps.conj_out; F.scale = ps.scale;
+    if (ps.big_n > 0) {
+      const int lb = ilog2(ps.big_n);
+      F.lo_bits = (lb + 1) / 2;
+      if ((st = twiddle_table(ps.big_n, 1, int64_t(1) << F.lo_bits, 1, &F.tw_lo))) return st;
+      if ((st = twiddle_table(ps.big_n, int64_t(1) << F.lo_bits, int64_t(1) << (lb - F.lo_bits), 2,
+                              &F.tw_hi))) return st;
+    }
+    return launch_fast(F, ps.N, ps.big_n > 0, ps.lines_per_outer, ps.n_outer, s);
+  }
   if (ps.big_n > 0) {
     const int lb = ilog2(ps.big_n);
     P.lo_bits = (lb + 1) / 2;
@@ -299,12 +522,24 @@ static int launch_pass(const Pass &ps, const float2 *in, float2 *out, cudaStream
 // Splits a long line length into N1 * N2 with both factors <= FFT_MAX_SMEM_N.
 static bool split_len(int64_t N, int &N1, int &N2) {
   const int L = ilog2(N);
-  const int l1 = (L + 1) / 2;
+  int l1 = (L + 1) / 2;
+  static const int forced = []() { const char *e = getenv("ENDIA_B200_FFT_SPLIT_L1"); return e ? atoi(e) : 0; }();
+  if (forced > 0 && forced < L) l1 = forced;
   N1 = 1 << l1; N2 = 1 << (L - l1);
   return N1 <= FFT_MAX_SMEM_N && N2 <= FFT_MAX_SMEM_N;
 }
 
 struct AxisInfo { int64_t outer, n, inner; };
+
+// Signals per four-step group. Grouping so that the intermediate stays in L2 measured slower than
+// two full-size passes (the passes are not HBM-bound and small launches fill the machine
+// badly), so by default a group is the whole batch; ENDIA_B200_FFT_GROUP_MIB overrides.
+static int64_t four_step_group(int64_t n, int64_t outer) {
+  static const int64_t mib = []() { const char *e = getenv("ENDIA_B200_FFT_GROUP_MIB"); return (int64_t)(e ? atoi(e) : 1 << 20); }();
+  int64_t g = (mib << 20) / (n * (int64_t)sizeof(float2));
+  if (g < 1) g = 1;
+  return g < outer ? g : outer;
+}
 
 static int collect_axes(const endia_b200_tensor *in, const int32_t *dims, int32_t n_dims,
                         std::vector<AxisInfo> &axes, bool &need_scratch) {
@@ -348,7 +583,14 @@ size_t endia_b200_fft_scratch_bytes(const endia_b200_tensor *in, const int32_t *
   std::vector<AxisInfo> axes;
   bool need = false;
   if (collect_axes(in, dims, n_dims, axes, need)) return 0;
-  return need ? sizeof(float2) * (size_t)numel(in) : 0;
+  if (!need) return 0;
+  size_t bytes = 0;
+  for (const AxisInfo &ai : axes)
+    if (ai.n > FFT_MAX_SMEM_N) {
+      const size_t b = sizeof(float2) * (size_t)ai.n * (size_t)four_step_group(ai.n, ai.outer);
+      if (b > bytes) bytes = b;
+    }
+  return bytes;
 }
 
 int endia_b200_fft_c2c(const endia_b200_tensor *in, const endia_b200_tensor *out,
@@ -407,19 +649,26 @@ int endia_b200_fft_c2c(const endia_b200_tensor *in, const endia_b200_tensor *out
       int n1, n2;
       split_len(ai.n, n1, n2);
       float2 *tmp = reinterpret_cast<float2 *>(scratch);
-      // Pass A: for every n2, transform over n1 (stride n2), then multiply by W_n^(k1*n2).
-      Pass pa{};
-      pa.N = n1; pa.n_outer = ai.outer; pa.lines_per_outer = n2;
-      pa.in_outer = pa.out_outer = ai.n; pa.in_line = pa.out_line = 1; pa.in_elem = pa.out_elem = n2;
-      pa.conj_in = cin; pa.conj_out = 0; pa.scale = 1.f; pa.big_n = ai.n;
-      if ((st = launch_pass(pa, src, tmp, s))) return st;
-      // Pass B: for every k1, transform the contiguous row over n2; X[k1 + n1*k2] = row[k2].
-      Pass pb{};
-      pb.N = n2; pb.n_outer = ai.outer; pb.lines_per_outer = n1;
-      pb.in_outer = pb.out_outer = ai.n; pb.in_line = n2; pb.in_elem = 1;
-      pb.out_line = 1; pb.out_elem = n1;
-      pb.conj_in = 0; pb.conj_out = cout; pb.scale = sc; pb.big_n = 0;
-      if ((st = launch_pass(pb, tmp, dst, s))) return st;
+      // The two passes run group by group over the signals, through one group-sized scratch
+      // buffer that is rewritten for every group: the intermediate then lives in L2 and HBM sees
+      // one read of the input and one write of the output.
+      const int64_t group = four_step_group(ai.n, ai.outer);
+      for (int64_t g0 = 0; g0 < ai.outer; g0 += group) {
+        const int64_t ng = ai.outer - g0 < group ? ai.outer - g0 : group;
+        // Pass A: for every n2, transform over n1 (stride n2), then multiply by W_n^(k1*n2).
+        Pass pa{};
+        pa.N = n1; pa.n_outer = ng; pa.lines_per_outer = n2;
+        pa.in_outer = pa.out_outer = ai.n; pa.in_line = pa.out_line = 1; pa.in_elem = pa.out_elem = n2;
+        pa.conj_in = cin; pa.conj_out = 0; pa.scale = 1.f; pa.big_n = ai.n;
+        if ((st = launch_pass(pa, src + g0 * ai.n, tmp, s))) return st;
+        // Pass B: for every k1, transform the contiguous row over n2; X[k1 + n1*k2] = row[k2].
+        Pass pb{};
+        pb.N = n2; pb.n_outer = ng; pb.lines_per_outer = n1;
+        pb.in_outer = pb.out_outer = ai.n; pb.in_line = n2; pb.in_elem = 1;
+        pb.out_line = 1; pb.out_elem = n1;
+        pb.conj_in = 0; pb.conj_out = cout; pb.scale = sc; pb.big_n = 0;
+        if ((st = launch_pass(pb, tmp, dst + g0 * ai.n, s))) return st;
+      }
     }
     src = dst;
   }
