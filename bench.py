@@ -110,7 +110,7 @@ class ClockSampler:
 
 
 class GemmTimer:
-    """Brackets every GEMM launch with CUDA events on the launching stream."""
+    """Brackets every GEMM (or FFT) call with CUDA events on the launching stream."""
 
     def __init__(self, torch):
         self.torch = torch
@@ -178,6 +178,107 @@ class TrainStep:
         return loss
 
 
+
+FFT_METRIC = "fftn fwd+VJP GB/s"
+
+
+class FFTStep:
+    """c4: 32 signals of 2^20 points, loss = sum(|fft(x)|^2) * 2^-20, forward + VJP w.r.t. x.
+    c5: 512^3 grid, loss = sum(real(fftn(x)) * w), forward + VJP; over N ranks the grid is split
+    along axis 0 (slab decomposition, one all-to-all per transform)."""
+
+    def __init__(self, nd, torch, workload, rank, world):
+        self.nd, self.torch, self.workload, self.rank, self.world = nd, torch, workload, rank, world
+        r = np.random.Generator(np.random.PCG64(0))
+        if workload == "c4":
+            self.shape = (32, 1 << 20)
+            x = (r.standard_normal(self.shape, dtype=np.float32) + 1j * r.standard_normal(self.shape, dtype=np.float32)).astype(np.complex64)
+            self.x_host = torch.from_numpy(x).pin_memory()
+            self.X = nd.Array(x, requires_grad=True)
+            self.alg_bytes = 4.0 * x.nbytes
+        else:
+            n = 512
+            self.shape = (n, n, n)
+            s0 = n // world
+            sub = (s0, n, n)
+            r = np.random.Generator(np.random.PCG64(rank))
+            x = (r.standard_normal(sub, dtype=np.float32) + 1j * r.standard_normal(sub, dtype=np.float32)).astype(np.complex64)
+            self.x_host = torch.from_numpy(x).pin_memory()
+            self.alg_bytes = 4.0 * 8.0 * n ** 3
+            if world == 1:
+                self.X = nd.Array(x, requires_grad=True)
+                self.W = nd.Array(r.uniform(-1, 1, sub).astype(np.float32))
+            else:
+                from endia_b200 import dist as ndist
+                self.slab = ndist.device_slab_fft(world)
+                self.xt = torch.from_numpy(x).cuda()
+                self.wt = torch.from_numpy(r.uniform(-1, 1, (n, n // world, n)).astype(np.float32)).cuda()
+        self.loss_host = torch.empty(1, dtype=torch.float32).pin_memory()
+
+    def step(self, host_io=False):
+        nd, torch = self.nd, self.torch
+        from endia_b200.dist import flat_tensor
+        if self.workload == "c5" and self.world > 1:
+            if host_io:
+                self.xt.copy_(self.x_host, non_blocking=True)
+            y = self.slab.forward(self.xt)
+            # loss = sum(real(y) * w); its gradient w.r.t. y is (w + 0i): formed on the device
+            loss = (y.real * self.wt).sum()
+            g = torch.complex(self.wt, torch.zeros_like(self.wt))
+            dx = self.slab.backward(g)
+            if host_io:
+                self.loss_host.copy_(loss.reshape(1), non_blocking=True)
+                torch.cuda.current_stream().synchronize()
+            return dx
+        if host_io:
+            flat_tensor(self.X).copy_(torch.view_as_real(self.x_host).reshape(-1), non_blocking=True)
+        if self.workload == "c4":
+            y = nd.fft(self.X)
+            loss = nd.sum(nd.square(nd.to_abs(y))) * (1.0 / (1 << 20))
+        else:
+            y = nd.fftn(self.X)
+            loss = nd.sum(nd.real(y) * self.W)
+        loss.backward()
+        dx = self.X.grad()
+        loss.zero_grad()
+        if host_io:
+            self.loss_host.copy_(flat_tensor(loss), non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+        return dx
+
+
+def fft_cpu_baseline(workload):
+    """Endia's CPU algorithm for the FFT configs (oracle port: float64 radix-2 with per-axis
+    gathers, rows spread over the host threads as the reference's parallelize does), forward + VJP,
+    on a bounded sample: c4 on 4 of the 32 signals, c5 on a 256^3 grid (scaled by points*log2)."""
+    from oracle import endia_oracle as eo
+    eo.build()
+    threads = max(1, (os.cpu_count() or 2) // 2)   # the reference uses the physical cores
+    eo.config["fft_threads"] = threads
+    r = np.random.Generator(np.random.PCG64(0))
+    if workload == "c4":
+        shape, full = (4, 1 << 20), 32 * (1 << 20) * 20.0
+        work = 4 * (1 << 20) * 20.0
+    else:
+        shape, full = (256, 256, 256), 512.0 ** 3 * 27
+        work = 256.0 ** 3 * 24
+    x = (r.standard_normal(shape) + 1j * r.standard_normal(shape)).astype(np.complex64)
+    t0 = time.perf_counter()
+    X = eo.Array(x, requires_grad=True)
+    if workload == "c4":
+        loss = eo.sum(eo.square(eo.to_abs(eo.fft(X)))) * (1.0 / (1 << 20))
+    else:
+        loss = eo.sum(eo.real(eo.fftn(X)) * eo.Array(r.uniform(-1, 1, shape).astype(np.float32)))
+    loss.backward()
+    dt = time.perf_counter() - t0
+    eo.config["fft_threads"] = 1
+    full_s = dt * full / work
+    alg = 4.0 * 8.0 * (32 * (1 << 20) if workload == "c4" else 512 ** 3)
+    return {"value": alg / full_s / 1e9, "unit": "GB/s", "cores": threads, "kind": "port",
+            "sample": "%s forward+VJP on shape %s in %.2f s, scaled by n*log2(n) to the full size" % (
+                workload, list(shape), dt), "host_cores_available": os.cpu_count(), "seconds": dt}
+
+
 def cpu_baseline(sample_rows=48, threads_note=True):
     """Endia's CPU algorithm (the oracle port, faithful mode: single-threaded dot-product matmul,
     one temporary per op, Adam as array expressions) on a bounded sample of the same workload:
@@ -240,6 +341,8 @@ def main():
     ap.add_argument("--cpu-rows", type=int, default=48)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--gemm", default="auto", choices=["auto", "ffma", "3xtf32"])
+    ap.add_argument("--workload", default="c2", choices=["c2", "c4", "c5"],
+                    help="c2 (default, the headline): MLP train step; c4 / c5: FFT forward + VJP")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
@@ -255,7 +358,8 @@ def main():
     rank, world = ndist.init_process_group()
     nd._array.device()
     nd.config.gemm_algo = {"auto": _lib.GEMM_AUTO, "ffma": _lib.GEMM_FFMA, "3xtf32": _lib.GEMM_3XTF32}[args.gemm]
-    work = TrainStep(nd, torch, rank, world)
+    is_fft = args.workload != "c2"
+    work = FFTStep(nd, torch, args.workload, rank, world) if is_fft else TrainStep(nd, torch, rank, world)
 
     def barrier():
         if world > 1:
@@ -270,6 +374,7 @@ def main():
     sampler = ClockSampler(torch.cuda.current_device())
     timer = GemmTimer(torch)
     nd.config.gemm_timer = timer
+    nd.config.fft_timer = timer
     launches0 = _lib.lib.endia_b200_launch_count()
     sampler.start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -281,6 +386,7 @@ def main():
     barrier()
     clocks = sampler.stop()
     nd.config.gemm_timer = None
+    nd.config.fft_timer = None
     launches = _lib.lib.endia_b200_launch_count() - launches0
     ms_total = e0.elapsed_time(e1)
     n_gemm, gemm_fl, gemm_ms = timer.summary()
@@ -307,6 +413,36 @@ def main():
         return
 
     pk = peaks()
+    if is_fft:
+        ms_step = ms_total / args.steps
+        hbm_peak = pk["hbm_gbs"]
+        ach = gemm_fl / (gemm_ms / 1000.0) / 1e9 if gemm_ms > 0 else 0.0
+        line = {
+            "metric": FFT_METRIC, "value": work.alg_bytes / (ms_step / 1000.0) / 1e9, "unit": "GB/s",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "c64",
+            "data": "synthetic",
+            "config": {"workload": "%s: %s complex64, forward + VJP" % (args.workload, list(work.shape)),
+                       "parallelism": ("slab%d" % world) if args.workload == "c5" else "single",
+                       "algorithmic_bytes_per_step": work.alg_bytes,
+                       "l2": "arrays of 256 MiB / 1 GiB exceed the 126 MB L2; no flush"},
+            "clocks": {"sm_mhz": clocks["sm_mhz"], "sm_max_mhz": clocks["sm_max_mhz"],
+                       "reasons": clocks["reasons"], "samples": clocks["samples"]},
+            "e2e": {"value": work.alg_bytes / (ms_e2e / args.steps / 1000.0) / 1e9, "unit": "GB/s",
+                    "h2d_bytes_per_step": int(work.x_host.numel() * 8) * world, "d2h_bytes_per_step": 4 * world},
+            "gpu_launches": int(launches),
+            "roofline": {"bound": "hbm", "achieved": ach, "peak": hbm_peak, "unit": "GB/s",
+                         "frac": ach / hbm_peak if hbm_peak else None, "traffic": None,
+                         "kernel": "fft_c2c calls (%d, %.1f%% of the step); algorithmic bytes = one read + "
+                                   "one write of the array per transform" % (n_gemm, 100.0 * gemm_ms / ms_total),
+                         "peak_note": "%s hbm_gbs (copy)" % pk["source"]},
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            line["cpu_baseline"] = fft_cpu_baseline(args.workload)
+        print(json.dumps(line))
+        if world > 1:
+            tdist.destroy_process_group()
+        return
     ms_step = ms_total / args.steps
     value = GLOBAL_BATCH / (ms_step / 1000.0)
     tflops = gemm_fl / (gemm_ms / 1000.0) / 1e12 if gemm_ms > 0 else 0.0

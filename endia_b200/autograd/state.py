@@ -9,3 +9,5 @@ gemm_algo = _lib.GEMM_AUTO
 # Optional object with start(flops) / stop() called around every GEMM launch (benchmarks bracket
 # the launches with events on the launching stream).
 gemm_timer = None
+# Same hook around every FFT call: start(algorithmic_bytes) / stop().
+fft_timer = None

@@ -6,7 +6,7 @@ import os
 import torch
 import torch.distributed as dist
 
-from ._array import Array, device
+from ._array import Array, ArrayShape, device
 
 
 def init_process_group():
@@ -42,9 +42,10 @@ class GradAllReducer:
             p.grad_hook = self._hook
 
     def _hook(self, param, grad):
-        from .functional._utils import contiguous
-        g = contiguous(grad)
-        if g is not grad:
+        g = grad
+        if not grad.is_contiguous():
+            from .functional._utils import contiguous
+            g = contiguous(grad)
             param.grad_(g)
         self.pending.append(dist.all_reduce(flat_tensor(g), op=dist.ReduceOp.SUM, group=self.group,
                                             async_op=True))
@@ -57,3 +58,83 @@ class GradAllReducer:
     def detach(self):
         for p in self.params:
             p.grad_hook = None
+
+
+# ---------------------------------------------------------------------------------------------
+# Slab-decomposed N-D FFT: the array is split along axis 0 over the ranks; the transform over the
+# trailing axes is local, one all-to-all re-splits the array along axis 1 so that axis 0 becomes
+# local, and the last transform runs there. The result stays split along axis 1 (the VJP runs the
+# same steps backwards, so no transpose back is needed).
+
+def slab_pack(local, world):
+    """[S0, N1, ...] -> [P, S0, N1/P, ...]: block q holds the part of axis 1 that rank q will own.
+    `local` is a torch tensor (any device); returns a contiguous tensor."""
+    s0, n1 = local.shape[0], local.shape[1]
+    rest = tuple(local.shape[2:])
+    return local.reshape((s0, world, n1 // world) + rest).transpose(0, 1).contiguous()
+
+
+def slab_unpack(blocks, world):
+    """Inverse of slab_pack: [P, S0, N1/P, ...] -> [S0, N1, ...]."""
+    s0, s1 = blocks.shape[1], blocks.shape[2]
+    rest = tuple(blocks.shape[3:])
+    return blocks.transpose(0, 1).reshape((s0, world * s1) + rest).contiguous()
+
+
+def slab_exchange(packed, group=None):
+    """All-to-all of the P blocks of `packed` ([P, ...], contiguous): block q goes to rank q; the
+    result's block q came from rank q. Received data lands in local memory (NCCL or gloo)."""
+    out = torch.empty_like(packed)
+    if dist.is_initialized() and dist.get_world_size(group) > 1:
+        dist.all_to_all_single(out, packed, group=group)
+    else:
+        out.copy_(packed)
+    return out
+
+
+class SlabFFT:
+    """fftn of an array whose axis 0 is split over the ranks. `fft_tail(t, inverse)` transforms
+    all axes but the first of a local torch tensor, `fft_head(t, inverse)` transforms axis 0; both
+    return tensors of the same shape. The product passes GPU kernels, the CPU tests pass torch.fft.
+
+    forward(x_local[S0, N1, ...]) -> y_local[N0, N1/P, ...]   (split along axis 1)
+    backward(g_local[N0, N1/P, ...]) -> dx_local[S0, N1, ...] (the VJP: conjugate-direction
+    transform without normalisation, endia fftn_op.mojo:43-49)"""
+
+    def __init__(self, fft_tail, fft_head, world, group=None):
+        self.fft_tail, self.fft_head, self.world, self.group = fft_tail, fft_head, world, group
+
+    def forward(self, x_local, inverse=False):
+        y = self.fft_tail(x_local, inverse)
+        blocks = slab_exchange(slab_pack(y, self.world), self.group)
+        # block q = rows of axis 0 owned by rank q: stacking the blocks restores axis 0
+        full0 = blocks.reshape((blocks.shape[0] * blocks.shape[1],) + tuple(blocks.shape[2:]))
+        return self.fft_head(full0, inverse)
+
+    def backward(self, g_local, inverse=True):
+        g = self.fft_head(g_local, inverse)
+        s0 = g.shape[0] // self.world
+        blocks = g.reshape((self.world, s0) + tuple(g.shape[1:]))
+        back = slab_exchange(blocks.contiguous(), self.group)
+        return self.fft_tail(slab_unpack(back, self.world), inverse)
+
+
+def device_slab_fft(world, group=None):
+    """SlabFFT over the device kernels: local transforms through endia_b200's fft_c2c on complex64
+    torch CUDA tensors viewed as interleaved float32 storage."""
+    from .functional.fft_ops import run_fft
+
+    def wrap(t):
+        arr = Array(ArrayShape(list(t.shape)))
+        arr.is_complex_flag = True
+        arr.buf = torch.view_as_real(t).reshape(-1)
+        return arr
+
+    def run(t, dims, inverse):
+        t = t.contiguous()
+        out = torch.empty_like(t)
+        run_fft(wrap(t), wrap(out), dims, inverse, 1.0)
+        return out
+
+    return SlabFFT(lambda t, inv: run(t, list(range(1, t.dim())), inv),
+                   lambda t, inv: run(t, [0], inv), world, group)

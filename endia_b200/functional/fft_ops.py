@@ -52,8 +52,13 @@ def run_fft(src, dst, dims, direction_inverse, scale):
     sd, dd = src.desc(), dst.desc()
     nbytes = _lib.lib.endia_b200_fft_scratch_bytes(sd, cd, len(dims))
     scratch = alloc((nbytes + 3) // 4) if nbytes else None
+    timer = _state.fft_timer
+    if timer is not None:
+        timer.start(16.0 * src.size())   # algorithmic bytes: one read and one write of the array
     _lib.call("endia_b200_fft_c2c", sd, dd, cd, len(dims), 1 if direction_inverse else 0,
               float(scale), scratch.data_ptr() if scratch is not None else None, stream())
+    if timer is not None:
+        timer.stop()
 
 
 def _as_complex(x):
