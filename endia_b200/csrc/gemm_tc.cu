@@ -25,7 +25,7 @@
 namespace eb {
 
 constexpr int TC_BM = 128;
-constexpr uint32_t TC_WAIT_LIMIT = 1u << 24;
+constexpr uint32_t TC_WAIT_LIMIT = 1u << 22;
 
 static __device__ int g_tc_status = 0;    // 0 ok, else the code of the first wait that gave up
 
@@ -280,6 +280,198 @@ gemm_tc_kernel(const __grid_constant__ TcMaps maps, const GemmParams p, int tile
   }
 }
 
+// ------------------------------------------------------------- two-CTA (cta_group::2) kernel
+// A pair of CTAs on neighbouring SMs computes one 256 x 256 tile: each CTA keeps its own 128 rows
+// of A and only HALF of the B tile in shared memory; the leader CTA issues tcgen05.mma with
+// cta_group::2 (M = 256), which reads both halves of B and writes each CTA's 128 accumulator rows
+// into that CTA's tensor memory. Per CTA this halves the B traffic into and out of shared
+// memory, the resource that bounds the one-CTA kernel. Loads of both CTAs signal the leader's
+// "full" barriers; the leader's commits are multicast to both CTAs' "empty" and accumulator
+// barriers. No load is multicast.
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Tile load whose completion bytes are counted on a barrier of the pair's leader CTA.
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap *map, uint32_t leader_bar,
+                                                 int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(map), "r"(leader_bar), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void tc_commit_pair(uint32_t bar) {
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+      ::"r"(bar), "h"((uint16_t)3) : "memory");
+}
+__device__ __forceinline__ void tc_mma_tf32_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                                 uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+
+template <bool A_MN, bool B_MN>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
+gemm_tc2_kernel(const __grid_constant__ TcMaps maps, const GemmParams p, int pairs_m) {
+  constexpr int BN = 256, BNH = 128, BK = 32, STAGES = 3;
+  extern __shared__ __align__(1024) uint8_t smem[];
+  constexpr uint32_t A_BYTES = TC_BM * BK * 4;      // this CTA's 128 rows of A
+  constexpr uint32_t B_BYTES = BNH * BK * 4;        // this CTA's half of the B tile
+  constexpr uint32_t BOX_BYTES = BK * 128;
+  constexpr uint32_t STAGE_BYTES = 2 * A_BYTES + 2 * B_BYTES;
+  const uint32_t smem_base = (smem_u32(smem) + 1023u) & ~1023u;
+  const uint32_t bars = smem_base + STAGES * STAGE_BYTES;
+  __shared__ uint32_t tmem_slot;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const bool leader = rank == 0;
+  const int pair = blockIdx.x >> 1;
+  const int tile_m = pair % pairs_m, tile_n = pair / pairs_m;
+  const int m0 = tile_m * 256 + (int)rank * 128;
+  const int n0 = tile_n * BN, nh0 = n0 + (int)rank * BNH;
+  const int nkb = (int)((p.K + BK - 1) / BK);
+  auto full_bar = [&](int s) { return bars + 8u * s; };
+  auto empty_bar = [&](int s) { return bars + 8u * (STAGES + s); };
+  const uint32_t acc_bar = bars + 8u * (2 * STAGES);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+    mbar_init(acc_bar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;"
+                 ::"r"(smem_u32(&tmem_slot)), "r"((uint32_t)(2 * BN)) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  cluster_sync();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int issued = 0;
+      bool ok = true;
+      for (int kb = 0; kb < nkb && ok; ++kb) {
+        const int s = kb % STAGES;
+        if (kb >= STAGES) ok = mbar_wait(empty_bar(s), ((kb / STAGES) - 1) & 1, 11);
+        if (!ok) break;
+        const uint32_t st = smem_base + s * STAGE_BYTES;
+        if (leader) mbar_expect_tx(full_bar(s), 2 * STAGE_BYTES);   // both CTAs' bytes
+        const uint32_t fb = map_to_cta(full_bar(s), 0);
+        const int k0 = kb * BK;
+        if constexpr (A_MN) {
+#pragma unroll
+          for (int j = 0; j < TC_BM / 32; ++j) {
+            tma_load_2d_pair(st + j * BOX_BYTES, &maps.a_hi, fb, m0 + 32 * j, k0);
+            tma_load_2d_pair(st + A_BYTES + j * BOX_BYTES, &maps.a_lo, fb, m0 + 32 * j, k0);
+          }
+        } else {
+          tma_load_2d_pair(st, &maps.a_hi, fb, k0, m0);
+          tma_load_2d_pair(st + A_BYTES, &maps.a_lo, fb, k0, m0);
+        }
+        const uint32_t sb = st + 2 * A_BYTES;
+        if constexpr (B_MN) {
+#pragma unroll
+          for (int j = 0; j < BNH / 32; ++j) {
+            tma_load_2d_pair(sb + j * BOX_BYTES, &maps.b_hi, fb, nh0 + 32 * j, k0);
+            tma_load_2d_pair(sb + B_BYTES + j * BOX_BYTES, &maps.b_lo, fb, nh0 + 32 * j, k0);
+          }
+        } else {
+          tma_load_2d_pair(sb, &maps.b_hi, fb, k0, nh0);
+          tma_load_2d_pair(sb + B_BYTES, &maps.b_lo, fb, k0, nh0);
+        }
+        ++issued;
+      }
+      (void)issued;
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && leader) {
+      // M = 256 over the pair, N = 256
+      const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((A_MN ? 1u : 0u) << 15) |
+                             ((B_MN ? 1u : 0u) << 16) | ((uint32_t)(BN >> 3) << 17) |
+                             ((uint32_t)(256 >> 4) << 24);
+      for (int kb = 0; kb < nkb; ++kb) {
+        const int s = kb % STAGES;
+        if (!mbar_wait(full_bar(s), (kb / STAGES) & 1, 13)) break;
+        tc_fence_after();
+        const uint32_t st = smem_base + s * STAGE_BYTES;
+        const uint64_t a_hi = tile_desc<A_MN, BK>(st), a_lo = tile_desc<A_MN, BK>(st + A_BYTES);
+        const uint32_t sb = st + 2 * A_BYTES;
+        const uint64_t b_hi = tile_desc<B_MN, BK>(sb), b_lo = tile_desc<B_MN, BK>(sb + B_BYTES);
+        constexpr uint64_t A_STEP = A_MN ? 64 : 2, B_STEP = B_MN ? 64 : 2;
+#pragma unroll
+        for (int ks = 0; ks < BK / 8; ++ks) {
+          const uint64_t ah = a_hi + ks * A_STEP, al = a_lo + ks * A_STEP;
+          const uint64_t bh = b_hi + ks * B_STEP, bl = b_lo + ks * B_STEP;
+          const uint32_t acc = (kb | ks) ? 1u : 0u;
+          tc_mma_tf32_pair(tmem_base + BN, al, bh, idesc, acc);
+          tc_mma_tf32_pair(tmem_base + BN, ah, bl, idesc, 1u);
+          tc_mma_tf32_pair(tmem_base, ah, bh, idesc, acc);
+        }
+        tc_commit_pair(empty_bar(s));
+      }
+      tc_commit_pair(acc_bar);
+    }
+  } else {
+    const int q = warp & 3;
+    const bool ok = mbar_wait(acc_bar, 0, 14);
+    tc_fence_after();
+    const int64_t m = (int64_t)m0 + q * 32 + lane;
+    if (ok && nkb > 0) {
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32], r2[32];
+        tc_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(c * 32), r);
+        tc_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(BN + c * 32), r2);
+        tc_wait_ld();
+#pragma unroll
+        for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) + __uint_as_float(r2[j]));
+        const int64_t nb = (int64_t)n0 + c * 32;
+        if (m < p.M && nb < p.N) {
+          float *crow = p.C + m * p.ldc + nb;
+          if (p.vec_c && nb + 32 <= p.N) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) {
+              float4 o;
+              o.x = apply_epilogue(p.epi, __uint_as_float(r[j + 0]), m, nb + j + 0, crow + j + 0);
+              o.y = apply_epilogue(p.epi, __uint_as_float(r[j + 1]), m, nb + j + 1, crow + j + 1);
+              o.z = apply_epilogue(p.epi, __uint_as_float(r[j + 2]), m, nb + j + 2, crow + j + 2);
+              o.w = apply_epilogue(p.epi, __uint_as_float(r[j + 3]), m, nb + j + 3, crow + j + 3);
+              *reinterpret_cast<float4 *>(crow + j) = o;
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (nb + j < p.N)
+                crow[j] = apply_epilogue(p.epi, __uint_as_float(r[j]), m, nb + j, crow + j);
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  cluster_sync();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)(2 * BN)) : "memory");
+  }
+}
+
 // lo = x - hi with hi = x truncated to tf32 (13 low mantissa bits cleared); exact in fp32.
 // Optionally also writes hi. Rows of `cols` floats, leading dimensions ld_in / ld_out.
 __global__ void __launch_bounds__(256)
@@ -385,6 +577,34 @@ static int launch_variant(const TcMaps &maps, const GemmParams &p, int trans_a, 
   return ENDIA_B200_OK;
 }
 
+static bool pair_mode() {
+  static const bool on = []() { const char *e = getenv("ENDIA_B200_TC_PAIR"); return !(e && atoi(e) == 0); }();
+  return on;
+}
+
+static int launch_pair(const TcMaps &maps, const GemmParams &p, int trans_a, int trans_b, cudaStream_t s) {
+  constexpr size_t SMEM = (size_t)3 * (2 * TC_BM * 32 * 4 + 2 * 128 * 32 * 4) + 1024 + 256;
+  const int pairs_m = (int)ceil_div(p.M, 256), tiles_n = (int)ceil_div(p.N, 256);
+  const dim3 grid((unsigned)(pairs_m * tiles_n * 2));
+#define EB_TC2_LAUNCH(AM, BM_)                                                                    \
+  do {                                                                                            \
+    auto kern = gemm_tc2_kernel<AM, BM_>;                                                         \
+    static bool attr = false;                                                                     \
+    if (!attr) {                                                                                  \
+      EB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM)); \
+      attr = true;                                                                                \
+    }                                                                                             \
+    kern<<<grid, 192, SMEM, s>>>(maps, p, pairs_m);                                               \
+  } while (0)
+  if (trans_a && !trans_b) EB_TC2_LAUNCH(true, true);
+  else if (trans_a && trans_b) EB_TC2_LAUNCH(true, false);
+  else if (!trans_a && !trans_b) EB_TC2_LAUNCH(false, true);
+  else EB_TC2_LAUNCH(false, false);
+#undef EB_TC2_LAUNCH
+  EB_LAUNCH_CHECK();
+  return ENDIA_B200_OK;
+}
+
 int launch_gemm_tc(const GemmParams &p, int trans_a, int trans_b, cudaStream_t s) {
   // Operand geometry in memory: A is [M, K] (K-major) or [K, M] (MN-major); B is [K, N] (MN-major,
   // the row-major weight of `x @ W`) or [N, K] (K-major).
@@ -405,18 +625,20 @@ int launch_gemm_tc(const GemmParams &p, int trans_a, int trans_b, cudaStream_t s
   // better than 32 floats with 2 or 3 stages in the same shared memory.
   static const int bk = []() {
     const char *e = getenv("ENDIA_B200_TC_BK");
-    return (e && atoi(e) == 32) ? 32 : 16;
+    return (e && atoi(e) == 16) ? 16 : 32;
   }();
   TcMaps maps;
   int st;
   // K-major operand: box [rows of the tile][bk k]; MN-major operand: box [bk k][32 rows].
   const int a_bi = trans_a ? 32 : bk, a_bo = trans_a ? bk : TC_BM;
-  const int b_bi = trans_b ? bk : 32, b_bo = trans_b ? bn : bk;
+  const bool pair = bn == 256 && bk == 32 && pair_mode();
+  const int b_bi = trans_b ? bk : 32, b_bo = trans_b ? (pair ? 128 : bn) : bk;
   if ((st = make_map(&maps.a_hi, p.A, a_cols, a_rows, p.lda, a_bi, a_bo, trans_a != 0))) return st;
   if ((st = make_map(&maps.a_lo, a_lo, a_cols, a_rows, a_ld, a_bi, a_bo, trans_a != 0))) return st;
   if ((st = make_map(&maps.b_hi, p.B, b_cols, b_rows, p.ldb, b_bi, b_bo, trans_b == 0))) return st;
   if ((st = make_map(&maps.b_lo, b_lo, b_cols, b_rows, b_ld, b_bi, b_bo, trans_b == 0))) return st;
-  if (bn == 256 && bk == 16) st = launch_variant<256, 16, 4>(maps, p, trans_a, trans_b, s);
+  if (pair) st = launch_pair(maps, p, trans_a, trans_b, s);
+  else if (bn == 256 && bk == 16) st = launch_variant<256, 16, 4>(maps, p, trans_a, trans_b, s);
   else if (bn == 256) st = launch_variant<256, 32, 2>(maps, p, trans_a, trans_b, s);
   else if (bk == 16) st = launch_variant<128, 16, 6>(maps, p, trans_a, trans_b, s);
   else st = launch_variant<128, 32, 3>(maps, p, trans_a, trans_b, s);
