@@ -205,39 +205,26 @@ class FFTStep:
             x = (r.standard_normal(sub, dtype=np.float32) + 1j * r.standard_normal(sub, dtype=np.float32)).astype(np.complex64)
             self.x_host = torch.from_numpy(x).pin_memory()
             self.alg_bytes = 4.0 * 8.0 * n ** 3
-            if world == 1:
-                self.X = nd.Array(x, requires_grad=True)
-                self.W = nd.Array(r.uniform(-1, 1, sub).astype(np.float32))
-            else:
-                from endia_b200 import dist as ndist
-                self.slab = ndist.device_slab_fft(world)
-                self.xt = torch.from_numpy(x).cuda()
-                self.wt = torch.from_numpy(r.uniform(-1, 1, (n, n // world, n)).astype(np.float32)).cuda()
+            self.X = nd.Array(x, requires_grad=True)
+            # w is split like the result: along axis 1 when the transform is slab-decomposed
+            self.W = nd.Array(r.uniform(-1, 1, (n, n // world, n)).astype(np.float32))
         self.loss_host = torch.empty(1, dtype=torch.float32).pin_memory()
 
     def step(self, host_io=False):
         nd, torch = self.nd, self.torch
         from endia_b200.dist import flat_tensor
-        if self.workload == "c5" and self.world > 1:
-            if host_io:
-                self.xt.copy_(self.x_host, non_blocking=True)
-            y = self.slab.forward(self.xt)
-            # loss = sum(real(y) * w); its gradient w.r.t. y is (w + 0i): formed on the device
-            loss = (y.real * self.wt).sum()
-            g = torch.complex(self.wt, torch.zeros_like(self.wt))
-            dx = self.slab.backward(g)
-            if host_io:
-                self.loss_host.copy_(loss.reshape(1), non_blocking=True)
-                torch.cuda.current_stream().synchronize()
-            return dx
         if host_io:
             flat_tensor(self.X).copy_(torch.view_as_real(self.x_host).reshape(-1), non_blocking=True)
         if self.workload == "c4":
             y = nd.fft(self.X)
             loss = nd.sum(nd.square(nd.to_abs(y))) * (1.0 / (1 << 20))
-        else:
+        elif self.world == 1:
             y = nd.fftn(self.X)
             loss = nd.sum(nd.real(y) * self.W)
+        else:
+            from endia_b200.dist import fftn_slab
+            y = fftn_slab(self.X, self.world)
+            loss = nd.sum(nd.real(y) * self.W)     # this rank's part of the global sum
         loss.backward()
         dx = self.X.grad()
         loss.zero_grad()

@@ -34,7 +34,7 @@ def device():
 
 def stream():
     """Raw cudaStream_t of torch's current stream; every kernel is enqueued on it."""
-    return torch.cuda.current_stream().cuda_stream
+    return torch._C._cuda_getCurrentRawStream(device().index)
 
 
 def alloc(n_floats):

@@ -119,22 +119,81 @@ class SlabFFT:
         return self.fft_tail(slab_unpack(back, self.world), inverse)
 
 
-def device_slab_fft(world, group=None):
-    """SlabFFT over the device kernels: local transforms through endia_b200's fft_c2c on complex64
-    torch CUDA tensors viewed as interleaved float32 storage."""
+def _strided_view(arr, shape, stride):
+    v = Array(ArrayShape(shape, stride, arr.storage_offset()))
+    v.buf = arr.buf
+    v.base_ = arr.base()
+    v.is_view = True
+    v.is_complex_flag = arr.is_complex()
+    return v
+
+
+def _exchange_arrays(src, world, group=None):
+    """All-to-all of the `world` equal blocks of a contiguous Array into a new Array."""
+    out = Array(ArrayShape(src.shape()))
+    out.is_complex_flag = src.is_complex()
+    out.buf = torch.empty_like(flat_tensor(src))
+    if dist.is_initialized() and dist.get_world_size(group) > 1:
+        dist.all_to_all_single(out.buf, flat_tensor(src), group=group)
+    else:
+        from . import _lib
+        from ._array import stream
+        _lib.call("endia_b200_d2d", out.data_ptr(), src.data_ptr(), src.size() * 8, stream())
+    return out
+
+
+def fftn_slab(x_local, world=None, group=None):
+    """fftn of a 3-D complex array whose axis 0 is split over the ranks (x_local is this rank's
+    slab [N0/P, N1, N2]); returns this rank's slab [N0, N1/P, N2] of the result, split along
+    axis 1. Differentiable: the VJP runs the conjugate-direction transforms and the exchange in
+    reverse order and returns a gradient laid out like x_local (fftn_op.mojo:43-49). Local
+    transforms, the block packing and every other step run in this library's kernels; the
+    exchange is one all-to-all into local memory."""
+    from .functional._utils import op_array, setup_shape_and_data, copy
     from .functional.fft_ops import run_fft
+    if world is None:
+        world = dist.get_world_size(group) if dist.is_initialized() else 1
+    s0, n1, n2 = x_local.shape()
+    n0, s1 = s0 * world, n1 // world
+    if n1 % world:
+        raise ValueError("fftn_slab: axis 1 (%d) must divide by the number of ranks (%d)" % (n1, world))
 
-    def wrap(t):
-        arr = Array(ArrayShape(list(t.shape)))
-        arr.is_complex_flag = True
-        arr.buf = torch.view_as_real(t).reshape(-1)
-        return arr
+    def new_like(shape):
+        a = Array(ArrayShape(shape))
+        a.is_complex_flag = True
+        setup_shape_and_data(a)
+        return a
 
-    def run(t, dims, inverse):
-        t = t.contiguous()
-        out = torch.empty_like(t)
-        run_fft(wrap(t), wrap(out), dims, inverse, 1.0)
+    def forward_impl(x):
+        y1 = new_like([s0, n1, n2])
+        run_fft(x, y1, [1, 2], False, 1.0)
+        # pack: block q = y1[:, q*s1:(q+1)*s1, :]  ->  [P, s0, s1, n2] contiguous
+        packed = copy(_strided_view(y1, [world, s0, s1, n2], [s1 * n2, n1 * n2, n2, 1]))
+        recv = _exchange_arrays(packed, world, group)          # [P*s0 = n0, s1, n2]
+        full0 = _strided_view(recv, [n0, s1, n2], [s1 * n2, n2, 1])
+        out = new_like([n0, s1, n2])
+        run_fft(full0, out, [0], False, 1.0)
         return out
 
-    return SlabFFT(lambda t, inv: run(t, list(range(1, t.dim())), inv),
-                   lambda t, inv: run(t, [0], inv), world, group)
+    def backward_impl(g):
+        g0 = new_like([n0, s1, n2])
+        run_fft(g, g0, [0], True, 1.0)                           # conj o fft o conj along axis 0
+        recv = _exchange_arrays(g0, world, group)              # block q: [s0, s1 (chunk q), n2]
+        # unpack: [P, s0, s1, n2] -> [s0, P*s1 = n1, n2]
+        unpacked = copy(_strided_view(recv, [s0, world, s1, n2], [s1 * n2, s0 * s1 * n2, n2, 1]))
+        flat = _strided_view(unpacked, [s0, n1, n2], [n1 * n2, n2, 1])
+        dx = new_like([s0, n1, n2])
+        run_fft(flat, dx, [1, 2], True, 1.0)
+        return dx
+
+    def call(curr, args):
+        res = forward_impl(args[0])
+        curr.buf = res.buf
+
+    def vjp(primals, grad, out):
+        from .functional._utils import contiguous
+        g = contiguous(grad)
+        if not g.is_complex():
+            raise ValueError("fftn_slab: the incoming gradient must be complex")
+        return [backward_impl(g)]
+    return op_array(ArrayShape([n0, s1, n2]), [x_local], "fftn_slab", call, vjp=vjp, is_complex_p=True)
