@@ -101,6 +101,8 @@ SIGNATURES = {
     "endia_b200_adam_step_multi": (C.c_int, [_i32, C.POINTER(_vp), C.POINTER(_vp), C.POINTER(_vp),
                                              C.POINTER(_vp), C.POINTER(_i64), _f32, _f32, _f32,
                                              _f32, _f32, _f32, _vp]),
+    "endia_b200_mlp_small_step": (C.c_int, [_i32, C.POINTER(_i32), _i32, _i32, _vp, _vp] + [C.POINTER(_vp)] * 8 +
+                                  [_vp, _i32, _f32, _f32, _f32, _f32, _f32, _vp]),
     "endia_b200_fft_scratch_bytes": (_sz, [_TP, C.POINTER(_i32), _i32]),
     "endia_b200_fft_c2c": (C.c_int, [_TP, _TP, C.POINTER(_i32), _i32, C.c_int, _f32, _vp, _vp]),
 }

@@ -1,0 +1,238 @@
+// Whole training step of a small MLP in ONE launch of ONE CTA: forward, MSE loss, backward and
+// the Adam update, with every activation held in shared memory. For networks as small as the
+// reference's own benchmark (widths <= 64, batch of a few hundred: endia/nn/modules/_mlp.mojo:47-53,
+// benchmarks/mlp_benchmarks/mlp_imp.mojo:47-75) the step is bound by launch latency, not by
+// arithmetic, so the ~60 separate op launches of the eager path are replaced by one.
+// Arithmetic follows the op chain of the reference: pred = act(a @ W + b) per layer
+// (_mlp.mojo:50-52), loss = sum((p-t)^2)/size (loss_ops/mse_op.mojo:18-20), the VJPs of
+// matmul/add/relu/tanh/sigmoid (matmul_op.mojo:278-284, expand_op.mojo:121-126, relu_op.mojo:95,
+// tanh_op.mojo:92, sigmoid_op.mojo:98) and Adam (optim/adam.mojo:47-65). Sums run in a fixed order.
+#include "common.cuh"
+
+namespace eb {
+
+constexpr int SM_MAX_LAYERS = 8;
+constexpr int SM_THREADS = 512;
+
+struct SmallMlpArgs {
+  int n_layers, batch, act;
+  int dims[SM_MAX_LAYERS + 1];
+  const float *x, *y;
+  float *W[SM_MAX_LAYERS], *b[SM_MAX_LAYERS];
+  float *gW[SM_MAX_LAYERS], *gb[SM_MAX_LAYERS];
+  float *mW[SM_MAX_LAYERS], *vW[SM_MAX_LAYERS], *mb[SM_MAX_LAYERS], *vb[SM_MAX_LAYERS];
+  float *loss;
+  int do_adam;
+  float lr, b1, b2, eps, omb1, omb2, c1, c2;
+  int act_off[SM_MAX_LAYERS + 2];  // float offsets of the activations in shared memory
+  int d_off[2], w_off;             // two gradient buffers and the weight staging buffer
+};
+
+__device__ __forceinline__ float small_act(int act, float v) {
+  if (act == ENDIA_B200_ACT_RELU) return fmaxf(v, 0.f);
+  if (act == ENDIA_B200_ACT_TANH) return tanhf(v);
+  if (act == ENDIA_B200_ACT_SIGMOID) return 1.f / (1.f + expf(-v));
+  return v;
+}
+__device__ __forceinline__ float small_dact(int act, float a) {
+  if (act == ENDIA_B200_ACT_RELU) return a > 0.f ? 1.f : 0.f;
+  if (act == ENDIA_B200_ACT_TANH) return 1.f - a * a;
+  if (act == ENDIA_B200_ACT_SIGMOID) return a * (1.f - a);
+  return 1.f;
+}
+__device__ __forceinline__ void small_adam(const SmallMlpArgs &a, float &p, float g, float &m, float &v) {
+  m = a.b1 * m + a.omb1 * g;
+  v = a.b2 * v + (a.omb2 * g) * g;
+  p = p - (a.lr * (m / a.c1)) / (sqrtf(v / a.c2) + a.eps);
+}
+
+__global__ void __launch_bounds__(SM_THREADS, 1) mlp_small_step_kernel(const __grid_constant__ SmallMlpArgs a) {
+  extern __shared__ float sm[];
+  __shared__ float red[SM_THREADS / 32];
+  const int tid = threadIdx.x, B = a.batch, L = a.n_layers;
+  float *Ws = sm + a.w_off;
+  // ---- forward
+  for (int i = tid; i < B * a.dims[0]; i += SM_THREADS) sm[a.act_off[0] + i] = a.x[i];
+  for (int l = 0; l < L; ++l) {
+    const int K = a.dims[l], N = a.dims[l + 1];
+    for (int i = tid; i < K * N; i += SM_THREADS) Ws[i] = a.W[l][i];
+    __syncthreads();
+    const float *in = sm + a.act_off[l];
+    float *out = sm + a.act_off[l + 1];
+    const int act = l < L - 1 ? a.act : ENDIA_B200_ACT_NONE;
+    if ((N & 3) == 0) {
+      // four adjacent outputs per thread: one broadcast read of the input and one 128-bit read
+      // of the weights feed four FMAs
+      const int N4 = N >> 2;
+      for (int i = tid; i < B * N4; i += SM_THREADS) {
+        const int bi = i / N4, n = (i - bi * N4) * 4;
+        float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int k = 0; k < K; ++k) {
+          const float x = in[bi * K + k];
+          const float4 w = *reinterpret_cast<const float4 *>(Ws + k * N + n);
+          s.x = fmaf(x, w.x, s.x); s.y = fmaf(x, w.y, s.y); s.z = fmaf(x, w.z, s.z); s.w = fmaf(x, w.w, s.w);
+        }
+        const float4 bb = *reinterpret_cast<const float4 *>(a.b[l] + n);
+        float4 o;
+        o.x = small_act(act, s.x + bb.x); o.y = small_act(act, s.y + bb.y);
+        o.z = small_act(act, s.z + bb.z); o.w = small_act(act, s.w + bb.w);
+        *reinterpret_cast<float4 *>(out + bi * N + n) = o;
+      }
+    } else {
+      for (int i = tid; i < B * N; i += SM_THREADS) {
+        const int bi = i / N, n = i - bi * N;
+        float s = 0.f;
+        for (int k = 0; k < K; ++k) s = fmaf(in[bi * K + k], Ws[k * N + n], s);
+        out[i] = small_act(act, s + a.b[l][n]);
+      }
+    }
+    __syncthreads();
+  }
+  // ---- loss and its gradient w.r.t. the prediction
+  const int NL = a.dims[L], total = B * NL;
+  const float inv = 1.f / (float)total;
+  float *dcur = sm + a.d_off[0], *dnext = sm + a.d_off[1];
+  float part = 0.f;
+  for (int i = tid; i < total; i += SM_THREADS) {
+    const float d = sm[a.act_off[L] + i] - a.y[i];
+    part += d * d;
+    dcur[i] = d * (inv + inv);
+  }
+  for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+  if ((tid & 31) == 0) red[tid >> 5] = part;
+  __syncthreads();
+  if (tid == 0) {
+    float s = 0.f;
+    for (int w = 0; w < SM_THREADS / 32; ++w) s += red[w];
+    a.loss[0] = s * inv;
+  }
+  // ---- backward, last layer first
+  for (int l = L - 1; l >= 0; --l) {
+    const int K = a.dims[l], N = a.dims[l + 1];
+    const float *in = sm + a.act_off[l], *outp = sm + a.act_off[l + 1];
+    const int act = l < L - 1 ? a.act : ENDIA_B200_ACT_NONE;
+    for (int i = tid; i < K * N; i += SM_THREADS) Ws[i] = a.W[l][i];
+    if (act != ENDIA_B200_ACT_NONE)
+      for (int i = tid; i < B * N; i += SM_THREADS) dcur[i] *= small_dact(act, outp[i]);
+    __syncthreads();
+    // gradient w.r.t. the layer input, with the weights as they were in the forward pass
+    if (l > 0) {
+      if ((N & 3) == 0) {
+        for (int i = tid; i < B * K; i += SM_THREADS) {
+          const int bi = i / K, k = i - bi * K;
+          float s = 0.f;
+          for (int n = 0; n < N; n += 4) {
+            const float4 d = *reinterpret_cast<const float4 *>(dcur + bi * N + n);
+            const float4 w = *reinterpret_cast<const float4 *>(Ws + k * N + n);
+            s = fmaf(d.x, w.x, s); s = fmaf(d.y, w.y, s); s = fmaf(d.z, w.z, s); s = fmaf(d.w, w.w, s);
+          }
+          dnext[i] = s;
+        }
+      } else {
+        for (int i = tid; i < B * K; i += SM_THREADS) {
+          const int bi = i / K, k = i - bi * K;
+          float s = 0.f;
+          for (int n = 0; n < N; ++n) s = fmaf(dcur[bi * N + n], Ws[k * N + n], s);
+          dnext[i] = s;
+        }
+      }
+    }
+    // weight and bias gradients, then Adam on both
+    if ((N & 3) == 0) {
+      const int N4 = N >> 2;
+      for (int i = tid; i < K * N4; i += SM_THREADS) {
+        const int k = i / N4, n = (i - k * N4) * 4;
+        float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int bi = 0; bi < B; ++bi) {
+          const float x = in[bi * K + k];
+          const float4 d = *reinterpret_cast<const float4 *>(dcur + bi * N + n);
+          s.x = fmaf(x, d.x, s.x); s.y = fmaf(x, d.y, s.y); s.z = fmaf(x, d.z, s.z); s.w = fmaf(x, d.w, s.w);
+        }
+        const float g[4] = {s.x, s.y, s.z, s.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int idx = k * N + n + j;
+          a.gW[l][idx] = g[j];
+          if (a.do_adam) small_adam(a, a.W[l][idx], g[j], a.mW[l][idx], a.vW[l][idx]);
+        }
+      }
+    } else {
+      for (int i = tid; i < K * N; i += SM_THREADS) {
+        const int k = i / N, n = i - k * N;
+        float s = 0.f;
+        for (int bi = 0; bi < B; ++bi) s = fmaf(in[bi * K + k], dcur[bi * N + n], s);
+        a.gW[l][i] = s;
+        if (a.do_adam) small_adam(a, a.W[l][i], s, a.mW[l][i], a.vW[l][i]);
+      }
+    }
+    for (int n = tid; n < N; n += SM_THREADS) {
+      float s = 0.f;
+      for (int bi = 0; bi < B; ++bi) s += dcur[bi * N + n];
+      a.gb[l][n] = s;
+      if (a.do_adam) small_adam(a, a.b[l][n], s, a.mb[l][n], a.vb[l][n]);
+    }
+    __syncthreads();
+    float *t = dcur; dcur = dnext; dnext = t;
+  }
+}
+
+}  // namespace eb
+
+using namespace eb;
+
+extern "C" int endia_b200_mlp_small_step(int32_t n_layers, const int32_t *dims, int32_t batch, int32_t act,
+                                         const float *x, const float *y, float *const *W, float *const *b,
+                                         float *const *gW, float *const *gb, float *const *mW,
+                                         float *const *vW, float *const *mb, float *const *vb, float *loss,
+                                         int32_t do_adam, float lr, float beta1, float beta2, float eps,
+                                         float t, void *stream) {
+  int st = require_device();
+  if (st) return st;
+  EB_REQUIRE(n_layers >= 1 && n_layers <= SM_MAX_LAYERS, ENDIA_B200_ELIMIT,
+             "mlp_small_step: 1..%d layers are supported, got %d", SM_MAX_LAYERS, n_layers);
+  EB_REQUIRE(dims && x && y && W && b && gW && gb && loss, ENDIA_B200_EINVAL, "mlp_small_step: NULL argument");
+  EB_REQUIRE(!do_adam || (mW && vW && mb && vb), ENDIA_B200_EINVAL, "mlp_small_step: Adam state is NULL");
+  EB_REQUIRE(batch >= 1 && act >= 0 && act <= ENDIA_B200_ACT_SIGMOID, ENDIA_B200_EINVAL,
+             "mlp_small_step: bad batch or activation");
+  EB_REQUIRE(!do_adam || t >= 1.f, ENDIA_B200_EINVAL, "mlp_small_step: step count t starts at 1");
+  SmallMlpArgs a{};
+  a.n_layers = n_layers; a.batch = batch; a.act = act; a.x = x; a.y = y; a.loss = loss;
+  int off = 0, dmax = 0, wmax = 0;
+  for (int l = 0; l <= n_layers; ++l) {
+    EB_REQUIRE(dims[l] >= 1 && dims[l] <= 256, ENDIA_B200_ELIMIT, "mlp_small_step: width %d outside [1, 256]", dims[l]);
+    a.dims[l] = dims[l];
+    a.act_off[l] = off;
+    off += (batch * dims[l] + 3) / 4 * 4;
+    if (l > 0 && dims[l] > dmax) dmax = dims[l];
+    if (l > 0 && dims[l - 1] > dmax) dmax = dims[l - 1];
+    if (l > 0 && dims[l - 1] * dims[l] > wmax) wmax = dims[l - 1] * dims[l];
+  }
+  a.d_off[0] = off; off += (batch * dmax + 3) / 4 * 4;
+  a.d_off[1] = off; off += (batch * dmax + 3) / 4 * 4;
+  a.w_off = off; off += wmax;
+  const size_t smem = sizeof(float) * (size_t)off;
+  EB_REQUIRE(smem <= 200 * 1024, ENDIA_B200_ELIMIT,
+             "mlp_small_step: the network's activations need %zu bytes of shared memory (limit %d); "
+             "use the layer-by-layer path", smem, 200 * 1024);
+  for (int l = 0; l < n_layers; ++l) {
+    EB_REQUIRE(W[l] && b[l] && gW[l] && gb[l], ENDIA_B200_EINVAL, "mlp_small_step: NULL pointer for layer %d", l);
+    a.W[l] = W[l]; a.b[l] = b[l]; a.gW[l] = gW[l]; a.gb[l] = gb[l];
+    if (do_adam) {
+      EB_REQUIRE(mW[l] && vW[l] && mb[l] && vb[l], ENDIA_B200_EINVAL, "mlp_small_step: NULL Adam state for layer %d", l);
+      a.mW[l] = mW[l]; a.vW[l] = vW[l]; a.mb[l] = mb[l]; a.vb[l] = vb[l];
+    }
+  }
+  a.do_adam = do_adam;
+  a.lr = lr; a.b1 = beta1; a.b2 = beta2; a.eps = eps;
+  a.omb1 = 1.f - beta1; a.omb2 = 1.f - beta2;
+  a.c1 = do_adam ? 1.f - powf(beta1, t) : 1.f;
+  a.c2 = do_adam ? 1.f - powf(beta2, t) : 1.f;
+  static size_t attr_bytes = 0;
+  if (smem > attr_bytes) {
+    EB_CUDA(cudaFuncSetAttribute(mlp_small_step_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    attr_bytes = 200 * 1024;
+  }
+  mlp_small_step_kernel<<<1, SM_THREADS, smem, as_stream(stream)>>>(a);
+  EB_LAUNCH_CHECK();
+  return ENDIA_B200_OK;
+}

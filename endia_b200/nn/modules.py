@@ -149,3 +149,85 @@ def mlp(args, activation="relu"):
         last = i == num_layers - 1
         pred = linear(pred, args[2 * i + 2], args[2 * i + 3], None if last else activation)
     return pred
+
+
+class SmallMLPStep:
+    """Prepared single-launch training step for a small MLP (see fused_train_step): gradient
+    buffers, the loss scalar and the argument arrays are built once, so that a step costs one
+    C-ABI call on the host."""
+
+    def __init__(self, weights, biases, optimizer=None, activation="relu"):
+        import ctypes as C
+        self.weights, self.biases, self.optimizer = list(weights), list(biases), optimizer
+        L = self.L = len(self.weights)
+        self.dims = [self.weights[0].shape()[0]] + [w.shape()[1] for w in self.weights]
+        for p in self.weights + self.biases:
+            if not p.is_contiguous() or p.is_complex():
+                raise _lib.EndiaError(_lib.EINVAL, "fused_train_step: parameters must be contiguous and real")
+        self.gW = [Array(ArrayShape(w.shape())) for w in self.weights]
+        self.gb = [Array(ArrayShape([1, b.shape()[0]])) for b in self.biases]
+        self.loss = Array(ArrayShape([1]))
+        for g in self.gW + self.gb + [self.loss]:
+            setup_shape_and_data(g)
+
+        def ptrs(arrs):
+            return (C.c_void_p * L)(*[a.data_ptr() for a in arrs])
+        self.c_dims = (C.c_int32 * (L + 1))(*self.dims)
+        self.p_W, self.p_b, self.p_gW, self.p_gb = ptrs(self.weights), ptrs(self.biases), ptrs(self.gW), ptrs(self.gb)
+        self.act = _ACTS[activation]
+        if optimizer is not None:
+            if len(optimizer.params) != 2 * L or any(
+                    optimizer.params[2 * i] is not self.weights[i] or optimizer.params[2 * i + 1] is not self.biases[i]
+                    for i in range(L)):
+                raise _lib.EndiaError(_lib.EINVAL, "fused_train_step: optimizer must hold [W0, b0, W1, b1, ...]")
+            self.p_mW, self.p_vW = ptrs(optimizer.m[0::2]), ptrs(optimizer.v[0::2])
+            self.p_mb, self.p_vb = ptrs(optimizer.m[1::2]), ptrs(optimizer.v[1::2])
+        else:
+            self.p_mW = self.p_vW = self.p_mb = self.p_vb = None
+        self._fn = _lib.lib.endia_b200_mlp_small_step
+
+    def __call__(self, x, target):
+        batch = x.shape()[0]
+        if x.shape() != [batch, self.dims[0]] or target.shape() != [batch, self.dims[-1]] or \
+                not x.is_contiguous() or not target.is_contiguous():
+            raise _lib.EndiaError(_lib.ESHAPE, "fused_train_step: x / target do not match the network")
+        opt = self.optimizer
+        if opt is not None:
+            st = self._fn(self.L, self.c_dims, batch, self.act, x.data_ptr(), target.data_ptr(), self.p_W, self.p_b,
+                          self.p_gW, self.p_gb, self.p_mW, self.p_vW, self.p_mb, self.p_vb, self.loss.data_ptr(), 1,
+                          opt.lr, opt.beta1, opt.beta2, opt.eps, opt.t, stream())
+        else:
+            st = self._fn(self.L, self.c_dims, batch, self.act, x.data_ptr(), target.data_ptr(), self.p_W, self.p_b,
+                          self.p_gW, self.p_gb, None, None, None, None, self.loss.data_ptr(), 0,
+                          0.0, 0.0, 0.0, 0.0, 1.0, stream())
+        _lib.check(st)
+        for w, b, g1, g2 in zip(self.weights, self.biases, self.gW, self.gb):
+            w.grad_node = g1
+            b.grad_node = g2
+        if opt is not None:
+            if opt.t == 1.0:   # bias moments take the gradient's (1, N) shape, as Adam.step does
+                for i in range(self.L):
+                    opt.m[2 * i + 1].array_shape_ = ArrayShape([1, self.dims[i + 1]])
+                    opt.v[2 * i + 1].array_shape_ = ArrayShape([1, self.dims[i + 1]])
+            opt.t += 1.0
+        return self.loss
+
+
+def fused_train_step(weights, biases, x, target, optimizer=None, activation="relu"):
+    """One training step of a small MLP in a single kernel launch: forward, mse loss, backward and
+    (when `optimizer` is an optim.Adam over exactly these parameters, weights and biases
+    interleaved as MLP.params() returns them) the Adam update. Equivalent to
+
+        loss = mse(mlp(x), target); loss.backward(); optimizer.step()
+
+    for networks that fit one CTA's shared memory (EndiaError with status ELIMIT otherwise; use
+    the layer-by-layer path then). Returns the loss (shape [1]; the same array is rewritten by the
+    next call); every parameter's gradient is stored as by backward() (bias gradients with shape
+    (1, N))."""
+    key = (tuple(id(w) for w in weights), tuple(id(b) for b in biases), id(optimizer), activation)
+    holder = weights[0]
+    cached = getattr(holder, "_small_step", None)
+    if cached is None or cached[0] != key:
+        cached = (key, SmallMLPStep(weights, biases, optimizer, activation))
+        holder._small_step = cached
+    return cached[1](x, target)

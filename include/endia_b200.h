@@ -260,6 +260,24 @@ int endia_b200_adam_step_multi(int32_t n_tensors, float *const *params, const fl
                                float beta1, float beta2, float eps, float t, float grad_scale,
                                void *stream);
 
+/* One whole training step of a small MLP (forward, MSE loss, backward, optional Adam update) in
+ * a single launch of one CTA, every activation in shared memory: for networks whose step is bound
+ * by launch latency (the reference's own benchmark sizes). x is [batch, dims[0]], y is
+ * [batch, dims[n_layers]], W[l] is [dims[l], dims[l+1]] row-major, b[l] is [dims[l+1]]; `act` is
+ * applied to all but the last layer. Writes loss[0], the gradients gW[l] / gb[l], and, with
+ * do_adam, updates W, b and the moments in place (t as in endia_b200_adam_step_multi). Limits:
+ * at most 8 layers, widths <= 256, and batch * (sum of widths + 2 * max width) + max weight matrix
+ * within 200 KiB of floats (ENDIA_B200_ELIMIT otherwise).
+ * Replaces, for such sizes, the op sequence of MLP.forward + mse + backward + Adam.step
+ * (endia/nn/modules/_mlp.mojo:47-53, loss_ops/mse_op.mojo:18-20, autograd/functional.mojo:26-67,
+ * optim/adam.mojo:47-65; the loop of benchmarks/mlp_benchmarks/mlp_imp.mojo:47-75). */
+int endia_b200_mlp_small_step(int32_t n_layers, const int32_t *dims, int32_t batch, int32_t act,
+                              const float *x, const float *y, float *const *W, float *const *b,
+                              float *const *gW, float *const *gb, float *const *mW,
+                              float *const *vW, float *const *mb, float *const *vb, float *loss,
+                              int32_t do_adam, float lr, float beta1, float beta2, float eps,
+                              float t, void *stream);
+
 /* --------------------------------------------------------------------- FFT ---- */
 
 /* Complex-to-complex FFT over the listed dims of `in` (contiguous or strided, complex) into

@@ -212,3 +212,33 @@ def test_c2_full_size_gemm_identities(nd):
         assert abs(y[i, j] - x[i].astype(np.float64) @ w[:, j]) <= 1e-4 * np.linalg.norm(x[i]) * np.linalg.norm(w[:, j])
     for (i, j) in [(0, 0), (K - 1, N - 1), (1234, 77)]:
         assert abs(dw[i, j] - x[:, i].astype(np.float64) @ g[:, j]) <= 1e-4 * np.linalg.norm(x[:, i]) * np.linalg.norm(g[:, j])
+
+
+@pytest.mark.parametrize("act,dims,batch", [("relu", [1, 32, 32, 32, 1], 128), ("tanh", [7, 64, 33, 5], 96),
+                                            ("sigmoid", [3, 16, 2], 17)])
+def test_fused_small_mlp_step_matches_oracle(nd, oracle, act, dims, batch):
+    """The single-launch whole-step kernel (c1 and other small networks) over three steps."""
+    Ws, bs, x, y = make_mlp_inputs(dims, batch, 0, x_dist="uniform" if dims[0] == 1 else "normal")
+    if dims[0] == 1:
+        y = np.sin(np.float32(15) * x).astype(np.float32)
+    o = train_step(oracle, fwd_unfused(act), Ws, bs, x, y, steps=3)
+    W = [nd.Array(w.copy(), requires_grad=True) for w in Ws]
+    B = [nd.Array(b.copy(), requires_grad=True) for b in bs]
+    params = [p for wb in zip(W, B) for p in wb]
+    opt = nd.optim.Adam(params, lr=1e-3)
+    X, Y = nd.Array(x), nd.Array(y)
+    for _ in range(3):
+        loss = nd.nn.fused_train_step(W, B, X, Y, opt, activation=act)
+    g = {"loss": loss.to_numpy(), "loss_shape": loss.shape(), "grads": [p.grad().to_numpy() for p in params],
+         "grad_shapes": [p.grad().shape() for p in params], "params": [p.to_numpy() for p in params],
+         "m": [m.to_numpy() for m in opt.m], "v": [v.to_numpy() for v in opt.v],
+         "m_shapes": [m.shape() for m in opt.m], "t": float(opt.t)}
+    compare_steps(g, o)
+
+
+def test_fused_small_mlp_step_rejects_large_networks(nd):
+    W = [nd.Array([512, 16])]
+    B = [nd.Array([16])]
+    with pytest.raises(nd.EndiaError) as ei:
+        nd.nn.fused_train_step(W, B, nd.Array([8, 512]), nd.Array([8, 16]))
+    assert ei.value.status == -8
