@@ -234,6 +234,81 @@ class FFTStep:
         return dx
 
 
+
+class SmallStep:
+    """c1: MLP 1-32-32-32-1 (ReLU, bias), batch 128, x ~ U[0,1), y = sin(15x), MSE + Adam: the whole
+    step is one kernel launch (nn.fused_train_step)."""
+    dims, batch = [1, 32, 32, 32, 1], 128
+
+    def __init__(self, nd, torch):
+        self.nd, self.torch = nd, torch
+        r = np.random.Generator(np.random.PCG64(0))
+        Ws, bs = [], []
+        for i in range(4):
+            lim = np.sqrt(6.0 / self.dims[i])
+            Ws.append(r.uniform(-lim, lim, (self.dims[i], self.dims[i + 1])).astype(np.float32))
+            bs.append(r.uniform(-lim, lim, (self.dims[i + 1],)).astype(np.float32))
+        x = r.uniform(0, 1, (self.batch, 1)).astype(np.float32)
+        y = np.sin(np.float32(15) * x).astype(np.float32)
+        self.x_host, self.y_host = torch.from_numpy(x).pin_memory(), torch.from_numpy(y).pin_memory()
+        self.W = [nd.Array(w, requires_grad=True) for w in Ws]
+        self.B = [nd.Array(b, requires_grad=True) for b in bs]
+        self.params = [p for wb in zip(self.W, self.B) for p in wb]
+        self.X, self.Y = nd.Array(x), nd.Array(y)
+        self.opt = nd.optim.Adam(self.params, lr=1e-3)
+        self.loss_host = torch.empty(1, dtype=torch.float32).pin_memory()
+        self.samples = self.batch
+        self.flops = 1.614e6
+
+    def step(self, host_io=False):
+        from endia_b200.dist import flat_tensor
+        if host_io:
+            flat_tensor(self.X).copy_(self.x_host.reshape(-1), non_blocking=True)
+            flat_tensor(self.Y).copy_(self.y_host.reshape(-1), non_blocking=True)
+        loss = self.nd.nn.fused_train_step(self.W, self.B, self.X, self.Y, self.opt, activation="relu")
+        if host_io:
+            self.loss_host.copy_(flat_tensor(loss), non_blocking=True)
+            self.torch.cuda.current_stream().synchronize()
+        return loss
+
+
+class PenaltyStep:
+    """c3: MLP 256-1024-1024-1 (tanh), batch 4096; loss = mean(f) + 0.1 * mean |df/dx|^2 with
+    create_graph=True, then gradients w.r.t. the parameters (double backward)."""
+    dims, batch = [256, 1024, 1024, 1], 4096
+
+    def __init__(self, nd, torch):
+        self.nd, self.torch = nd, torch
+        r = np.random.Generator(np.random.PCG64(0))
+        Ws = [r.uniform(-np.sqrt(6.0 / self.dims[i]), np.sqrt(6.0 / self.dims[i]),
+                        (self.dims[i], self.dims[i + 1])).astype(np.float32) for i in range(3)]
+        x = r.standard_normal((self.batch, self.dims[0])).astype(np.float32)
+        self.x_host = torch.from_numpy(x).pin_memory()
+        self.W = [nd.Array(w, requires_grad=True) for w in Ws]
+        self.B = [nd.Array([self.dims[i + 1]], requires_grad=True) for i in range(3)]
+        self.X = nd.Array(x, requires_grad=True)
+        self.loss_host = torch.empty(1, dtype=torch.float32).pin_memory()
+        self.samples = self.batch
+        self.flops = 62.32e9
+
+    def step(self, host_io=False):
+        nd = self.nd
+        from endia_b200.dist import flat_tensor
+        if host_io:
+            flat_tensor(self.X).copy_(self.x_host.reshape(-1), non_blocking=True)
+        args = [self.X, None]
+        for w, b in zip(self.W, self.B):
+            args += [w, b]
+        f = nd.nn.mlp(args, activation="tanh")
+        gx = nd.grad(outs=[nd.sum(f)], inputs=[self.X], create_graph=True)[0]
+        loss = nd.mean(f, [0, 1]) + 0.1 * (nd.sum(gx * gx) / float(self.batch))
+        grads = nd.grad(outs=[loss], inputs=self.W + self.B)
+        if host_io:
+            self.loss_host.copy_(flat_tensor(loss), non_blocking=True)
+            self.torch.cuda.current_stream().synchronize()
+        return grads
+
+
 def fft_cpu_baseline(workload):
     """Endia's CPU algorithm for the FFT configs (oracle port: float64 radix-2 with per-axis
     gathers, rows spread over the host threads as the reference's parallelize does), forward + VJP,
@@ -328,8 +403,9 @@ def main():
     ap.add_argument("--cpu-rows", type=int, default=48)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--gemm", default="auto", choices=["auto", "ffma", "3xtf32"])
-    ap.add_argument("--workload", default="c2", choices=["c2", "c4", "c5"],
-                    help="c2 (default, the headline): MLP train step; c4 / c5: FFT forward + VJP")
+    ap.add_argument("--workload", default="c2", choices=["c1", "c2", "c3", "c4", "c5"],
+                    help="c2 (default, the headline): MLP train step; c1: small MLP, single-launch step; "
+                         "c3: gradient-penalty (second-order) step; c4 / c5: FFT forward + VJP")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
@@ -345,8 +421,16 @@ def main():
     rank, world = ndist.init_process_group()
     nd._array.device()
     nd.config.gemm_algo = {"auto": _lib.GEMM_AUTO, "ffma": _lib.GEMM_FFMA, "3xtf32": _lib.GEMM_3XTF32}[args.gemm]
-    is_fft = args.workload != "c2"
-    work = FFTStep(nd, torch, args.workload, rank, world) if is_fft else TrainStep(nd, torch, rank, world)
+    is_fft = args.workload in ("c4", "c5")
+    is_small = args.workload in ("c1", "c3")
+    if is_fft:
+        work = FFTStep(nd, torch, args.workload, rank, world)
+    elif args.workload == "c1":
+        work = SmallStep(nd, torch)
+    elif args.workload == "c3":
+        work = PenaltyStep(nd, torch)
+    else:
+        work = TrainStep(nd, torch, rank, world)
 
     def barrier():
         if world > 1:
@@ -400,6 +484,28 @@ def main():
         return
 
     pk = peaks()
+    if is_small:
+        ms_step = ms_total / args.steps
+        line = {
+            "metric": METRIC if args.workload == "c1" else "gradient-penalty step samples/s (fwd + double backward)",
+            "value": work.samples / (ms_step / 1000.0), "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "replicas only",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": "%s: MLP %s, batch %d" % (args.workload, "-".join(map(str, work.dims)), work.batch),
+                       "note": "c1 is bound by launch latency (one launch per step); no roofline is quoted for it"
+                               if args.workload == "c1" else "create_graph=True path: every VJP is a composition of ops"},
+            "clocks": {"sm_mhz": clocks["sm_mhz"], "sm_max_mhz": clocks["sm_max_mhz"],
+                       "reasons": clocks["reasons"], "samples": clocks["samples"]},
+            "e2e": {"value": work.samples / (ms_e2e / args.steps / 1000.0), "unit": UNIT,
+                    "h2d_bytes_per_step": int(work.x_host.numel() * 4), "d2h_bytes_per_step": 4},
+            "gpu_launches": int(launches),
+            "roofline": {"bound": "tensor", "achieved": (gemm_fl / (gemm_ms / 1000.0) / 1e12) if gemm_ms > 0 else None,
+                         "peak": pk["bf16_tflops_sustained"] / 6.0, "unit": "TFLOP/s", "frac": None, "traffic": None,
+                         "kernel": "gemm calls (%d, %.1f%% of the step)" % (n_gemm, 100.0 * gemm_ms / ms_total if ms_total else 0.0),
+                         "algorithmic_gflop_per_step": work.flops / 1e9},
+        }
+        print(json.dumps(line))
+        return
     if is_fft:
         ms_step = ms_total / args.steps
         hbm_peak = pk["hbm_gbs"]

@@ -67,6 +67,8 @@ int endia_b200_gemm(int trans_a, int trans_b, int64_t M, int64_t N, int64_t K, c
                (long long)batch);
   }
   int tile_m = 128;
+  if (!use_tc && algo == ENDIA_B200_GEMM_AUTO && skinny_gemm_supported(p, trans_b, batch))
+    return launch_gemm_skinny(p, trans_a, trans_b, s);
   if (use_tc) st = launch_gemm_tc(p, trans_a, trans_b, s);
   else st = launch_gemm_ffma(p, trans_a, trans_b, batch, s);
   if (st) return st;

@@ -20,6 +20,9 @@ struct GemmParams {
   int64_t stride_a, stride_b, stride_c;
   bool vec_a, vec_b, vec_c;  // 16-byte aligned base, leading dimension and batch stride
   EpiParams epi;
+  // split-K: partial[split][M][ld_partial] receives the raw sums of each K range
+  float *partial;
+  int64_t ld_partial;
 };
 
 __device__ __forceinline__ float act_fwd(int act, float v) {
@@ -54,6 +57,11 @@ __device__ __forceinline__ float apply_epilogue(const EpiParams &e, float acc, i
 int launch_gemm_ffma(const GemmParams &p, int trans_a, int trans_b, int64_t batch, cudaStream_t s);
 int launch_colsum_finish(const float *partial, float *out, int64_t N, int tiles, int64_t batch,
                          cudaStream_t s);
+// Degenerate shapes (N <= 8, K <= 8, or M <= 8 with a row-major B): one pass over the large operand.
+bool skinny_gemm_supported(const GemmParams &p, int trans_b, int64_t batch);
+int launch_gemm_skinny(const GemmParams &p, int trans_a, int trans_b, cudaStream_t s);
+// C = epilogue(sum over `splits` slices of p.partial, in order).
+int launch_splitk_finish(const GemmParams &p, int splits, cudaStream_t s);
 // tcgen05 3xTF32 path: true when the shape/alignment is one it handles.
 bool tc_gemm_supported(const GemmParams &p, int trans_a, int trans_b, int64_t batch,
                        bool explicit_request);

@@ -132,7 +132,24 @@ gemm_tc_kernel(const __grid_constant__ TcMaps maps, const GemmParams p, int tile
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tile_m = blockIdx.x % tiles_m, tile_n = blockIdx.x / tiles_m;
   const int m0 = tile_m * TC_BM, n0 = tile_n * BN;
-  const int nkb = (int)((p.K + BK - 1) / BK);
+  // split-K: blockIdx.y takes one contiguous range of k-blocks and writes raw sums to its slice
+  // of p.partial; a second kernel adds the slices in order and applies the epilogue.
+  const int splits = gridDim.y;
+  const int nkb_total = (int)((p.K + BK - 1) / BK);
+  const int kb_per = (nkb_total + splits - 1) / splits;
+  const int kb0 = blockIdx.y * kb_per;
+  int nkb = nkb_total - kb0;
+  nkb = nkb < 0 ? 0 : (nkb > kb_per ? kb_per : nkb);
+  float *Cout = p.C;
+  int64_t ldc = p.ldc;
+  EpiParams epi = p.epi;
+  bool vec_c = p.vec_c;
+  if (splits > 1) {
+    Cout = p.partial + (int64_t)blockIdx.y * p.M * p.ld_partial;
+    ldc = p.ld_partial;
+    epi = EpiParams{1.f, 0.f, nullptr, 0, 0, nullptr, 0, nullptr};
+    vec_c = true;
+  }
   auto full_bar = [&](int s) { return bars + 8u * s; };
   auto empty_bar = [&](int s) { return bars + 8u * (STAGES + s); };
   const uint32_t acc_bar = bars + 8u * (2 * STAGES);
@@ -164,7 +181,7 @@ gemm_tc_kernel(const __grid_constant__ TcMaps maps, const GemmParams p, int tile
         const uint32_t st = smem_base + s * STAGE_BYTES;
         const uint32_t fb = full_bar(s);
         mbar_expect_tx(fb, STAGE_BYTES);
-        const int k0 = kb * BK;
+        const int k0 = (kb0 + kb) * BK;
         if constexpr (A_MN) {
 #pragma unroll
           for (int j = 0; j < TC_BM / 32; ++j) {
@@ -247,29 +264,29 @@ gemm_tc_kernel(const __grid_constant__ TcMaps maps, const GemmParams p, int tile
         for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) + __uint_as_float(r2[j]));
         const int64_t nb = (int64_t)n0 + c * 32;
         if (m < p.M && nb < p.N) {
-          float *crow = p.C + m * p.ldc + nb;
-          if (p.vec_c && nb + 32 <= p.N) {
+          float *crow = Cout + m * ldc + nb;
+          if (vec_c && nb + 32 <= p.N) {
 #pragma unroll
             for (int j = 0; j < 32; j += 4) {
               float4 o;
-              o.x = apply_epilogue(p.epi, __uint_as_float(r[j + 0]), m, nb + j + 0, crow + j + 0);
-              o.y = apply_epilogue(p.epi, __uint_as_float(r[j + 1]), m, nb + j + 1, crow + j + 1);
-              o.z = apply_epilogue(p.epi, __uint_as_float(r[j + 2]), m, nb + j + 2, crow + j + 2);
-              o.w = apply_epilogue(p.epi, __uint_as_float(r[j + 3]), m, nb + j + 3, crow + j + 3);
+              o.x = apply_epilogue(epi, __uint_as_float(r[j + 0]), m, nb + j + 0, crow + j + 0);
+              o.y = apply_epilogue(epi, __uint_as_float(r[j + 1]), m, nb + j + 1, crow + j + 1);
+              o.z = apply_epilogue(epi, __uint_as_float(r[j + 2]), m, nb + j + 2, crow + j + 2);
+              o.w = apply_epilogue(epi, __uint_as_float(r[j + 3]), m, nb + j + 3, crow + j + 3);
               *reinterpret_cast<float4 *>(crow + j) = o;
             }
           } else {
 #pragma unroll
             for (int j = 0; j < 32; ++j)
               if (nb + j < p.N)
-                crow[j] = apply_epilogue(p.epi, __uint_as_float(r[j]), m, nb + j, crow + j);
+                crow[j] = apply_epilogue(epi, __uint_as_float(r[j]), m, nb + j, crow + j);
           }
         }
       }
     } else if (ok && m < p.M) {
       // K == 0: the product is empty, the epilogue applies to zeros.
       for (int64_t n = n0; n < n0 + BN && n < p.N; ++n)
-        p.C[m * p.ldc + n] = apply_epilogue(p.epi, 0.f, m, n, p.C + m * p.ldc + n);
+        Cout[m * ldc + n] = apply_epilogue(epi, 0.f, m, n, Cout + m * ldc + n);
     }
   }
   tc_fence_before();
@@ -472,6 +489,24 @@ gemm_tc2_kernel(const __grid_constant__ TcMaps maps, const GemmParams p, int pai
   }
 }
 
+// Second stage of split-K: C = epilogue(sum over the splits, in order).
+__global__ void __launch_bounds__(256) splitk_finish_kernel(GemmParams p, int splits) {
+  const int64_t total = p.M * p.N;
+  const int64_t step = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += step) {
+    const int64_t m = i / p.N, n = i - m * p.N;
+    float v = 0.f;
+    for (int s = 0; s < splits; ++s) v += p.partial[((int64_t)s * p.M + m) * p.ld_partial + n];
+    p.C[m * p.ldc + n] = apply_epilogue(p.epi, v, m, n, p.C + m * p.ldc + n);
+  }
+}
+
+int launch_splitk_finish(const GemmParams &p, int splits, cudaStream_t s) {
+  splitk_finish_kernel<<<grid_for(p.M * p.N, 256), 256, 0, s>>>(p, splits);
+  EB_LAUNCH_CHECK();
+  return ENDIA_B200_OK;
+}
+
 // lo = x - hi with hi = x truncated to tf32 (13 low mantissa bits cleared); exact in fp32.
 // Optionally also writes hi. Rows of `cols` floats, leading dimensions ld_in / ld_out.
 __global__ void __launch_bounds__(256)
@@ -554,10 +589,10 @@ bool tc_gemm_supported(const GemmParams &p, int trans_a, int trans_b, int64_t ba
 
 template <int BN, int BK, int STAGES>
 static int launch_variant(const TcMaps &maps, const GemmParams &p, int trans_a, int trans_b,
-                          cudaStream_t s) {
+                          cudaStream_t s, int splits = 1) {
   constexpr size_t SMEM = (size_t)STAGES * (2 * TC_BM * BK * 4 + 2 * BN * BK * 4) + 1024 + 256;
   const int tiles_m = (int)ceil_div(p.M, TC_BM), tiles_n = (int)ceil_div(p.N, BN);
-  const dim3 grid((unsigned)(tiles_m * tiles_n));
+  const dim3 grid((unsigned)(tiles_m * tiles_n), (unsigned)splits);
 #define EB_TC_LAUNCH(AM, BM_)                                                                     \
   do {                                                                                            \
     auto kern = gemm_tc_kernel<BN, BK, STAGES, AM, BM_>;                                              \
@@ -620,7 +655,21 @@ int launch_gemm_tc(const GemmParams &p, int trans_a, int trans_b, cudaStream_t s
   tf32_split_kernel<<<grid_for(b_rows * (b_ld / 4), 256), 256, 0, s>>>(p.B, b_lo, nullptr, b_rows,
                                                                        b_ld / 4, p.ldb, b_ld);
   EB_LAUNCH_CHECK();
-  const int bn = p.N >= 256 ? 256 : 128;
+  int bn = p.N >= 256 ? 256 : 128;
+  // Few output tiles and a long reduction: split K over CTAs (128 x 128 tiles) so that the machine
+  // is filled; the partial sums go through a work buffer and are added in a fixed order.
+  int splits = 1;
+  {
+    const int64_t ctas_wide = 2 * ceil_div(p.M, 256) * ceil_div(p.N, 256);
+    const int64_t tiles = ceil_div(p.M, 128) * ceil_div(p.N, 128);
+    const int64_t nkb32 = ceil_div(p.K, 32);
+    if ((bn == 128 ? tiles : ctas_wide) < 100 && nkb32 >= 16) {
+      int64_t sp = 148 / tiles;
+      if (sp > nkb32 / 8) sp = nkb32 / 8;
+      if (sp > 16) sp = 16;
+      if (sp >= 2) { splits = (int)sp; bn = 128; }
+    }
+  }
   // k-block depth: 16 floats per stage with a 4- or 6-deep ring hides the tile-load latency
   // better than 32 floats with 2 or 3 stages in the same shared memory.
   static const int bk = []() {
@@ -632,6 +681,13 @@ int launch_gemm_tc(const GemmParams &p, int trans_a, int trans_b, cudaStream_t s
   // K-major operand: box [rows of the tile][bk k]; MN-major operand: box [bk k][32 rows].
   const int a_bi = trans_a ? 32 : bk, a_bo = trans_a ? bk : TC_BM;
   const bool pair = bn == 256 && bk == 32 && pair_mode();
+  GemmParams q = p;
+  float *partial = nullptr;
+  if (splits > 1) {
+    q.ld_partial = (p.N + 3) / 4 * 4;
+    EB_CUDA(cudaMallocAsync(&partial, sizeof(float) * (size_t)splits * p.M * q.ld_partial, s));
+    q.partial = partial;
+  }
   const int b_bi = trans_b ? bk : 32, b_bo = trans_b ? (pair ? 128 : bn) : bk;
   if ((st = make_map(&maps.a_hi, p.A, a_cols, a_rows, p.lda, a_bi, a_bo, trans_a != 0))) return st;
   if ((st = make_map(&maps.a_lo, a_lo, a_cols, a_rows, a_ld, a_bi, a_bo, trans_a != 0))) return st;
@@ -640,8 +696,12 @@ int launch_gemm_tc(const GemmParams &p, int trans_a, int trans_b, cudaStream_t s
   if (pair) st = launch_pair(maps, p, trans_a, trans_b, s);
   else if (bn == 256 && bk == 16) st = launch_variant<256, 16, 4>(maps, p, trans_a, trans_b, s);
   else if (bn == 256) st = launch_variant<256, 32, 2>(maps, p, trans_a, trans_b, s);
-  else if (bk == 16) st = launch_variant<128, 16, 6>(maps, p, trans_a, trans_b, s);
-  else st = launch_variant<128, 32, 3>(maps, p, trans_a, trans_b, s);
+  else if (bk == 16) st = launch_variant<128, 16, 6>(maps, q, trans_a, trans_b, s, splits);
+  else st = launch_variant<128, 32, 3>(maps, q, trans_a, trans_b, s, splits);
+  if (splits > 1 && st == ENDIA_B200_OK) {
+    st = launch_splitk_finish(q, splits, s);
+    cudaFreeAsync(partial, s);
+  }
   EB_CUDA(cudaFreeAsync(a_lo, s));
   EB_CUDA(cudaFreeAsync(b_lo, s));
   return st;

@@ -32,7 +32,7 @@ def dot_scale(am, bm):
 
 @pytest.mark.parametrize("ta,tb", [(0, 0), (0, 1), (1, 0), (1, 1)])
 @pytest.mark.parametrize("M,N,K", [(128, 128, 32), (256, 256, 64), (384, 512, 256), (200, 328, 100),
-                                   (1024, 1024, 1024), (136, 260, 36)])
+                                   (1024, 1024, 1024), (136, 260, 36), (256, 1024, 4096), (200, 136, 2048)])
 def test_3xtf32_all_layouts(nd, ta, tb, M, N, K):
     from endia_b200 import _lib
     if not _lib.lib.endia_b200_has_tcgen05():

@@ -242,3 +242,29 @@ def test_fused_small_mlp_step_rejects_large_networks(nd):
     with pytest.raises(nd.EndiaError) as ei:
         nd.nn.fused_train_step(W, B, nd.Array([8, 512]), nd.Array([8, 16]))
     assert ei.value.status == -8
+
+
+@pytest.mark.parametrize("name,kw", [("SGD", {"lr": 0.1}), ("SGD", {"lr": 0.1, "momentum": 0.9, "weight_decay": 0.01}),
+                                     ("RMSprop", {"lr": 0.01}), ("Adagrad", {"lr": 0.1})])
+def test_other_optimizers_vs_torch(nd, name, kw):
+    """SGD / RMSprop / Adagrad over two steps against torch.optim with the same hyper-parameters."""
+    import torch
+    r = rng(3)
+    w = r.standard_normal((6, 5)).astype(np.float32)
+    x = r.standard_normal((9, 6)).astype(np.float32)
+    W = nd.Array(w.copy(), requires_grad=True)
+    tw = torch.tensor(w.copy(), requires_grad=True)
+    opt = getattr(nd.optim, name)([W], **kw)
+    tkw = dict(kw)
+    if name == "RMSprop":
+        tkw["alpha"] = 0.99
+    topt = getattr(torch.optim, name)([tw], **tkw)
+    for _ in range(2):
+        loss = nd.sum(nd.square(nd.Array(x) @ W))
+        loss.backward()
+        opt.step()
+        loss.zero_grad()
+        topt.zero_grad()
+        ((torch.tensor(x) @ tw) ** 2).sum().backward()
+        topt.step()
+    assert max_rel(W.to_numpy(), tw.detach().numpy()) < 1e-4

@@ -166,7 +166,8 @@ def test_view_ops_metadata_and_grads(nd, oracle):
         assert g.storage_offset() == o.storage_offset()
 
 
-MM_SHAPES = [((2, 30, 40), (40, 50)), ((128, 1), (1, 32)), ((128, 32), (32, 32)), ((128, 32), (32, 1)),
+MM_SHAPES = [((4096, 1024), (1024, 1)), ((4096, 1), (1, 1024)), ((1000, 300), (300, 3)), ((64, 4), (4, 200)),
+             ((2, 30, 40), (40, 50)), ((128, 1), (1, 32)), ((128, 32), (32, 32)), ((128, 32), (32, 1)),
              ((1, 1), (1, 1)), ((33, 7), (7, 129)), ((257, 130), (130, 65)), ((3, 2, 9, 5), (2, 5, 4)),
              ((512, 300), (300, 260))]
 
@@ -271,3 +272,31 @@ def test_empty_arrays(nd):
     assert nd.relu(e).to_numpy().shape == (0, 5)
     m = nd.matmul(nd.Array([0, 3]), nd.Array([3, 4]))
     assert m.shape() == [0, 4]
+
+
+@pytest.mark.parametrize("ta,tb", [(0, 0), (0, 1), (1, 0), (1, 1)])
+@pytest.mark.parametrize("M,N,K", [(300, 1, 257), (300, 5, 64), (129, 70, 1), (64, 100, 3), (1, 1024, 4096),
+                                   (3, 300, 200), (1024, 1, 4096)])
+def test_gemm_degenerate_shapes_with_epilogue(nd, ta, tb, M, N, K):
+    """N <= 8 and K <= 8 take the one-pass kernels under GEMM_AUTO; bias, activation, mask and
+    accumulation are fused there as well."""
+    from endia_b200 import _lib
+    from endia_b200._array import stream
+    r = rng(21)
+    a = r.standard_normal((K, M) if ta else (M, K)).astype(np.float32)
+    b = r.standard_normal((N, K) if tb else (K, N)).astype(np.float32)
+    bias = r.standard_normal(N).astype(np.float32)
+    saved = r.standard_normal((M, N)).astype(np.float32)
+    c0 = r.standard_normal((M, N)).astype(np.float32)
+    A, B, BIAS, SAVED, Cd = _dev(nd, a), _dev(nd, b), _dev(nd, bias), _dev(nd, saved), _dev(nd, c0)
+    epi = _lib.Epilogue()
+    epi.alpha, epi.beta = 0.5, 2.0
+    epi.bias = BIAS.data_ptr()
+    epi.act, epi.dact = _lib.ACT_TANH, _lib.ACT_RELU
+    epi.dact_src, epi.ld_dact = SAVED.data_ptr(), N
+    _lib.call("endia_b200_gemm", ta, tb, M, N, K, A.data_ptr(), a.shape[1], B.data_ptr(), b.shape[1],
+              Cd.data_ptr(), N, 1, 0, 0, 0, C.byref(epi), _lib.GEMM_AUTO, stream())
+    am = (a.T if ta else a).astype(np.float64)
+    bm = (b.T if tb else b).astype(np.float64)
+    v = np.tanh(0.5 * (am @ bm) + bias) * (saved > 0) + 2.0 * c0
+    assert max_rel(Cd.to_numpy(), v) < TOL
