@@ -54,7 +54,7 @@ GEMM_AUTO, GEMM_FFMA, GEMM_3XTF32 = 0, 1, 2
 (UN_COPY, UN_NEG, UN_RELU, UN_TANH, UN_SIGMOID, UN_SQUARE, UN_SQRT, UN_ABS, UN_SIGN, UN_CONJ,
  UN_EXP, UN_LOG, UN_SIN, UN_COS, UN_RECIPROCAL) = range(15)
 (BIN_ADD, BIN_SUB, BIN_MUL, BIN_DIV, BIN_POW, BIN_GREATER, BIN_RELU_BWD, BIN_TANH_BWD,
- BIN_SIGMOID_BWD, BIN_COMPLEX) = range(10)
+ BIN_SIGMOID_BWD, BIN_COMPLEX, BIN_ABS_BWD, BIN_SQUARE_BWD) = range(12)
 
 _vp, _i64, _i32, _f32, _sz = C.c_void_p, C.c_int64, C.c_int32, C.c_float, C.c_size_t
 _TP = C.POINTER(Tensor)

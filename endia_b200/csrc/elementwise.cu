@@ -69,6 +69,8 @@ __device__ __forceinline__ float bin_real(float a, float b) {
     return (1.f - t * t) * b;
   }
   if constexpr (OP == ENDIA_B200_BIN_SIGMOID_BWD) return a * (1.f - a) * b;  // sigmoid_op.mojo:98
+  if constexpr (OP == ENDIA_B200_BIN_ABS_BWD) return (a / fabsf(a)) * b;     // abs_op.mojo:93, sign_op.mojo:78-80
+  if constexpr (OP == ENDIA_B200_BIN_SQUARE_BWD) return (2.f * a) * b;       // square_op.mojo:96
   return a;
 }
 
@@ -137,6 +139,15 @@ __device__ __forceinline__ c32 bin_cplx(c32 a, c32 b) {
     r.re = u * c; r.im = u * s;
   }
   if constexpr (OP == ENDIA_B200_BIN_COMPLEX) { r.re = a.re; r.im = b.re; }
+  if constexpr (OP == ENDIA_B200_BIN_ABS_BWD) {   // sign(a) * b as a complex product (no conjugation)
+    const float nrm = sqrtf(a.re * a.re + a.im * a.im);
+    const float sr = a.re / nrm, si = a.im / nrm;
+    r.re = sr * b.re - si * b.im; r.im = sr * b.im + si * b.re;
+  }
+  if constexpr (OP == ENDIA_B200_BIN_SQUARE_BWD) {
+    const float tr = 2.f * a.re, ti = 2.f * a.im;
+    r.re = tr * b.re - ti * b.im; r.im = tr * b.im + ti * b.re;
+  }
   return r;
 }
 
@@ -316,7 +327,7 @@ static int dispatch_binary(const EwParams &p, bool a_c, bool b_c, cudaStream_t s
     return launch_cplx<OP, true>(p, 1, 1, st);
   }
   if (!a_c && !b_c) return launch_real<OP, true>(p, st);
-  if constexpr (OP <= ENDIA_B200_BIN_POW) {
+  if constexpr (OP <= ENDIA_B200_BIN_POW || OP == ENDIA_B200_BIN_ABS_BWD || OP == ENDIA_B200_BIN_SQUARE_BWD) {
     return launch_cplx<OP, true>(p, !a_c, !b_c, st);
   } else {
     set_error("ew_binary: op %d is not defined for complex input", OP);
@@ -401,6 +412,7 @@ int endia_b200_ew_binary(int op, const endia_b200_tensor *a, const endia_b200_te
     EB_CASE(ENDIA_B200_BIN_DIV) EB_CASE(ENDIA_B200_BIN_POW) EB_CASE(ENDIA_B200_BIN_GREATER)
     EB_CASE(ENDIA_B200_BIN_RELU_BWD) EB_CASE(ENDIA_B200_BIN_TANH_BWD)
     EB_CASE(ENDIA_B200_BIN_SIGMOID_BWD) EB_CASE(ENDIA_B200_BIN_COMPLEX)
+    EB_CASE(ENDIA_B200_BIN_ABS_BWD) EB_CASE(ENDIA_B200_BIN_SQUARE_BWD)
 #undef EB_CASE
   }
   return ENDIA_B200_EINVAL;

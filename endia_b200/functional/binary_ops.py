@@ -88,6 +88,7 @@ def fused_binary(opcode, a, b):
     shape = broadcast_shapes(a.shape(), b.shape())
     a0, a1 = expand(a, shape), expand(b, shape)
     out = Array(ArrayShape(shape))
+    out.is_complex_flag = a.is_complex() or b.is_complex()
     setup_shape_and_data(out)
     if out.size():
         launch_binary(opcode, a0, a1, out)

@@ -67,9 +67,16 @@ def sigmoid(arg0):
     return unary_op_array(arg0, "sigmoid", _lib.UN_SIGMOID, _sigmoid_vjp)
 
 
-def square(arg0):
+def _square_vjp(primals, grad, out):
+    # 2 * x * grad (square_op.mojo:96); one fused pass when no graph of the gradient is kept
+    if not _state.create_graph:
+        return [_fused(_lib.BIN_SQUARE_BWD, primals[0], grad)]
     from .binary_ops import mul
-    return unary_op_array(arg0, "square", _lib.UN_SQUARE, lambda p, g, o: [mul(2.0 * p[0], g)])  # square_op.mojo:96
+    return [mul(2.0 * primals[0], grad)]
+
+
+def square(arg0):
+    return unary_op_array(arg0, "square", _lib.UN_SQUARE, _square_vjp)
 
 
 def sqrt(arg0):
@@ -86,9 +93,16 @@ def sign(arg0):
     return unary_op_array(arg0, "sign", _lib.UN_SIGN, default_vjp)  # sign_op.mojo: default vjp
 
 
-def abs(arg0):
+def _abs_vjp(primals, grad, out):
+    # sign(x) * grad (abs_op.mojo:93); one fused pass when no graph of the gradient is kept
+    if not _state.create_graph:
+        return [_fused(_lib.BIN_ABS_BWD, primals[0], grad)]
     from .binary_ops import mul
-    return unary_op_array(arg0, "abs", _lib.UN_ABS, lambda p, g, o: [mul(sign(p[0]), g)])  # abs_op.mojo:93
+    return [mul(sign(primals[0]), grad)]
+
+
+def abs(arg0):
+    return unary_op_array(arg0, "abs", _lib.UN_ABS, _abs_vjp)
 
 
 def to_abs(arg0):

@@ -205,7 +205,8 @@ def real(arg0):
 
     def vjp(primals, grad, out):
         from .init_ops import complex as make_complex
-        return [make_complex(grad, Array(grad.shape()))]
+        # the zero imaginary part is a broadcast scalar, never a materialised array
+        return [make_complex(grad, expand(Array([1]), grad.shape()))]
     res = op_array(shape, [arg0], "real", _view_call, vjp=vjp, is_view=True)
     res.is_complex_flag = False
     return res

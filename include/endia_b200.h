@@ -179,6 +179,8 @@ enum {
   ENDIA_B200_BIN_SIGMOID_BWD,  /* out = a*(1-a) * b          a = sigmoid output           */
   ENDIA_B200_BIN_COMPLEX,      /* out = a + i*b, a and b real, out complex (`complex(re, im)`,
                                   init_ops.mojo:419-433)                                      */
+  ENDIA_B200_BIN_ABS_BWD,      /* out = a/|a| * b            Abs.vjp sign(x)*grad, abs_op.mojo:93          */
+  ENDIA_B200_BIN_SQUARE_BWD,   /* out = 2*a*b                Square.vjp, square_op.mojo:96                 */
   ENDIA_B200_BIN_COUNT
 };
 
