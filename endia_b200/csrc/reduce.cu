@@ -70,8 +70,24 @@ __global__ void __launch_bounds__(256) reduce_generic_kernel(RedParams p) {
       const int64_t r0 = (int64_t)s * p.red_per_split;
       int64_t r1 = r0 + p.red_per_split;
       if (r1 > p.n_red) r1 = p.n_red;
-      for (int64_t r = r0 + t_in_g; r < r1; r += GROUP)
-        acc += p.in[base + offs(p.rshape, p.rstride, p.nr, r)];
+      if (p.nr == 1 && p.rstride[0] == 1) {
+        // one contiguous run: 128-bit loads over the aligned middle, scalars at the ends
+        const float *src = p.in + base;
+        int64_t a0 = r0, a1 = r1;
+        while (a0 < a1 && (reinterpret_cast<uintptr_t>(src + a0) & 15)) ++a0;
+        a1 = a0 + ((a1 - a0) & ~int64_t(3));
+        for (int64_t r = r0 + t_in_g; r < a0; r += GROUP) acc += src[r];
+        float a2 = 0.f, a3 = 0.f, a4 = 0.f;
+        for (int64_t r = a0 + 4 * (int64_t)t_in_g; r < a1; r += 4 * GROUP) {
+          const float4 v = __ldg(reinterpret_cast<const float4 *>(src + r));
+          acc += v.x; a2 += v.y; a3 += v.z; a4 += v.w;
+        }
+        acc = (acc + a2) + (a3 + a4);
+        for (int64_t r = a1 + t_in_g; r < r1; r += GROUP) acc += src[r];
+      } else {
+        for (int64_t r = r0 + t_in_g; r < r1; r += GROUP)
+          acc += p.in[base + offs(p.rshape, p.rstride, p.nr, r)];
+      }
     }
     if constexpr (GROUP == 256) {
       acc = block_sum(acc);
@@ -97,36 +113,65 @@ reduce_finish_kernel(const float *partial, float *out, int64_t n_out, int splits
 }
 
 // Layout [A, R, C] with C contiguous: dst[(a*chunks + chunk)*C + c] = sum over the chunk's rows.
+// VEC = 4: one thread owns 4 adjacent columns (128-bit loads).
+template <int VEC>
 __global__ void __launch_bounds__(256)
 colsum_partial_kernel(const float *in, float *dst, int64_t R, int64_t C, int64_t a_stride,
                       int64_t r_stride, int64_t rows_per_chunk) {
-  const int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t c = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * VEC;
   if (c >= C) return;
   const int64_t chunk = blockIdx.y, a = blockIdx.z;
   const int64_t r0 = chunk * rows_per_chunk;
   int64_t r1 = r0 + rows_per_chunk;
   if (r1 > R) r1 = R;
   const float *src = in + a * a_stride + c;
-  float acc0 = 0.f, acc1 = 0.f, acc2 = 0.f, acc3 = 0.f;
+  float acc[2][VEC];
+#pragma unroll
+  for (int j = 0; j < VEC; ++j) acc[0][j] = acc[1][j] = 0.f;
   int64_t r = r0;
-  for (; r + 3 < r1; r += 4) {
-    acc0 += src[(r + 0) * r_stride];
-    acc1 += src[(r + 1) * r_stride];
-    acc2 += src[(r + 2) * r_stride];
-    acc3 += src[(r + 3) * r_stride];
+  for (; r + 1 < r1; r += 2) {
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      if constexpr (VEC == 4) {
+        const float4 v = __ldg(reinterpret_cast<const float4 *>(src + (r + u) * r_stride));
+        acc[u][0] += v.x; acc[u][1] += v.y; acc[u][2] += v.z; acc[u][3] += v.w;
+      } else {
+        acc[u][0] += src[(r + u) * r_stride];
+      }
+    }
   }
-  for (; r < r1; ++r) acc0 += src[r * r_stride];
-  dst[(a * gridDim.y + chunk) * C + c] = (acc0 + acc1) + (acc2 + acc3);
+  for (; r < r1; ++r) {
+    if constexpr (VEC == 4) {
+      const float4 v = __ldg(reinterpret_cast<const float4 *>(src + r * r_stride));
+      acc[0][0] += v.x; acc[0][1] += v.y; acc[0][2] += v.z; acc[0][3] += v.w;
+    } else {
+      acc[0][0] += src[r * r_stride];
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < VEC; ++j) dst[(a * gridDim.y + chunk) * C + c + j] = acc[0][j] + acc[1][j];
 }
-// out[a*C + c] = sum over chunks, sequential.
+// out[a*C + c] = sum over chunks in a fixed order: 32 columns x 8 chunk slices per CTA, each slice
+// summed sequentially, the 8 slice sums added in order through shared memory.
 __global__ void __launch_bounds__(256)
 colsum_finish_kernel(const float *partial, float *out, int64_t A, int64_t C, int chunks) {
-  const int64_t step = (int64_t)gridDim.x * blockDim.x;
-  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < A * C; i += step) {
-    const int64_t a = i / C, c = i - a * C;
+  __shared__ float part[8][33];
+  const int cx = threadIdx.x & 31, sl = threadIdx.x >> 5;
+  const int64_t col_blocks = (C + 31) / 32;
+  for (int64_t blk = blockIdx.x; blk < A * col_blocks; blk += gridDim.x) {
+    const int64_t a = blk / col_blocks, c = (blk - a * col_blocks) * 32 + cx;
     float acc = 0.f;
-    for (int k = 0; k < chunks; ++k) acc += partial[(a * chunks + k) * C + c];
-    out[i] = acc;
+    if (c < C)
+      for (int k = sl; k < chunks; k += 8) acc += partial[(a * chunks + k) * C + c];
+    part[sl][cx] = acc;
+    __syncthreads();
+    if (sl == 0 && c < C) {
+      float v = 0.f;
+#pragma unroll
+      for (int q = 0; q < 8; ++q) v += part[q][cx];
+      out[a * C + c] = v;
+    }
+    __syncthreads();
   }
 }
 
@@ -264,8 +309,8 @@ static int make_plan(const endia_b200_tensor *in, uint32_t axes_mask, RedPlan &p
     pl.R = p.rshape[0]; pl.r_stride = p.rstride[0];
     pl.A = p.nk == 2 ? p.kshape[0] : 1;
     pl.a_stride = p.nk == 2 ? p.kstride[0] : 0;
-    const int64_t ctas_x = ceil_div(pl.C, 256) * pl.A;
-    int64_t want = ceil_div((int64_t)4 * 148, ctas_x);
+    const int64_t ctas_x = ceil_div(ceil_div(pl.C, 4), 256) * pl.A;
+    int64_t want = ceil_div((int64_t)8 * 148, ctas_x);
     int64_t max_chunks = ceil_div(pl.R, 16);
     if (want > max_chunks) want = max_chunks;
     if (want < 1) want = 1;
@@ -333,13 +378,21 @@ int endia_b200_reduce_add(const endia_b200_tensor *in, uint32_t axes_mask, float
     return ENDIA_B200_OK;
   }
   if (pl.colsum) {
-    dim3 grid((unsigned)ceil_div(pl.C, 256), (unsigned)pl.chunks, (unsigned)pl.A);
     float *dst = pl.chunks > 1 ? static_cast<float *>(scratch) : out;
-    colsum_partial_kernel<<<grid, 256, 0, s>>>(pl.p.in, dst, pl.R, pl.C, pl.a_stride, pl.r_stride,
-                                               pl.rows_per_chunk);
+    const bool vec = pl.C % 4 == 0 && pl.a_stride % 4 == 0 && pl.r_stride % 4 == 0 &&
+                     (reinterpret_cast<uintptr_t>(pl.p.in) & 15) == 0;
+    if (vec) {
+      dim3 grid((unsigned)ceil_div(pl.C / 4, 256), (unsigned)pl.chunks, (unsigned)pl.A);
+      colsum_partial_kernel<4><<<grid, 256, 0, s>>>(pl.p.in, dst, pl.R, pl.C, pl.a_stride, pl.r_stride,
+                                                    pl.rows_per_chunk);
+    } else {
+      dim3 grid((unsigned)ceil_div(pl.C, 256), (unsigned)pl.chunks, (unsigned)pl.A);
+      colsum_partial_kernel<1><<<grid, 256, 0, s>>>(pl.p.in, dst, pl.R, pl.C, pl.a_stride, pl.r_stride,
+                                                    pl.rows_per_chunk);
+    }
     EB_LAUNCH_CHECK();
     if (pl.chunks > 1) {
-      colsum_finish_kernel<<<grid_for(pl.A * pl.C, 256), 256, 0, s>>>(
+      colsum_finish_kernel<<<grid_for(pl.A * ceil_div(pl.C, 32) * 256, 256), 256, 0, s>>>(
           static_cast<const float *>(scratch), out, pl.A, pl.C, pl.chunks);
       EB_LAUNCH_CHECK();
     }
@@ -417,7 +470,7 @@ int endia_b200_act_bwd_colsum(int act, const float *act_out, const float *grad, 
   }
   EB_LAUNCH_CHECK();
   if (colsum) {
-    colsum_finish_kernel<<<grid_for(N, 256), 256, 0, s>>>(partial, colsum, 1, N, chunks);
+    colsum_finish_kernel<<<grid_for(ceil_div(N, 32) * 256, 256), 256, 0, s>>>(partial, colsum, 1, N, chunks);
     EB_LAUNCH_CHECK();
   }
   return ENDIA_B200_OK;
