@@ -155,7 +155,7 @@ class TrainStep:
         self.opt = nd.optim.Adam(self.params, lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8)
         self.reducer = None
         if world > 1:
-            self.reducer = ndist.GradAllReducer(self.params)
+            self.reducer = ndist.GradAllReducer(self.params, overlap=os.environ.get("ENDIA_B200_DP_OVERLAP", "1") != "0")
             self.opt.grad_scale = 1.0 / world   # global-mean loss = mean of the ranks' local means
         self.flat = ndist.flat_tensor
 

@@ -34,10 +34,12 @@ class GradAllReducer:
     backward GEMMs; wait() joins them before the optimizer step. The mean over ranks is folded into
     the optimizer's gradient scale instead of a separate pass."""
 
-    def __init__(self, params, group=None):
+    def __init__(self, params, group=None, overlap=True):
         self.params = list(params)
         self.group = group
+        self.overlap = overlap      # False: all-reduce only in wait(), after the backward pass
         self.pending = []
+        self.deferred = []
         for p in self.params:
             p.grad_hook = self._hook
 
@@ -47,10 +49,17 @@ class GradAllReducer:
             from .functional._utils import contiguous
             g = contiguous(grad)
             param.grad_(g)
+        if not self.overlap:
+            self.deferred.append(g)
+            return
         self.pending.append(dist.all_reduce(flat_tensor(g), op=dist.ReduceOp.SUM, group=self.group,
                                             async_op=True))
 
     def wait(self):
+        for g in self.deferred:
+            self.pending.append(dist.all_reduce(flat_tensor(g), op=dist.ReduceOp.SUM, group=self.group,
+                                                async_op=True))
+        self.deferred = []
         for w in self.pending:
             w.wait()
         self.pending = []

@@ -69,3 +69,65 @@ def test_fftn_slab_two_ranks_nccl(nd, tmp_path):
     assert len(lines) == 2, out.stdout + out.stderr
     for _, rank, e1, e2 in lines:
         assert float(e1) < 1e-5 and float(e2) < 1e-5
+
+
+_DP_WORKER = r'''
+import os, sys, numpy as np, torch
+sys.path.insert(0, %(root)r)
+sys.path.insert(0, os.path.join(%(root)r, "tests"))
+import endia_b200 as nd
+from endia_b200 import dist as ndist
+from test_gpu_mlp import make_mlp_inputs
+rank, world = ndist.init_process_group()
+nd._array.device()
+dims, batch = [64, 256, 256, 32], 512
+Ws, bs, x, y = make_mlp_inputs(dims, batch, 0)
+lo, hi = rank * batch // world, (rank + 1) * batch // world
+W = [nd.Array(w.copy(), requires_grad=True) for w in Ws]
+B = [nd.Array(b.copy(), requires_grad=True) for b in bs]
+params = [p for wb in zip(W, B) for p in wb]
+opt = nd.optim.Adam(params, lr=1e-3)
+opt.grad_scale = 1.0 / world
+red = ndist.GradAllReducer(params)
+X, Y = nd.Array(x[lo:hi]), nd.Array(y[lo:hi])
+loss = nd.mse(nd.nn.mlp([X, None] + params, activation="tanh"), Y)
+loss.backward()
+red.wait()
+grads = [p.grad().to_numpy() / world for p in params]     # mean over ranks of the local-mean gradients
+opt.step()
+np.savez(os.path.join(%(out)r, "rank%%d.npz" %% rank), *(grads + [p.to_numpy() for p in params]))
+torch.distributed.destroy_process_group()
+'''
+
+
+def test_data_parallel_step_matches_single_gpu(nd, oracle, tmp_path):
+    """Two ranks, each on half of the batch, gradients all-reduced during the backward pass and
+    averaged inside Adam: the updated weights must equal the single-process result (oracle)."""
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    from test_gpu_mlp import make_mlp_inputs, train_step, fwd_unfused
+    from conftest import max_rel
+    script = tmp_path / "dp_worker.py"
+    script.write_text(_DP_WORKER % {"root": ROOT, "out": str(tmp_path)})
+    s = socket.socket(); s.bind(("127.0.0.1", 0)); port = s.getsockname()[1]; s.close()
+    out = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
+                          "--master-addr", "127.0.0.1", "--master-port", str(port), str(script)],
+                         capture_output=True, text=True, timeout=300, env=dict(os.environ, NCCL_NVLS_ENABLE="0"))
+    assert out.returncode == 0, out.stdout + out.stderr
+    Ws, bs, x, y = make_mlp_inputs([64, 256, 256, 32], 512, 0)
+    oracle.config["mode"] = "fast"
+    try:
+        ref = train_step(oracle, fwd_unfused("tanh"), Ws, bs, x, y, steps=1)
+    finally:
+        oracle.config["mode"] = "faithful"
+    n = len(ref["params"])
+    for rank in range(2):
+        got = np.load(tmp_path / ("rank%d.npz" % rank))
+        for i in range(n):
+            g_ref, p_ref = ref["grads"][i], ref["params"][i]
+            assert max_rel(got["arr_%d" % i].reshape(g_ref.shape), g_ref) < 1e-4
+            a = got["arr_%d" % (n + i)]
+            tiny = np.abs(g_ref.reshape(p_ref.shape)) < 1e-6     # Adam's step is discontinuous at g = 0
+            assert max_rel(np.where(tiny, p_ref, a), p_ref) < 1e-4
+            assert np.abs(a - p_ref).max() <= 2.5e-3
