@@ -25,6 +25,7 @@
 namespace eb {
 
 constexpr int TC_BM = 128;
+constexpr int TC_GROUP_M = 8;
 constexpr uint32_t TC_WAIT_LIMIT = 1u << 22;
 
 static __device__ int g_tc_status = 0;    // 0 ok, else the code of the first wait that gave up
@@ -341,7 +342,7 @@ __device__ __forceinline__ void tc_mma_tf32_pair(uint32_t d_tmem, uint64_t a_des
 
 template <bool A_MN, bool B_MN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
-gemm_tc2_kernel(const __grid_constant__ TcMaps maps, const GemmParams p, int pairs_m) {
+gemm_tc2_kernel(const __grid_constant__ TcMaps maps, const GemmParams p, int pairs_m, int group_m) {
   constexpr int BN = 256, BNH = 128, BK = 32, STAGES = 3;
   extern __shared__ __align__(1024) uint8_t smem[];
   constexpr uint32_t A_BYTES = TC_BM * BK * 4;      // this CTA's 128 rows of A
@@ -355,8 +356,16 @@ gemm_tc2_kernel(const __grid_constant__ TcMaps maps, const GemmParams p, int pai
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();
   const bool leader = rank == 0;
+  // Tile order: groups of TC_GROUP_M row-pairs; inside a group the column tiles of one row-pair
+  // band follow each other, so the CTAs running at the same time share a few A bands and a few
+  // B tiles that fit in L2 together.
   const int pair = blockIdx.x >> 1;
-  const int tile_m = pair % pairs_m, tile_n = pair / pairs_m;
+  const int tiles_n = (int)((gridDim.x >> 1) / pairs_m);
+  const int group = pair / (group_m * tiles_n);
+  const int gm0 = group * group_m;
+  const int gh = pairs_m - gm0 < group_m ? pairs_m - gm0 : group_m;
+  const int rem = pair - group * (group_m * tiles_n);
+  const int tile_m = gm0 + rem % gh, tile_n = rem / gh;
   const int m0 = tile_m * 256 + (int)rank * 128;
   const int n0 = tile_n * BN, nh0 = n0 + (int)rank * BNH;
   const int nkb = (int)((p.K + BK - 1) / BK);
@@ -621,6 +630,8 @@ static int launch_pair(const TcMaps &maps, const GemmParams &p, int trans_a, int
   constexpr size_t SMEM = (size_t)3 * (2 * TC_BM * 32 * 4 + 2 * 128 * 32 * 4) + 1024 + 256;
   const int pairs_m = (int)ceil_div(p.M, 256), tiles_n = (int)ceil_div(p.N, 256);
   const dim3 grid((unsigned)(pairs_m * tiles_n * 2));
+  static const int group_env = []() { const char *e = getenv("ENDIA_B200_TC_GROUP_M"); return e ? atoi(e) : TC_GROUP_M; }();
+  const int group_m = group_env > 0 ? group_env : pairs_m;
 #define EB_TC2_LAUNCH(AM, BM_)                                                                    \
   do {                                                                                            \
     auto kern = gemm_tc2_kernel<AM, BM_>;                                                         \
@@ -629,7 +640,7 @@ static int launch_pair(const TcMaps &maps, const GemmParams &p, int trans_a, int
       EB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM)); \
       attr = true;                                                                                \
     }                                                                                             \
-    kern<<<grid, 192, SMEM, s>>>(maps, p, pairs_m);                                               \
+    kern<<<grid, 192, SMEM, s>>>(maps, p, pairs_m, group_m);                                      \
   } while (0)
   if (trans_a && !trans_b) EB_TC2_LAUNCH(true, true);
   else if (trans_a && trans_b) EB_TC2_LAUNCH(true, false);
