@@ -44,6 +44,8 @@ class Epilogue(C.Structure):
         ("ld_dact", C.c_int64),
         ("colsum", C.c_void_p),
         ("colsum_scratch", C.c_void_p),
+        ("a_lo", C.c_void_p),
+        ("b_lo", C.c_void_p),
     ]
 
 
@@ -85,6 +87,7 @@ SIGNATURES = {
     "endia_b200_gemm_colsum_scratch_bytes": (_sz, [_i64, _i64]),
     "endia_b200_gemm": (C.c_int, [C.c_int, C.c_int, _i64, _i64, _i64, _vp, _i64, _vp, _i64, _vp,
                                   _i64, _i64, _i64, _i64, _i64, C.POINTER(Epilogue), C.c_int, _vp]),
+    "endia_b200_tf32_split": (C.c_int, [_vp, _vp, _i64, _i64, _i64, _i64, _vp]),
     "endia_b200_gemm_complex": (C.c_int, [C.c_int, C.c_int, _i64, _i64, _i64, _vp, _i64, _vp, _i64,
                                           _vp, _i64, _i64, _i64, _i64, _i64, _vp]),
     "endia_b200_ew_unary": (C.c_int, [C.c_int, _TP, _TP, _vp]),
@@ -101,6 +104,9 @@ SIGNATURES = {
     "endia_b200_adam_step_multi": (C.c_int, [_i32, C.POINTER(_vp), C.POINTER(_vp), C.POINTER(_vp),
                                              C.POINTER(_vp), C.POINTER(_i64), _f32, _f32, _f32,
                                              _f32, _f32, _f32, _vp]),
+    "endia_b200_adam_step_multi_lo": (C.c_int, [_i32, C.POINTER(_vp), C.POINTER(_vp), C.POINTER(_vp),
+                                                C.POINTER(_vp), C.POINTER(_vp), C.POINTER(_i64), _f32, _f32,
+                                                _f32, _f32, _f32, _f32, _vp]),
     "endia_b200_mlp_small_step": (C.c_int, [_i32, C.POINTER(_i32), _i32, _i32, _vp, _vp] + [C.POINTER(_vp)] * 8 +
                                   [_vp, _i32, _f32, _f32, _f32, _f32, _f32, _vp]),
     "endia_b200_fft_scratch_bytes": (_sz, [_TP, C.POINTER(_i32), _i32]),

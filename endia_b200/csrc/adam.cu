@@ -5,7 +5,7 @@
 
 namespace eb {
 
-constexpr int ADAM_MAX_TENSORS = 48;  // per launch; longer lists are issued in groups
+constexpr int ADAM_MAX_TENSORS = 40;  // per launch; longer lists are issued in groups
 constexpr int ADAM_CHUNK = 256 * 4 * 8;  // elements per CTA work item
 
 struct AdamArgs {
@@ -13,11 +13,16 @@ struct AdamArgs {
   const float *g[ADAM_MAX_TENSORS];
   float *m[ADAM_MAX_TENSORS];
   float *v[ADAM_MAX_TENSORS];
+  float *lo[ADAM_MAX_TENSORS];   // optional: tf32 low part of the updated parameter
   int64_t chunk_start[ADAM_MAX_TENSORS + 1];  // prefix sum of chunks per tensor
   int64_t numel[ADAM_MAX_TENSORS];
   int n;
   float lr, b1, b2, eps, omb1, omb2, c1, c2, gscale;
 };
+
+__device__ __forceinline__ float tf32_lo(float x) {
+  return x - __uint_as_float(__float_as_uint(x) & 0xFFFFE000u);
+}
 
 __device__ __forceinline__ void adam_one(float &p, float g, float &m, float &v, const AdamArgs &a) {
   g *= a.gscale;
@@ -38,6 +43,7 @@ __global__ void __launch_bounds__(256) adam_kernel(const __grid_constant__ AdamA
     int64_t e1 = e0 + ADAM_CHUNK;
     if (e1 > n) e1 = n;
     float *p = a.p[t]; const float *g = a.g[t]; float *m = a.m[t]; float *v = a.v[t];
+    float *lo = a.lo[t];
     const bool vec = ((reinterpret_cast<uintptr_t>(p) | reinterpret_cast<uintptr_t>(g) |
                        reinterpret_cast<uintptr_t>(m) | reinterpret_cast<uintptr_t>(v)) & 15) == 0;
     if (vec) {
@@ -52,10 +58,20 @@ __global__ void __launch_bounds__(256) adam_kernel(const __grid_constant__ AdamA
         *reinterpret_cast<float4 *>(p + i) = pp;
         *reinterpret_cast<float4 *>(m + i) = mm;
         *reinterpret_cast<float4 *>(v + i) = vv;
+        if (lo) {
+          lo[i + 0] = tf32_lo(pp.x); lo[i + 1] = tf32_lo(pp.y);
+          lo[i + 2] = tf32_lo(pp.z); lo[i + 3] = tf32_lo(pp.w);
+        }
       }
-      for (int64_t i = v1 + threadIdx.x; i < e1; i += 256) adam_one(p[i], g[i], m[i], v[i], a);
+      for (int64_t i = v1 + threadIdx.x; i < e1; i += 256) {
+        adam_one(p[i], g[i], m[i], v[i], a);
+        if (lo) lo[i] = tf32_lo(p[i]);
+      }
     } else {
-      for (int64_t i = e0 + threadIdx.x; i < e1; i += 256) adam_one(p[i], g[i], m[i], v[i], a);
+      for (int64_t i = e0 + threadIdx.x; i < e1; i += 256) {
+        adam_one(p[i], g[i], m[i], v[i], a);
+        if (lo) lo[i] = tf32_lo(p[i]);
+      }
     }
   }
 }
@@ -64,11 +80,11 @@ __global__ void __launch_bounds__(256) adam_kernel(const __grid_constant__ AdamA
 
 using namespace eb;
 
-extern "C" int endia_b200_adam_step_multi(int32_t n_tensors, float *const *params,
-                                          const float *const *grads, float *const *m,
-                                          float *const *v, const int64_t *numel, float lr,
-                                          float beta1, float beta2, float eps, float t,
-                                          float grad_scale, void *stream) {
+extern "C" int endia_b200_adam_step_multi_lo(int32_t n_tensors, float *const *params,
+                                             const float *const *grads, float *const *m,
+                                             float *const *v, float *const *p_lo, const int64_t *numel,
+                                             float lr, float beta1, float beta2, float eps, float t,
+                                             float grad_scale, void *stream) {
   int st = require_device();
   if (st) return st;
   EB_REQUIRE(n_tensors >= 0, ENDIA_B200_EINVAL, "adam: negative tensor count");
@@ -85,6 +101,7 @@ extern "C" int endia_b200_adam_step_multi(int32_t n_tensors, float *const *param
       EB_REQUIRE(params[i] && grads[i] && m[i] && v[i], ENDIA_B200_EINVAL,
                  "adam: NULL pointer for tensor %d", i);
       a.p[a.n] = params[i]; a.g[a.n] = grads[i]; a.m[a.n] = m[i]; a.v[a.n] = v[i];
+      a.lo[a.n] = p_lo ? p_lo[i] : nullptr;
       a.numel[a.n] = numel[i];
       a.chunk_start[a.n + 1] = a.chunk_start[a.n] + ceil_div(numel[i], ADAM_CHUNK);
       ++a.n;
@@ -103,4 +120,13 @@ extern "C" int endia_b200_adam_step_multi(int32_t n_tensors, float *const *param
     EB_LAUNCH_CHECK();
   }
   return ENDIA_B200_OK;
+}
+
+extern "C" int endia_b200_adam_step_multi(int32_t n_tensors, float *const *params,
+                                          const float *const *grads, float *const *m,
+                                          float *const *v, const int64_t *numel, float lr,
+                                          float beta1, float beta2, float eps, float t,
+                                          float grad_scale, void *stream) {
+  return endia_b200_adam_step_multi_lo(n_tensors, params, grads, m, v, nullptr, numel, lr, beta1, beta2,
+                                       eps, t, grad_scale, stream);
 }

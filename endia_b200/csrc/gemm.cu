@@ -45,6 +45,7 @@ int endia_b200_gemm(int trans_a, int trans_b, int64_t M, int64_t N, int64_t K, c
     p.epi.alpha = epi->alpha; p.epi.beta = epi->beta; p.epi.bias = epi->bias;
     p.epi.act = epi->act; p.epi.dact = epi->dact; p.epi.dact_src = epi->dact_src;
     p.epi.ld_dact = epi->ld_dact;
+    p.a_lo = epi->a_lo; p.b_lo = epi->b_lo;
     EB_REQUIRE(epi->act >= 0 && epi->act <= ENDIA_B200_ACT_SIGMOID && epi->dact >= 0 &&
                    epi->dact <= ENDIA_B200_ACT_SIGMOID, ENDIA_B200_EINVAL, "gemm: unknown activation");
     EB_REQUIRE(epi->dact == 0 || (epi->dact_src && epi->ld_dact >= N), ENDIA_B200_EINVAL,
@@ -77,3 +78,16 @@ int endia_b200_gemm(int trans_a, int trans_b, int64_t M, int64_t N, int64_t K, c
 }
 
 }  // extern "C"
+
+extern "C" int endia_b200_tf32_split(const float *x, float *lo, int64_t rows, int64_t cols, int64_t ld_in,
+                                     int64_t ld_out, void *stream) {
+  int st = require_device();
+  if (st) return st;
+  EB_REQUIRE(rows >= 0 && cols >= 0, ENDIA_B200_EINVAL, "tf32_split: negative size");
+  if (rows == 0 || cols == 0) return ENDIA_B200_OK;
+  EB_REQUIRE(x && lo, ENDIA_B200_EINVAL, "tf32_split: NULL pointer");
+  EB_REQUIRE(cols % 4 == 0 && ld_in % 4 == 0 && ld_out % 4 == 0 && ld_in >= cols && ld_out >= cols &&
+                 aligned16(x) && aligned16(lo), ENDIA_B200_EINVAL,
+             "tf32_split: cols and leading dimensions must be multiples of 4 and pointers 16-byte aligned");
+  return launch_tf32_split(x, lo, rows, cols, ld_in, ld_out, as_stream(stream));
+}

@@ -23,6 +23,8 @@ struct GemmParams {
   // split-K: partial[split][M][ld_partial] receives the raw sums of each K range
   float *partial;
   int64_t ld_partial;
+  // optional precomputed tf32 low parts, laid out like A / B
+  const float *a_lo, *b_lo;
 };
 
 __device__ __forceinline__ float act_fwd(int act, float v) {
@@ -60,6 +62,8 @@ int launch_colsum_finish(const float *partial, float *out, int64_t N, int tiles,
 // Degenerate shapes (N <= 8, K <= 8, or M <= 8 with a row-major B): one pass over the large operand.
 bool skinny_gemm_supported(const GemmParams &p, int trans_b, int64_t batch);
 int launch_gemm_skinny(const GemmParams &p, int trans_a, int trans_b, cudaStream_t s);
+int launch_tf32_split(const float *x, float *lo, int64_t rows, int64_t cols, int64_t ld_in, int64_t ld_out,
+                      cudaStream_t s);
 // C = epilogue(sum over `splits` slices of p.partial, in order).
 int launch_splitk_finish(const GemmParams &p, int splits, cudaStream_t s);
 // tcgen05 3xTF32 path: true when the shape/alignment is one it handles.

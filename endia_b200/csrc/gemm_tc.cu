@@ -536,6 +536,13 @@ tf32_split_kernel(const float *__restrict__ x, float *__restrict__ lo, float *__
   }
 }
 
+int launch_tf32_split(const float *x, float *lo, int64_t rows, int64_t cols, int64_t ld_in, int64_t ld_out,
+                      cudaStream_t s) {
+  tf32_split_kernel<<<grid_for(rows * (cols / 4), 256), 256, 0, s>>>(x, lo, nullptr, rows, cols / 4, ld_in, ld_out);
+  EB_LAUNCH_CHECK();
+  return ENDIA_B200_OK;
+}
+
 // ---------------------------------------------------------------------------------- host side
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
                                   const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
@@ -657,15 +664,23 @@ int launch_gemm_tc(const GemmParams &p, int trans_a, int trans_b, cudaStream_t s
   const int64_t a_rows = trans_a ? p.K : p.M, a_cols = trans_a ? p.M : p.K;
   const int64_t b_rows = trans_b ? p.N : p.K, b_cols = trans_b ? p.K : p.N;
   const int64_t a_ld = (a_cols + 3) / 4 * 4, b_ld = (b_cols + 3) / 4 * 4;
-  float *a_lo = nullptr, *b_lo = nullptr;
-  EB_CUDA(cudaMallocAsync(&a_lo, sizeof(float) * a_rows * a_ld, s));
-  EB_CUDA(cudaMallocAsync(&b_lo, sizeof(float) * b_rows * b_ld, s));
-  tf32_split_kernel<<<grid_for(a_rows * (a_ld / 4), 256), 256, 0, s>>>(p.A, a_lo, nullptr, a_rows,
-                                                                       a_ld / 4, p.lda, a_ld);
-  EB_LAUNCH_CHECK();
-  tf32_split_kernel<<<grid_for(b_rows * (b_ld / 4), 256), 256, 0, s>>>(p.B, b_lo, nullptr, b_rows,
-                                                                       b_ld / 4, p.ldb, b_ld);
-  EB_LAUNCH_CHECK();
+  // Low parts: taken from the caller when provided (same layout as the operand), else computed
+  // into stream-ordered work buffers.
+  float *a_lo_buf = nullptr, *b_lo_buf = nullptr;
+  const float *a_lo = p.a_lo, *b_lo = p.b_lo;
+  int64_t a_lo_ld = p.lda, b_lo_ld = p.ldb;
+  if (!a_lo) {
+    EB_CUDA(cudaMallocAsync(&a_lo_buf, sizeof(float) * a_rows * a_ld, s));
+    int st0 = launch_tf32_split(p.A, a_lo_buf, a_rows, a_ld, p.lda, a_ld, s);
+    if (st0) return st0;
+    a_lo = a_lo_buf; a_lo_ld = a_ld;
+  }
+  if (!b_lo) {
+    EB_CUDA(cudaMallocAsync(&b_lo_buf, sizeof(float) * b_rows * b_ld, s));
+    int st0 = launch_tf32_split(p.B, b_lo_buf, b_rows, b_ld, p.ldb, b_ld, s);
+    if (st0) return st0;
+    b_lo = b_lo_buf; b_lo_ld = b_ld;
+  }
   int bn = p.N >= 256 ? 256 : 128;
   // Few output tiles and a long reduction: split K over CTAs (128 x 128 tiles) so that the machine
   // is filled; the partial sums go through a work buffer and are added in a fixed order.
@@ -701,9 +716,9 @@ int launch_gemm_tc(const GemmParams &p, int trans_a, int trans_b, cudaStream_t s
   }
   const int b_bi = trans_b ? bk : 32, b_bo = trans_b ? (pair ? 128 : bn) : bk;
   if ((st = make_map(&maps.a_hi, p.A, a_cols, a_rows, p.lda, a_bi, a_bo, trans_a != 0))) return st;
-  if ((st = make_map(&maps.a_lo, a_lo, a_cols, a_rows, a_ld, a_bi, a_bo, trans_a != 0))) return st;
+  if ((st = make_map(&maps.a_lo, a_lo, a_cols, a_rows, a_lo_ld, a_bi, a_bo, trans_a != 0))) return st;
   if ((st = make_map(&maps.b_hi, p.B, b_cols, b_rows, p.ldb, b_bi, b_bo, trans_b == 0))) return st;
-  if ((st = make_map(&maps.b_lo, b_lo, b_cols, b_rows, b_ld, b_bi, b_bo, trans_b == 0))) return st;
+  if ((st = make_map(&maps.b_lo, b_lo, b_cols, b_rows, b_lo_ld, b_bi, b_bo, trans_b == 0))) return st;
   if (pair) st = launch_pair(maps, p, trans_a, trans_b, s);
   else if (bn == 256 && bk == 16) st = launch_variant<256, 16, 4>(maps, p, trans_a, trans_b, s);
   else if (bn == 256) st = launch_variant<256, 32, 2>(maps, p, trans_a, trans_b, s);
@@ -713,8 +728,8 @@ int launch_gemm_tc(const GemmParams &p, int trans_a, int trans_b, cudaStream_t s
     st = launch_splitk_finish(q, splits, s);
     cudaFreeAsync(partial, s);
   }
-  EB_CUDA(cudaFreeAsync(a_lo, s));
-  EB_CUDA(cudaFreeAsync(b_lo, s));
+  if (a_lo_buf) EB_CUDA(cudaFreeAsync(a_lo_buf, s));
+  if (b_lo_buf) EB_CUDA(cudaFreeAsync(b_lo_buf, s));
   return st;
 }
 

@@ -99,3 +99,4 @@ def copy_into(src, dst):
     if s.is_complex() != dst.is_complex():
         raise _lib.EndiaError(_lib.EINVAL, "in-place update: complex flag mismatch")
     _lib.call("endia_b200_d2d", dst.data_ptr(), s.data_ptr(), dst.size() * w * 4, stream())
+    dst.base()._tf32_lo = None   # a cached tf32 low part no longer matches the storage

@@ -169,6 +169,16 @@ def gemm_arrays(a, b, out, epi=None, algo=None):
         _lib.call("endia_b200_gemm_complex", la[0], lb[0], M, N, K, a.data_ptr(), la[1], b.data_ptr(),
                   lb[1], out.data_ptr(), N, nbatch, sa, sb, M * N, stream())
         return
+    # A weight whose tf32 low part was written by the optimizer (valid while its storage has not
+    # been rewritten since): hand it to the 3xTF32 kernel instead of recomputing it per product.
+    base = b.base()
+    lo = getattr(base, "_tf32_lo", None)
+    if lo is not None and nbatch == 1 and b.storage_offset() == 0 and base._tf32_lo_ptr == base.buf.data_ptr() \
+            and b.buf is base.buf:
+        if epi is None:
+            epi = _lib.Epilogue()
+            epi.alpha = 1.0
+        epi.b_lo = lo.data_ptr()
     timer = _state.gemm_timer
     if timer is not None:
         timer.start(2.0 * M * N * K * nbatch)

@@ -202,6 +202,8 @@ class SmallMLPStep:
                           0.0, 0.0, 0.0, 0.0, 1.0, stream())
         _lib.check(st)
         for w, b, g1, g2 in zip(self.weights, self.biases, self.gW, self.gb):
+            if opt is not None:
+                w._tf32_lo = None
             w.grad_node = g1
             b.grad_node = g2
         if opt is not None:

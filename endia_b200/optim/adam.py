@@ -2,7 +2,7 @@
 import ctypes as C
 
 from .. import _lib
-from .._array import Array, ArrayShape, stream
+from .._array import Array, ArrayShape, alloc, stream
 from ..functional._utils import contiguous, broadcast_shapes
 
 
@@ -31,7 +31,19 @@ class Adam:
             if g.size() != p.size():
                 raise _lib.EndiaError(_lib.ESHAPE, "Adam: gradient %s does not match parameter %s" % (
                     g.shape(), p.shape()))
-        _lib.call("endia_b200_adam_step_multi", n, P, G, M, V, numel, self.lr, self.beta1, self.beta2,
+        # Matrices also get the tf32 low part of their new value, which the 3xTF32 GEMMs of the next
+        # step read instead of recomputing it (the cache is dropped by any other in-place update).
+        lo_ptrs = []
+        for p in self.params:
+            if p.ndim() == 2 and p.size() % 4 == 0 and p.size() >= 128 * 128 and not p.is_complex():
+                if getattr(p, "_tf32_lo", None) is None:
+                    p._tf32_lo = alloc(p.size())
+                p._tf32_lo_ptr = p.buf.data_ptr()
+                lo_ptrs.append(p._tf32_lo.data_ptr())
+            else:
+                lo_ptrs.append(None)
+        LO = (C.c_void_p * n)(*lo_ptrs)
+        _lib.call("endia_b200_adam_step_multi_lo", n, P, G, M, V, LO, numel, self.lr, self.beta1, self.beta2,
                   self.eps, self.t, self.grad_scale, stream())
         # m and v take the broadcast shape of (state, grad): a bias gradient is (1, N), so the
         # moments become (1, N) while the parameter keeps (N) (adam.mojo:49-56, expand_op.mojo:121-126).

@@ -133,9 +133,20 @@ typedef struct endia_b200_epilogue {
   int64_t ld_dact;
   float *colsum;
   float *colsum_scratch;
+  /* Optional, used only by the 3xTF32 kernel: the low parts x - tf32(x) of A and/or B, laid out
+   * exactly like A / B (same leading dimension), e.g. as endia_b200_tf32_split or
+   * endia_b200_adam_step_multi_lo wrote them. NULL = computed inside the call. */
+  const float *a_lo;
+  const float *b_lo;
 } endia_b200_epilogue;
 
 size_t endia_b200_gemm_colsum_scratch_bytes(int64_t M, int64_t N);
+
+/* lo[i] = x[i] - (x[i] with its 13 low mantissa bits cleared), for `rows` rows of `cols` floats
+ * (cols and both leading dimensions multiples of 4, 16-byte aligned pointers): the second operand
+ * part of the 3xTF32 product, for callers that reuse it over several GEMMs. */
+int endia_b200_tf32_split(const float *x, float *lo, int64_t rows, int64_t cols, int64_t ld_in,
+                          int64_t ld_out, void *stream);
 
 /* C[M,N] = epilogue(op(A)[M,K] · op(B)[K,N]), fp32, row-major storage.
  *   trans_a = 0: A is stored [M,K] with leading dimension lda >= K
@@ -279,6 +290,14 @@ int endia_b200_mlp_small_step(int32_t n_layers, const int32_t *dims, int32_t bat
                               float *const *vW, float *const *mb, float *const *vb, float *loss,
                               int32_t do_adam, float lr, float beta1, float beta2, float eps,
                               float t, void *stream);
+
+/* endia_b200_adam_step_multi that also writes, for every tensor with a non-NULL entry in `p_lo`,
+ * the tf32 low part of the UPDATED parameter (same layout), so that the GEMMs of the next step
+ * need not recompute it for the weights. */
+int endia_b200_adam_step_multi_lo(int32_t n_tensors, float *const *params, const float *const *grads,
+                                  float *const *m, float *const *v, float *const *p_lo,
+                                  const int64_t *numel, float lr, float beta1, float beta2, float eps,
+                                  float t, float grad_scale, void *stream);
 
 /* --------------------------------------------------------------------- FFT ---- */
 

@@ -100,3 +100,28 @@ def test_auto_falls_back_to_ffma_for_unaligned_or_small(nd):
     st = _lib.lib.endia_b200_gemm(0, 0, 130, 257, 33, A.data_ptr(), 33, B.data_ptr(), 257, Cd.data_ptr(),
                                   257, 1, 0, 0, 0, None, _lib.GEMM_3XTF32, stream())
     assert st == _lib.EINVAL
+
+
+def test_weight_low_part_cache_written_by_adam(nd):
+    """Adam leaves the tf32 low part of each updated weight matrix behind; the next products with
+    that weight (plain and transposed) read it, and any other in-place update drops it."""
+    from endia_b200 import _lib
+    r = rng(9)
+    w = r.standard_normal((256, 384)).astype(np.float32)
+    x = r.standard_normal((512, 256)).astype(np.float32)
+    g = r.standard_normal((512, 384)).astype(np.float32)
+    W = nd.Array(w, requires_grad=True)
+    W.grad_(nd.Array(r.standard_normal((256, 384)).astype(np.float32)))
+    nd.optim.Adam([W]).step()
+    assert getattr(W, "_tf32_lo", None) is not None
+    wn = W.to_numpy().astype(np.float64)
+    lo = W._tf32_lo.cpu().numpy().reshape(256, 384)
+    hi = (W.to_numpy().view(np.uint32) & np.uint32(0xFFFFE000)).view(np.float32)
+    assert np.array_equal(lo, W.to_numpy() - hi)
+    y = nd.matmul(nd.Array(x), W).to_numpy()
+    dx = nd.matmul(nd.Array(g), W.T()).to_numpy()
+    assert max_rel(y, x.astype(np.float64) @ wn) < 2e-5
+    assert max_rel(dx, g.astype(np.float64) @ wn.T) < 2e-5
+    W -= nd.Array(np.ones((256, 384), np.float32))
+    assert W._tf32_lo is None
+    assert max_rel(nd.matmul(nd.Array(x), W).to_numpy(), x.astype(np.float64) @ (wn - 1.0)) < 2e-5
