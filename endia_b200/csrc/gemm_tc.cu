@@ -3,14 +3,15 @@
 //   a*b ~= a_hi*b_hi + a_hi*b_lo + a_lo*b_hi        (fp32 accumulation in tensor memory)
 // which keeps ~21 bits of each product, so gradients stay within 1e-4 of the fp32 result.
 //
-// Structure of one CTA (192 threads, one 128 x BN output tile):
+// Structure of one CTA (320 threads, one 128 x BN output tile):
 //   warp 0   : producer - one lane issues TMA tile loads (hi and lo tiles of A and B, 128-byte
 //              swizzle) into a ring of shared-memory stages, signalled through mbarriers
 //   warp 1   : allocates tensor memory (two accumulators of BN columns: the hi*hi sum and the
 //              sum of the two correction products); one lane issues tcgen05.mma (kind::tf32,
 //              M = 128, N = BN, K = 8) three times per k-step and commits each stage back
-//   warps 2-5: epilogue - tcgen05.ld of the accumulator (one row per thread), the fused epilogue
-//              of endia_b200_epilogue, 128-bit stores
+//   warps 2-9: epilogue - tcgen05.ld of the accumulators (one row per thread, two warps per lane
+//              quarter, each half of the columns), the fused epilogue of endia_b200_epilogue,
+//              128-bit stores
 // Operands are consumed in the layout they have in global memory: a row-major [rows, K] operand
 // is K-major, a stored-transposed one ([K, rows]) is MN-major, selected in the instruction and
 // shared-memory descriptors, so dX = dY*W^T and dW = X^T*dY need no transposed copies
@@ -115,11 +116,63 @@ struct TcMaps {
   CUtensorMap a_hi, a_lo, b_hi, b_lo;
 };
 
+// Epilogue of one warp: rows of tensor-memory lane quarter q, column chunks [c_begin, c_end) of
+// 32 columns each. The two accumulators are added, the fused epilogue applied and the row segment
+// stored with 128-bit stores. The loads of the next chunk are in flight while a chunk is processed.
+template <int BN>
+__device__ __forceinline__ void tc_epilogue_warp(uint32_t tmem_base, int q, int lane, int c_begin, int c_end,
+                                                 int64_t m0, int64_t n0, int64_t M, int64_t N, float *Cout,
+                                                 int64_t ldc, const EpiParams &epi, bool vec_c) {
+  const uint32_t row_addr = tmem_base + ((uint32_t)(q * 32) << 16);
+  const int64_t m = m0 + q * 32 + lane;
+  uint32_t a0[32], b0[32], a1[32], b1[32];
+  auto process = [&](uint32_t (&ra)[32], uint32_t (&rb)[32], int c) {
+    const int64_t nb = n0 + c * 32;
+    if (m >= M || nb >= N) return;
+    float *crow = Cout + m * ldc + nb;
+    if (vec_c && nb + 32 <= N) {
+#pragma unroll
+      for (int j = 0; j < 32; j += 4) {
+        float4 o;
+        o.x = apply_epilogue(epi, __uint_as_float(ra[j + 0]) + __uint_as_float(rb[j + 0]), m, nb + j + 0, crow + j + 0);
+        o.y = apply_epilogue(epi, __uint_as_float(ra[j + 1]) + __uint_as_float(rb[j + 1]), m, nb + j + 1, crow + j + 1);
+        o.z = apply_epilogue(epi, __uint_as_float(ra[j + 2]) + __uint_as_float(rb[j + 2]), m, nb + j + 2, crow + j + 2);
+        o.w = apply_epilogue(epi, __uint_as_float(ra[j + 3]) + __uint_as_float(rb[j + 3]), m, nb + j + 3, crow + j + 3);
+        *reinterpret_cast<float4 *>(crow + j) = o;
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (nb + j < N)
+          crow[j] = apply_epilogue(epi, __uint_as_float(ra[j]) + __uint_as_float(rb[j]), m, nb + j, crow + j);
+    }
+  };
+  tc_ld32(row_addr + (uint32_t)(c_begin * 32), a0);
+  tc_ld32(row_addr + (uint32_t)(BN + c_begin * 32), b0);
+#pragma unroll 1
+  for (int c = c_begin; c < c_end; c += 2) {
+    tc_wait_ld();
+    if (c + 1 < c_end) {
+      tc_ld32(row_addr + (uint32_t)((c + 1) * 32), a1);
+      tc_ld32(row_addr + (uint32_t)(BN + (c + 1) * 32), b1);
+    }
+    process(a0, b0, c);
+    if (c + 1 < c_end) {
+      tc_wait_ld();
+      if (c + 2 < c_end) {
+        tc_ld32(row_addr + (uint32_t)((c + 2) * 32), a0);
+        tc_ld32(row_addr + (uint32_t)(BN + (c + 2) * 32), b0);
+      }
+      process(a1, b1, c + 1);
+    }
+  }
+}
+
 // ------------------------------------------------------------------------------------ kernel
 // A_MN / B_MN: the operand is MN-major in global memory (stored [K, rows]); its tile then arrives
 // as rows/32 boxes of [BK k][32 rows].
 template <int BN, int BK, int STAGES, bool A_MN, bool B_MN>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(320, 1)
 gemm_tc_kernel(const __grid_constant__ TcMaps maps, const GemmParams p, int tiles_m) {
   extern __shared__ __align__(1024) uint8_t smem[];
   constexpr uint32_t A_BYTES = TC_BM * BK * 4;
@@ -251,40 +304,14 @@ gemm_tc_kernel(const __grid_constant__ TcMaps maps, const GemmParams p, int tile
   } else {
     // --------------------------------------------------------------------- epilogue
     const int q = warp & 3;        // tensor-memory lane quarter this warp may read
+    const int half = (warp - 2) >> 2;   // warps 2-5 take the first half of the columns, 6-9 the second
     const bool ok = mbar_wait(acc_bar, 0, 4);
     tc_fence_after();
     const int64_t m = (int64_t)m0 + q * 32 + lane;
     if (ok && nkb > 0) {
-#pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t r[32], r2[32];
-        tc_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(c * 32), r);
-        tc_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(BN + c * 32), r2);
-        tc_wait_ld();
-#pragma unroll
-        for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) + __uint_as_float(r2[j]));
-        const int64_t nb = (int64_t)n0 + c * 32;
-        if (m < p.M && nb < p.N) {
-          float *crow = Cout + m * ldc + nb;
-          if (vec_c && nb + 32 <= p.N) {
-#pragma unroll
-            for (int j = 0; j < 32; j += 4) {
-              float4 o;
-              o.x = apply_epilogue(epi, __uint_as_float(r[j + 0]), m, nb + j + 0, crow + j + 0);
-              o.y = apply_epilogue(epi, __uint_as_float(r[j + 1]), m, nb + j + 1, crow + j + 1);
-              o.z = apply_epilogue(epi, __uint_as_float(r[j + 2]), m, nb + j + 2, crow + j + 2);
-              o.w = apply_epilogue(epi, __uint_as_float(r[j + 3]), m, nb + j + 3, crow + j + 3);
-              *reinterpret_cast<float4 *>(crow + j) = o;
-            }
-          } else {
-#pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (nb + j < p.N)
-                crow[j] = apply_epilogue(epi, __uint_as_float(r[j]), m, nb + j, crow + j);
-          }
-        }
-      }
-    } else if (ok && m < p.M) {
+      constexpr int CH = BN / 64;
+      tc_epilogue_warp<BN>(tmem_base, q, lane, half * CH, (half + 1) * CH, m0, n0, p.M, p.N, Cout, ldc, epi, vec_c);
+    } else if (ok && m < p.M && half == 0) {
       // K == 0: the product is empty, the epilogue applies to zeros.
       for (int64_t n = n0; n < n0 + BN && n < p.N; ++n)
         Cout[m * ldc + n] = apply_epilogue(epi, 0.f, m, n, Cout + m * ldc + n);
@@ -341,7 +368,7 @@ __device__ __forceinline__ void tc_mma_tf32_pair(uint32_t d_tmem, uint64_t a_des
 }
 
 template <bool A_MN, bool B_MN>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(320, 1)
 gemm_tc2_kernel(const __grid_constant__ TcMaps maps, const GemmParams p, int pairs_m, int group_m) {
   constexpr int BN = 256, BNH = 128, BK = 32, STAGES = 3;
   extern __shared__ __align__(1024) uint8_t smem[];
@@ -455,39 +482,13 @@ gemm_tc2_kernel(const __grid_constant__ TcMaps maps, const GemmParams p, int pai
     }
   } else {
     const int q = warp & 3;
+    const int half = (warp - 2) >> 2;
     const bool ok = mbar_wait(acc_bar, 0, 14);
     tc_fence_after();
-    const int64_t m = (int64_t)m0 + q * 32 + lane;
     if (ok && nkb > 0) {
-#pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t r[32], r2[32];
-        tc_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(c * 32), r);
-        tc_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(BN + c * 32), r2);
-        tc_wait_ld();
-#pragma unroll
-        for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) + __uint_as_float(r2[j]));
-        const int64_t nb = (int64_t)n0 + c * 32;
-        if (m < p.M && nb < p.N) {
-          float *crow = p.C + m * p.ldc + nb;
-          if (p.vec_c && nb + 32 <= p.N) {
-#pragma unroll
-            for (int j = 0; j < 32; j += 4) {
-              float4 o;
-              o.x = apply_epilogue(p.epi, __uint_as_float(r[j + 0]), m, nb + j + 0, crow + j + 0);
-              o.y = apply_epilogue(p.epi, __uint_as_float(r[j + 1]), m, nb + j + 1, crow + j + 1);
-              o.z = apply_epilogue(p.epi, __uint_as_float(r[j + 2]), m, nb + j + 2, crow + j + 2);
-              o.w = apply_epilogue(p.epi, __uint_as_float(r[j + 3]), m, nb + j + 3, crow + j + 3);
-              *reinterpret_cast<float4 *>(crow + j) = o;
-            }
-          } else {
-#pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (nb + j < p.N)
-                crow[j] = apply_epilogue(p.epi, __uint_as_float(r[j]), m, nb + j, crow + j);
-          }
-        }
-      }
+      constexpr int CH = BN / 64;
+      tc_epilogue_warp<BN>(tmem_base, q, lane, half * CH, (half + 1) * CH, m0, n0, p.M, p.N, p.C, p.ldc, p.epi,
+                           p.vec_c);
     }
   }
   tc_fence_before();
@@ -617,7 +618,7 @@ static int launch_variant(const TcMaps &maps, const GemmParams &p, int trans_a, 
       EB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM)); \
       attr = true;                                                                                \
     }                                                                                             \
-    kern<<<grid, 192, SMEM, s>>>(maps, p, tiles_m);                                               \
+    kern<<<grid, 320, SMEM, s>>>(maps, p, tiles_m);                                               \
   } while (0)
   if (trans_a && !trans_b) EB_TC_LAUNCH(true, true);
   else if (trans_a && trans_b) EB_TC_LAUNCH(true, false);
@@ -647,7 +648,7 @@ static int launch_pair(const TcMaps &maps, const GemmParams &p, int trans_a, int
       EB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM)); \
       attr = true;                                                                                \
     }                                                                                             \
-    kern<<<grid, 192, SMEM, s>>>(maps, p, pairs_m, group_m);                                      \
+    kern<<<grid, 320, SMEM, s>>>(maps, p, pairs_m, group_m);                                      \
   } while (0)
   if (trans_a && !trans_b) EB_TC2_LAUNCH(true, true);
   else if (trans_a && trans_b) EB_TC2_LAUNCH(true, false);
