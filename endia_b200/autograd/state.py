@@ -6,6 +6,8 @@ from .. import _lib
 create_graph = False
 # GEMM algorithm handed to endia_b200_gemm (AUTO = tcgen05 3xTF32 when the shape allows).
 gemm_algo = _lib.GEMM_AUTO
+# Keep the tf32 low part of an op result beside it after its first use as a GEMM operand.
+cache_tf32_lo = True
 # Optional object with start(flops) / stop() called around every GEMM launch (benchmarks bracket
 # the launches with events on the launching stream).
 gemm_timer = None

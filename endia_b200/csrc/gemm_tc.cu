@@ -31,6 +31,22 @@ constexpr uint32_t TC_WAIT_LIMIT = 1u << 22;
 
 static __device__ int g_tc_status = 0;    // 0 ok, else the code of the first wait that gave up
 
+#ifdef EB_TC_TRACE
+// Debug build only: SM clock stamps of CTA 0 of the persistent kernel, 8 slots per tile.
+static __device__ long long g_tc_trace[16 * 8];
+#define EB_TRACE(tile, slot)                                                   \
+  do {                                                                         \
+    if (blockIdx.x == 0 && (tile) < 16) g_tc_trace[(tile) * 8 + (slot)] = clock64(); \
+  } while (0)
+#define EB_TRACE2(on, idx)                                                      \
+  do {                                                                         \
+    if ((on) && (idx) < 64) g_tc_trace[64 + (idx)] = clock64();                \
+  } while (0)
+#else
+#define EB_TRACE(tile, slot) do { } while (0)
+#define EB_TRACE2(on, idx) do { } while (0)
+#endif
+
 // ------------------------------------------------------------------------------- PTX helpers
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {
   return (uint32_t)__cvta_generic_to_shared(p);
@@ -114,57 +130,120 @@ __device__ __forceinline__ uint64_t tile_desc(uint32_t addr) {
 
 struct TcMaps {
   CUtensorMap a_hi, a_lo, b_hi, b_lo;
+  CUtensorMap c;   // output, boxes of [32 rows][32 floats] (persistent kernel, when C allows 128-bit access)
 };
 
+// Bulk tensor store of one [32 rows][128 bytes] shared-memory box (128-byte swizzle) to C at
+// column x, row y; rows and columns beyond the array are clipped by the copy engine.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap *map, uint32_t src, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+               ::"l"(map), "r"(src), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_read0() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait0() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+__device__ __forceinline__ float4 lds128(uint32_t a) {
+  float4 v;
+  asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(a));
+  return v;
+}
+__device__ __forceinline__ void sts128(uint32_t a, float4 v) {
+  asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(a), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
+}
+
+// The fused epilogue on four consecutive columns n..n+3 of row m; `vec` says that the bias, the
+// activation-derivative source and C may be read with 128-bit loads at this position.
+__device__ __forceinline__ float4 apply_epilogue4(const EpiParams &e, float4 acc, int64_t m, int64_t n,
+                                                  const float *c_old, bool vec) {
+  if (!vec) {
+    float4 o;
+    o.x = apply_epilogue(e, acc.x, m, n + 0, c_old + 0);
+    o.y = apply_epilogue(e, acc.y, m, n + 1, c_old + 1);
+    o.z = apply_epilogue(e, acc.z, m, n + 2, c_old + 2);
+    o.w = apply_epilogue(e, acc.w, m, n + 3, c_old + 3);
+    return o;
+  }
+  float4 v = make_float4(e.alpha * acc.x, e.alpha * acc.y, e.alpha * acc.z, e.alpha * acc.w);
+  if (e.bias) {
+    const float4 b = __ldg(reinterpret_cast<const float4 *>(e.bias + n));
+    v.x += b.x; v.y += b.y; v.z += b.z; v.w += b.w;
+  }
+  if (e.act) { v.x = act_fwd(e.act, v.x); v.y = act_fwd(e.act, v.y); v.z = act_fwd(e.act, v.z); v.w = act_fwd(e.act, v.w); }
+  if (e.dact) {
+    const float4 d = __ldg(reinterpret_cast<const float4 *>(e.dact_src + m * e.ld_dact + n));
+    v.x *= act_bwd(e.dact, d.x); v.y *= act_bwd(e.dact, d.y); v.z *= act_bwd(e.dact, d.z); v.w *= act_bwd(e.dact, d.w);
+  }
+  if (e.beta != 0.f) {
+    const float4 c = *reinterpret_cast<const float4 *>(c_old);
+    v.x += e.beta * c.x; v.y += e.beta * c.y; v.z += e.beta * c.z; v.w += e.beta * c.w;
+  }
+  return v;
+}
+
 // Epilogue of one warp: rows of tensor-memory lane quarter q, column chunks [c_begin, c_end) of
-// 32 columns each. The two accumulators are added, the fused epilogue applied and the row segment
-// stored with 128-bit stores. The loads of the next chunk are in flight while a chunk is processed.
-template <int BN>
+// 32 columns each. tcgen05.ld hands each thread one ROW of the chunk; storing that directly would
+// touch 32 different rows per instruction. So the sum of the two accumulators goes through a
+// [32 rows][128 bytes] shared-memory buffer (16-byte units XOR-swizzled with the row, two buffers
+// per warp at `buf`, taken from the operand stages that are free by now) and is read back with
+// eight lanes along each row: every global access of the fused epilogue (C, the activation
+// source, the bias) then covers whole 128-byte lines. The tensor-memory loads of the next chunk
+// are in flight while a chunk is processed.
+template <int BN, bool DOUBLE_BUF = true>
 __device__ __forceinline__ void tc_epilogue_warp(uint32_t tmem_base, int q, int lane, int c_begin, int c_end,
                                                  int64_t m0, int64_t n0, int64_t M, int64_t N, float *Cout,
-                                                 int64_t ldc, const EpiParams &epi, bool vec_c) {
+                                                 int64_t ldc, const EpiParams &epi, bool vec_c, uint32_t buf,
+                                                 bool trace = false) {
+  (void)trace;
   const uint32_t row_addr = tmem_base + ((uint32_t)(q * 32) << 16);
-  const int64_t m = m0 + q * 32 + lane;
-  uint32_t a0[32], b0[32], a1[32], b1[32];
-  auto process = [&](uint32_t (&ra)[32], uint32_t (&rb)[32], int c) {
-    const int64_t nb = n0 + c * 32;
-    if (m >= M || nb >= N) return;
-    float *crow = Cout + m * ldc + nb;
-    if (vec_c && nb + 32 <= N) {
-#pragma unroll
-      for (int j = 0; j < 32; j += 4) {
-        float4 o;
-        o.x = apply_epilogue(epi, __uint_as_float(ra[j + 0]) + __uint_as_float(rb[j + 0]), m, nb + j + 0, crow + j + 0);
-        o.y = apply_epilogue(epi, __uint_as_float(ra[j + 1]) + __uint_as_float(rb[j + 1]), m, nb + j + 1, crow + j + 1);
-        o.z = apply_epilogue(epi, __uint_as_float(ra[j + 2]) + __uint_as_float(rb[j + 2]), m, nb + j + 2, crow + j + 2);
-        o.w = apply_epilogue(epi, __uint_as_float(ra[j + 3]) + __uint_as_float(rb[j + 3]), m, nb + j + 3, crow + j + 3);
-        *reinterpret_cast<float4 *>(crow + j) = o;
-      }
-    } else {
-#pragma unroll
-      for (int j = 0; j < 32; ++j)
-        if (nb + j < N)
-          crow[j] = apply_epilogue(epi, __uint_as_float(ra[j]) + __uint_as_float(rb[j]), m, nb + j, crow + j);
-    }
-  };
-  tc_ld32(row_addr + (uint32_t)(c_begin * 32), a0);
-  tc_ld32(row_addr + (uint32_t)(BN + c_begin * 32), b0);
+  const bool vec_epi = vec_c && (!epi.bias || (reinterpret_cast<uintptr_t>(epi.bias) & 15) == 0) &&
+                       (!epi.dact || ((reinterpret_cast<uintptr_t>(epi.dact_src) & 15) == 0 && epi.ld_dact % 4 == 0));
+  uint32_t ra[32], rb[32];
+  const int c4 = lane & 7, rsub = lane >> 3;
+  tc_ld32(row_addr + (uint32_t)(c_begin * 32), ra);
+  tc_ld32(row_addr + (uint32_t)(BN + c_begin * 32), rb);
 #pragma unroll 1
-  for (int c = c_begin; c < c_end; c += 2) {
+  for (int c = c_begin; c < c_end; ++c) {
+    const uint32_t bb = buf + (DOUBLE_BUF ? (uint32_t)(c & 1) * 4096u : 0u);
+    EB_TRACE2(trace, (c - c_begin) * 5 + 0);
     tc_wait_ld();
-    if (c + 1 < c_end) {
-      tc_ld32(row_addr + (uint32_t)((c + 1) * 32), a1);
-      tc_ld32(row_addr + (uint32_t)(BN + (c + 1) * 32), b1);
+    EB_TRACE2(trace, (c - c_begin) * 5 + 1);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      float4 v;
+      v.x = __uint_as_float(ra[4 * j + 0]) + __uint_as_float(rb[4 * j + 0]);
+      v.y = __uint_as_float(ra[4 * j + 1]) + __uint_as_float(rb[4 * j + 1]);
+      v.z = __uint_as_float(ra[4 * j + 2]) + __uint_as_float(rb[4 * j + 2]);
+      v.w = __uint_as_float(ra[4 * j + 3]) + __uint_as_float(rb[4 * j + 3]);
+      sts128(bb + (uint32_t)lane * 128u + (uint32_t)((j ^ (lane & 7)) * 16), v);
     }
-    process(a0, b0, c);
-    if (c + 1 < c_end) {
-      tc_wait_ld();
-      if (c + 2 < c_end) {
-        tc_ld32(row_addr + (uint32_t)((c + 2) * 32), a0);
-        tc_ld32(row_addr + (uint32_t)(BN + (c + 2) * 32), b0);
+    if (c + 1 < c_end) {   // in flight while this chunk goes out to global memory
+      tc_ld32(row_addr + (uint32_t)((c + 1) * 32), ra);
+      tc_ld32(row_addr + (uint32_t)(BN + (c + 1) * 32), rb);
+    }
+    EB_TRACE2(trace, (c - c_begin) * 5 + 2);
+    __syncwarp();
+    EB_TRACE2(trace, (c - c_begin) * 5 + 3);
+    const int64_t n = n0 + c * 32 + c4 * 4;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int r = rsub + 4 * i;
+      const int64_t m = m0 + q * 32 + r;
+      const float4 v = lds128(bb + (uint32_t)r * 128u + (uint32_t)((c4 ^ (r & 7)) * 16));
+      if (m >= M || n >= N) continue;
+      float *cp = Cout + m * ldc + n;
+      if (vec_c && n + 4 <= N) {
+        *reinterpret_cast<float4 *>(cp) = apply_epilogue4(epi, v, m, n, cp, vec_epi);
+      } else {
+        const float e[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int t = 0; t < 4; ++t)
+          if (n + t < N) cp[t] = apply_epilogue(epi, e[t], m, n + t, cp + t);
       }
-      process(a1, b1, c + 1);
     }
+    EB_TRACE2(trace, (c - c_begin) * 5 + 4);
+    if (!DOUBLE_BUF) __syncwarp();   // the buffer is rewritten by the next chunk
   }
 }
 
@@ -310,7 +389,8 @@ gemm_tc_kernel(const __grid_constant__ TcMaps maps, const GemmParams p, int tile
     const int64_t m = (int64_t)m0 + q * 32 + lane;
     if (ok && nkb > 0) {
       constexpr int CH = BN / 64;
-      tc_epilogue_warp<BN>(tmem_base, q, lane, half * CH, (half + 1) * CH, m0, n0, p.M, p.N, Cout, ldc, epi, vec_c);
+      tc_epilogue_warp<BN>(tmem_base, q, lane, half * CH, (half + 1) * CH, m0, n0, p.M, p.N, Cout, ldc, epi, vec_c,
+                           smem_base + (uint32_t)(warp - 2) * 8192u);
     } else if (ok && m < p.M && half == 0) {
       // K == 0: the product is empty, the epilogue applies to zeros.
       for (int64_t n = n0; n < n0 + BN && n < p.N; ++n)
@@ -367,42 +447,145 @@ __device__ __forceinline__ void tc_mma_tf32_pair(uint32_t d_tmem, uint64_t a_des
       ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
 }
 
+// Epilogue of one warp of the persistent kernel: like tc_epilogue_warp, but the finished
+// [32 x 32] chunk leaves shared memory through a bulk tensor store issued by one lane (the
+// register path of 128-bit stores drains a tile several times slower). The fused epilogue
+// runs in place on the shared-memory chunk with eight lanes along each row, so that its reads
+// of the activation source, the bias and C are coalesced; a plain product skips that pass.
+template <int BN>
+__device__ __forceinline__ void tc_epilogue_warp_bulk(uint32_t tmem_base, int q, int lane, int c_begin, int c_end,
+                                                      int64_t m0, int64_t n0, int64_t M, int64_t N, const float *Cout,
+                                                      int64_t ldc, const EpiParams &epi, const CUtensorMap *cmap,
+                                                      uint32_t buf, bool trace = false) {
+  (void)trace;
+  const uint32_t row_addr = tmem_base + ((uint32_t)(q * 32) << 16);
+  const bool plain = epi.alpha == 1.f && !epi.bias && !epi.act && !epi.dact && epi.beta == 0.f;
+  const bool vec_epi = (!epi.bias || (reinterpret_cast<uintptr_t>(epi.bias) & 15) == 0) &&
+                       (!epi.dact || ((reinterpret_cast<uintptr_t>(epi.dact_src) & 15) == 0 && epi.ld_dact % 4 == 0));
+  uint32_t ra[32], rb[32];
+  const int c4 = lane & 7, rsub = lane >> 3;
+  tc_ld32(row_addr + (uint32_t)(c_begin * 32), ra);
+  tc_ld32(row_addr + (uint32_t)(BN + c_begin * 32), rb);
+#pragma unroll 1
+  for (int c = c_begin; c < c_end; ++c) {
+    EB_TRACE2(trace, (c - c_begin) * 5 + 0);
+    tc_wait_ld();
+    // the previous chunk's store has read the buffer
+    if (lane == 0) bulk_wait_read0();
+    __syncwarp();
+    EB_TRACE2(trace, (c - c_begin) * 5 + 1);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      float4 v;
+      v.x = __uint_as_float(ra[4 * j + 0]) + __uint_as_float(rb[4 * j + 0]);
+      v.y = __uint_as_float(ra[4 * j + 1]) + __uint_as_float(rb[4 * j + 1]);
+      v.z = __uint_as_float(ra[4 * j + 2]) + __uint_as_float(rb[4 * j + 2]);
+      v.w = __uint_as_float(ra[4 * j + 3]) + __uint_as_float(rb[4 * j + 3]);
+      sts128(buf + (uint32_t)lane * 128u + (uint32_t)((j ^ (lane & 7)) * 16), v);
+    }
+    if (c + 1 < c_end) {   // in flight while this chunk is finished and stored
+      tc_ld32(row_addr + (uint32_t)((c + 1) * 32), ra);
+      tc_ld32(row_addr + (uint32_t)(BN + (c + 1) * 32), rb);
+    }
+    EB_TRACE2(trace, (c - c_begin) * 5 + 2);
+    const int64_t nb = n0 + c * 32;
+    if (!plain) {
+      __syncwarp();
+      const int64_t n = nb + c4 * 4;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int r = rsub + 4 * i;
+        const int64_t m = m0 + q * 32 + r;
+        const uint32_t a = buf + (uint32_t)r * 128u + (uint32_t)((c4 ^ (r & 7)) * 16);
+        if (m >= M || n >= N) continue;
+        float4 v = lds128(a);
+        const float *cp = Cout + m * ldc + n;
+        if (n + 4 <= N) {
+          v = apply_epilogue4(epi, v, m, n, cp, vec_epi);
+        } else {
+          float e[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+          for (int t = 0; t < 4; ++t)
+            if (n + t < N) e[t] = apply_epilogue(epi, e[t], m, n + t, cp + t);
+          v = make_float4(e[0], e[1], e[2], e[3]);
+        }
+        sts128(a, v);
+      }
+    }
+    fence_async_smem();
+    __syncwarp();
+    EB_TRACE2(trace, (c - c_begin) * 5 + 3);
+    if (lane == 0 && nb < N && m0 + q * 32 < M) {
+      tma_store_2d(cmap, buf, (int)nb, (int)(m0 + q * 32));
+      bulk_commit();
+    }
+    EB_TRACE2(trace, (c - c_begin) * 5 + 4);
+  }
+}
+
+// --------------------------------------------------------- persistent form of the two-CTA kernel
+// One CTA pair per SM pair walks over the 256 x 256 tiles t = pair, pair + pairs, ... The ring of
+// operand stages runs on across tile boundaries, so the loads of the next tile are in flight while
+// the epilogue warps drain tensor memory; the MMA issuer only waits until every epilogue warp of
+// both CTAs has read the accumulators ("acc_empty") before it overwrites them. What is saved per
+// tile: the CTA launch, the tensor-memory allocation, the barrier set-up and the empty pipeline.
+// The epilogue warps have 4 KB of shared memory each of their own (the stages are never free).
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
+}
+// Bounded wait that acquires at cluster scope (the arrivals come from both CTAs of the pair).
+__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, int code) {
+  for (uint32_t it = 0; it < TC_WAIT_LIMIT; ++it) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    if (ok) return true;
+  }
+  atomicCAS(&g_tc_status, 0, code);
+  return false;
+}
+
 template <bool A_MN, bool B_MN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(320, 1)
-gemm_tc2_kernel(const __grid_constant__ TcMaps maps, const GemmParams p, int pairs_m, int group_m) {
-  constexpr int BN = 256, BNH = 128, BK = 32, STAGES = 3;
+gemm_tc2p_kernel(const __grid_constant__ TcMaps maps, const GemmParams p, int pairs_m, int tiles_n, int group_m) {
+  constexpr int BN = 256, BNH = 128, BK = 32, STAGES = 3, EPI_WARPS = 8;
   extern __shared__ __align__(1024) uint8_t smem[];
-  constexpr uint32_t A_BYTES = TC_BM * BK * 4;      // this CTA's 128 rows of A
-  constexpr uint32_t B_BYTES = BNH * BK * 4;        // this CTA's half of the B tile
+  constexpr uint32_t A_BYTES = TC_BM * BK * 4;
+  constexpr uint32_t B_BYTES = BNH * BK * 4;
   constexpr uint32_t BOX_BYTES = BK * 128;
   constexpr uint32_t STAGE_BYTES = 2 * A_BYTES + 2 * B_BYTES;
   const uint32_t smem_base = (smem_u32(smem) + 1023u) & ~1023u;
-  const uint32_t bars = smem_base + STAGES * STAGE_BYTES;
+  const uint32_t epi_base = smem_base + STAGES * STAGE_BYTES;
+  const uint32_t bars = epi_base + EPI_WARPS * 4096u;
   __shared__ uint32_t tmem_slot;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();
   const bool leader = rank == 0;
-  // Tile order: groups of TC_GROUP_M row-pairs; inside a group the column tiles of one row-pair
-  // band follow each other, so the CTAs running at the same time share a few A bands and a few
-  // B tiles that fit in L2 together.
-  const int pair = blockIdx.x >> 1;
-  const int tiles_n = (int)((gridDim.x >> 1) / pairs_m);
-  const int group = pair / (group_m * tiles_n);
-  const int gm0 = group * group_m;
-  const int gh = pairs_m - gm0 < group_m ? pairs_m - gm0 : group_m;
-  const int rem = pair - group * (group_m * tiles_n);
-  const int tile_m = gm0 + rem % gh, tile_n = rem / gh;
-  const int m0 = tile_m * 256 + (int)rank * 128;
-  const int n0 = tile_n * BN, nh0 = n0 + (int)rank * BNH;
+  const int num_pairs = (int)(gridDim.x >> 1), pair_id = (int)(blockIdx.x >> 1);
+  const int num_tiles = pairs_m * tiles_n;
   const int nkb = (int)((p.K + BK - 1) / BK);
+  // Tile order: groups of group_m row-pairs; inside a group the column tiles of one row-pair band
+  // follow each other, so the pairs running at the same time share a few A bands and B tiles.
+  auto tile_origin = [&](int t, int &m0, int &n0) {
+    const int group = t / (group_m * tiles_n);
+    const int gm0 = group * group_m;
+    const int gh = pairs_m - gm0 < group_m ? pairs_m - gm0 : group_m;
+    const int rem = t - group * (group_m * tiles_n);
+    m0 = (gm0 + rem % gh) * 256 + (int)rank * 128;
+    n0 = (rem / gh) * BN;
+  };
   auto full_bar = [&](int s) { return bars + 8u * s; };
   auto empty_bar = [&](int s) { return bars + 8u * (STAGES + s); };
-  const uint32_t acc_bar = bars + 8u * (2 * STAGES);
+  const uint32_t acc_full = bars + 8u * (2 * STAGES), acc_empty = bars + 8u * (2 * STAGES + 1);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
-    mbar_init(acc_bar, 1);
+    mbar_init(acc_full, 1);
+    mbar_init(acc_empty, 2 * EPI_WARPS);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
@@ -417,79 +600,108 @@ gemm_tc2_kernel(const __grid_constant__ TcMaps maps, const GemmParams p, int pai
 
   if (warp == 0) {
     if (lane == 0) {
-      int issued = 0;
+      uint32_t it = 0;
       bool ok = true;
-      for (int kb = 0; kb < nkb && ok; ++kb) {
-        const int s = kb % STAGES;
-        if (kb >= STAGES) ok = mbar_wait(empty_bar(s), ((kb / STAGES) - 1) & 1, 11);
-        if (!ok) break;
-        const uint32_t st = smem_base + s * STAGE_BYTES;
-        if (leader) mbar_expect_tx(full_bar(s), 2 * STAGE_BYTES);   // both CTAs' bytes
-        const uint32_t fb = map_to_cta(full_bar(s), 0);
-        const int k0 = kb * BK;
-        if constexpr (A_MN) {
+      for (int t = pair_id; t < num_tiles && ok; t += num_pairs) {
+        int m0, n0;
+        tile_origin(t, m0, n0);
+        const int nh0 = n0 + (int)rank * BNH;
+        for (int kb = 0; kb < nkb; ++kb, ++it) {
+          const int s = (int)(it % STAGES);
+          if (it >= STAGES && !mbar_wait(empty_bar(s), ((it / STAGES) - 1) & 1, 31)) { ok = false; break; }
+          const uint32_t st = smem_base + s * STAGE_BYTES;
+          if (leader) mbar_expect_tx(full_bar(s), 2 * STAGE_BYTES);   // both CTAs' bytes
+          const uint32_t fb = map_to_cta(full_bar(s), 0);
+          const int k0 = kb * BK;
+          if constexpr (A_MN) {
 #pragma unroll
-          for (int j = 0; j < TC_BM / 32; ++j) {
-            tma_load_2d_pair(st + j * BOX_BYTES, &maps.a_hi, fb, m0 + 32 * j, k0);
-            tma_load_2d_pair(st + A_BYTES + j * BOX_BYTES, &maps.a_lo, fb, m0 + 32 * j, k0);
+            for (int j = 0; j < TC_BM / 32; ++j) {
+              tma_load_2d_pair(st + j * BOX_BYTES, &maps.a_hi, fb, m0 + 32 * j, k0);
+              tma_load_2d_pair(st + A_BYTES + j * BOX_BYTES, &maps.a_lo, fb, m0 + 32 * j, k0);
+            }
+          } else {
+            tma_load_2d_pair(st, &maps.a_hi, fb, k0, m0);
+            tma_load_2d_pair(st + A_BYTES, &maps.a_lo, fb, k0, m0);
           }
-        } else {
-          tma_load_2d_pair(st, &maps.a_hi, fb, k0, m0);
-          tma_load_2d_pair(st + A_BYTES, &maps.a_lo, fb, k0, m0);
-        }
-        const uint32_t sb = st + 2 * A_BYTES;
-        if constexpr (B_MN) {
+          const uint32_t sb = st + 2 * A_BYTES;
+          if constexpr (B_MN) {
 #pragma unroll
-          for (int j = 0; j < BNH / 32; ++j) {
-            tma_load_2d_pair(sb + j * BOX_BYTES, &maps.b_hi, fb, nh0 + 32 * j, k0);
-            tma_load_2d_pair(sb + B_BYTES + j * BOX_BYTES, &maps.b_lo, fb, nh0 + 32 * j, k0);
+            for (int j = 0; j < BNH / 32; ++j) {
+              tma_load_2d_pair(sb + j * BOX_BYTES, &maps.b_hi, fb, nh0 + 32 * j, k0);
+              tma_load_2d_pair(sb + B_BYTES + j * BOX_BYTES, &maps.b_lo, fb, nh0 + 32 * j, k0);
+            }
+          } else {
+            tma_load_2d_pair(sb, &maps.b_hi, fb, k0, nh0);
+            tma_load_2d_pair(sb + B_BYTES, &maps.b_lo, fb, k0, nh0);
           }
-        } else {
-          tma_load_2d_pair(sb, &maps.b_hi, fb, k0, nh0);
-          tma_load_2d_pair(sb + B_BYTES, &maps.b_lo, fb, k0, nh0);
         }
-        ++issued;
       }
-      (void)issued;
     }
   } else if (warp == 1) {
     if (lane == 0 && leader) {
-      // M = 256 over the pair, N = 256
       const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((A_MN ? 1u : 0u) << 15) |
                              ((B_MN ? 1u : 0u) << 16) | ((uint32_t)(BN >> 3) << 17) |
                              ((uint32_t)(256 >> 4) << 24);
-      for (int kb = 0; kb < nkb; ++kb) {
-        const int s = kb % STAGES;
-        if (!mbar_wait(full_bar(s), (kb / STAGES) & 1, 13)) break;
+      uint32_t it = 0;
+      int j = 0;
+      bool ok = true;
+      for (int t = pair_id; t < num_tiles && ok; t += num_pairs, ++j) {
+        // the epilogue warps of both CTAs have read the previous tile's accumulators
+        EB_TRACE(j, 0);
+        if (j > 0 && !mbar_wait_cluster(acc_empty, (uint32_t)(j - 1) & 1, 32)) break;
         tc_fence_after();
-        const uint32_t st = smem_base + s * STAGE_BYTES;
-        const uint64_t a_hi = tile_desc<A_MN, BK>(st), a_lo = tile_desc<A_MN, BK>(st + A_BYTES);
-        const uint32_t sb = st + 2 * A_BYTES;
-        const uint64_t b_hi = tile_desc<B_MN, BK>(sb), b_lo = tile_desc<B_MN, BK>(sb + B_BYTES);
-        constexpr uint64_t A_STEP = A_MN ? 64 : 2, B_STEP = B_MN ? 64 : 2;
+        EB_TRACE(j, 1);
+        for (int kb = 0; kb < nkb; ++kb, ++it) {
+          const int s = (int)(it % STAGES);
+          if (!mbar_wait(full_bar(s), (it / STAGES) & 1, 33)) { ok = false; break; }
+          tc_fence_after();
+          if (kb == 0) EB_TRACE(j, 2);
+          const uint32_t st = smem_base + s * STAGE_BYTES;
+          const uint64_t a_hi = tile_desc<A_MN, BK>(st), a_lo = tile_desc<A_MN, BK>(st + A_BYTES);
+          const uint32_t sb = st + 2 * A_BYTES;
+          const uint64_t b_hi = tile_desc<B_MN, BK>(sb), b_lo = tile_desc<B_MN, BK>(sb + B_BYTES);
+          constexpr uint64_t A_STEP = A_MN ? 64 : 2, B_STEP = B_MN ? 64 : 2;
 #pragma unroll
-        for (int ks = 0; ks < BK / 8; ++ks) {
-          const uint64_t ah = a_hi + ks * A_STEP, al = a_lo + ks * A_STEP;
-          const uint64_t bh = b_hi + ks * B_STEP, bl = b_lo + ks * B_STEP;
-          const uint32_t acc = (kb | ks) ? 1u : 0u;
-          tc_mma_tf32_pair(tmem_base + BN, al, bh, idesc, acc);
-          tc_mma_tf32_pair(tmem_base + BN, ah, bl, idesc, 1u);
-          tc_mma_tf32_pair(tmem_base, ah, bh, idesc, acc);
+          for (int ks = 0; ks < BK / 8; ++ks) {
+            const uint64_t ah = a_hi + ks * A_STEP, al = a_lo + ks * A_STEP;
+            const uint64_t bh = b_hi + ks * B_STEP, bl = b_lo + ks * B_STEP;
+            const uint32_t acc = (kb | ks) ? 1u : 0u;
+            tc_mma_tf32_pair(tmem_base + BN, al, bh, idesc, acc);
+            tc_mma_tf32_pair(tmem_base + BN, ah, bl, idesc, 1u);
+            tc_mma_tf32_pair(tmem_base, ah, bh, idesc, acc);
+          }
+          tc_commit_pair(empty_bar(s));
         }
-        tc_commit_pair(empty_bar(s));
+        tc_commit_pair(acc_full);   // also on the give-up path, so that the epilogue warps move on
+        EB_TRACE(j, 3);
       }
-      tc_commit_pair(acc_bar);
     }
   } else {
     const int q = warp & 3;
     const int half = (warp - 2) >> 2;
-    const bool ok = mbar_wait(acc_bar, 0, 14);
-    tc_fence_after();
-    if (ok && nkb > 0) {
+    const uint32_t acc_empty_leader = map_to_cta(acc_empty, 0);
+    int j = 0;
+    for (int t = pair_id; t < num_tiles; t += num_pairs, ++j) {
+      int m0, n0;
+      tile_origin(t, m0, n0);
+      if (!mbar_wait(acc_full, (uint32_t)j & 1, 34)) break;
+      tc_fence_after();
+      if (warp == 2 && lane == 0) EB_TRACE(j, 4);
       constexpr int CH = BN / 64;
-      tc_epilogue_warp<BN>(tmem_base, q, lane, half * CH, (half + 1) * CH, m0, n0, p.M, p.N, p.C, p.ldc, p.epi,
-                           p.vec_c);
+      if (p.vec_c)
+        tc_epilogue_warp_bulk<BN>(tmem_base, q, lane, half * CH, (half + 1) * CH, m0, n0, p.M, p.N, p.C, p.ldc,
+                                  p.epi, &maps.c, epi_base + (uint32_t)(warp - 2) * 4096u,
+                                  blockIdx.x == 0 && warp == 2 && lane == 0 && j == 1);
+      else
+        tc_epilogue_warp<BN, false>(tmem_base, q, lane, half * CH, (half + 1) * CH, m0, n0, p.M, p.N, p.C, p.ldc,
+                                    p.epi, p.vec_c, epi_base + (uint32_t)(warp - 2) * 4096u);
+      tc_fence_before();
+      __syncwarp();
+      if (warp == 2 && lane == 0) EB_TRACE(j, 5);
+      if (warp == 9 && lane == 0) EB_TRACE(j, 6);
+      if (lane == 0) mbar_arrive_cluster(acc_empty_leader);
     }
+    if (lane == 0) bulk_wait0();   // the stores have left shared memory and are complete
   }
   tc_fence_before();
   cluster_sync();
@@ -634,27 +846,46 @@ static bool pair_mode() {
   return on;
 }
 
-static int launch_pair(const TcMaps &maps, const GemmParams &p, int trans_a, int trans_b, cudaStream_t s) {
-  constexpr size_t SMEM = (size_t)3 * (2 * TC_BM * 32 * 4 + 2 * 128 * 32 * 4) + 1024 + 256;
+// Persistent two-CTA kernel: as many CTA pairs as can be resident, each walking over its tiles.
+static int launch_pair_persistent(const TcMaps &maps, const GemmParams &p, int trans_a, int trans_b,
+                                  cudaStream_t s) {
+  constexpr size_t SMEM = (size_t)3 * (2 * TC_BM * 32 * 4 + 2 * 128 * 32 * 4) + 8 * 4096 + 1024 + 256;
   const int pairs_m = (int)ceil_div(p.M, 256), tiles_n = (int)ceil_div(p.N, 256);
-  const dim3 grid((unsigned)(pairs_m * tiles_n * 2));
   static const int group_env = []() { const char *e = getenv("ENDIA_B200_TC_GROUP_M"); return e ? atoi(e) : TC_GROUP_M; }();
   const int group_m = group_env > 0 ? group_env : pairs_m;
-#define EB_TC2_LAUNCH(AM, BM_)                                                                    \
+#define EB_TC2P_LAUNCH(AM, BM_)                                                                   \
   do {                                                                                            \
-    auto kern = gemm_tc2_kernel<AM, BM_>;                                                         \
-    static bool attr = false;                                                                     \
-    if (!attr) {                                                                                  \
+    auto kern = gemm_tc2p_kernel<AM, BM_>;                                                        \
+    static int max_pairs = 0;                                                                     \
+    if (!max_pairs) {                                                                             \
       EB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM)); \
-      attr = true;                                                                                \
+      cudaLaunchConfig_t cfg = {};                                                                \
+      cfg.gridDim = dim3(2);                                                                      \
+      cfg.blockDim = dim3(320);                                                                   \
+      cfg.dynamicSmemBytes = SMEM;                                                                \
+      cudaLaunchAttribute at;                                                                     \
+      at.id = cudaLaunchAttributeClusterDimension;                                                \
+      at.val.clusterDim.x = 2; at.val.clusterDim.y = 1; at.val.clusterDim.z = 1;                  \
+      cfg.attrs = &at;                                                                            \
+      cfg.numAttrs = 1;                                                                           \
+      int nc = 0;                                                                                 \
+      if (cudaOccupancyMaxActiveClusters(&nc, kern, &cfg) != cudaSuccess || nc <= 0) {            \
+        cudaGetLastError();                                                                       \
+        int dev = 0, sms = 0;                                                                     \
+        cudaGetDevice(&dev);                                                                      \
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);                        \
+        nc = sms / 2;                                                                             \
+      }                                                                                           \
+      max_pairs = nc;                                                                             \
     }                                                                                             \
-    kern<<<grid, 320, SMEM, s>>>(maps, p, pairs_m, group_m);                                      \
+    const int pairs = pairs_m * tiles_n < max_pairs ? pairs_m * tiles_n : max_pairs;              \
+    kern<<<dim3((unsigned)(2 * pairs)), 320, SMEM, s>>>(maps, p, pairs_m, tiles_n, group_m);      \
   } while (0)
-  if (trans_a && !trans_b) EB_TC2_LAUNCH(true, true);
-  else if (trans_a && trans_b) EB_TC2_LAUNCH(true, false);
-  else if (!trans_a && !trans_b) EB_TC2_LAUNCH(false, true);
-  else EB_TC2_LAUNCH(false, false);
-#undef EB_TC2_LAUNCH
+  if (trans_a && !trans_b) EB_TC2P_LAUNCH(true, true);
+  else if (trans_a && trans_b) EB_TC2P_LAUNCH(true, false);
+  else if (!trans_a && !trans_b) EB_TC2P_LAUNCH(false, true);
+  else EB_TC2P_LAUNCH(false, false);
+#undef EB_TC2P_LAUNCH
   EB_LAUNCH_CHECK();
   return ENDIA_B200_OK;
 }
@@ -720,7 +951,13 @@ int launch_gemm_tc(const GemmParams &p, int trans_a, int trans_b, cudaStream_t s
   if ((st = make_map(&maps.a_lo, a_lo, a_cols, a_rows, a_lo_ld, a_bi, a_bo, trans_a != 0))) return st;
   if ((st = make_map(&maps.b_hi, p.B, b_cols, b_rows, p.ldb, b_bi, b_bo, trans_b == 0))) return st;
   if ((st = make_map(&maps.b_lo, b_lo, b_cols, b_rows, b_lo_ld, b_bi, b_bo, trans_b == 0))) return st;
-  if (pair) st = launch_pair(maps, p, trans_a, trans_b, s);
+  if (pair && p.vec_c) {
+    // output map: [M][N] floats with leading dimension ldc, boxes of 32 rows x 32 floats
+    if ((st = make_map(&maps.c, p.C, p.N, p.M, p.ldc, 32, 32, false))) return st;
+  } else {
+    maps.c = maps.a_hi;
+  }
+  if (pair) st = launch_pair_persistent(maps, p, trans_a, trans_b, s);
   else if (bn == 256 && bk == 16) st = launch_variant<256, 16, 4>(maps, p, trans_a, trans_b, s);
   else if (bn == 256) st = launch_variant<256, 32, 2>(maps, p, trans_a, trans_b, s);
   else if (bk == 16) st = launch_variant<128, 16, 6>(maps, q, trans_a, trans_b, s, splits);
@@ -746,6 +983,12 @@ int tc_status_and_clear(cudaStream_t s) {
 }
 
 }  // namespace eb
+
+#ifdef EB_TC_TRACE
+extern "C" int endia_b200_debug_tc_trace(long long *out128) {
+  return cudaMemcpyFromSymbol(out128, eb::g_tc_trace, sizeof(long long) * 128) == cudaSuccess ? 0 : 1;
+}
+#endif
 
 extern "C" int endia_b200_has_tcgen05(void) { return eb::encode_fn() != nullptr ? 1 : 0; }
 

@@ -145,6 +145,28 @@ def _batch_stride(a, batch):
     return base
 
 
+_LO_CACHE_MIN = 1 << 20
+
+
+def _tf32_lo_ptr(x):
+    """Device address of the tf32 low part matching operand view `x`, or None. The low part of a
+    whole storage buffer is valid for every view of it. Leaves (user inputs, parameters) are not
+    cached here: their storage may be rewritten by the caller between steps."""
+    base = x.base()
+    if base.buf is None or x.buf is not base.buf or base.is_complex():
+        return None
+    lo = getattr(base, "_tf32_lo", None)
+    if lo is None or base._tf32_lo_ptr != base.buf.data_ptr():
+        n = base.buf.numel()
+        if base.name == "arg" or n < _LO_CACHE_MIN or n % 4 or not _state.cache_tf32_lo:
+            return None
+        lo = alloc(n)
+        _lib.call("endia_b200_tf32_split", base.buf.data_ptr(), lo.data_ptr(), 1, n, n, n, stream())
+        base._tf32_lo = lo
+        base._tf32_lo_ptr = base.buf.data_ptr()
+    return lo.data_ptr() + (x.data_ptr() - base.buf.data_ptr())
+
+
 def gemm_arrays(a, b, out, epi=None, algo=None):
     """out = a @ b over the last two dims; a and b are already expanded over the batch dims.
     Transposed views are passed as such (no materialised copy, unlike matmul_op.mojo:107-136)."""
@@ -169,16 +191,16 @@ def gemm_arrays(a, b, out, epi=None, algo=None):
         _lib.call("endia_b200_gemm_complex", la[0], lb[0], M, N, K, a.data_ptr(), la[1], b.data_ptr(),
                   lb[1], out.data_ptr(), N, nbatch, sa, sb, M * N, stream())
         return
-    # A weight whose tf32 low part was written by the optimizer (valid while its storage has not
-    # been rewritten since): hand it to the 3xTF32 kernel instead of recomputing it per product.
-    base = b.base()
-    lo = getattr(base, "_tf32_lo", None)
-    if lo is not None and nbatch == 1 and b.storage_offset() == 0 and base._tf32_lo_ptr == base.buf.data_ptr() \
-            and b.buf is base.buf:
-        if epi is None:
-            epi = _lib.Epilogue()
-            epi.alpha = 1.0
-        epi.b_lo = lo.data_ptr()
+    # tf32 low parts kept beside an operand's storage (written by the optimizer for weights, computed
+    # here once for the result of an op, which is used by two products: the next layer's forward
+    # and a weight gradient): handed to the 3xTF32 kernel instead of being recomputed per product.
+    if nbatch == 1 and algo != _lib.GEMM_FFMA and M >= 128 and N >= 128 and 32 <= K <= 8192:
+        a_lo, b_lo = _tf32_lo_ptr(a), _tf32_lo_ptr(b)
+        if a_lo or b_lo:
+            if epi is None:
+                epi = _lib.Epilogue()
+                epi.alpha = 1.0
+            epi.a_lo, epi.b_lo = a_lo, b_lo
     timer = _state.gemm_timer
     if timer is not None:
         timer.start(2.0 * M * N * K * nbatch)

@@ -72,6 +72,7 @@ def linear(x, weight, bias=None, activation=None):
         if act or need_db:
             ds = Array(ArrayShape([B, N])) if act else g
             if act:
+                ds.name = "linear_vjp"   # a temporary of this pass, never rewritten (see _tf32_lo_ptr)
                 setup_shape_and_data(ds)
             if need_db:
                 db = Array(ArrayShape([1, N]))  # kept dim, like Expand.vjp's reduce_add

@@ -38,3 +38,51 @@ def remove_grad_rec(out):
 def zero_grad_rec(out):
     """general.mojo:44-47; like the reference this removes the gradients."""
     remove_grad_rec(out)
+
+
+class HostBatchFeeder:
+    """Feeds host batches to the device through two sets of device arrays and a copy stream: while
+    a step computes on one set, the next batch is copied into the other. `host` is a list of pinned
+    torch tensors (one per input); next() returns the list of device Arrays holding the batch it
+    was last asked to stage and starts staging the following one."""
+
+    def __init__(self, host, shapes):
+        import torch
+        from .._array import Array, device
+        self._torch = torch
+        self.host = host
+        self.sets = [[Array(list(s)) for s in shapes] for _ in range(2)]
+        self.copy_stream = torch.cuda.Stream(device=device())
+        self.ready = [None, None]
+        self.last_use = [None, None]
+        self.cur = 0
+
+    def _stage(self, idx):
+        torch = self._torch
+        if self.last_use[idx] is not None:
+            self.copy_stream.wait_event(self.last_use[idx])   # the set's last readers are done
+        with torch.cuda.stream(self.copy_stream):
+            for arr, h in zip(self.sets[idx], self.host):
+                arr.buf[:h.numel()].copy_(h.reshape(-1), non_blocking=True)
+            ev = torch.cuda.Event()
+            ev.record(self.copy_stream)
+        self.ready[idx] = ev
+
+    def next(self):
+        torch = self._torch
+        # everything enqueued so far includes all readers of the set handed out last time
+        ev = torch.cuda.Event()
+        ev.record(torch.cuda.current_stream())
+        self.last_use[self.cur ^ 1] = ev
+        if self.ready[self.cur] is None:
+            self._stage(self.cur)
+        torch.cuda.current_stream().wait_event(self.ready[self.cur])
+        self.ready[self.cur] = None
+        out = self.sets[self.cur]
+        self.cur ^= 1
+        return out
+
+    def prefetch(self):
+        """Start the copy of the following batch (call after the step's kernels are enqueued)."""
+        if self.ready[self.cur] is None:
+            self._stage(self.cur)
