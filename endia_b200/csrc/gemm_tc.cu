@@ -139,6 +139,11 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap *map, uint32_t sr
   asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
                ::"l"(map), "r"(src), "r"(x), "r"(y) : "memory");
 }
+// The same box added (fp32) to what C holds.
+__device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap *map, uint32_t src, int x, int y) {
+  asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];"
+               ::"l"(map), "r"(src), "r"(x), "r"(y) : "memory");
+}
 __device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void bulk_wait_read0() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
 __device__ __forceinline__ void bulk_wait0() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
@@ -456,7 +461,7 @@ template <int BN>
 __device__ __forceinline__ void tc_epilogue_warp_bulk(uint32_t tmem_base, int q, int lane, int c_begin, int c_end,
                                                       int64_t m0, int64_t n0, int64_t M, int64_t N, const float *Cout,
                                                       int64_t ldc, const EpiParams &epi, const CUtensorMap *cmap,
-                                                      uint32_t buf, bool trace = false) {
+                                                      uint32_t buf, bool reduce, bool trace = false) {
   (void)trace;
   const uint32_t row_addr = tmem_base + ((uint32_t)(q * 32) << 16);
   const bool plain = epi.alpha == 1.f && !epi.bias && !epi.act && !epi.dact && epi.beta == 0.f;
@@ -516,7 +521,8 @@ __device__ __forceinline__ void tc_epilogue_warp_bulk(uint32_t tmem_base, int q,
     __syncwarp();
     EB_TRACE2(trace, (c - c_begin) * 5 + 3);
     if (lane == 0 && nb < N && m0 + q * 32 < M) {
-      tma_store_2d(cmap, buf, (int)nb, (int)(m0 + q * 32));
+      if (reduce) tma_reduce_add_2d(cmap, buf, (int)nb, (int)(m0 + q * 32));
+      else tma_store_2d(cmap, buf, (int)nb, (int)(m0 + q * 32));
       bulk_commit();
     }
     EB_TRACE2(trace, (c - c_begin) * 5 + 4);
@@ -550,7 +556,8 @@ __device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity,
 
 template <bool A_MN, bool B_MN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(320, 1)
-gemm_tc2p_kernel(const __grid_constant__ TcMaps maps, const GemmParams p, int pairs_m, int tiles_n, int group_m) {
+gemm_tc2p_kernel(const __grid_constant__ TcMaps maps, const GemmParams p, int pairs_m, int tiles_n, int group_m,
+                 int ksplit) {
   constexpr int BN = 256, BNH = 128, BK = 32, STAGES = 3, EPI_WARPS = 8;
   extern __shared__ __align__(1024) uint8_t smem[];
   constexpr uint32_t A_BYTES = TC_BM * BK * 4;
@@ -566,11 +573,21 @@ gemm_tc2p_kernel(const __grid_constant__ TcMaps maps, const GemmParams p, int pa
   const uint32_t rank = cluster_ctarank();
   const bool leader = rank == 0;
   const int num_pairs = (int)(gridDim.x >> 1), pair_id = (int)(blockIdx.x >> 1);
-  const int num_tiles = pairs_m * tiles_n;
-  const int nkb = (int)((p.K + BK - 1) / BK);
+  // Work items: every tile once per K range (ksplit = 2 halves the reduction so that a tile count
+  // that fills the last round of pairs badly is balanced; the halves are then added into a zeroed
+  // C by the copy engine, and two addends give the same sum in either order).
+  const int num_tiles = pairs_m * tiles_n * ksplit;
+  const int tiles_mn = pairs_m * tiles_n;
+  const int nkb_all = (int)((p.K + BK - 1) / BK);
+  auto k_range = [&](int t, int &kb0, int &nkb) {
+    const int part = t / tiles_mn, per = nkb_all / ksplit;
+    kb0 = part * per;
+    nkb = part == ksplit - 1 ? nkb_all - kb0 : per;
+  };
   // Tile order: groups of group_m row-pairs; inside a group the column tiles of one row-pair band
   // follow each other, so the pairs running at the same time share a few A bands and B tiles.
-  auto tile_origin = [&](int t, int &m0, int &n0) {
+  auto tile_origin = [&](int w, int &m0, int &n0) {
+    const int t = w % tiles_mn;
     const int group = t / (group_m * tiles_n);
     const int gm0 = group * group_m;
     const int gh = pairs_m - gm0 < group_m ? pairs_m - gm0 : group_m;
@@ -603,8 +620,9 @@ gemm_tc2p_kernel(const __grid_constant__ TcMaps maps, const GemmParams p, int pa
       uint32_t it = 0;
       bool ok = true;
       for (int t = pair_id; t < num_tiles && ok; t += num_pairs) {
-        int m0, n0;
+        int m0, n0, kb0, nkb;
         tile_origin(t, m0, n0);
+        k_range(t, kb0, nkb);
         const int nh0 = n0 + (int)rank * BNH;
         for (int kb = 0; kb < nkb; ++kb, ++it) {
           const int s = (int)(it % STAGES);
@@ -612,7 +630,7 @@ gemm_tc2p_kernel(const __grid_constant__ TcMaps maps, const GemmParams p, int pa
           const uint32_t st = smem_base + s * STAGE_BYTES;
           if (leader) mbar_expect_tx(full_bar(s), 2 * STAGE_BYTES);   // both CTAs' bytes
           const uint32_t fb = map_to_cta(full_bar(s), 0);
-          const int k0 = kb * BK;
+          const int k0 = (kb0 + kb) * BK;
           if constexpr (A_MN) {
 #pragma unroll
             for (int j = 0; j < TC_BM / 32; ++j) {
@@ -651,6 +669,8 @@ gemm_tc2p_kernel(const __grid_constant__ TcMaps maps, const GemmParams p, int pa
         if (j > 0 && !mbar_wait_cluster(acc_empty, (uint32_t)(j - 1) & 1, 32)) break;
         tc_fence_after();
         EB_TRACE(j, 1);
+        int kb0, nkb;
+        k_range(t, kb0, nkb);
         for (int kb = 0; kb < nkb; ++kb, ++it) {
           const int s = (int)(it % STAGES);
           if (!mbar_wait(full_bar(s), (it / STAGES) & 1, 33)) { ok = false; break; }
@@ -690,7 +710,7 @@ gemm_tc2p_kernel(const __grid_constant__ TcMaps maps, const GemmParams p, int pa
       constexpr int CH = BN / 64;
       if (p.vec_c)
         tc_epilogue_warp_bulk<BN>(tmem_base, q, lane, half * CH, (half + 1) * CH, m0, n0, p.M, p.N, p.C, p.ldc,
-                                  p.epi, &maps.c, epi_base + (uint32_t)(warp - 2) * 4096u,
+                                  p.epi, &maps.c, epi_base + (uint32_t)(warp - 2) * 4096u, ksplit > 1,
                                   blockIdx.x == 0 && warp == 2 && lane == 0 && j == 1);
       else
         tc_epilogue_warp<BN, false>(tmem_base, q, lane, half * CH, (half + 1) * CH, m0, n0, p.M, p.N, p.C, p.ldc,
@@ -846,9 +866,14 @@ static bool pair_mode() {
   return on;
 }
 
+static bool ksplit_mode() {
+  static const bool on = []() { const char *e = getenv("ENDIA_B200_TC_KSPLIT"); return !(e && atoi(e) == 0); }();
+  return on;
+}
+
 // Persistent two-CTA kernel: as many CTA pairs as can be resident, each walking over its tiles.
 static int launch_pair_persistent(const TcMaps &maps, const GemmParams &p, int trans_a, int trans_b,
-                                  cudaStream_t s) {
+                                  cudaStream_t s, int ksplit_max) {
   constexpr size_t SMEM = (size_t)3 * (2 * TC_BM * 32 * 4 + 2 * 128 * 32 * 4) + 8 * 4096 + 1024 + 256;
   const int pairs_m = (int)ceil_div(p.M, 256), tiles_n = (int)ceil_div(p.N, 256);
   static const int group_env = []() { const char *e = getenv("ENDIA_B200_TC_GROUP_M"); return e ? atoi(e) : TC_GROUP_M; }();
@@ -878,8 +903,21 @@ static int launch_pair_persistent(const TcMaps &maps, const GemmParams &p, int t
       }                                                                                           \
       max_pairs = nc;                                                                             \
     }                                                                                             \
-    const int pairs = pairs_m * tiles_n < max_pairs ? pairs_m * tiles_n : max_pairs;              \
-    kern<<<dim3((unsigned)(2 * pairs)), 320, SMEM, s>>>(maps, p, pairs_m, tiles_n, group_m);      \
+    const int tiles = pairs_m * tiles_n;                                                          \
+    int ksplit = 1;                                                                               \
+    if (ksplit_max >= 2 && tiles > max_pairs) {                                                   \
+      /* rounds of pairs with and without halving K, in units of half tiles */                    \
+      const int r1 = 2 * ((tiles + max_pairs - 1) / max_pairs);                                   \
+      const int r2 = (2 * tiles + max_pairs - 1) / max_pairs;                                     \
+      if (r2 * 100 <= r1 * 95) ksplit = 2;                                                        \
+    }                                                                                             \
+    if (ksplit > 1) {                                                                             \
+      if (p.ldc == p.N) EB_CUDA(cudaMemsetAsync(p.C, 0, sizeof(float) * p.M * p.N, s));           \
+      else EB_CUDA(cudaMemset2DAsync(p.C, sizeof(float) * p.ldc, 0, sizeof(float) * p.N, p.M, s)); \
+    }                                                                                             \
+    const int items = tiles * ksplit;                                                             \
+    const int pairs = items < max_pairs ? items : max_pairs;                                      \
+    kern<<<dim3((unsigned)(2 * pairs)), 320, SMEM, s>>>(maps, p, pairs_m, tiles_n, group_m, ksplit); \
   } while (0)
   if (trans_a && !trans_b) EB_TC2P_LAUNCH(true, true);
   else if (trans_a && trans_b) EB_TC2P_LAUNCH(true, false);
@@ -957,7 +995,11 @@ int launch_gemm_tc(const GemmParams &p, int trans_a, int trans_b, cudaStream_t s
   } else {
     maps.c = maps.a_hi;
   }
-  if (pair) st = launch_pair_persistent(maps, p, trans_a, trans_b, s);
+  // Halving K needs the bulk-store epilogue, a product that is linear in the accumulator and a
+  // reduction long enough for the second pass over C to be cheap.
+  const bool linear_epi = !p.epi.bias && !p.epi.act && !p.epi.dact && p.epi.beta == 0.f;
+  if (pair) st = launch_pair_persistent(maps, p, trans_a, trans_b, s,
+                                        (p.vec_c && linear_epi && p.K >= 4096 && ksplit_mode()) ? 2 : 1);
   else if (bn == 256 && bk == 16) st = launch_variant<256, 16, 4>(maps, p, trans_a, trans_b, s);
   else if (bn == 256) st = launch_variant<256, 32, 2>(maps, p, trans_a, trans_b, s);
   else if (bk == 16) st = launch_variant<128, 16, 6>(maps, q, trans_a, trans_b, s, splits);

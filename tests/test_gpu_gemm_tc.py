@@ -50,6 +50,31 @@ def test_3xtf32_all_layouts(nd, ta, tb, M, N, K):
     assert max_rel(out, ffma) < 1e-4
 
 
+@pytest.mark.parametrize("ta,tb,alpha", [(1, 0, 1.0), (0, 1, 0.5)])
+def test_3xtf32_halved_reduction(nd, ta, tb, alpha):
+    """81 tiles of 256 x 256 fill the last round of CTA pairs badly: the persistent kernel halves K
+    and the two halves are added into a zeroed C by the copy engine. The result must not depend on
+    which half lands first, so two runs agree bit for bit; C starts out as garbage."""
+    from endia_b200 import _lib
+    r = rng(77)
+    M = N = 2304
+    K = 4096
+    a = r.standard_normal((K, M) if ta else (M, K)).astype(np.float32)
+    b = r.standard_normal((N, K) if tb else (K, N)).astype(np.float32)
+    epi = _lib.Epilogue()
+    epi.alpha, epi.beta = alpha, 0.0
+    junk = np.full((M, N), 1e30, np.float32)
+    out = run_gemm(nd, a, b, ta, tb, _lib.GEMM_3XTF32, epi=epi, c0=junk)
+    out2 = run_gemm(nd, a, b, ta, tb, _lib.GEMM_3XTF32, epi=epi, c0=junk)
+    assert np.array_equal(out, out2)
+    am = (a.T if ta else a).astype(np.float64)
+    bm = (b.T if tb else b).astype(np.float64)
+    rows = slice(0, M, 7)        # every 7th row keeps the float64 product short
+    ref = alpha * (am[rows] @ bm)
+    err = np.abs(out[rows] - ref) / dot_scale(am[rows], bm)
+    assert err.max() < 5e-6, err.max()
+
+
 def test_3xtf32_fused_epilogue(nd):
     from endia_b200 import _lib
     r = rng(5)
