@@ -572,9 +572,9 @@ def main():
                      # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant GEMM shape
                      # (8192 x 4096 x 4096, the forward and dX products of the 4096-wide layers), from
                      # the committed ncu capture; the other shapes of the step were not captured
-                     "traffic": 1.38e9 if (tc and world == 1) else None,
-                     "traffic_note": "bytes per launch of gemm_tc2_kernel at 8192x4096x4096 (ncu, "
-                                     "profiles/gemm_tc2_8192x4096x4096_ncu.md); compulsory 0.51e9",
+                     "traffic": 1.49e9 if (tc and world == 1) else None,
+                     "traffic_note": "bytes per launch of gemm_tc2p_kernel at 8192x4096x4096 (ncu, "
+                                     "profiles/gemm_tc2p_8192x4096x4096_ncu.md); compulsory 0.51e9",
                      "kernel": "gemm (%d launches, %.1f%% of the step)" % (
                          n_gemm, 100.0 * gemm_ms / ms_total if ms_total else 0.0),
                      "peak_note": "%s bf16_tflops_sustained %.1f / 2 (tf32 rate) / 3 (MMAs per 3xTF32 product)" % (
