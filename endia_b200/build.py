@@ -93,7 +93,7 @@ def _compile(digest, stamp, verbose):
             sys.stderr.write("nvcc failed on %s\n" % src)
     if failed:
         raise RuntimeError("building libendia_b200.so failed")
-    link = [nvcc, "-Wno-deprecated-gpu-targets", "-shared", "-o", LIBPATH] + objs + ["-lcudart"]
+    link = [nvcc, "-Wno-deprecated-gpu-targets", "-shared", "-o", LIBPATH] + objs + ["-lcudart", "-ldl"]
     subprocess.check_call(link)
     with open(stamp, "w") as fh:
         fh.write(digest)

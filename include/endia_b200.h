@@ -316,6 +316,29 @@ int endia_b200_fft_c2c(const endia_b200_tensor *in, const endia_b200_tensor *out
                        const int32_t *dims, int32_t n_dims, int inverse, float scale,
                        void *scratch, void *stream);
 
+/* ------------------------------------------------------------- collectives ---- */
+
+/* One NCCL communicator per (process, device); libnccl.so.2 is opened at first use
+ * (ENDIA_B200_ENODEV when it cannot be). The reference has no communication layer
+ * (single-process, single-threaded graph walk, endia/autograd/functional.mojo:26-67); these are the
+ * two exchange steps of its sharded forms: the sum of the per-rank gradients of a data-parallel
+ * train step (matmul_vjp's dW, endia/functional/binary_ops/matmul_op.mojo:278-284, summed before
+ * Adam.step, endia/optim/adam.mojo:47-65) and the slab transpose between the axes of fftn
+ * (the per-dimension gather of endia/functional/fft_ops/fft_cooley_tukey.mojo:251-257).
+ *   comm_unique_id: rank 0 fills a 128-byte id and hands it to the other ranks by any host channel.
+ *   comm_init:      collective over the ranks; endia_b200_init must have selected the device.
+ *   allreduce_sum_f32: recv[i] = sum over ranks of send[i]; send == recv allowed.
+ *   alltoall_bytes: block p (bytes_per_peer bytes) of `send` goes to rank p, whose block with this
+ *                   rank's index lands in block p of `recv`; send and recv must not overlap.
+ * All calls are ordered on `stream`. */
+#define ENDIA_B200_COMM_ID_BYTES 128
+int endia_b200_comm_unique_id(void *id128);
+int endia_b200_comm_init(int32_t rank, int32_t nranks, const void *id128, void **comm_out);
+int endia_b200_comm_destroy(void *comm);
+int endia_b200_allreduce_sum_f32(void *comm, const float *send, float *recv, int64_t count, void *stream);
+int endia_b200_alltoall_bytes(void *comm, const void *send, void *recv, int64_t bytes_per_peer,
+                              void *stream);
+
 #ifdef __cplusplus
 }
 #endif

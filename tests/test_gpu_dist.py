@@ -131,3 +131,85 @@ def test_data_parallel_step_matches_single_gpu(nd, oracle, tmp_path):
             tiny = np.abs(g_ref.reshape(p_ref.shape)) < 1e-6     # Adam's step is discontinuous at g = 0
             assert max_rel(np.where(tiny, p_ref, a), p_ref) < 1e-4
             assert np.abs(a - p_ref).max() <= 2.5e-3
+
+
+_ABI_COMM_WORKER = r'''
+import os, sys, ctypes as C, numpy as np
+sys.path.insert(0, %(root)r)
+rank, world, idfile = int(sys.argv[1]), int(sys.argv[2]), sys.argv[3]
+os.environ["LOCAL_RANK"] = str(rank)
+import endia_b200 as nd
+from endia_b200 import _lib
+from endia_b200._array import stream
+nd._array.device()
+ident = (C.c_ubyte * 128)()
+if rank == 0:
+    _lib.call("endia_b200_comm_unique_id", ident)
+    with open(idfile + ".tmp", "wb") as f:
+        f.write(bytes(ident))
+    os.replace(idfile + ".tmp", idfile)
+else:
+    import time
+    for _ in range(600):
+        if os.path.exists(idfile):
+            break
+        time.sleep(0.1)
+    C.memmove(ident, open(idfile, "rb").read(), 128)
+comm = C.c_void_p()
+_lib.call("endia_b200_comm_init", rank, world, ident, C.byref(comm))
+n = 1 << 20
+x = nd.Array(np.full(n, rank + 1, np.float32) + np.arange(n, dtype=np.float32) %% 7)
+y = nd.Array([n])
+_lib.call("endia_b200_allreduce_sum_f32", comm, x.data_ptr(), y.data_ptr(), n, stream())
+want = sum(np.full(n, r + 1, np.float32) + np.arange(n, dtype=np.float32) %% 7 for r in range(world))
+ok1 = bool(np.array_equal(y.to_numpy(), want))
+blk = 4096
+send = nd.Array((np.arange(world * blk, dtype=np.float32) + 1000.0 * rank))
+recv = nd.Array([world * blk])
+_lib.call("endia_b200_alltoall_bytes", comm, send.data_ptr(), recv.data_ptr(), blk * 4, stream())
+got = recv.to_numpy().reshape(world, blk)
+ok2 = all(np.array_equal(got[p], np.arange(rank * blk, (rank + 1) * blk, dtype=np.float32) + 1000.0 * p)
+          for p in range(world))
+st = _lib.lib.endia_b200_alltoall_bytes(comm, send.data_ptr(), send.data_ptr(), blk * 4, stream())
+_lib.call("endia_b200_comm_destroy", comm)
+print("RESULT", rank, ok1, ok2, st == _lib.EINVAL, flush=True)
+'''
+
+
+def test_c_abi_collectives_two_ranks(nd, tmp_path):
+    """endia_b200_comm_init / allreduce_sum_f32 / alltoall_bytes between two processes that share
+    nothing but the 128-byte id (written to a file by rank 0)."""
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    script = tmp_path / "comm_worker.py"
+    script.write_text(_ABI_COMM_WORKER % {"root": ROOT})
+    idfile = str(tmp_path / "nccl_id.bin")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    env.pop("LOCAL_RANK", None)
+    procs = [subprocess.Popen([sys.executable, str(script), str(r), "2", idfile], stdout=subprocess.PIPE,
+                              stderr=subprocess.PIPE, text=True, env=env) for r in range(2)]
+    outs = [p.communicate(timeout=300) for p in procs]
+    lines = [l.split() for o, _ in outs for l in o.splitlines() if l.startswith("RESULT")]
+    assert len(lines) == 2, "\n".join(o + e for o, e in outs)
+    for l in lines:
+        assert l[2:] == ["True", "True", "True"], lines
+
+
+def test_c_abi_collectives_single_rank(nd):
+    """With one rank the sum is the input and the exchange is a copy; bad arguments are refused."""
+    import ctypes as C
+    from endia_b200 import _lib
+    from endia_b200._array import stream
+    ident = (C.c_ubyte * 128)()
+    _lib.call("endia_b200_comm_unique_id", ident)
+    comm = C.c_void_p()
+    assert _lib.lib.endia_b200_comm_init(1, 1, ident, C.byref(comm)) == _lib.EINVAL
+    _lib.call("endia_b200_comm_init", 0, 1, ident, C.byref(comm))
+    x = rng(3).standard_normal(5000).astype(np.float32)
+    X, Y, Z = nd.Array(x), nd.Array([5000]), nd.Array([5000])
+    _lib.call("endia_b200_allreduce_sum_f32", comm, X.data_ptr(), Y.data_ptr(), 5000, stream())
+    _lib.call("endia_b200_alltoall_bytes", comm, X.data_ptr(), Z.data_ptr(), 5000 * 4, stream())
+    assert np.array_equal(Y.to_numpy(), x) and np.array_equal(Z.to_numpy(), x)
+    assert _lib.lib.endia_b200_allreduce_sum_f32(None, X.data_ptr(), Y.data_ptr(), 5000, stream()) == _lib.EINVAL
+    _lib.call("endia_b200_comm_destroy", comm)
