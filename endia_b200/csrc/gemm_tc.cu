@@ -901,7 +901,11 @@ static int launch_pair_persistent(const TcMaps &maps, const GemmParams &p, int t
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);                        \
         nc = sms / 2;                                                                             \
       }                                                                                           \
-      max_pairs = nc;                                                                             \
+      /* SMs left free for kernels that run beside the GEMMs (a collective on another stream): a \
+         pair that cannot become resident would otherwise start its share of the tiles late */    \
+      const char *rs = getenv("ENDIA_B200_TC_RESERVE_SMS");                                       \
+      const int reserve = rs ? atoi(rs) / 2 : 0;                                                  \
+      max_pairs = nc - reserve >= 8 ? nc - reserve : (nc >= 8 ? 8 : nc);                          \
     }                                                                                             \
     const int tiles = pairs_m * tiles_n;                                                          \
     int ksplit = 1;                                                                               \

@@ -12,6 +12,11 @@ from ._array import Array, ArrayShape, device
 def init_process_group():
     """One process per GPU, launched by torchrun (RANK / LOCAL_RANK / WORLD_SIZE / MASTER_*)."""
     world = int(os.environ.get("WORLD_SIZE", "1"))
+    if world > 1:
+        # The gradient all-reduce runs beside the backward GEMMs: keep NCCL to 16 CTAs and leave
+        # 16 SMs out of the persistent GEMM grid, so that neither waits for the other's SMs.
+        os.environ.setdefault("NCCL_MAX_CTAS", "16")
+        os.environ.setdefault("ENDIA_B200_TC_RESERVE_SMS", "16")
     if world > 1 and not dist.is_initialized():
         backend = "nccl" if torch.cuda.is_available() else "gloo"
         if backend == "nccl":
