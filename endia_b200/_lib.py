@@ -111,6 +111,12 @@ SIGNATURES = {
                                   [_vp, _i32, _f32, _f32, _f32, _f32, _f32, _vp]),
     "endia_b200_fft_scratch_bytes": (_sz, [_TP, C.POINTER(_i32), _i32]),
     "endia_b200_fft_c2c": (C.c_int, [_TP, _TP, C.POINTER(_i32), _i32, C.c_int, _f32, _vp, _vp]),
+    "endia_b200_sgd_step_multi": (C.c_int, [_i32, C.POINTER(_vp), C.POINTER(_vp), C.POINTER(_vp),
+                                            C.POINTER(_i64), _f32, _f32, _f32, _f32, _vp]),
+    "endia_b200_rmsprop_step_multi": (C.c_int, [_i32, C.POINTER(_vp), C.POINTER(_vp), C.POINTER(_vp),
+                                                C.POINTER(_i64), _f32, _f32, _f32, _f32, _vp]),
+    "endia_b200_adagrad_step_multi": (C.c_int, [_i32, C.POINTER(_vp), C.POINTER(_vp), C.POINTER(_vp),
+                                                C.POINTER(_i64), _f32, _f32, _f32, _vp]),
     "endia_b200_comm_unique_id": (C.c_int, [_vp]),
     "endia_b200_comm_init": (C.c_int, [_i32, _i32, _vp, C.POINTER(_vp)]),
     "endia_b200_comm_destroy": (C.c_int, [_vp]),

@@ -299,6 +299,24 @@ int endia_b200_adam_step_multi_lo(int32_t n_tensors, float *const *params, const
                                   const int64_t *numel, float lr, float beta1, float beta2, float eps,
                                   float t, float grad_scale, void *stream);
 
+/* The other optimizers of the reference as single multi-tensor launches, same conventions as
+ * endia_b200_adam_step_multi (flat numel per tensor, gradients multiplied by grad_scale first):
+ *   sgd      (endia/optim/sgd.mojo:40-63): g' = g + weight_decay * p when weight_decay > 0;
+ *            momentum > 0: velocity = momentum * velocity - lr * g', p += velocity (`velocity`
+ *            required); momentum == 0: p -= lr * g' (`velocity` may be NULL)
+ *   rmsprop  (endia/optim/rmsprop.mojo:39-53): cache = alpha * cache + (1 - alpha) * g * g,
+ *            p -= lr * g / (sqrt(cache) + eps)
+ *   adagrad  (endia/optim/adagrad.mojo:36-45): cache += g * g, p -= lr * g / (sqrt(cache) + eps) */
+int endia_b200_sgd_step_multi(int32_t n_tensors, float *const *params, const float *const *grads,
+                              float *const *velocity, const int64_t *numel, float lr, float momentum,
+                              float weight_decay, float grad_scale, void *stream);
+int endia_b200_rmsprop_step_multi(int32_t n_tensors, float *const *params, const float *const *grads,
+                                  float *const *cache, const int64_t *numel, float lr, float alpha,
+                                  float eps, float grad_scale, void *stream);
+int endia_b200_adagrad_step_multi(int32_t n_tensors, float *const *params, const float *const *grads,
+                                  float *const *cache, const int64_t *numel, float lr, float eps,
+                                  float grad_scale, void *stream);
+
 /* --------------------------------------------------------------------- FFT ---- */
 
 /* Complex-to-complex FFT over the listed dims of `in` (contiguous or strided, complex) into

@@ -245,6 +245,7 @@ def test_fused_small_mlp_step_rejects_large_networks(nd):
 
 
 @pytest.mark.parametrize("name,kw", [("SGD", {"lr": 0.1}), ("SGD", {"lr": 0.1, "momentum": 0.9, "weight_decay": 0.01}),
+                                     ("SGD", {"lr": 0.1, "weight_decay": 0.01}), ("SGD", {"lr": 0.1, "momentum": 0.9}),
                                      ("RMSprop", {"lr": 0.01}), ("Adagrad", {"lr": 0.1})])
 def test_other_optimizers_vs_torch(nd, name, kw):
     """SGD / RMSprop / Adagrad over two steps against torch.optim with the same hyper-parameters."""
@@ -268,3 +269,38 @@ def test_other_optimizers_vs_torch(nd, name, kw):
         ((torch.tensor(x) @ tw) ** 2).sum().backward()
         topt.step()
     assert max_rel(W.to_numpy(), tw.detach().numpy()) < 1e-4
+
+
+@pytest.mark.parametrize("name", ["SGD", "RMSprop", "Adagrad"])
+def test_fused_optimizers_multi_tensor_formulas(nd, name):
+    """One launch over a weight (odd size, so the scalar tail runs), and a bias whose gradient is
+    (1, N): two steps against the reference's fp32 expressions evaluated in numpy, state shapes
+    included (sgd.mojo:40-63, rmsprop.mojo:39-53, adagrad.mojo:36-45)."""
+    r = rng(11)
+    f32 = np.float32
+    w, b = r.standard_normal((37, 29)).astype(f32), r.standard_normal(29).astype(f32)
+    W, B = nd.Array(w.copy(), requires_grad=True), nd.Array(b.copy(), requires_grad=True)
+    kw = {"SGD": dict(lr=0.05, momentum=0.9, weight_decay=0.01), "RMSprop": dict(lr=0.01, alpha=0.9, eps=1e-8),
+          "Adagrad": dict(lr=0.1, eps=1e-10)}[name]
+    opt = getattr(nd.optim, name)([W, B], **kw)
+    sw, sb = np.zeros_like(w), np.zeros((1, 29), f32)
+    for step in range(2):
+        gw = r.standard_normal((37, 29)).astype(f32)
+        gb = r.standard_normal((1, 29)).astype(f32)
+        W.grad_(nd.Array(gw))
+        B.grad_(nd.Array(gb))
+        opt.step()
+        for (p, g, s) in ((w, gw, sw), (b.reshape(1, 29), gb, sb)):
+            if name == "SGD":
+                s[...] = f32(0.9) * s - f32(0.05) * (g + f32(0.01) * p)
+                p += s
+            elif name == "RMSprop":
+                s[...] = f32(0.9) * s + (f32(1) - f32(0.9)) * g * g
+                p -= f32(0.01) * g / (np.sqrt(s) + f32(1e-8))
+            else:
+                s[...] = s + g * g
+                p -= f32(0.1) * g / (np.sqrt(s) + f32(1e-10))
+    state = opt.velocity if name == "SGD" else opt.cache
+    assert state[1].shape() == [1, 29] and B.shape() == [29]
+    assert max_rel(W.to_numpy(), w) < 1e-5 and max_rel(B.to_numpy(), b) < 1e-5
+    assert max_rel(state[0].to_numpy(), sw) < 1e-5 and max_rel(state[1].to_numpy(), sb) < 1e-5
