@@ -304,3 +304,56 @@ def test_fused_optimizers_multi_tensor_formulas(nd, name):
     assert state[1].shape() == [1, 29] and B.shape() == [29]
     assert max_rel(W.to_numpy(), w) < 1e-5 and max_rel(B.to_numpy(), b) < 1e-5
     assert max_rel(state[0].to_numpy(), sw) < 1e-5 and max_rel(state[1].to_numpy(), sb) < 1e-5
+
+
+BENCH_DIMS = [1, 32, 64, 128, 128, 128, 64, 32, 1]
+
+
+def _bench_inputs():
+    """Network and data of the reference's own benchmark programs
+    (benchmarks/mlp_benchmarks/mlp_imp.mojo:20-37): batch 128, x ~ U[0, 1), y = sin(50 (x + 1) / 2)."""
+    Ws, bs, x, _ = make_mlp_inputs(BENCH_DIMS, 128, 21, x_dist="uniform")
+    y = np.sin(np.float32(50) * (x + np.float32(1)) / np.float32(2)).astype(np.float32)
+    return Ws, bs, x, y
+
+
+def test_reference_benchmark_mlp_imperative(nd, oracle):
+    """mlp_imp.mojo:35-75: nn.MLP of the benchmark's depth, mse, backward, Adam.step, three steps."""
+    Ws, bs, x, y = _bench_inputs()
+    g = train_step(nd, fwd_fused("relu"), Ws, bs, x, y, steps=3)
+    o = train_step(oracle, fwd_unfused("relu"), Ws, bs, x, y, steps=3)
+    compare_steps(g, o)
+
+
+def test_reference_benchmark_mlp_functional(nd, oracle):
+    """mlp_func.mojo:86-131: value_and_grad of a pure forward function over the argument list
+    [x, y, W1, b1, ...] and Adam written as array expressions with in-place updates."""
+    Ws, bs, x, y = _bench_inputs()
+    args = [nd.Array(x), nd.Array(y)]
+    for w, b in zip(Ws, bs):
+        args += [nd.Array(w.copy()), nd.Array(b.copy())]
+
+    def fwd(a):
+        return nd.mse(nd.nn.mlp([a[0], None] + list(a[2:]), activation="relu"), a[1])
+
+    vag = nd.value_and_grad(fwd)
+    f32 = np.float32
+    lr, b1, b2, eps = 1e-3, 0.9, 0.999, 1e-8
+    m = [nd.Array(a.shape()) for a in args]
+    v = [nd.Array(a.shape()) for a in args]
+    loss = None
+    for t in range(1, 3):
+        res = vag(args)
+        loss, grads = res[0][0], res[1]
+        for i in range(2, len(args)):
+            m[i] = b1 * m[i] + float(f32(1) - f32(b1)) * grads[i]
+            v[i] = b2 * v[i] + float(f32(1) - f32(b2)) * grads[i] * grads[i]
+            m_hat = m[i] / float(f32(1) - f32(b1) ** f32(t))
+            v_hat = v[i] / float(f32(1) - f32(b2) ** f32(t))
+            args[i] -= lr * m_hat / (nd.sqrt(v_hat) + eps)
+    o = train_step(oracle, fwd_unfused("relu"), Ws, bs, x, y, steps=2)
+    assert abs(loss.to_numpy()[0] - o["loss"][0]) <= TOL * abs(o["loss"][0])
+    for i, (a, ref, gr) in enumerate(zip(args[2:], o["params"], o["grads"])):
+        tiny = np.abs(gr.reshape(ref.shape)) < 1e-6
+        got = a.to_numpy().reshape(ref.shape)
+        assert max_rel(np.where(tiny, ref, got), ref) < TOL, i
