@@ -42,6 +42,14 @@ def alloc(n_floats):
     return torch.empty(max(int(n_floats), 0), dtype=torch.float32, device=device())
 
 
+def drop_operand_parts(arr):
+    """Forget the cached GEMM operand parts (tf32 low part, bf16 split) of an array whose storage
+    has just been rewritten in place."""
+    base = arr.base()
+    base._tf32_lo = None
+    base._pair16 = None
+
+
 def compute_stride(shape):
     """Row-major element strides (endia/utils/_array_shape.mojo:24-30)."""
     stride = [1] * len(shape)

@@ -46,13 +46,15 @@ class Epilogue(C.Structure):
         ("colsum_scratch", C.c_void_p),
         ("a_lo", C.c_void_p),
         ("b_lo", C.c_void_p),
+        ("a16", C.c_void_p),
+        ("b16", C.c_void_p),
     ]
 
 
 # status codes
 OK, EINVAL, ECUDA, ENODEV, ENOMEM, ESHAPE, EPOW2, ETIMEOUT, ELIMIT = 0, -1, -2, -3, -4, -5, -6, -7, -8
 ACT_NONE, ACT_RELU, ACT_TANH, ACT_SIGMOID = 0, 1, 2, 3
-GEMM_AUTO, GEMM_FFMA, GEMM_3XTF32 = 0, 1, 2
+GEMM_AUTO, GEMM_FFMA, GEMM_3XTF32, GEMM_TF32_BF16X2 = 0, 1, 2, 3
 (UN_COPY, UN_NEG, UN_RELU, UN_TANH, UN_SIGMOID, UN_SQUARE, UN_SQRT, UN_ABS, UN_SIGN, UN_CONJ,
  UN_EXP, UN_LOG, UN_SIN, UN_COS, UN_RECIPROCAL) = range(15)
 (BIN_ADD, BIN_SUB, BIN_MUL, BIN_DIV, BIN_POW, BIN_GREATER, BIN_RELU_BWD, BIN_TANH_BWD,
@@ -107,6 +109,10 @@ SIGNATURES = {
     "endia_b200_adam_step_multi_lo": (C.c_int, [_i32, C.POINTER(_vp), C.POINTER(_vp), C.POINTER(_vp),
                                                 C.POINTER(_vp), C.POINTER(_vp), C.POINTER(_i64), _f32, _f32,
                                                 _f32, _f32, _f32, _f32, _vp]),
+    "endia_b200_adam_step_multi_bf16": (C.c_int, [_i32, C.POINTER(_vp), C.POINTER(_vp), C.POINTER(_vp),
+                                                  C.POINTER(_vp), C.POINTER(_vp), C.POINTER(_i64), _f32, _f32,
+                                                  _f32, _f32, _f32, _f32, _vp]),
+    "endia_b200_bf16_split": (C.c_int, [_vp, _vp, _i64, _vp]),
     "endia_b200_mlp_small_step": (C.c_int, [_i32, C.POINTER(_i32), _i32, _i32, _vp, _vp] + [C.POINTER(_vp)] * 8 +
                                   [_vp, _i32, _f32, _f32, _f32, _f32, _f32, _vp]),
     "endia_b200_fft_scratch_bytes": (_sz, [_TP, C.POINTER(_i32), _i32]),

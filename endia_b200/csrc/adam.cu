@@ -4,6 +4,7 @@
 // (endia/optim/adagrad.mojo:36-45); the operation order inside an element follows the reference
 // so that fp32 results agree to rounding.
 #include "common.cuh"
+#include <cuda_bf16.h>
 
 namespace eb {
 
@@ -15,7 +16,8 @@ struct AdamArgs {
   const float *g[ADAM_MAX_TENSORS];
   float *m[ADAM_MAX_TENSORS];
   float *v[ADAM_MAX_TENSORS];
-  float *lo[ADAM_MAX_TENSORS];   // optional: tf32 low part of the updated parameter
+  float *lo[ADAM_MAX_TENSORS];   // optional: tf32 low part of the updated parameter, or its bf16 split
+  int lo_is_bf16;                // lo[t] holds [numel bf16(p)][numel bf16(p - tf32(p))] instead
   int64_t chunk_start[ADAM_MAX_TENSORS + 1];  // prefix sum of chunks per tensor
   int64_t numel[ADAM_MAX_TENSORS];
   int n;
@@ -120,19 +122,41 @@ __global__ void __launch_bounds__(256) adam_kernel(const __grid_constant__ AdamA
         *reinterpret_cast<float4 *>(p + i) = pp;
         *reinterpret_cast<float4 *>(m + i) = mm;
         *reinterpret_cast<float4 *>(v + i) = vv;
-        if (lo) {
+        if (lo && !a.lo_is_bf16) {
           lo[i + 0] = tf32_lo(pp.x); lo[i + 1] = tf32_lo(pp.y);
           lo[i + 2] = tf32_lo(pp.z); lo[i + 3] = tf32_lo(pp.w);
+        } else if (lo) {
+          __nv_bfloat16 *h16 = reinterpret_cast<__nv_bfloat16 *>(lo), *l16 = h16 + n;
+          __nv_bfloat162 h01 = __floats2bfloat162_rn(pp.x, pp.y), h23 = __floats2bfloat162_rn(pp.z, pp.w);
+          __nv_bfloat162 l01 = __floats2bfloat162_rn(tf32_lo(pp.x), tf32_lo(pp.y));
+          __nv_bfloat162 l23 = __floats2bfloat162_rn(tf32_lo(pp.z), tf32_lo(pp.w));
+          uint2 hv, lv;
+          hv.x = *reinterpret_cast<uint32_t *>(&h01); hv.y = *reinterpret_cast<uint32_t *>(&h23);
+          lv.x = *reinterpret_cast<uint32_t *>(&l01); lv.y = *reinterpret_cast<uint32_t *>(&l23);
+          *reinterpret_cast<uint2 *>(h16 + i) = hv;
+          *reinterpret_cast<uint2 *>(l16 + i) = lv;
         }
       }
       for (int64_t i = v1 + threadIdx.x; i < e1; i += 256) {
         adam_one(p[i], g[i], m[i], v[i], a);
-        if (lo) lo[i] = tf32_lo(p[i]);
+        if (lo && !a.lo_is_bf16) {
+          lo[i] = tf32_lo(p[i]);
+        } else if (lo) {
+          __nv_bfloat16 *h16 = reinterpret_cast<__nv_bfloat16 *>(lo);
+          h16[i] = __float2bfloat16_rn(p[i]);
+          h16[n + i] = __float2bfloat16_rn(tf32_lo(p[i]));
+        }
       }
     } else {
       for (int64_t i = e0 + threadIdx.x; i < e1; i += 256) {
         adam_one(p[i], g[i], m[i], v[i], a);
-        if (lo) lo[i] = tf32_lo(p[i]);
+        if (lo && !a.lo_is_bf16) {
+          lo[i] = tf32_lo(p[i]);
+        } else if (lo) {
+          __nv_bfloat16 *h16 = reinterpret_cast<__nv_bfloat16 *>(lo);
+          h16[i] = __float2bfloat16_rn(p[i]);
+          h16[n + i] = __float2bfloat16_rn(tf32_lo(p[i]));
+        }
       }
     }
   }
@@ -142,11 +166,9 @@ __global__ void __launch_bounds__(256) adam_kernel(const __grid_constant__ AdamA
 
 using namespace eb;
 
-extern "C" int endia_b200_adam_step_multi_lo(int32_t n_tensors, float *const *params,
-                                             const float *const *grads, float *const *m,
-                                             float *const *v, float *const *p_lo, const int64_t *numel,
-                                             float lr, float beta1, float beta2, float eps, float t,
-                                             float grad_scale, void *stream) {
+static int adam_launch(int32_t n_tensors, float *const *params, const float *const *grads, float *const *m,
+                       float *const *v, float *const *p_lo, int lo_is_bf16, const int64_t *numel, float lr,
+                       float beta1, float beta2, float eps, float t, float grad_scale, void *stream) {
   int st = require_device();
   if (st) return st;
   EB_REQUIRE(n_tensors >= 0, ENDIA_B200_EINVAL, "adam: negative tensor count");
@@ -164,12 +186,16 @@ extern "C" int endia_b200_adam_step_multi_lo(int32_t n_tensors, float *const *pa
                  "adam: NULL pointer for tensor %d", i);
       a.p[a.n] = params[i]; a.g[a.n] = grads[i]; a.m[a.n] = m[i]; a.v[a.n] = v[i];
       a.lo[a.n] = p_lo ? p_lo[i] : nullptr;
+      EB_REQUIRE(!(lo_is_bf16 && a.lo[a.n]) || (numel[i] % 8 == 0 && (reinterpret_cast<uintptr_t>(params[i]) & 15) == 0 &&
+                                                (reinterpret_cast<uintptr_t>(a.lo[a.n]) & 15) == 0),
+                 ENDIA_B200_EINVAL, "adam: the bf16 split needs numel %% 8 == 0 and 16-byte aligned arrays (tensor %d)", i);
       a.numel[a.n] = numel[i];
       a.chunk_start[a.n + 1] = a.chunk_start[a.n] + ceil_div(numel[i], ADAM_CHUNK);
       ++a.n;
     }
     if (a.n == 0) continue;
     a.lr = lr; a.b1 = beta1; a.b2 = beta2; a.eps = eps; a.gscale = grad_scale;
+    a.lo_is_bf16 = lo_is_bf16;
     // fp32 scalars exactly as the reference forms them (adam.mojo:50, 54, 57-58).
     a.omb1 = 1.f - beta1;
     a.omb2 = 1.f - beta2;
@@ -182,6 +208,23 @@ extern "C" int endia_b200_adam_step_multi_lo(int32_t n_tensors, float *const *pa
     EB_LAUNCH_CHECK();
   }
   return ENDIA_B200_OK;
+}
+
+extern "C" int endia_b200_adam_step_multi_lo(int32_t n_tensors, float *const *params,
+                                             const float *const *grads, float *const *m,
+                                             float *const *v, float *const *p_lo, const int64_t *numel,
+                                             float lr, float beta1, float beta2, float eps, float t,
+                                             float grad_scale, void *stream) {
+  return adam_launch(n_tensors, params, grads, m, v, p_lo, 0, numel, lr, beta1, beta2, eps, t, grad_scale, stream);
+}
+
+extern "C" int endia_b200_adam_step_multi_bf16(int32_t n_tensors, float *const *params,
+                                               const float *const *grads, float *const *m,
+                                               float *const *v, void *const *p16, const int64_t *numel,
+                                               float lr, float beta1, float beta2, float eps, float t,
+                                               float grad_scale, void *stream) {
+  return adam_launch(n_tensors, params, grads, m, v, reinterpret_cast<float *const *>(p16), 1, numel, lr, beta1,
+                     beta2, eps, t, grad_scale, stream);
 }
 
 extern "C" int endia_b200_adam_step_multi(int32_t n_tensors, float *const *params,

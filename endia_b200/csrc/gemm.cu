@@ -30,7 +30,7 @@ int endia_b200_gemm(int trans_a, int trans_b, int64_t M, int64_t N, int64_t K, c
              (long long)ldb, (long long)ldc);
   EB_REQUIRE(stride_a >= 0 && stride_b >= 0 && stride_c >= 0, ENDIA_B200_EINVAL,
              "gemm: negative batch stride");
-  EB_REQUIRE(algo >= ENDIA_B200_GEMM_AUTO && algo <= ENDIA_B200_GEMM_3XTF32, ENDIA_B200_EINVAL,
+  EB_REQUIRE(algo >= ENDIA_B200_GEMM_AUTO && algo <= ENDIA_B200_GEMM_TF32_BF16X2, ENDIA_B200_EINVAL,
              "gemm: unknown algo %d", algo);
   GemmParams p{};
   p.A = A; p.B = B; p.C = C;
@@ -46,6 +46,7 @@ int endia_b200_gemm(int trans_a, int trans_b, int64_t M, int64_t N, int64_t K, c
     p.epi.act = epi->act; p.epi.dact = epi->dact; p.epi.dact_src = epi->dact_src;
     p.epi.ld_dact = epi->ld_dact;
     p.a_lo = epi->a_lo; p.b_lo = epi->b_lo;
+    p.a16 = epi->a16; p.b16 = epi->b16;
     EB_REQUIRE(epi->act >= 0 && epi->act <= ENDIA_B200_ACT_SIGMOID && epi->dact >= 0 &&
                    epi->dact <= ENDIA_B200_ACT_SIGMOID, ENDIA_B200_EINVAL, "gemm: unknown activation");
     EB_REQUIRE(epi->dact == 0 || (epi->dact_src && epi->ld_dact >= N), ENDIA_B200_EINVAL,
@@ -61,7 +62,14 @@ int endia_b200_gemm(int trans_a, int trans_b, int64_t M, int64_t N, int64_t K, c
   cudaStream_t s = as_stream(stream);
   bool use_tc = false;
   if (algo != ENDIA_B200_GEMM_FFMA) {
-    use_tc = tc_gemm_supported(p, trans_a, trans_b, batch, algo == ENDIA_B200_GEMM_3XTF32);
+    use_tc = tc_gemm_supported(p, trans_a, trans_b, batch, algo != ENDIA_B200_GEMM_AUTO);
+    // AUTO takes the bf16-compensated scheme where the two-CTA kernel applies (N >= 256).
+    p.scheme_forced = algo != ENDIA_B200_GEMM_AUTO;
+    p.scheme = algo == ENDIA_B200_GEMM_3XTF32 ? 0 : (algo == ENDIA_B200_GEMM_TF32_BF16X2 ? 1 : tc_default_scheme());
+    if (N < 256) {
+      EB_REQUIRE(algo != ENDIA_B200_GEMM_TF32_BF16X2, ENDIA_B200_EINVAL, "gemm: TF32_BF16X2 needs N >= 256");
+      p.scheme = 0;
+    }
     EB_REQUIRE(use_tc || algo == ENDIA_B200_GEMM_AUTO, ENDIA_B200_EINVAL,
                "gemm: the 3xTF32 tcgen05 kernel does not take this shape/alignment "
                "(M %lld N %lld K %lld batch %lld)", (long long)M, (long long)N, (long long)K,
@@ -78,6 +86,17 @@ int endia_b200_gemm(int trans_a, int trans_b, int64_t M, int64_t N, int64_t K, c
 }
 
 }  // extern "C"
+
+extern "C" int endia_b200_bf16_split(const float *x, void *pair16, int64_t numel, void *stream) {
+  int st = require_device();
+  if (st) return st;
+  EB_REQUIRE(numel >= 0, ENDIA_B200_EINVAL, "bf16_split: negative size");
+  if (numel == 0) return ENDIA_B200_OK;
+  EB_REQUIRE(x && pair16 && numel % 8 == 0 && aligned16(x) && aligned16(pair16), ENDIA_B200_EINVAL,
+             "bf16_split: numel must be a multiple of 8 and the pointers 16-byte aligned");
+  return launch_bf16_split(x, pair16, static_cast<char *>(pair16) + 2 * numel, 1, numel, numel, numel,
+                           as_stream(stream));
+}
 
 extern "C" int endia_b200_tf32_split(const float *x, float *lo, int64_t rows, int64_t cols, int64_t ld_in,
                                      int64_t ld_out, void *stream) {

@@ -25,6 +25,11 @@ struct GemmParams {
   int64_t ld_partial;
   // optional precomputed tf32 low parts, laid out like A / B
   const float *a_lo, *b_lo;
+  // optional precomputed bf16 splits of the operands' storage (endia_b200_bf16_split)
+  const void *a16, *b16;
+  // 0 = 3xTF32, 1 = one tf32 MMA + two bf16 correction MMAs per product
+  int scheme;
+  bool scheme_forced;   // the caller named the algorithm (GEMM_AUTO may fall back to 3xTF32 split-K)
 };
 
 __device__ __forceinline__ float act_fwd(int act, float v) {
@@ -64,11 +69,16 @@ bool skinny_gemm_supported(const GemmParams &p, int trans_b, int64_t batch);
 int launch_gemm_skinny(const GemmParams &p, int trans_a, int trans_b, cudaStream_t s);
 int launch_tf32_split(const float *x, float *lo, int64_t rows, int64_t cols, int64_t ld_in, int64_t ld_out,
                       cudaStream_t s);
+// hi16 = bf16(x), lo16 = bf16(x - tf32(x)) for rows of `cols` floats (cols % 4 == 0).
+int launch_bf16_split(const float *x, void *hi16, void *lo16, int64_t rows, int64_t cols, int64_t ld_in,
+                      int64_t ld_out, cudaStream_t s);
 // C = epilogue(sum over `splits` slices of p.partial, in order).
 int launch_splitk_finish(const GemmParams &p, int splits, cudaStream_t s);
 // tcgen05 3xTF32 path: true when the shape/alignment is one it handles.
 bool tc_gemm_supported(const GemmParams &p, int trans_a, int trans_b, int64_t batch,
                        bool explicit_request);
 int launch_gemm_tc(const GemmParams &p, int trans_a, int trans_b, cudaStream_t s);
+// Scheme GEMM_AUTO uses on the two-CTA kernel (1 unless ENDIA_B200_TC_SCHEME=3xtf32).
+int tc_default_scheme();
 
 }  // namespace eb

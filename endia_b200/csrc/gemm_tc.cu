@@ -21,6 +21,7 @@
 #include "common.cuh"
 #include "gemm.cuh"
 #include <cuda.h>
+#include <cuda_bf16.h>
 #include <stdlib.h>
 
 namespace eb {
@@ -130,6 +131,7 @@ __device__ __forceinline__ uint64_t tile_desc(uint32_t addr) {
 
 struct TcMaps {
   CUtensorMap a_hi, a_lo, b_hi, b_lo;
+  CUtensorMap a16h, a16l, b16h, b16l;   // bf16 parts of the operands (bf16-compensated scheme)
   CUtensorMap c;   // output, boxes of [32 rows][32 floats] (persistent kernel, when C allows 128-bit access)
 };
 
@@ -452,6 +454,22 @@ __device__ __forceinline__ void tc_mma_tf32_pair(uint32_t d_tmem, uint64_t a_des
       ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
 }
 
+__device__ __forceinline__ void tc_mma_bf16_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                                 uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// bf16 tiles of 32 k: K-major rows of 64 bytes (64-byte swizzle, 8-row groups 512 bytes apart);
+// MN-major boxes of [32 k][64 rows] (128 bytes per k-row, 128-byte swizzle, 8 k-rows per atom,
+// boxes 4096 bytes apart).
+template <bool MN_MAJOR>
+__device__ __forceinline__ uint64_t tile_desc16(uint32_t addr) {
+  return MN_MAJOR ? smem_desc(addr, 4096, 1024, 2) : smem_desc(addr, 16, 512, 4);
+}
+
 // Epilogue of one warp of the persistent kernel: like tc_epilogue_warp, but the finished
 // [32 x 32] chunk leaves shared memory through a bulk tensor store issued by one lane (the
 // register path of 128-bit stores drains a tile several times slower). The fused epilogue
@@ -554,7 +572,11 @@ __device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity,
   return false;
 }
 
-template <bool A_MN, bool B_MN>
+// SCHEME 0: 3xTF32, the stage holds the fp32 tile and its fp32 low part of each operand.
+// SCHEME 1: the stage holds the fp32 tile (tf32 MMA hi*hi into the main accumulator) and two bf16
+// tiles of half its size, bf16(x) and bf16(x - tf32(x)); the two correction products are bf16
+// MMAs (K = 16 per instruction, so two per 32 k) into the second accumulator.
+template <bool A_MN, bool B_MN, int SCHEME>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(320, 1)
 gemm_tc2p_kernel(const __grid_constant__ TcMaps maps, const GemmParams p, int pairs_m, int tiles_n, int group_m,
                  int ksplit) {
@@ -631,26 +653,56 @@ gemm_tc2p_kernel(const __grid_constant__ TcMaps maps, const GemmParams p, int pa
           if (leader) mbar_expect_tx(full_bar(s), 2 * STAGE_BYTES);   // both CTAs' bytes
           const uint32_t fb = map_to_cta(full_bar(s), 0);
           const int k0 = (kb0 + kb) * BK;
+          const uint32_t sb = st + 2 * A_BYTES;
           if constexpr (A_MN) {
 #pragma unroll
-            for (int j = 0; j < TC_BM / 32; ++j) {
-              tma_load_2d_pair(st + j * BOX_BYTES, &maps.a_hi, fb, m0 + 32 * j, k0);
-              tma_load_2d_pair(st + A_BYTES + j * BOX_BYTES, &maps.a_lo, fb, m0 + 32 * j, k0);
-            }
+            for (int j = 0; j < TC_BM / 32; ++j) tma_load_2d_pair(st + j * BOX_BYTES, &maps.a_hi, fb, m0 + 32 * j, k0);
           } else {
             tma_load_2d_pair(st, &maps.a_hi, fb, k0, m0);
-            tma_load_2d_pair(st + A_BYTES, &maps.a_lo, fb, k0, m0);
           }
-          const uint32_t sb = st + 2 * A_BYTES;
           if constexpr (B_MN) {
 #pragma unroll
-            for (int j = 0; j < BNH / 32; ++j) {
-              tma_load_2d_pair(sb + j * BOX_BYTES, &maps.b_hi, fb, nh0 + 32 * j, k0);
-              tma_load_2d_pair(sb + B_BYTES + j * BOX_BYTES, &maps.b_lo, fb, nh0 + 32 * j, k0);
-            }
+            for (int j = 0; j < BNH / 32; ++j) tma_load_2d_pair(sb + j * BOX_BYTES, &maps.b_hi, fb, nh0 + 32 * j, k0);
           } else {
             tma_load_2d_pair(sb, &maps.b_hi, fb, k0, nh0);
-            tma_load_2d_pair(sb + B_BYTES, &maps.b_lo, fb, k0, nh0);
+          }
+          if constexpr (SCHEME == 0) {
+            if constexpr (A_MN) {
+#pragma unroll
+              for (int j = 0; j < TC_BM / 32; ++j)
+                tma_load_2d_pair(st + A_BYTES + j * BOX_BYTES, &maps.a_lo, fb, m0 + 32 * j, k0);
+            } else {
+              tma_load_2d_pair(st + A_BYTES, &maps.a_lo, fb, k0, m0);
+            }
+            if constexpr (B_MN) {
+#pragma unroll
+              for (int j = 0; j < BNH / 32; ++j)
+                tma_load_2d_pair(sb + B_BYTES + j * BOX_BYTES, &maps.b_lo, fb, nh0 + 32 * j, k0);
+            } else {
+              tma_load_2d_pair(sb + B_BYTES, &maps.b_lo, fb, k0, nh0);
+            }
+          } else {
+            // bf16 parts: [hi16 | lo16], half a fp32 tile each
+            if constexpr (A_MN) {
+#pragma unroll
+              for (int j = 0; j < TC_BM / 64; ++j) {
+                tma_load_2d_pair(st + A_BYTES + j * 4096, &maps.a16h, fb, m0 + 64 * j, k0);
+                tma_load_2d_pair(st + A_BYTES + A_BYTES / 2 + j * 4096, &maps.a16l, fb, m0 + 64 * j, k0);
+              }
+            } else {
+              tma_load_2d_pair(st + A_BYTES, &maps.a16h, fb, k0, m0);
+              tma_load_2d_pair(st + A_BYTES + A_BYTES / 2, &maps.a16l, fb, k0, m0);
+            }
+            if constexpr (B_MN) {
+#pragma unroll
+              for (int j = 0; j < BNH / 64; ++j) {
+                tma_load_2d_pair(sb + B_BYTES + j * 4096, &maps.b16h, fb, nh0 + 64 * j, k0);
+                tma_load_2d_pair(sb + B_BYTES + B_BYTES / 2 + j * 4096, &maps.b16l, fb, nh0 + 64 * j, k0);
+              }
+            } else {
+              tma_load_2d_pair(sb + B_BYTES, &maps.b16h, fb, k0, nh0);
+              tma_load_2d_pair(sb + B_BYTES + B_BYTES / 2, &maps.b16l, fb, k0, nh0);
+            }
           }
         }
       }
@@ -660,6 +712,11 @@ gemm_tc2p_kernel(const __grid_constant__ TcMaps maps, const GemmParams p, int pa
       const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((A_MN ? 1u : 0u) << 15) |
                              ((B_MN ? 1u : 0u) << 16) | ((uint32_t)(BN >> 3) << 17) |
                              ((uint32_t)(256 >> 4) << 24);
+      // the same with bf16 operands (format 1) for the correction products
+      const uint32_t idesc16 = (1u << 4) | (1u << 7) | (1u << 10) | ((A_MN ? 1u : 0u) << 15) |
+                               ((B_MN ? 1u : 0u) << 16) | ((uint32_t)(BN >> 3) << 17) |
+                               ((uint32_t)(256 >> 4) << 24);
+      (void)idesc16;
       uint32_t it = 0;
       int j = 0;
       bool ok = true;
@@ -677,18 +734,34 @@ gemm_tc2p_kernel(const __grid_constant__ TcMaps maps, const GemmParams p, int pa
           tc_fence_after();
           if (kb == 0) EB_TRACE(j, 2);
           const uint32_t st = smem_base + s * STAGE_BYTES;
-          const uint64_t a_hi = tile_desc<A_MN, BK>(st), a_lo = tile_desc<A_MN, BK>(st + A_BYTES);
           const uint32_t sb = st + 2 * A_BYTES;
-          const uint64_t b_hi = tile_desc<B_MN, BK>(sb), b_lo = tile_desc<B_MN, BK>(sb + B_BYTES);
+          const uint64_t a_hi = tile_desc<A_MN, BK>(st), b_hi = tile_desc<B_MN, BK>(sb);
           constexpr uint64_t A_STEP = A_MN ? 64 : 2, B_STEP = B_MN ? 64 : 2;
+          if constexpr (SCHEME == 0) {
+            const uint64_t a_lo = tile_desc<A_MN, BK>(st + A_BYTES), b_lo = tile_desc<B_MN, BK>(sb + B_BYTES);
 #pragma unroll
-          for (int ks = 0; ks < BK / 8; ++ks) {
-            const uint64_t ah = a_hi + ks * A_STEP, al = a_lo + ks * A_STEP;
-            const uint64_t bh = b_hi + ks * B_STEP, bl = b_lo + ks * B_STEP;
-            const uint32_t acc = (kb | ks) ? 1u : 0u;
-            tc_mma_tf32_pair(tmem_base + BN, al, bh, idesc, acc);
-            tc_mma_tf32_pair(tmem_base + BN, ah, bl, idesc, 1u);
-            tc_mma_tf32_pair(tmem_base, ah, bh, idesc, acc);
+            for (int ks = 0; ks < BK / 8; ++ks) {
+              const uint64_t ah = a_hi + ks * A_STEP, al = a_lo + ks * A_STEP;
+              const uint64_t bh = b_hi + ks * B_STEP, bl = b_lo + ks * B_STEP;
+              const uint32_t acc = (kb | ks) ? 1u : 0u;
+              tc_mma_tf32_pair(tmem_base + BN, al, bh, idesc, acc);
+              tc_mma_tf32_pair(tmem_base + BN, ah, bl, idesc, 1u);
+              tc_mma_tf32_pair(tmem_base, ah, bh, idesc, acc);
+            }
+          } else {
+            const uint64_t a16h = tile_desc16<A_MN>(st + A_BYTES), a16l = tile_desc16<A_MN>(st + A_BYTES + A_BYTES / 2);
+            const uint64_t b16h = tile_desc16<B_MN>(sb + B_BYTES), b16l = tile_desc16<B_MN>(sb + B_BYTES + B_BYTES / 2);
+            // 16 k further: 32 bytes along a K-major row, 16 k-rows (2048 bytes) of an MN-major box
+            constexpr uint64_t A16_STEP = A_MN ? 128 : 2, B16_STEP = B_MN ? 128 : 2;
+#pragma unroll
+            for (int ks = 0; ks < BK / 16; ++ks) {
+              const uint32_t acc = (kb | ks) ? 1u : 0u;
+              tc_mma_bf16_pair(tmem_base + BN, a16l + ks * A16_STEP, b16h + ks * B16_STEP, idesc16, acc);
+              tc_mma_bf16_pair(tmem_base + BN, a16h + ks * A16_STEP, b16l + ks * B16_STEP, idesc16, 1u);
+            }
+#pragma unroll
+            for (int ks = 0; ks < BK / 8; ++ks)
+              tc_mma_tf32_pair(tmem_base, a_hi + ks * A_STEP, b_hi + ks * B_STEP, idesc, (kb | ks) ? 1u : 0u);
           }
           tc_commit_pair(empty_bar(s));
         }
@@ -776,6 +849,46 @@ int launch_tf32_split(const float *x, float *lo, int64_t rows, int64_t cols, int
   return ENDIA_B200_OK;
 }
 
+// hi16 = bf16(x) and lo16 = bf16(x - tf32(x)), round to nearest; the operand parts of the
+// bf16-compensated scheme. Rows of `cols` floats, leading dimensions ld_in (floats) / ld_out (bf16).
+__global__ void __launch_bounds__(256)
+bf16_split_kernel(const float *__restrict__ x, __nv_bfloat16 *__restrict__ hi, __nv_bfloat16 *__restrict__ lo,
+                  int64_t rows, int64_t cols4, int64_t ld_in, int64_t ld_out) {
+  const int64_t total = rows * cols4;
+  const int64_t step = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += step) {
+    const int64_t r = i / cols4, c = (i - r * cols4) * 4;
+    const float4 v = __ldg(reinterpret_cast<const float4 *>(x + r * ld_in + c));
+    const float l0 = v.x - __uint_as_float(__float_as_uint(v.x) & 0xFFFFE000u);
+    const float l1 = v.y - __uint_as_float(__float_as_uint(v.y) & 0xFFFFE000u);
+    const float l2 = v.z - __uint_as_float(__float_as_uint(v.z) & 0xFFFFE000u);
+    const float l3 = v.w - __uint_as_float(__float_as_uint(v.w) & 0xFFFFE000u);
+    __nv_bfloat162 h01 = __floats2bfloat162_rn(v.x, v.y), h23 = __floats2bfloat162_rn(v.z, v.w);
+    __nv_bfloat162 l01 = __floats2bfloat162_rn(l0, l1), l23 = __floats2bfloat162_rn(l2, l3);
+    uint2 hv, lv;
+    hv.x = *reinterpret_cast<uint32_t *>(&h01); hv.y = *reinterpret_cast<uint32_t *>(&h23);
+    lv.x = *reinterpret_cast<uint32_t *>(&l01); lv.y = *reinterpret_cast<uint32_t *>(&l23);
+    *reinterpret_cast<uint2 *>(hi + r * ld_out + c) = hv;
+    *reinterpret_cast<uint2 *>(lo + r * ld_out + c) = lv;
+  }
+}
+
+int launch_bf16_split(const float *x, void *hi16, void *lo16, int64_t rows, int64_t cols, int64_t ld_in,
+                      int64_t ld_out, cudaStream_t s) {
+  bf16_split_kernel<<<grid_for(rows * (cols / 4), 256), 256, 0, s>>>(
+      x, static_cast<__nv_bfloat16 *>(hi16), static_cast<__nv_bfloat16 *>(lo16), rows, cols / 4, ld_in, ld_out);
+  EB_LAUNCH_CHECK();
+  return ENDIA_B200_OK;
+}
+
+int tc_default_scheme() {
+  static const int scheme = []() {
+    const char *e = getenv("ENDIA_B200_TC_SCHEME");
+    return (e && (e[0] == '3' || e[0] == '0')) ? 0 : 1;
+  }();
+  return scheme;
+}
+
 // ---------------------------------------------------------------------------------- host side
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
                                   const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
@@ -815,6 +928,26 @@ static int make_map(CUtensorMap *map, const float *base, int64_t inner, int64_t 
                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
     set_error("gemm: cuTensorMapEncodeTiled failed with code %d", (int)r);
+    return ENDIA_B200_ECUDA;
+  }
+  return ENDIA_B200_OK;
+}
+
+// Tensor map over a row-major [outer, inner] bf16 array with leading dimension ld (elements).
+// K-major tiles: box [box_outer rows][32 k] with the 64-byte swizzle; MN-major tiles: box
+// [32 k][64 rows] with the 128-byte swizzle.
+static int make_map16(CUtensorMap *map, const void *base, int64_t inner, int64_t outer, int64_t ld,
+                      int box_inner, int box_outer, bool mn_major) {
+  cuuint64_t dims[2] = {(cuuint64_t)inner, (cuuint64_t)outer};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  cuuint32_t box[2] = {(cuuint32_t)box_inner, (cuuint32_t)box_outer};
+  cuuint32_t estr[2] = {1u, 1u};
+  CUresult r = encode_fn()(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(base), dims, strides, box,
+                           estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                           mn_major ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
+                           CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_error("gemm: cuTensorMapEncodeTiled (bf16) failed with code %d", (int)r);
     return ENDIA_B200_ECUDA;
   }
   return ENDIA_B200_OK;
@@ -872,6 +1005,7 @@ static bool ksplit_mode() {
 }
 
 // Persistent two-CTA kernel: as many CTA pairs as can be resident, each walking over its tiles.
+template <int SCHEME>
 static int launch_pair_persistent(const TcMaps &maps, const GemmParams &p, int trans_a, int trans_b,
                                   cudaStream_t s, int ksplit_max) {
   constexpr size_t SMEM = (size_t)3 * (2 * TC_BM * 32 * 4 + 2 * 128 * 32 * 4) + 8 * 4096 + 1024 + 256;
@@ -880,7 +1014,7 @@ static int launch_pair_persistent(const TcMaps &maps, const GemmParams &p, int t
   const int group_m = group_env > 0 ? group_env : pairs_m;
 #define EB_TC2P_LAUNCH(AM, BM_)                                                                   \
   do {                                                                                            \
-    auto kern = gemm_tc2p_kernel<AM, BM_>;                                                        \
+    auto kern = gemm_tc2p_kernel<AM, BM_, SCHEME>;                                                \
     static int max_pairs = 0;                                                                     \
     if (!max_pairs) {                                                                             \
       EB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM)); \
@@ -937,29 +1071,12 @@ int launch_gemm_tc(const GemmParams &p, int trans_a, int trans_b, cudaStream_t s
   // the row-major weight of `x @ W`) or [N, K] (K-major).
   const int64_t a_rows = trans_a ? p.K : p.M, a_cols = trans_a ? p.M : p.K;
   const int64_t b_rows = trans_b ? p.N : p.K, b_cols = trans_b ? p.K : p.N;
-  const int64_t a_ld = (a_cols + 3) / 4 * 4, b_ld = (b_cols + 3) / 4 * 4;
-  // Low parts: taken from the caller when provided (same layout as the operand), else computed
-  // into stream-ordered work buffers.
-  float *a_lo_buf = nullptr, *b_lo_buf = nullptr;
-  const float *a_lo = p.a_lo, *b_lo = p.b_lo;
-  int64_t a_lo_ld = p.lda, b_lo_ld = p.ldb;
-  if (!a_lo) {
-    EB_CUDA(cudaMallocAsync(&a_lo_buf, sizeof(float) * a_rows * a_ld, s));
-    int st0 = launch_tf32_split(p.A, a_lo_buf, a_rows, a_ld, p.lda, a_ld, s);
-    if (st0) return st0;
-    a_lo = a_lo_buf; a_lo_ld = a_ld;
-  }
-  if (!b_lo) {
-    EB_CUDA(cudaMallocAsync(&b_lo_buf, sizeof(float) * b_rows * b_ld, s));
-    int st0 = launch_tf32_split(p.B, b_lo_buf, b_rows, b_ld, p.ldb, b_ld, s);
-    if (st0) return st0;
-    b_lo = b_lo_buf; b_lo_ld = b_ld;
-  }
   int bn = p.N >= 256 ? 256 : 128;
   // Few output tiles and a long reduction: split K over CTAs (128 x 128 tiles) so that the machine
   // is filled; the partial sums go through a work buffer and are added in a fixed order.
   int splits = 1;
-  {
+  int scheme = p.scheme;
+  if (scheme == 0 || !p.scheme_forced) {
     const int64_t ctas_wide = 2 * ceil_div(p.M, 256) * ceil_div(p.N, 256);
     const int64_t tiles = ceil_div(p.M, 128) * ceil_div(p.N, 128);
     const int64_t nkb32 = ceil_div(p.K, 32);
@@ -967,20 +1084,73 @@ int launch_gemm_tc(const GemmParams &p, int trans_a, int trans_b, cudaStream_t s
       int64_t sp = 148 / tiles;
       if (sp > nkb32 / 8) sp = nkb32 / 8;
       if (sp > 16) sp = 16;
-      if (sp >= 2) { splits = (int)sp; bn = 128; }
+      if (sp >= 2) { splits = (int)sp; bn = 128; scheme = 0; }
     }
   }
-  // k-block depth: 16 floats per stage with a 4- or 6-deep ring hides the tile-load latency
-  // better than 32 floats with 2 or 3 stages in the same shared memory.
+  // k-block depth of the one-CTA kernel: 32 floats per stage, or 16 with a deeper ring.
   static const int bk = []() {
     const char *e = getenv("ENDIA_B200_TC_BK");
     return (e && atoi(e) == 16) ? 16 : 32;
   }();
+  const bool pair = bn == 256 && ((bk == 32 && pair_mode()) || scheme == 1);
+  const bool bf16c = pair && scheme == 1;
   TcMaps maps;
   int st;
-  // K-major operand: box [rows of the tile][bk k]; MN-major operand: box [bk k][32 rows].
-  const int a_bi = trans_a ? 32 : bk, a_bo = trans_a ? bk : TC_BM;
-  const bool pair = bn == 256 && bk == 32 && pair_mode();
+  // K-major operand: box [rows of the tile][k]; MN-major operand: box [k][32 rows].
+  const int kbox = pair ? 32 : bk;
+  const int a_bi = trans_a ? 32 : kbox, a_bo = trans_a ? kbox : TC_BM;
+  const int b_bi = trans_b ? kbox : 32, b_bo = trans_b ? (pair ? 128 : bn) : kbox;
+  if ((st = make_map(&maps.a_hi, p.A, a_cols, a_rows, p.lda, a_bi, a_bo, trans_a != 0))) return st;
+  if ((st = make_map(&maps.b_hi, p.B, b_cols, b_rows, p.ldb, b_bi, b_bo, trans_b == 0))) return st;
+  maps.a_lo = maps.a16h = maps.a16l = maps.a_hi;
+  maps.b_lo = maps.b16h = maps.b16l = maps.b_hi;
+
+  // Operand parts: taken from the caller when provided (laid out like the operand's storage), else
+  // computed into stream-ordered work buffers.
+  void *a_buf = nullptr, *b_buf = nullptr;
+  if (bf16c) {
+    // bf16(x) and bf16(x - tf32(x)), each [rows][ld16] bf16
+    const int64_t a_ld16 = (a_cols + 7) / 8 * 8, b_ld16 = (b_cols + 7) / 8 * 8;
+    const char *a16 = static_cast<const char *>(p.a16), *b16 = static_cast<const char *>(p.b16);
+    int64_t a_ld = p.lda, b_ld = p.ldb;
+    if (!a16 || p.lda % 8 || !aligned16(a16)) {
+      EB_CUDA(cudaMallocAsync(&a_buf, (size_t)4 * a_rows * a_ld16, s));
+      if ((st = launch_bf16_split(p.A, a_buf, static_cast<char *>(a_buf) + 2 * a_rows * a_ld16, a_rows,
+                                  (a_cols + 3) / 4 * 4 <= a_ld16 ? (a_cols + 3) / 4 * 4 : a_cols, p.lda, a_ld16, s)))
+        return st;
+      a16 = static_cast<const char *>(a_buf); a_ld = a_ld16;
+    }
+    if (!b16 || p.ldb % 8 || !aligned16(b16)) {
+      EB_CUDA(cudaMallocAsync(&b_buf, (size_t)4 * b_rows * b_ld16, s));
+      if ((st = launch_bf16_split(p.B, b_buf, static_cast<char *>(b_buf) + 2 * b_rows * b_ld16, b_rows,
+                                  (b_cols + 3) / 4 * 4 <= b_ld16 ? (b_cols + 3) / 4 * 4 : b_cols, p.ldb, b_ld16, s)))
+        return st;
+      b16 = static_cast<const char *>(b_buf); b_ld = b_ld16;
+    }
+    // K-major: box [tile rows][32 k]; MN-major: box [32 k][64 rows]
+    const int a16_bi = trans_a ? 64 : 32, a16_bo = trans_a ? 32 : TC_BM;
+    const int b16_bi = trans_b ? 32 : 64, b16_bo = trans_b ? 128 : 32;
+    if ((st = make_map16(&maps.a16h, a16, a_cols, a_rows, a_ld, a16_bi, a16_bo, trans_a != 0))) return st;
+    if ((st = make_map16(&maps.a16l, a16 + 2 * a_rows * a_ld, a_cols, a_rows, a_ld, a16_bi, a16_bo, trans_a != 0))) return st;
+    if ((st = make_map16(&maps.b16h, b16, b_cols, b_rows, b_ld, b16_bi, b16_bo, trans_b == 0))) return st;
+    if ((st = make_map16(&maps.b16l, b16 + 2 * b_rows * b_ld, b_cols, b_rows, b_ld, b16_bi, b16_bo, trans_b == 0))) return st;
+  } else {
+    const int64_t a_ld4 = (a_cols + 3) / 4 * 4, b_ld4 = (b_cols + 3) / 4 * 4;
+    const float *a_lo = p.a_lo, *b_lo = p.b_lo;
+    int64_t a_lo_ld = p.lda, b_lo_ld = p.ldb;
+    if (!a_lo) {
+      EB_CUDA(cudaMallocAsync(&a_buf, sizeof(float) * a_rows * a_ld4, s));
+      if ((st = launch_tf32_split(p.A, static_cast<float *>(a_buf), a_rows, a_ld4, p.lda, a_ld4, s))) return st;
+      a_lo = static_cast<const float *>(a_buf); a_lo_ld = a_ld4;
+    }
+    if (!b_lo) {
+      EB_CUDA(cudaMallocAsync(&b_buf, sizeof(float) * b_rows * b_ld4, s));
+      if ((st = launch_tf32_split(p.B, static_cast<float *>(b_buf), b_rows, b_ld4, p.ldb, b_ld4, s))) return st;
+      b_lo = static_cast<const float *>(b_buf); b_lo_ld = b_ld4;
+    }
+    if ((st = make_map(&maps.a_lo, a_lo, a_cols, a_rows, a_lo_ld, a_bi, a_bo, trans_a != 0))) return st;
+    if ((st = make_map(&maps.b_lo, b_lo, b_cols, b_rows, b_lo_ld, b_bi, b_bo, trans_b == 0))) return st;
+  }
   GemmParams q = p;
   float *partial = nullptr;
   if (splits > 1) {
@@ -988,11 +1158,6 @@ int launch_gemm_tc(const GemmParams &p, int trans_a, int trans_b, cudaStream_t s
     EB_CUDA(cudaMallocAsync(&partial, sizeof(float) * (size_t)splits * p.M * q.ld_partial, s));
     q.partial = partial;
   }
-  const int b_bi = trans_b ? bk : 32, b_bo = trans_b ? (pair ? 128 : bn) : bk;
-  if ((st = make_map(&maps.a_hi, p.A, a_cols, a_rows, p.lda, a_bi, a_bo, trans_a != 0))) return st;
-  if ((st = make_map(&maps.a_lo, a_lo, a_cols, a_rows, a_lo_ld, a_bi, a_bo, trans_a != 0))) return st;
-  if ((st = make_map(&maps.b_hi, p.B, b_cols, b_rows, p.ldb, b_bi, b_bo, trans_b == 0))) return st;
-  if ((st = make_map(&maps.b_lo, b_lo, b_cols, b_rows, b_lo_ld, b_bi, b_bo, trans_b == 0))) return st;
   if (pair && p.vec_c) {
     // output map: [M][N] floats with leading dimension ldc, boxes of 32 rows x 32 floats
     if ((st = make_map(&maps.c, p.C, p.N, p.M, p.ldc, 32, 32, false))) return st;
@@ -1002,8 +1167,9 @@ int launch_gemm_tc(const GemmParams &p, int trans_a, int trans_b, cudaStream_t s
   // Halving K needs the bulk-store epilogue, a product that is linear in the accumulator and a
   // reduction long enough for the second pass over C to be cheap.
   const bool linear_epi = !p.epi.bias && !p.epi.act && !p.epi.dact && p.epi.beta == 0.f;
-  if (pair) st = launch_pair_persistent(maps, p, trans_a, trans_b, s,
-                                        (p.vec_c && linear_epi && p.K >= 4096 && ksplit_mode()) ? 2 : 1);
+  const int ksplit_max = (p.vec_c && linear_epi && p.K >= 4096 && ksplit_mode()) ? 2 : 1;
+  if (bf16c) st = launch_pair_persistent<1>(maps, p, trans_a, trans_b, s, ksplit_max);
+  else if (pair) st = launch_pair_persistent<0>(maps, p, trans_a, trans_b, s, ksplit_max);
   else if (bn == 256 && bk == 16) st = launch_variant<256, 16, 4>(maps, p, trans_a, trans_b, s);
   else if (bn == 256) st = launch_variant<256, 32, 2>(maps, p, trans_a, trans_b, s);
   else if (bk == 16) st = launch_variant<128, 16, 6>(maps, q, trans_a, trans_b, s, splits);
@@ -1012,8 +1178,8 @@ int launch_gemm_tc(const GemmParams &p, int trans_a, int trans_b, cudaStream_t s
     st = launch_splitk_finish(q, splits, s);
     cudaFreeAsync(partial, s);
   }
-  if (a_lo_buf) EB_CUDA(cudaFreeAsync(a_lo_buf, s));
-  if (b_lo_buf) EB_CUDA(cudaFreeAsync(b_lo_buf, s));
+  if (a_buf) EB_CUDA(cudaFreeAsync(a_buf, s));
+  if (b_buf) EB_CUDA(cudaFreeAsync(b_buf, s));
   return st;
 }
 

@@ -4,7 +4,7 @@ fills `curr`'s buffer by enqueuing kernels, plus a VJP written in differentiable
 `create_graph=True` yields graphs of gradients.
 """
 from .. import _lib
-from .._array import Array, ArrayShape, alloc, compute_stride, stream
+from .._array import Array, ArrayShape, alloc, compute_stride, stream, drop_operand_parts
 
 
 def clone_shape(array_shape):
@@ -99,4 +99,4 @@ def copy_into(src, dst):
     if s.is_complex() != dst.is_complex():
         raise _lib.EndiaError(_lib.EINVAL, "in-place update: complex flag mismatch")
     _lib.call("endia_b200_d2d", dst.data_ptr(), s.data_ptr(), dst.size() * w * 4, stream())
-    dst.base()._tf32_lo = None   # a cached tf32 low part no longer matches the storage
+    drop_operand_parts(dst)   # cached GEMM operand parts no longer match the storage

@@ -3,6 +3,8 @@
 broadcast operands through stride-0 dims; VJPs are compositions of these same ops, so gradients
 of gradients work (create_graph=True). When no graph of the gradient is wanted the VJPs switch to
 fused single-pass kernels."""
+import os
+
 from .. import _lib
 from .._array import Array, ArrayShape, alloc, stream
 from ..autograd import state as _state
@@ -148,23 +150,51 @@ def _batch_stride(a, batch):
 _LO_CACHE_MIN = 1 << 20
 
 
-def _tf32_lo_ptr(x):
-    """Device address of the tf32 low part matching operand view `x`, or None. The low part of a
-    whole storage buffer is valid for every view of it. Leaves (user inputs, parameters) are not
-    cached here: their storage may be rewritten by the caller between steps."""
+def _tc_plan(M, N, K, nbatch, algo):
+    """Which operand parts the tcgen05 kernel that endia_b200_gemm will pick reads: "pair16" (bf16
+    split, two-CTA kernel), "lo32" (fp32 low parts, 3xTF32 kernels) or None (FFMA / skinny kernels).
+    A wrong guess only costs time: the kernel computes the parts it was not handed."""
+    if nbatch != 1 or algo == _lib.GEMM_FFMA or M < 128 or N < 128 or not 32 <= K <= 8192:
+        return None
+    if algo == _lib.GEMM_3XTF32 or N < 256:
+        return "lo32"
+    if algo == _lib.GEMM_AUTO:
+        if os.environ.get("ENDIA_B200_TC_SCHEME", "")[:1] in ("3", "0"):
+            return "lo32"
+        wide = 2 * (-(-M // 256)) * (-(-N // 256))
+        tiles = (-(-M // 128)) * (-(-N // 128))
+        if wide < 100 and K >= 512 and min(148 // tiles, K // 256, 16) >= 2:
+            return "lo32"      # few tiles, long K: the split-K 3xTF32 kernel
+    return "pair16"
+
+
+def _operand_parts_ptr(x, kind):
+    """Device address of the operand parts (`kind`: "lo32" or "pair16") matching operand view `x`,
+    or None. The parts of a whole storage buffer serve every view of it that starts at its first
+    element. They are written by the optimizer for weights and computed here once for the result
+    of an op (used by two products: the next layer's forward and a weight gradient). Leaves (user
+    inputs, parameters) are not cached here: their storage may be rewritten between steps."""
     base = x.base()
     if base.buf is None or x.buf is not base.buf or base.is_complex():
         return None
-    lo = getattr(base, "_tf32_lo", None)
-    if lo is None or base._tf32_lo_ptr != base.buf.data_ptr():
+    attr = "_tf32_lo" if kind == "lo32" else "_pair16"
+    parts = getattr(base, attr, None)
+    if parts is None or base._parts_ptr != base.buf.data_ptr():
         n = base.buf.numel()
-        if base.name == "arg" or n < _LO_CACHE_MIN or n % 4 or not _state.cache_tf32_lo:
+        if base.name == "arg" or n < _LO_CACHE_MIN or n % 8 or not _state.cache_tf32_lo:
             return None
-        lo = alloc(n)
-        _lib.call("endia_b200_tf32_split", base.buf.data_ptr(), lo.data_ptr(), 1, n, n, n, stream())
-        base._tf32_lo = lo
-        base._tf32_lo_ptr = base.buf.data_ptr()
-    return lo.data_ptr() + (x.data_ptr() - base.buf.data_ptr())
+        parts = alloc(n)
+        if kind == "lo32":
+            _lib.call("endia_b200_tf32_split", base.buf.data_ptr(), parts.data_ptr(), 1, n, n, n, stream())
+        else:
+            _lib.call("endia_b200_bf16_split", base.buf.data_ptr(), parts.data_ptr(), n, stream())
+        setattr(base, attr, parts)
+        base._parts_ptr = base.buf.data_ptr()
+    off = x.data_ptr() - base.buf.data_ptr()
+    if kind == "pair16":
+        # [bf16(x) | bf16(lo)] of the whole buffer: only a view that covers all of it can use it
+        return parts.data_ptr() if off == 0 and x.size() == base.buf.numel() else None
+    return parts.data_ptr() + off
 
 
 def gemm_arrays(a, b, out, epi=None, algo=None):
@@ -191,16 +221,19 @@ def gemm_arrays(a, b, out, epi=None, algo=None):
         _lib.call("endia_b200_gemm_complex", la[0], lb[0], M, N, K, a.data_ptr(), la[1], b.data_ptr(),
                   lb[1], out.data_ptr(), N, nbatch, sa, sb, M * N, stream())
         return
-    # tf32 low parts kept beside an operand's storage (written by the optimizer for weights, computed
-    # here once for the result of an op, which is used by two products: the next layer's forward
-    # and a weight gradient): handed to the 3xTF32 kernel instead of being recomputed per product.
-    if nbatch == 1 and algo != _lib.GEMM_FFMA and M >= 128 and N >= 128 and 32 <= K <= 8192:
-        a_lo, b_lo = _tf32_lo_ptr(a), _tf32_lo_ptr(b)
-        if a_lo or b_lo:
+    # Operand parts kept beside an operand's storage are handed to the tensor-core kernel instead
+    # of being recomputed per product.
+    plan = _tc_plan(M, N, K, nbatch, algo)
+    if plan is not None:
+        pa, pb = _operand_parts_ptr(a, plan), _operand_parts_ptr(b, plan)
+        if pa or pb:
             if epi is None:
                 epi = _lib.Epilogue()
                 epi.alpha = 1.0
-            epi.a_lo, epi.b_lo = a_lo, b_lo
+            if plan == "lo32":
+                epi.a_lo, epi.b_lo = pa, pb
+            else:
+                epi.a16, epi.b16 = pa, pb
     timer = _state.gemm_timer
     if timer is not None:
         timer.start(2.0 * M * N * K * nbatch)

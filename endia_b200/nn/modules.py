@@ -3,7 +3,7 @@ epilogue adds the bias and applies the activation; its VJP is one fused mask+bia
 and two GEMMs that read transposed operands in place. With create_graph=True the VJP is the
 reference's composition of differentiable ops instead, so higher-order gradients work."""
 from .. import _lib
-from .._array import Array, ArrayShape, alloc, stream
+from .._array import Array, ArrayShape, alloc, stream, drop_operand_parts
 from ..autograd import state as _state
 from ..functional import init_ops
 from ..functional._utils import op_array, setup_shape_and_data, contiguous
@@ -72,7 +72,7 @@ def linear(x, weight, bias=None, activation=None):
         if act or need_db:
             ds = Array(ArrayShape([B, N])) if act else g
             if act:
-                ds.name = "linear_vjp"   # a temporary of this pass, never rewritten (see _tf32_lo_ptr)
+                ds.name = "linear_vjp"   # a temporary of this pass, never rewritten (see _operand_parts_ptr)
                 setup_shape_and_data(ds)
             if need_db:
                 db = Array(ArrayShape([1, N]))  # kept dim, like Expand.vjp's reduce_add
@@ -204,7 +204,7 @@ class SmallMLPStep:
         _lib.check(st)
         for w, b, g1, g2 in zip(self.weights, self.biases, self.gW, self.gb):
             if opt is not None:
-                w._tf32_lo = None
+                drop_operand_parts(w)
             w.grad_node = g1
             b.grad_node = g2
         if opt is not None:

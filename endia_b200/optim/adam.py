@@ -31,19 +31,23 @@ class Adam:
             if g.size() != p.size():
                 raise _lib.EndiaError(_lib.ESHAPE, "Adam: gradient %s does not match parameter %s" % (
                     g.shape(), p.shape()))
-        # Matrices also get the tf32 low part of their new value, which the 3xTF32 GEMMs of the next
-        # step read instead of recomputing it (the cache is dropped by any other in-place update).
-        lo_ptrs = []
+        # Matrices also get the operand parts of their new value (the bf16 split the two-CTA GEMM
+        # reads), so that the products of the next step need not recompute them for the weights
+        # (the cache is dropped by any other in-place update).
+        parts = []
         for p in self.params:
-            if p.ndim() == 2 and p.size() % 4 == 0 and p.size() >= 128 * 128 and not p.is_complex():
-                if getattr(p, "_tf32_lo", None) is None:
-                    p._tf32_lo = alloc(p.size())
-                p._tf32_lo_ptr = p.buf.data_ptr()
-                lo_ptrs.append(p._tf32_lo.data_ptr())
+            if p.ndim() == 2 and p.size() % 8 == 0 and p.size() >= 128 * 128 and not p.is_complex():
+                if getattr(p, "_pair16", None) is None:
+                    p._pair16 = alloc(p.size())
+                p._tf32_lo = None
+                p._parts_ptr = p.buf.data_ptr()
+                parts.append(p._pair16.data_ptr())
             else:
-                lo_ptrs.append(None)
-        LO = (C.c_void_p * n)(*lo_ptrs)
-        _lib.call("endia_b200_adam_step_multi_lo", n, P, G, M, V, LO, numel, self.lr, self.beta1, self.beta2,
+                p._tf32_lo = None
+                p._pair16 = None
+                parts.append(None)
+        P16 = (C.c_void_p * n)(*parts)
+        _lib.call("endia_b200_adam_step_multi_bf16", n, P, G, M, V, P16, numel, self.lr, self.beta1, self.beta2,
                   self.eps, self.t, self.grad_scale, stream())
         # m and v take the broadcast shape of (state, grad): a bias gradient is (1, N), so the
         # moments become (1, N) while the parameter keeps (N) (adam.mojo:49-56, expand_op.mojo:121-126).

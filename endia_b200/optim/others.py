@@ -5,7 +5,7 @@ gradient is (1, N), so the velocity / cache of a bias becomes (1, N)."""
 import ctypes as C
 
 from .. import _lib
-from .._array import Array, ArrayShape, stream
+from .._array import Array, ArrayShape, stream, drop_operand_parts
 from ..functional._utils import contiguous, broadcast_shapes
 
 
@@ -37,7 +37,7 @@ class _FusedOptimizer:
         for s, g in zip(state, grads):
             s.array_shape_ = ArrayShape(broadcast_shapes(s.shape(), g.shape()))
         for p in self.params:
-            p.base()._tf32_lo = None   # the storage changed; a cached tf32 low part is stale
+            drop_operand_parts(p)   # the storage changed
             p.clear_args()
 
 

@@ -101,9 +101,14 @@ int endia_b200_event_elapsed_ms(void *start, void *stop, float *ms);
 enum { ENDIA_B200_ACT_NONE = 0, ENDIA_B200_ACT_RELU = 1, ENDIA_B200_ACT_TANH = 2,
        ENDIA_B200_ACT_SIGMOID = 3 };
 
-enum { ENDIA_B200_GEMM_AUTO = 0,   /* tcgen05 3xTF32 when the shape allows, else FFMA */
+enum { ENDIA_B200_GEMM_AUTO = 0,   /* a tcgen05 split-precision kernel when the shape allows, else FFMA */
        ENDIA_B200_GEMM_FFMA = 1,   /* fp32 FFMA tiles                                 */
-       ENDIA_B200_GEMM_3XTF32 = 2  /* tcgen05 tf32 MMAs, hi/lo split, fp32 accumulate */ };
+       ENDIA_B200_GEMM_3XTF32 = 2, /* tcgen05 tf32 MMAs, hi/lo split, fp32 accumulate */
+       /* a_hi*b_hi as one tf32 MMA; the two correction products a_lo*b + a*b_lo as bf16 MMAs
+        * (their operands only need 8 bits: error 2^-19 of |a||b| per product instead of 2^-22,
+        * far inside the 1e-4 bound on gradients). Two thirds of the tensor-core time of 3xTF32.
+        * Needs N >= 256. */
+       ENDIA_B200_GEMM_TF32_BF16X2 = 3 };
 
 /* Work fused into the GEMM's store, applied in this order to acc = op(A)·op(B):
  *   v = alpha*acc
@@ -138,6 +143,11 @@ typedef struct endia_b200_epilogue {
    * endia_b200_adam_step_multi_lo wrote them. NULL = computed inside the call. */
   const float *a_lo;
   const float *b_lo;
+  /* Optional, used only by the TF32_BF16X2 kernel: the bf16 split of A and/or B as
+   * endia_b200_bf16_split wrote it for the operand's whole [rows, ld] storage. NULL = computed
+   * inside the call. */
+  const void *a16;
+  const void *b16;
 } endia_b200_epilogue;
 
 size_t endia_b200_gemm_colsum_scratch_bytes(int64_t M, int64_t N);
@@ -147,6 +157,12 @@ size_t endia_b200_gemm_colsum_scratch_bytes(int64_t M, int64_t N);
  * part of the 3xTF32 product, for callers that reuse it over several GEMMs. */
 int endia_b200_tf32_split(const float *x, float *lo, int64_t rows, int64_t cols, int64_t ld_in,
                           int64_t ld_out, void *stream);
+
+/* The operand parts of the TF32_BF16X2 product for an array of `numel` floats (numel a multiple
+ * of 8, 16-byte aligned pointers): pair16[0 .. numel) = bf16(x) and pair16[numel .. 2*numel) =
+ * bf16(x - tf32(x)), round to nearest, 2 bytes each, laid out like x. `pair16` holds
+ * 4*numel bytes. */
+int endia_b200_bf16_split(const float *x, void *pair16, int64_t numel, void *stream);
 
 /* C[M,N] = epilogue(op(A)[M,K] · op(B)[K,N]), fp32, row-major storage.
  *   trans_a = 0: A is stored [M,K] with leading dimension lda >= K
@@ -298,6 +314,13 @@ int endia_b200_adam_step_multi_lo(int32_t n_tensors, float *const *params, const
                                   float *const *m, float *const *v, float *const *p_lo,
                                   const int64_t *numel, float lr, float beta1, float beta2, float eps,
                                   float t, float grad_scale, void *stream);
+
+/* The same with the bf16 split of the updated parameter (endia_b200_bf16_split's layout, numel a
+ * multiple of 8) for every tensor with a non-NULL entry in `p16`. */
+int endia_b200_adam_step_multi_bf16(int32_t n_tensors, float *const *params, const float *const *grads,
+                                    float *const *m, float *const *v, void *const *p16,
+                                    const int64_t *numel, float lr, float beta1, float beta2, float eps,
+                                    float t, float grad_scale, void *stream);
 
 /* The other optimizers of the reference as single multi-tensor launches, same conventions as
  * endia_b200_adam_step_multi (flat numel per tensor, gradients multiplied by grad_scale first):

@@ -37,15 +37,40 @@ def test_3xtf32_all_layouts(nd, ta, tb, M, N, K):
     from endia_b200 import _lib
     if not _lib.lib.endia_b200_has_tcgen05():
         pytest.fail("library built without the tcgen05 GEMM")
+    check_layout_case(nd, ta, tb, M, N, K, _lib.GEMM_3XTF32, 5e-6)
+
+
+@pytest.mark.parametrize("ta,tb", [(0, 0), (0, 1), (1, 0), (1, 1)])
+@pytest.mark.parametrize("M,N,K", [(256, 256, 64), (384, 512, 256), (200, 328, 100), (1024, 1024, 1024),
+                                   (136, 260, 36), (256, 1024, 4096), (1000, 520, 2048)])
+def test_tf32_bf16x2_all_layouts(nd, ta, tb, M, N, K):
+    """One tf32 MMA plus two bf16 correction MMAs per product: the correction operands carry 8
+    bits, so the bound is 2^-19 of |a||b| per product in the worst case (measured far below)."""
+    from endia_b200 import _lib
+    check_layout_case(nd, ta, tb, M, N, K, _lib.GEMM_TF32_BF16X2, 8e-6)
+
+
+def test_tf32_bf16x2_needs_wide_output(nd):
+    from endia_b200 import _lib
+    from endia_b200._array import stream
+    A, B, Cd = nd.Array([256, 64]), nd.Array([64, 128]), nd.Array([256, 128])
+    st = _lib.lib.endia_b200_gemm(0, 0, 256, 128, 64, A.data_ptr(), 64, B.data_ptr(), 128, Cd.data_ptr(), 128,
+                                  1, 0, 0, 0, None, _lib.GEMM_TF32_BF16X2, stream())
+    assert st == _lib.EINVAL
+
+
+def check_layout_case(nd, ta, tb, M, N, K, algo, bound):
+    from endia_b200 import _lib
     r = rng(M + N + K)
     a = r.standard_normal((K, M) if ta else (M, K)).astype(np.float32)
     b = r.standard_normal((N, K) if tb else (K, N)).astype(np.float32)
-    out = run_gemm(nd, a, b, ta, tb, _lib.GEMM_3XTF32)
+    out = run_gemm(nd, a, b, ta, tb, algo)
     am = (a.T if ta else a).astype(np.float64)
     bm = (b.T if tb else b).astype(np.float64)
     ref = am @ bm
     err = np.abs(out - ref) / dot_scale(am, bm)
-    assert err.max() < 5e-6, err.max()          # plain tf32 would be ~1e-3
+    print("max error / (|a|.|b|): %.3g" % err.max())
+    assert err.max() < bound, err.max()          # plain tf32 would be ~1e-3
     ffma = run_gemm(nd, a, b, ta, tb, _lib.GEMM_FFMA)
     assert max_rel(out, ffma) < 1e-4
 
@@ -127,10 +152,11 @@ def test_auto_falls_back_to_ffma_for_unaligned_or_small(nd):
     assert st == _lib.EINVAL
 
 
-def test_weight_low_part_cache_written_by_adam(nd):
-    """Adam leaves the tf32 low part of each updated weight matrix behind; the next products with
-    that weight (plain and transposed) read it, and any other in-place update drops it."""
-    from endia_b200 import _lib
+def test_weight_operand_parts_written_by_adam(nd):
+    """Adam leaves the bf16 split of each updated weight matrix behind (bf16(w) and
+    bf16(w - tf32(w))); the next products with that weight (plain and transposed) read it, and any
+    other in-place update drops it."""
+    import torch
     r = rng(9)
     w = r.standard_normal((256, 384)).astype(np.float32)
     x = r.standard_normal((512, 256)).astype(np.float32)
@@ -138,15 +164,17 @@ def test_weight_low_part_cache_written_by_adam(nd):
     W = nd.Array(w, requires_grad=True)
     W.grad_(nd.Array(r.standard_normal((256, 384)).astype(np.float32)))
     nd.optim.Adam([W]).step()
-    assert getattr(W, "_tf32_lo", None) is not None
-    wn = W.to_numpy().astype(np.float64)
-    lo = W._tf32_lo.cpu().numpy().reshape(256, 384)
-    hi = (W.to_numpy().view(np.uint32) & np.uint32(0xFFFFE000)).view(np.float32)
-    assert np.array_equal(lo, W.to_numpy() - hi)
+    assert getattr(W, "_pair16", None) is not None
+    wn32 = W.to_numpy()
+    wn = wn32.astype(np.float64)
+    pair = W._pair16.view(torch.bfloat16).float().cpu().numpy().reshape(2, 256, 384)
+    hi = (wn32.view(np.uint32) & np.uint32(0xFFFFE000)).view(np.float32)
+    assert np.array_equal(pair[0], torch.from_numpy(wn32).to(torch.bfloat16).float().numpy())
+    assert np.array_equal(pair[1], torch.from_numpy(wn32 - hi).to(torch.bfloat16).float().numpy())
     y = nd.matmul(nd.Array(x), W).to_numpy()
     dx = nd.matmul(nd.Array(g), W.T()).to_numpy()
     assert max_rel(y, x.astype(np.float64) @ wn) < 2e-5
     assert max_rel(dx, g.astype(np.float64) @ wn.T) < 2e-5
     W -= nd.Array(np.ones((256, 384), np.float32))
-    assert W._tf32_lo is None
+    assert W._pair16 is None and W._tf32_lo is None
     assert max_rel(nd.matmul(nd.Array(x), W).to_numpy(), x.astype(np.float64) @ (wn - 1.0)) < 2e-5
