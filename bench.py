@@ -401,6 +401,13 @@ def run_reference(args):
     print(json.dumps(line))
 
 
+def tc_scheme(gemm_flag):
+    """Scheme the two-CTA tcgen05 kernel runs for this --gemm flag (mirrors the library's choice)."""
+    if gemm_flag == "3xtf32" or (gemm_flag == "auto" and os.environ.get("ENDIA_B200_TC_SCHEME", "")[:1] in ("3", "0")):
+        return "3xtf32"
+    return "tf32_bf16x2"
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -409,7 +416,9 @@ def main():
     ap.add_argument("--impl", default="endia_b200", choices=["endia_b200", "reference"])
     ap.add_argument("--cpu-rows", type=int, default=48)
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--gemm", default="auto", choices=["auto", "ffma", "3xtf32"])
+    ap.add_argument("--gemm", default="auto", choices=["auto", "ffma", "3xtf32", "tf32_bf16x2"],
+                    help="auto = tf32_bf16x2 on the two-CTA tcgen05 kernel (one tf32 MMA + two bf16 correction "
+                         "MMAs per product), 3xTF32 split-K or FFMA where that kernel does not apply")
     ap.add_argument("--workload", default="c2", choices=["c1", "c2", "c3", "c4", "c5"],
                     help="c2 (default, the headline): MLP train step; c1: small MLP, single-launch step; "
                          "c3: gradient-penalty (second-order) step; c4 / c5: FFT forward + VJP")
@@ -427,7 +436,8 @@ def main():
 
     rank, world = ndist.init_process_group()
     nd._array.device()
-    nd.config.gemm_algo = {"auto": _lib.GEMM_AUTO, "ffma": _lib.GEMM_FFMA, "3xtf32": _lib.GEMM_3XTF32}[args.gemm]
+    nd.config.gemm_algo = {"auto": _lib.GEMM_AUTO, "ffma": _lib.GEMM_FFMA, "3xtf32": _lib.GEMM_3XTF32,
+                           "tf32_bf16x2": _lib.GEMM_TF32_BF16X2}[args.gemm]
     is_fft = args.workload in ("c4", "c5")
     is_small = args.workload in ("c1", "c3")
     if is_fft:
@@ -547,9 +557,11 @@ def main():
     value = GLOBAL_BATCH / (ms_step / 1000.0)
     tflops = gemm_fl / (gemm_ms / 1000.0) / 1e12 if gemm_ms > 0 else 0.0
     tc = bool(_lib.lib.endia_b200_has_tcgen05()) and args.gemm != "ffma"
-    # 3xTF32 issues three tf32 MMAs per logical product and tf32 runs at half the bf16 rate, so the
-    # ceiling for logical flops is the measured bf16 throughput / 6.
-    peak = pk["bf16_tflops_sustained"] / 6.0
+    # Tensor-core time per logical product in units of one bf16 MMA: 3xTF32 issues three tf32 MMAs
+    # (tf32 runs at half the bf16 rate) = 6; the bf16-compensated scheme one tf32 and two bf16 = 4.
+    # The ceiling for logical flops is the measured bf16 throughput divided by that.
+    bf16c = tc_scheme(args.gemm) == "tf32_bf16x2"
+    peak = pk["bf16_tflops_sustained"] / (4.0 if bf16c else 6.0)
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
@@ -557,7 +569,9 @@ def main():
         "config": {"workload": "c2: MLP 1024-4096-4096-4096-1024 tanh, global batch 8192, MSE+Adam",
                    "global_batch": GLOBAL_BATCH, "per_gpu_batch": GLOBAL_BATCH // world,
                    "parallelism": "dp%d" % world,
-                   "gemm": "tcgen05 3xTF32 (fp32 accumulate)" if tc else "fp32 FFMA",
+                   "gemm": ("tcgen05, one tf32 MMA + two bf16 correction MMAs per product (fp32 accumulate, "
+                            "error <= 2.3e-6 of |a||b|)" if bf16c else "tcgen05 3xTF32 (fp32 accumulate)")
+                   if tc else "fp32 FFMA",
                    "l2": "activations and weights (>= 32 MiB each, 1.3 GB per step) exceed the 126 MB L2; no flush",
                    "e2e_io": "each step's batch is copied from pinned host memory on a copy stream while the "
                              "previous step computes; the loss is read back every step"},
@@ -572,13 +586,17 @@ def main():
                      # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant GEMM shape
                      # (8192 x 4096 x 4096, the forward and dX products of the 4096-wide layers), from
                      # the committed ncu capture; the other shapes of the step were not captured
-                     "traffic": 1.49e9 if (tc and world == 1) else None,
-                     "traffic_note": "bytes per launch of gemm_tc2p_kernel at 8192x4096x4096 (ncu, "
-                                     "profiles/gemm_tc2p_8192x4096x4096_ncu.md); compulsory 0.51e9",
+                     "traffic": (1.37e9 if bf16c else 1.49e9) if (tc and world == 1) else None,
+                     "traffic_note": "bytes per launch of gemm_tc2p_kernel at 8192x4096x4096 (ncu, profiles/%s); "
+                                     "compulsory 0.51e9" % ("gemm_tc2p_tf32_bf16x2_8192x4096x4096_ncu.md" if bf16c
+                                                            else "gemm_tc2p_8192x4096x4096_ncu.md"),
                      "kernel": "gemm (%d launches, %.1f%% of the step)" % (
                          n_gemm, 100.0 * gemm_ms / ms_total if ms_total else 0.0),
-                     "peak_note": "%s bf16_tflops_sustained %.1f / 2 (tf32 rate) / 3 (MMAs per 3xTF32 product)" % (
+                     "peak_note": ("%s bf16_tflops_sustained %.1f / 4 (one tf32 MMA = 2 bf16 MMA times, plus two "
+                                   "bf16 MMAs per product)" if bf16c else
+                                   "%s bf16_tflops_sustained %.1f / 2 (tf32 rate) / 3 (MMAs per 3xTF32 product)") % (
                          pk["source"], pk["bf16_tflops_sustained"]),
+                     "frac_of_3xtf32_ceiling": tflops / (pk["bf16_tflops_sustained"] / 6.0),
                      "frac_of_bf16_%s" % pk["source"]: tflops / pk["bf16_tflops_sustained"],
                      "algorithmic_gflop_per_step": gemm_flops(GLOBAL_BATCH) / 1e9 / world},
     }

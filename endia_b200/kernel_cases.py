@@ -57,7 +57,7 @@ def main():
     ap.add_argument("--k", type=int, default=4096)
     ap.add_argument("--ta", type=int, default=0)
     ap.add_argument("--tb", type=int, default=0)
-    ap.add_argument("--algo", default="auto", choices=["auto", "ffma", "3xtf32"])
+    ap.add_argument("--algo", default="auto", choices=["auto", "ffma", "3xtf32", "tf32_bf16x2"])
     ap.add_argument("--batch", type=int, default=32)
     ap.add_argument("--shape", default="256,256,256")
     ap.add_argument("--rows", type=int, default=8192)
@@ -73,7 +73,8 @@ def main():
     out = {"case": a.case}
 
     if a.case == "gemm":
-        algo = {"auto": _lib.GEMM_AUTO, "ffma": _lib.GEMM_FFMA, "3xtf32": _lib.GEMM_3XTF32}[a.algo]
+        algo = {"auto": _lib.GEMM_AUTO, "ffma": _lib.GEMM_FFMA, "3xtf32": _lib.GEMM_3XTF32,
+                "tf32_bf16x2": _lib.GEMM_TF32_BF16X2}[a.algo]
         A = _randn((a.k, a.m) if a.ta else (a.m, a.k), 1)
         B = _randn((a.n, a.k) if a.tb else (a.k, a.n), 2)
         Cc = nd.Array([a.m, a.n])
