@@ -1,17 +1,26 @@
-// fp32 GEMM on the 5th-generation tensor cores (tcgen05) with the 3xTF32 split:
-//   a = a_hi + a_lo,  a_hi = a with the 13 low mantissa bits cleared (exactly a tf32 value),
-//   a*b ~= a_hi*b_hi + a_hi*b_lo + a_lo*b_hi        (fp32 accumulation in tensor memory)
-// which keeps ~21 bits of each product, so gradients stay within 1e-4 of the fp32 result.
+// fp32 GEMM on the 5th-generation tensor cores (tcgen05) with split-precision products:
+//   a = a_hi + a_lo,  a_hi = a with the 13 low mantissa bits cleared (exactly a tf32 value; the
+//   tensor core reads fp32 storage that way, so the raw array is the hi operand),
+//   a*b ~= a_hi*b_hi + a_lo*b + a*b_lo              (fp32 accumulation in tensor memory)
+// 3xTF32 forms all three products with tf32 MMAs on fp32 low parts (~21 bits per product); the
+// bf16-compensated scheme forms the two corrections with bf16 MMAs on bf16(a_lo), bf16(b), bf16(a),
+// bf16(b_lo) (~19 bits per product, two thirds of the tensor-core time). Either way gradients stay
+// within 1e-4 of the fp32 result; plain tf32 (one product) is never used.
 //
-// Structure of one CTA (320 threads, one 128 x BN output tile):
-//   warp 0   : producer - one lane issues TMA tile loads (hi and lo tiles of A and B, 128-byte
-//              swizzle) into a ring of shared-memory stages, signalled through mbarriers
+// Two kernels:
+//   gemm_tc2p_kernel  persistent, clusters of two CTAs (cta_group::2, 256 x 256 tiles), both
+//                     schemes, bulk-tensor-store epilogue, optional two-way K split (N >= 256)
+//   gemm_tc_kernel    one CTA per 128 x BN tile, 3xTF32, optional split-K over blockIdx.y
+// Structure of a CTA (320 threads):
+//   warp 0   : producer - one lane issues TMA tile loads (the fp32 tile and the operand parts of A
+//              and B, swizzled) into a ring of shared-memory stages, signalled through mbarriers
 //   warp 1   : allocates tensor memory (two accumulators of BN columns: the hi*hi sum and the
-//              sum of the two correction products); one lane issues tcgen05.mma (kind::tf32,
-//              M = 128, N = BN, K = 8) three times per k-step and commits each stage back
+//              sum of the two correction products); one lane issues tcgen05.mma and commits each
+//              stage back to the producer
 //   warps 2-9: epilogue - tcgen05.ld of the accumulators (one row per thread, two warps per lane
-//              quarter, each half of the columns), the fused epilogue of endia_b200_epilogue,
-//              128-bit stores
+//              quarter, each half of the columns), their sum through a swizzled shared-memory
+//              chunk, the fused epilogue of endia_b200_epilogue with eight lanes along a row, and
+//              the store (bulk tensor store in the persistent kernel, 128-bit stores otherwise)
 // Operands are consumed in the layout they have in global memory: a row-major [rows, K] operand
 // is K-major, a stored-transposed one ([K, rows]) is MN-major, selected in the instruction and
 // shared-memory descriptors, so dX = dY*W^T and dW = X^T*dY need no transposed copies

@@ -75,8 +75,9 @@ def check_layout_case(nd, ta, tb, M, N, K, algo, bound):
     assert max_rel(out, ffma) < 1e-4
 
 
+@pytest.mark.parametrize("scheme", ["3xtf32", "tf32_bf16x2"])
 @pytest.mark.parametrize("ta,tb,alpha", [(1, 0, 1.0), (0, 1, 0.5)])
-def test_3xtf32_halved_reduction(nd, ta, tb, alpha):
+def test_halved_reduction(nd, ta, tb, alpha, scheme):
     """81 tiles of 256 x 256 fill the last round of CTA pairs badly: the persistent kernel halves K
     and the two halves are added into a zeroed C by the copy engine. The result must not depend on
     which half lands first, so two runs agree bit for bit; C starts out as garbage."""
@@ -89,15 +90,16 @@ def test_3xtf32_halved_reduction(nd, ta, tb, alpha):
     epi = _lib.Epilogue()
     epi.alpha, epi.beta = alpha, 0.0
     junk = np.full((M, N), 1e30, np.float32)
-    out = run_gemm(nd, a, b, ta, tb, _lib.GEMM_3XTF32, epi=epi, c0=junk)
-    out2 = run_gemm(nd, a, b, ta, tb, _lib.GEMM_3XTF32, epi=epi, c0=junk)
+    algo = _lib.GEMM_3XTF32 if scheme == "3xtf32" else _lib.GEMM_TF32_BF16X2
+    out = run_gemm(nd, a, b, ta, tb, algo, epi=epi, c0=junk)
+    out2 = run_gemm(nd, a, b, ta, tb, algo, epi=epi, c0=junk)
     assert np.array_equal(out, out2)
     am = (a.T if ta else a).astype(np.float64)
     bm = (b.T if tb else b).astype(np.float64)
     rows = slice(0, M, 7)        # every 7th row keeps the float64 product short
     ref = alpha * (am[rows] @ bm)
     err = np.abs(out[rows] - ref) / dot_scale(am[rows], bm)
-    assert err.max() < 5e-6, err.max()
+    assert err.max() < (5e-6 if scheme == "3xtf32" else 8e-6), err.max()
 
 
 def test_3xtf32_fused_epilogue(nd):
