@@ -49,3 +49,26 @@ def test_fft_meta_data_encoding():
     assert fft_ops.encode_fft_params([0, 1, 2], "ortho") == [3, 0, 1, 2, 2]
     with pytest.raises(_lib.EndiaError):
         fft_ops.encode_fft_params([0], "bogus")
+
+
+def test_gemm_operand_parts_plan(monkeypatch):
+    """Which operand parts the host hands to endia_b200_gemm for the shapes of the configs: the
+    bf16 split where the two-CTA kernel runs, fp32 low parts for the 3xTF32 kernels, none for the
+    FFMA and skinny paths."""
+    monkeypatch.delenv("ENDIA_B200_TC_SCHEME", raising=False)
+    plan = binary_ops._tc_plan
+    A = _lib.GEMM_AUTO
+    for M, N, K in [(8192, 4096, 1024), (8192, 4096, 4096), (8192, 1024, 4096), (4096, 4096, 8192),
+                    (1024, 4096, 8192), (4096, 1024, 256)]:
+        assert plan(M, N, K, 1, A) == "pair16", (M, N, K)
+    assert plan(256, 1024, 4096, 1, A) == "lo32"        # few tiles, long K: split-K 3xTF32 kernel
+    assert plan(1024, 1024, 4096, 1, A) == "lo32"
+    assert plan(4096, 128, 1024, 1, A) == "lo32"        # N < 256: one-CTA kernel
+    assert plan(4096, 4096, 16384, 1, A) is None        # K > 8192 stays on FFMA
+    assert plan(4096, 1, 1024, 1, A) is None and plan(64, 512, 512, 1, A) is None
+    assert plan(8192, 4096, 4096, 2, A) is None         # batched products
+    assert plan(8192, 4096, 4096, 1, _lib.GEMM_FFMA) is None
+    assert plan(8192, 4096, 4096, 1, _lib.GEMM_3XTF32) == "lo32"
+    assert plan(8192, 4096, 4096, 1, _lib.GEMM_TF32_BF16X2) == "pair16"
+    monkeypatch.setenv("ENDIA_B200_TC_SCHEME", "3xtf32")
+    assert plan(8192, 4096, 4096, 1, A) == "lo32"
