@@ -86,3 +86,36 @@ class HostBatchFeeder:
         """Start the copy of the following batch (call after the step's kernels are enqueued)."""
         if self.ready[self.cur] is None:
             self._stage(self.cur)
+
+
+class CapturedStep:
+    """Replays a step as one CUDA graph. `fn()` must be static: the same ops on the same shapes
+    every call, inputs read from Arrays that exist before the capture (refill them in place, e.g.
+    with HostBatchFeeder-style copies, between replays), no host reads inside (to_numpy, item).
+    fn runs `warmup` times eagerly first, so that first-use set-up (kernel attributes, twiddle
+    tables) is done, then once more under capture; its return value from that run is kept and
+    returned by every call, its Arrays refilled by the replay. A step whose kernels are short next
+    to the ~25 us of host work per launch (the create_graph=True double-backward step has about
+    110 launches) becomes GPU-bound this way."""
+
+    def __init__(self, fn, warmup=2):
+        import torch
+        from .._array import device
+        device()
+        for _ in range(warmup):
+            fn()
+        torch.cuda.synchronize()
+        from .. import _lib
+        before = _lib.lib.endia_b200_launch_count()
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            self.out = fn()
+        torch.cuda.synchronize()
+        # kernels of this library inside the graph (endia_b200_launch_count only sees enqueues)
+        self.launches_per_replay = int(_lib.lib.endia_b200_launch_count() - before)
+        self.replays = 0
+
+    def __call__(self):
+        self.graph.replay()
+        self.replays += 1
+        return self.out

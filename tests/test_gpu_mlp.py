@@ -357,3 +357,43 @@ def test_reference_benchmark_mlp_functional(nd, oracle):
         tiny = np.abs(gr.reshape(ref.shape)) < 1e-6
         got = a.to_numpy().reshape(ref.shape)
         assert max_rel(np.where(tiny, ref, got), ref) < TOL, i
+
+
+def test_captured_step_replays_double_backward(nd):
+    """utils.CapturedStep: the create_graph=True step replayed as a CUDA graph gives the eager
+    result, and follows its input array when that is refilled in place between replays."""
+    import torch
+    from endia_b200.utils.general import CapturedStep
+    from endia_b200.dist import flat_tensor
+    d = [64, 512, 512, 1]
+    Ws, bs, x, _ = make_mlp_inputs(d, 512, 5, bias_zero=True)
+    W = [nd.Array(w, requires_grad=True) for w in Ws]
+    B = [nd.Array(b, requires_grad=True) for b in bs]
+    X = nd.Array(x, requires_grad=True)
+
+    def step():
+        args = [X, None]
+        for w, b in zip(W, B):
+            args += [w, b]
+        f = nd.nn.mlp(args, activation="tanh")
+        gx = nd.grad(outs=[nd.sum(f)], inputs=[X], create_graph=True)[0]
+        loss = nd.mean(f, [0, 1]) + 0.1 * (nd.sum(gx * gx) / 512.0)
+        return loss, nd.grad(outs=[loss], inputs=W + B)
+
+    loss_e, grads_e = step()
+    ref = [loss_e.to_numpy()] + [g.to_numpy() for g in grads_e]
+    cap = CapturedStep(step)
+    assert cap.launches_per_replay > 20
+    loss_c, grads_c = cap()
+    got = [loss_c.to_numpy()] + [g.to_numpy() for g in grads_c]
+    for a, b in zip(got, ref):
+        assert np.array_equal(a, b)
+    x2 = rng(6).standard_normal(x.shape).astype(np.float32)
+    flat_tensor(X).copy_(torch.from_numpy(x2).reshape(-1))
+    loss_c, grads_c = cap()
+    got2 = [loss_c.to_numpy()] + [g.to_numpy() for g in grads_c]
+    X2 = nd.Array(x2, requires_grad=True)
+    X_saved, X = X, X2          # eager run on the new input
+    loss_e2, grads_e2 = step()
+    for a, b in zip(got2, [loss_e2.to_numpy()] + [g.to_numpy() for g in grads_e2]):
+        assert np.array_equal(a, b)
