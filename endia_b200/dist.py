@@ -133,13 +133,102 @@ class SlabFFT:
         return self.fft_tail(slab_unpack(back, self.world), inverse)
 
 
-def _strided_view(arr, shape, stride):
-    v = Array(ArrayShape(shape, stride, arr.storage_offset()))
+def _strided_view(arr, shape, stride, offset=0):
+    v = Array(ArrayShape(shape, stride, arr.storage_offset() + offset))
     v.buf = arr.buf
     v.base_ = arr.base()
     v.is_view = True
     v.is_complex_flag = arr.is_complex()
     return v
+
+
+class PeerBuffers:
+    """One device buffer per rank, mapped into every rank of the machine through CUDA IPC, plus
+    the stream-ordered barrier that orders the ranks' accesses (a one-element NCCL all-reduce:
+    when it completes on a rank, every rank has reached that point of its stream). A rank writes
+    into the others' buffers with endia_b200_copy_strided (plain stores over NVLink)."""
+
+    _cache = {}
+
+    @classmethod
+    def get(cls, nbytes, group=None):
+        """Buffers of at least nbytes, created collectively on first use and reused; None when the
+        ranks cannot map each other's memory (the exchange then goes through NCCL)."""
+        key = id(group)
+        cur = cls._cache.get(key)
+        if cur is not None and (cur is False or cur.nbytes >= nbytes):
+            return cur or None
+        try:
+            made = cls(nbytes, group)
+        except Exception as exc:   # e.g. no peer access between the devices
+            if os.environ.get("ENDIA_B200_DEBUG"):
+                print("endia_b200: peer buffers unavailable (%s); using NCCL all-to-all" % exc)
+            made = False
+        # every rank must take the same path
+        flag = torch.tensor([1.0 if made else 0.0], device=device())
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=group)
+        if float(flag.item()) == 0.0:
+            made = False
+        cls._cache[key] = made
+        return made or None
+
+    def __init__(self, nbytes, group=None):
+        import ctypes as C
+        from . import _lib
+        self.nbytes, self.group = int(nbytes), group
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        local = C.c_void_p()
+        handle = (C.c_ubyte * 64)()
+        _lib.call("endia_b200_ipc_alloc", self.nbytes, C.byref(local), handle)
+        handles = [None] * self.world
+        dist.all_gather_object(handles, bytes(handle), group=group)
+        self.ptrs = []
+        for r, h in enumerate(handles):
+            if r == self.rank:
+                self.ptrs.append(local.value)
+            else:
+                p = C.c_void_p()
+                hb = (C.c_ubyte * 64).from_buffer_copy(h)
+                _lib.call("endia_b200_ipc_open", hb, C.byref(p))
+                self.ptrs.append(p.value)
+        self._flag = torch.zeros(1, device=device())
+
+    def barrier(self):
+        dist.all_reduce(self._flag, group=self.group)
+
+    def tensor(self, rank, shape, stride, offset=0, is_complex=True):
+        """C descriptor of a view of rank `rank`'s buffer."""
+        from ._lib import Tensor as _CTensor
+        t = _CTensor()
+        t.data = self.ptrs[rank]
+        for i, (e, st) in enumerate(zip(shape, stride)):
+            t.shape[i] = e
+            t.stride[i] = st
+        t.offset = offset
+        t.ndim = len(shape)
+        t.is_complex = 1 if is_complex else 0
+        return t
+
+    def local_array(self, shape):
+        """This rank's buffer as a contiguous complex Array (no copy, not owned by the Array)."""
+        n = 1
+        for e in shape:
+            n *= e
+        a = Array(ArrayShape(shape))
+        a.is_complex_flag = True
+        a.buf = _wrap_device_memory(self.ptrs[self.rank], 2 * n)
+        a._keepalive = self
+        return a
+
+
+def _wrap_device_memory(ptr, n_floats):
+    """float32 torch tensor over device memory this library allocated itself."""
+    class _Mem:
+        pass
+    holder = _Mem()
+    holder.__cuda_array_interface__ = {"shape": (int(n_floats),), "typestr": "<f4", "data": (int(ptr), False),
+                                       "version": 3, "strides": None}
+    return torch.as_tensor(holder, device=device())
 
 
 def _exchange_arrays(src, world, group=None):
@@ -178,9 +267,34 @@ def fftn_slab(x_local, world=None, group=None):
         setup_shape_and_data(a)
         return a
 
+    peers = None
+    if world > 1 and dist.is_initialized() and dist.get_backend(group) == "nccl" \
+            and os.environ.get("ENDIA_B200_SLAB_PEER", "1") != "0":
+        peers = PeerBuffers.get(8 * s0 * n1 * n2, group)
+    rank = dist.get_rank(group) if (dist.is_initialized() and world > 1) else 0
+
+    def push(src_desc_of_block, dst_desc_of_block):
+        """Each rank writes block q of its array into its place in rank q's buffer; the barriers
+        order the writes against the previous and the next readers of the buffers."""
+        from . import _lib
+        from ._array import stream
+        peers.barrier()
+        for i in range(world):
+            q = (rank + i) % world          # start with the own block, then round-robin over the peers
+            _lib.call("endia_b200_copy_strided", src_desc_of_block(q), dst_desc_of_block(q), stream())
+        peers.barrier()
+
     def forward_impl(x):
         y1 = new_like([s0, n1, n2])
         run_fft(x, y1, [1, 2], False, 1.0)
+        if peers is not None:
+            # block q = y1[:, q*s1:(q+1)*s1, :] lands as rows [rank*s0, (rank+1)*s0) of rank q's
+            # [n0, s1, n2] array: packing, exchange and placement in one pass
+            push(lambda q: _strided_view(y1, [s0, s1, n2], [n1 * n2, n2, 1], q * s1 * n2).desc(),
+                 lambda q: peers.tensor(q, [s0, s1, n2], [s1 * n2, n2, 1], rank * s0 * s1 * n2))
+            out = new_like([n0, s1, n2])
+            run_fft(peers.local_array([n0, s1, n2]), out, [0], False, 1.0)
+            return out
         # pack: block q = y1[:, q*s1:(q+1)*s1, :]  ->  [P, s0, s1, n2] contiguous
         packed = copy(_strided_view(y1, [world, s0, s1, n2], [s1 * n2, n1 * n2, n2, 1]))
         recv = _exchange_arrays(packed, world, group)          # [P*s0 = n0, s1, n2]
@@ -192,6 +306,14 @@ def fftn_slab(x_local, world=None, group=None):
     def backward_impl(g):
         g0 = new_like([n0, s1, n2])
         run_fft(g, g0, [0], True, 1.0)                           # conj o fft o conj along axis 0
+        if peers is not None:
+            # block q = g0[q*s0:(q+1)*s0] lands as columns [rank*s1, (rank+1)*s1) of axis 1 of rank
+            # q's [s0, n1, n2] array (a strided destination): no unpacking pass
+            push(lambda q: _strided_view(g0, [s0, s1, n2], [s1 * n2, n2, 1], q * s0 * s1 * n2).desc(),
+                 lambda q: peers.tensor(q, [s0, s1, n2], [n1 * n2, n2, 1], rank * s1 * n2))
+            dx = new_like([s0, n1, n2])
+            run_fft(peers.local_array([s0, n1, n2]), dx, [1, 2], True, 1.0)
+            return dx
         recv = _exchange_arrays(g0, world, group)              # block q: [s0, s1 (chunk q), n2]
         # unpack: [P, s0, s1, n2] -> [s0, P*s1 = n1, n2]
         unpacked = copy(_strided_view(recv, [s0, world, s1, n2], [s1 * n2, s0 * s1 * n2, n2, 1]))

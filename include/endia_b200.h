@@ -380,6 +380,26 @@ int endia_b200_allreduce_sum_f32(void *comm, const float *send, float *recv, int
 int endia_b200_alltoall_bytes(void *comm, const void *send, void *recv, int64_t bytes_per_peer,
                               void *stream);
 
+/* ---------------------------------------------- memory shared between ranks ---- */
+
+/* dst = src for two views of the same shape that may both be strided (the last dim contiguous on
+ * both sides); 128-bit accesses when the runs allow. Either side may lie in another GPU's memory
+ * mapped with endia_b200_ipc_open (plain loads and stores over NVLink). Used by the slab-
+ * decomposed fftn to write each rank's block of the transpose straight into its place in the
+ * receiving rank's array (the gather of fft_cooley_tukey.mojo:251-257, across GPUs). */
+int endia_b200_copy_strided(const endia_b200_tensor *src, const endia_b200_tensor *dst, void *stream);
+
+/* A device allocation that other processes on the same machine can map (CUDA IPC):
+ *   ipc_alloc: allocates `bytes` and fills a 64-byte handle to pass to the other ranks
+ *   ipc_open:  maps another process's allocation from its handle (peer access over NVLink)
+ *   ipc_close / ipc_free: unmap a peer's allocation / free an own one (after all peers closed it)
+ * The caller orders accesses between ranks itself (a collective on the stream serves as barrier). */
+#define ENDIA_B200_IPC_HANDLE_BYTES 64
+int endia_b200_ipc_alloc(size_t bytes, void **ptr, void *handle64);
+int endia_b200_ipc_open(const void *handle64, void **ptr);
+int endia_b200_ipc_close(void *ptr);
+int endia_b200_ipc_free(void *ptr);
+
 #ifdef __cplusplus
 }
 #endif

@@ -300,3 +300,33 @@ def test_gemm_degenerate_shapes_with_epilogue(nd, ta, tb, M, N, K):
     bm = (b.T if tb else b).astype(np.float64)
     v = np.tanh(0.5 * (am @ bm) + bias) * (saved > 0) + 2.0 * c0
     assert max_rel(Cd.to_numpy(), v) < TOL
+
+
+def test_copy_strided_both_sides(nd):
+    """endia_b200_copy_strided: strided source into a strided destination (the placement step of
+    the slab transpose), complex and real, with and without 128-bit runs."""
+    from endia_b200 import _lib
+    from endia_b200._array import stream, ArrayShape, Array
+    r = rng(12)
+
+    def view(arr, shape, stride, offset):
+        v = Array(ArrayShape(shape, stride, offset))
+        v.buf = arr.buf
+        v.is_complex_flag = arr.is_complex()
+        return v
+
+    z = (r.standard_normal((6, 8, 10)) + 1j * r.standard_normal((6, 8, 10))).astype(np.complex64)
+    src = nd.Array(z)
+    dst_host = np.zeros((6, 16, 10), np.complex64)
+    dst = nd.Array(dst_host)
+    # rows 2..5 of axis 1 of src -> columns 8..11 of axis 1 of dst
+    _lib.call("endia_b200_copy_strided", view(src, [6, 4, 10], [80, 10, 1], 20).desc(),
+              view(dst, [6, 4, 10], [160, 10, 1], 80).desc(), stream())
+    dst_host[:, 8:12, :] = z[:, 2:6, :]
+    assert np.array_equal(dst.to_numpy(), dst_host)
+    x = r.standard_normal((5, 7, 9)).astype(np.float32)          # odd run: scalar path
+    a, b = nd.Array(x), nd.Array(np.zeros((7, 5, 9), np.float32))
+    _lib.call("endia_b200_copy_strided", a.desc(), view(b, [5, 7, 9], [9, 45, 1], 0).desc(), stream())
+    assert np.array_equal(b.to_numpy(), x.transpose(1, 0, 2))
+    st = _lib.lib.endia_b200_copy_strided(view(a, [5, 9, 7], [63, 1, 9], 0).desc(), b.desc(), stream())
+    assert st in (_lib.EINVAL, _lib.ESHAPE)
