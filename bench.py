@@ -425,7 +425,7 @@ def main():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="endia_b200", choices=["endia_b200", "reference"])
-    ap.add_argument("--cpu-rows", type=int, default=48)
+    ap.add_argument("--cpu-rows", type=int, default=160)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--gemm", default="auto", choices=["auto", "ffma", "3xtf32", "tf32_bf16x2"],
                     help="auto = tf32_bf16x2 on the two-CTA tcgen05 kernel (one tf32 MMA + two bf16 correction "
