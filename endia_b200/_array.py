@@ -326,5 +326,36 @@ class Array:
         return self._inplace(self.__truediv__(other))
 
 
+class LazyComplex(Array):
+    """complex(re, 0) whose storage is only written when something asks for it. The gradient of
+    real() is such an array (view_ops/real_op.mojo:75-77) and its usual consumer, the
+    conjugate-direction FFT of FFTN.vjp, reads the real array itself (the FFT kernels take a real
+    input as complex with a zero imaginary part), so the complex copy is never made on that path;
+    any other reader gets it on first access of `buf`."""
+    re_part = None
+
+    def __init__(self, re):
+        super().__init__(ArrayShape(re.shape()))
+        self.is_complex_flag = True
+        self.name = "complex"
+        self.re_part = re
+        self._buf = None
+
+    @property
+    def buf(self):
+        if self._buf is None and self.re_part is not None:
+            from .functional.init_ops import complex as make_complex
+            from .functional.view_ops import expand
+            self._buf = make_complex(self.re_part, expand(Array([1]), self.re_part.shape())).buf
+        return self._buf
+
+    @buf.setter
+    def buf(self, value):
+        self._buf = value
+
+    def materialised(self):
+        return self._buf is not None
+
+
 Tensor = Array
 ndarray = Array

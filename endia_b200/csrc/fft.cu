@@ -35,7 +35,14 @@ struct FftParams {
   // W_big^(j*l) = tw_hi[(j*l) >> lo_bits] * tw_lo[(j*l) & mask].
   const float2 *tw_hi, *tw_lo;
   int lo_bits;
+  int in_real;                   // `in` points at floats (one per element): the imaginary part is 0
 };
+
+// Element `idx` (in elements from `base`) of the input, which is complex or, with `real`, real.
+__device__ __forceinline__ float2 load_in(const float2 *base, int64_t idx, int real) {
+  if (real) return make_float2(reinterpret_cast<const float *>(base)[idx], 0.f);
+  return base[idx];
+}
 
 __device__ __forceinline__ float2 cmul(float2 a, float2 b) {
   return make_float2(a.x * b.x - a.y * b.y, a.x * b.y + a.y * b.x);
@@ -146,12 +153,12 @@ __global__ void __launch_bounds__(1024, 1) fft_tile_kernel(const __grid_constant
     int64_t nl64 = P.lines_per_outer - line0;
     const int nl = nl64 < T ? (int)nl64 : T;
     // ---- load
-    const float2 *src = P.in + o * P.in_outer_stride + line0 * P.in_line_stride;
+    const int64_t src0 = o * P.in_outer_stride + line0 * P.in_line_stride;
     if (P.in_elem_stride == 1) {
       for (int w = tid; w < total; w += nthr) {
         const int t = w / N, j = w - t * N;
         float2 v = make_float2(0.f, 0.f);
-        if (t < nl) v = src[(int64_t)t * P.in_line_stride + j];
+        if (t < nl) v = load_in(P.in, src0 + (int64_t)t * P.in_line_stride + j, P.in_real);
         if (P.conj_in) v.y = -v.y;
         sm[j * LS + t] = v;
       }
@@ -159,7 +166,7 @@ __global__ void __launch_bounds__(1024, 1) fft_tile_kernel(const __grid_constant
       for (int w = tid; w < total; w += nthr) {
         const int t = w & (T - 1), j = w >> P.logT;
         float2 v = make_float2(0.f, 0.f);
-        if (t < nl) v = src[(int64_t)t * P.in_line_stride + (int64_t)j * P.in_elem_stride];
+        if (t < nl) v = load_in(P.in, src0 + (int64_t)t * P.in_line_stride + (int64_t)j * P.in_elem_stride, P.in_real);
         if (P.conj_in) v.y = -v.y;
         sm[j * LS + t] = v;
       }
@@ -221,6 +228,7 @@ struct FastParams {
   int lo_bits;
   int conj_in, conj_out;
   float scale;
+  int in_real;                   // as in FftParams
 };
 
 enum { FAST_COL = 0, FAST_ROW = 1, FAST_COL_STAGED_IN = 2 };
@@ -251,7 +259,7 @@ __device__ __forceinline__ void fast_store(const FastParams &P, float2 *dst, int
   dst[(int64_t)j * P.out_elem] = v;
 }
 
-template <int LOGN, int MODE, bool TW, int T>
+template <int LOGN, int MODE, bool TW, int T, bool REAL>
 __global__ void __launch_bounds__((T << LOGN) / 16, 16384 / (T << LOGN))
 fft_fast_kernel(const __grid_constant__ FastParams P) {
   constexpr int N = 1 << LOGN, NT = T * N / 16, Q = N / 16, R3 = N / 256;
@@ -272,11 +280,11 @@ fft_fast_kernel(const __grid_constant__ FastParams P) {
     if constexpr (MODE == FAST_COL_STAGED_IN) {
       // contiguous lines: a warp reads 32 consecutive points of one line, the swizzle makes the
       // point-major shared store conflict-free as well
-      const float2 *src = P.in + o * P.in_outer + (int64_t)line0 * P.in_line;
+      const int64_t src0 = o * P.in_outer + (int64_t)line0 * P.in_line;
 #pragma unroll
       for (int e = 0; e < 16; ++e) {
         const int w = tid + e * NT, j = w & (N - 1), tt = w >> LOGN;
-        float2 v = src[(int64_t)tt * P.in_line + j];
+        float2 v = load_in(P.in, src0 + (int64_t)tt * P.in_line + j, REAL ? 1 : 0);
         if (P.conj_in) v.y = -v.y;
         sm[fast_phys<LOGN, MODE, T>(j, tt)] = v;
       }
@@ -285,9 +293,16 @@ fft_fast_kernel(const __grid_constant__ FastParams P) {
       for (int r = 0; r < 16; ++r) u[r] = sm[fast_phys<LOGN, MODE, T>(i0 + r * Q, t)];
       __syncthreads();
     } else {
-      const float2 *src = P.in + o * P.in_outer + (int64_t)line * P.in_line;
+      const int64_t src0 = o * P.in_outer + (int64_t)line * P.in_line;
+      if constexpr (REAL) {
+        const float *srcr = reinterpret_cast<const float *>(P.in) + src0;
 #pragma unroll
-      for (int r = 0; r < 16; ++r) u[r] = src[(int64_t)(i0 + r * Q) * P.in_elem];
+        for (int r = 0; r < 16; ++r) u[r] = make_float2(srcr[(int64_t)(i0 + r * Q) * P.in_elem], 0.f);
+      } else {
+        const float2 *src = P.in + src0;
+#pragma unroll
+        for (int r = 0; r < 16; ++r) u[r] = src[(int64_t)(i0 + r * Q) * P.in_elem];
+      }
       if (P.conj_in) {
 #pragma unroll
         for (int r = 0; r < 16; ++r) u[r].y = -u[r].y;
@@ -399,13 +414,13 @@ static int pick_T(int N) {
   return T;
 }
 
-template <int LOGN, int MODE, bool TW, int T>
+template <int LOGN, int MODE, bool TW, int T, bool REAL>
 static int launch_fast_variant(FastParams F, int64_t lines_per_outer, int64_t n_outer, cudaStream_t s) {
   constexpr int N = 1 << LOGN;
   constexpr size_t SMEM = sizeof(float2) * (size_t)N * (T + 1);   // T lines of data + the twiddle table
   F.tiles_per_outer = lines_per_outer / T;
   F.n_tiles = F.tiles_per_outer * n_outer;
-  auto kern = fft_fast_kernel<LOGN, MODE, TW, T>;
+  auto kern = fft_fast_kernel<LOGN, MODE, TW, T, REAL>;
   static bool attr = false;
   if (!attr) {
     EB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM));
@@ -419,23 +434,30 @@ static int launch_fast_variant(FastParams F, int64_t lines_per_outer, int64_t n_
   return ENDIA_B200_OK;
 }
 
-template <int LOGN>
-static int launch_fast_n(const FastParams &F, bool tw, int64_t lpo, int64_t no, cudaStream_t s) {
+template <int LOGN, bool REAL>
+static int launch_fast_nr(const FastParams &F, bool tw, int64_t lpo, int64_t no, cudaStream_t s) {
   const bool row_in = F.in_elem == 1, row_out = F.out_elem == 1;
-  if (row_in && row_out) return launch_fast_variant<LOGN, FAST_ROW, false, 8>(F, lpo, no, s);
+  if (row_in && row_out) return launch_fast_variant<LOGN, FAST_ROW, false, 8, REAL>(F, lpo, no, s);
   // 16 lines per tile give 128-byte segments on the strided side; they fit next to 2 CTAs per SM
   // for lines up to 512 points (and, with one 1024-thread CTA per SM, for 1024 points).
   static const int wide_max = []() { const char *e = getenv("ENDIA_B200_FFT_WIDE_MAX"); return e ? atoi(e) : 1024; }();
   if constexpr (LOGN <= 10) {
     if ((1 << LOGN) <= wide_max && lpo % 16 == 0) {
-      if (row_in) return launch_fast_variant<LOGN, FAST_COL_STAGED_IN, false, 16>(F, lpo, no, s);
-      return tw ? launch_fast_variant<LOGN, FAST_COL, true, 16>(F, lpo, no, s)
-                : launch_fast_variant<LOGN, FAST_COL, false, 16>(F, lpo, no, s);
+      if (row_in) return launch_fast_variant<LOGN, FAST_COL_STAGED_IN, false, 16, REAL>(F, lpo, no, s);
+      return tw ? launch_fast_variant<LOGN, FAST_COL, true, 16, REAL>(F, lpo, no, s)
+                : launch_fast_variant<LOGN, FAST_COL, false, 16, REAL>(F, lpo, no, s);
     }
   }
-  if (row_in) return launch_fast_variant<LOGN, FAST_COL_STAGED_IN, false, 8>(F, lpo, no, s);
-  return tw ? launch_fast_variant<LOGN, FAST_COL, true, 8>(F, lpo, no, s)
-            : launch_fast_variant<LOGN, FAST_COL, false, 8>(F, lpo, no, s);
+  if (row_in) return launch_fast_variant<LOGN, FAST_COL_STAGED_IN, false, 8, REAL>(F, lpo, no, s);
+  return tw ? launch_fast_variant<LOGN, FAST_COL, true, 8, REAL>(F, lpo, no, s)
+            : launch_fast_variant<LOGN, FAST_COL, false, 8, REAL>(F, lpo, no, s);
+}
+
+template <int LOGN>
+static int launch_fast_n(const FastParams &F, bool tw, int64_t lpo, int64_t no, cudaStream_t s) {
+  // a real source (read with a zero imaginary part) has kernels of its own, so that the complex
+  // ones keep their register budget
+  return F.in_real ? launch_fast_nr<LOGN, true>(F, tw, lpo, no, s) : launch_fast_nr<LOGN, false>(F, tw, lpo, no, s);
 }
 
 // Supported combinations: strided in and out (optionally with the four-step twiddle), contiguous
@@ -464,9 +486,10 @@ struct Pass {
   int64_t big_n;  // > 0: four-step twiddle W_big^(j*line) at the store
 };
 
-static int launch_pass(const Pass &ps, const float2 *in, float2 *out, cudaStream_t s) {
+static int launch_pass(const Pass &ps, const float2 *in, float2 *out, cudaStream_t s, bool in_real = false) {
   FftParams P{};
   P.in = in; P.out = out; P.N = ps.N;
+  P.in_real = in_real ? 1 : 0;
   P.T = pick_T(ps.N); P.logT = ilog2(P.T);
   plan_radices(ps.N, P);
   P.lines_per_outer = ps.lines_per_outer;
@@ -482,6 +505,7 @@ static int launch_pass(const Pass &ps, const float2 *in, float2 *out, cudaStream
       fast_supported(ps.in_elem, ps.out_elem, ps.big_n > 0)) {
     FastParams F{};
     F.in = in; F.out = out;
+    F.in_real = in_real ? 1 : 0;
     F.tiles_per_outer = ps.lines_per_outer / 8;
     F.n_tiles = F.tiles_per_outer * ps.n_outer;
     F.in_outer = ps.in_outer; F.in_line = ps.in_line; F.in_elem = ps.in_elem;
@@ -600,7 +624,10 @@ int endia_b200_fft_c2c(const endia_b200_tensor *in, const endia_b200_tensor *out
   if (st) return st;
   if ((st = check_tensor(in, "fft: in"))) return st;
   if ((st = check_tensor(out, "fft: out"))) return st;
-  EB_REQUIRE(in->is_complex && out->is_complex, ENDIA_B200_EINVAL, "fft: in and out must be complex");
+  // A real `in` (contiguous) is read as complex with a zero imaginary part by the first pass.
+  EB_REQUIRE(out->is_complex, ENDIA_B200_EINVAL, "fft: out must be complex");
+  bool real_in = !in->is_complex;
+  EB_REQUIRE(!real_in || is_contiguous(in), ENDIA_B200_EINVAL, "fft: a real input must be contiguous");
   EB_REQUIRE(n_dims >= 0 && n_dims <= ENDIA_B200_MAX_DIMS && (n_dims == 0 || dims), ENDIA_B200_EINVAL,
              "fft: bad dims list");
   EB_REQUIRE(in->ndim == out->ndim, ENDIA_B200_ESHAPE, "fft: rank mismatch");
@@ -615,7 +642,8 @@ int endia_b200_fft_c2c(const endia_b200_tensor *in, const endia_b200_tensor *out
   const int64_t total = numel(in);
   if (total == 0) return ENDIA_B200_OK;
   cudaStream_t s = as_stream(stream);
-  const float2 *src = reinterpret_cast<const float2 *>(in->data) + in->offset;
+  const float2 *src = real_in ? reinterpret_cast<const float2 *>(static_cast<const float *>(in->data) + in->offset)
+                              : reinterpret_cast<const float2 *>(in->data) + in->offset;
   float2 *dst = reinterpret_cast<float2 *>(out->data) + out->offset;
   if (!is_contiguous(in)) {
     // Gather the strided view once; the transform then runs in place on `out`.
@@ -625,7 +653,7 @@ int endia_b200_fft_c2c(const endia_b200_tensor *in, const endia_b200_tensor *out
   if (axes.empty()) {
     // Nothing to transform: out = scale * in (the inverse of a length-1 transform is itself).
     Pass ps{1, 1, total, 0, 1, 1, 0, 1, 1, 0, 0, scale, 0};
-    return launch_pass(ps, src, dst, s);
+    return launch_pass(ps, src, dst, s, real_in);
   }
   // Innermost axis first: its pass reads `in` in long contiguous runs.
   for (size_t a = axes.size(); a-- > 0;) {
@@ -644,7 +672,7 @@ int endia_b200_fft_c2c(const endia_b200_tensor *in, const endia_b200_tensor *out
         ps.in_outer = ps.out_outer = ai.n * ai.inner; ps.in_line = ps.out_line = 1;
         ps.in_elem = ps.out_elem = ai.inner;
       }
-      if ((st = launch_pass(ps, src, dst, s))) return st;
+      if ((st = launch_pass(ps, src, dst, s, real_in))) return st;
     } else {
       int n1, n2;
       split_len(ai.n, n1, n2);
@@ -660,7 +688,10 @@ int endia_b200_fft_c2c(const endia_b200_tensor *in, const endia_b200_tensor *out
         pa.N = n1; pa.n_outer = ng; pa.lines_per_outer = n2;
         pa.in_outer = pa.out_outer = ai.n; pa.in_line = pa.out_line = 1; pa.in_elem = pa.out_elem = n2;
         pa.conj_in = cin; pa.conj_out = 0; pa.scale = 1.f; pa.big_n = ai.n;
-        if ((st = launch_pass(pa, src + g0 * ai.n, tmp, s))) return st;
+        // (a real source is indexed in floats: the group offset is applied in those units)
+        const float2 *src_g = real_in ? reinterpret_cast<const float2 *>(reinterpret_cast<const float *>(src) + g0 * ai.n)
+                                      : src + g0 * ai.n;
+        if ((st = launch_pass(pa, src_g, tmp, s, real_in))) return st;
         // Pass B: for every k1, transform the contiguous row over n2; X[k1 + n1*k2] = row[k2].
         Pass pb{};
         pb.N = n2; pb.n_outer = ng; pb.lines_per_outer = n1;
@@ -671,6 +702,7 @@ int endia_b200_fft_c2c(const endia_b200_tensor *in, const endia_b200_tensor *out
       }
     }
     src = dst;
+    real_in = false;
   }
   return ENDIA_B200_OK;
 }

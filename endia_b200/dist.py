@@ -12,9 +12,12 @@ from ._array import Array, ArrayShape, device
 def init_process_group():
     """One process per GPU, launched by torchrun (RANK / LOCAL_RANK / WORLD_SIZE / MASTER_*)."""
     world = int(os.environ.get("WORLD_SIZE", "1"))
-    if world > 1:
-        # The gradient all-reduce runs beside the backward GEMMs: keep NCCL to 16 CTAs and leave
-        # 16 SMs out of the persistent GEMM grid, so that neither waits for the other's SMs.
+    if world == 2:
+        # The gradient all-reduce runs beside the backward GEMMs: with two ranks NCCL needs few
+        # CTAs, so keep it to 16 and leave 16 SMs out of the persistent GEMM grid; neither then
+        # waits for the other's SMs (measured 5.21 -> 5.09 ms per c2 step). With 8 ranks the same
+        # limits make the all-reduce the bottleneck (3.12 ms against 2.08 ms without them), so
+        # larger groups keep NCCL's defaults and the full GEMM grid.
         os.environ.setdefault("NCCL_MAX_CTAS", "16")
         os.environ.setdefault("ENDIA_B200_TC_RESERVE_SMS", "16")
     if world > 1 and not dist.is_initialized():

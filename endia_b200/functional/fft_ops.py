@@ -62,10 +62,15 @@ def run_fft(src, dst, dims, direction_inverse, scale):
 
 
 def _as_complex(x):
+    """The transform's source: a complex array, or a contiguous real one, which the kernels read
+    as complex with a zero imaginary part (fft_cooley_tukey.mojo:204-206) without a copy."""
+    from .._array import LazyComplex
+    from ._utils import contiguous
+    if isinstance(x, LazyComplex) and not x.materialised():
+        return contiguous(x.re_part)
     if x.is_complex():
         return x
-    from .init_ops import complex as make_complex
-    return make_complex(x, Array(x.shape()))  # fft_cooley_tukey.mojo:204-206
+    return contiguous(x)
 
 
 def _transform(x, dims, norm, inverse):

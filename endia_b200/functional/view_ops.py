@@ -205,7 +205,11 @@ def real(arg0):
 
     def vjp(primals, grad, out):
         from .init_ops import complex as make_complex
-        # the zero imaginary part is a broadcast scalar, never a materialised array
+        from ..autograd import state as _state
+        from .._array import LazyComplex
+        from ._utils import contiguous
+        if not _state.create_graph and not grad.is_complex():
+            return [LazyComplex(contiguous(grad))]   # complex(grad, 0), written only if read as such
         return [make_complex(grad, expand(Array([1]), grad.shape()))]
     res = op_array(shape, [arg0], "real", _view_call, vjp=vjp, is_view=True)
     res.is_complex_flag = False

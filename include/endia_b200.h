@@ -342,8 +342,9 @@ int endia_b200_adagrad_step_multi(int32_t n_tensors, float *const *params, const
 
 /* --------------------------------------------------------------------- FFT ---- */
 
-/* Complex-to-complex FFT over the listed dims of `in` (contiguous or strided, complex) into
- * `out` (contiguous, same shape):
+/* Complex-to-complex FFT over the listed dims of `in` (contiguous or strided complex, or
+ * contiguous real: read as complex with a zero imaginary part, fft_cooley_tukey.mojo:204-206)
+ * into `out` (contiguous complex, same shape):
  *   inverse = 0: sign -  (forward DFT),  inverse = 1: sign +  (conjugate-direction transform,
  *   i.e. conj(fft(conj(x))), which is both FFTN.vjp and the core of ifftn)
  *   every output element is multiplied by `scale`.

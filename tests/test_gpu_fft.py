@@ -147,3 +147,50 @@ def test_fft_matches_golden_fixture(nd):
     loss.backward()
     assert rel_l2(y.to_numpy(), f["y"]) < TOL and rel_l2(X.grad().to_numpy(), f["grad"]) < TOL
     assert abs(loss.to_numpy()[0] - f["loss"][0]) <= 1e-4 * abs(f["loss"][0])
+
+
+@pytest.mark.parametrize("shape,dims", [((4, 1024), [1]), ((8, 16384), [1]), ((16, 32, 64), [0, 1, 2]),
+                                        ((6, 256), [1]), ((3, 40), [0])])
+def test_fft_reads_real_source_without_copy(nd, shape, dims):
+    """endia_b200_fft_c2c with a real contiguous source (complex with zero imaginary part,
+    fft_cooley_tukey.mojo:204-206): forward and conjugate direction, fast, four-step and generic
+    kernels; shapes whose length is not a power of two are still refused."""
+    import ctypes as C
+    from endia_b200 import _lib
+    from endia_b200._array import stream, alloc
+    r = rng(31)
+    x = r.standard_normal(shape).astype(np.float32)
+    X, Y = nd.Array(x), nd.Array(list(shape), is_complex=True)
+    cd = (C.c_int32 * len(dims))(*dims)
+    nb = _lib.lib.endia_b200_fft_scratch_bytes(X.desc(), cd, len(dims))
+    scratch = alloc(nb // 4 + 1) if nb else None
+    sp = scratch.data_ptr() if scratch is not None else None
+    if shape == (3, 40):
+        st = _lib.lib.endia_b200_fft_c2c(X.desc(), Y.desc(), cd, len(dims), 0, 1.0, sp, stream())
+        assert st != 0
+        return
+    for inverse in (0, 1):
+        _lib.call("endia_b200_fft_c2c", X.desc(), Y.desc(), cd, len(dims), inverse, 1.0, sp, stream())
+        ref = np.fft.fftn(x.astype(np.float64), axes=dims)
+        if inverse:
+            ref = np.conj(ref)        # conj(F(conj(x))) with real x
+        assert rel_l2(Y.to_numpy(), ref) < 1e-5
+
+
+def test_real_vjp_gradient_stays_lazy_into_fft(nd):
+    """d/dx sum(real(fftn(x)) * w): the gradient of real() is complex(g, 0), which the FFT VJP reads
+    from the real array; asking for it as an array gives the same values."""
+    from endia_b200._array import LazyComplex
+    r = rng(32)
+    z = (r.standard_normal((8, 16, 32)) + 1j * r.standard_normal((8, 16, 32))).astype(np.complex64)
+    w = r.uniform(-1, 1, (8, 16, 32)).astype(np.float32)
+    X = nd.Array(z, requires_grad=True)
+    y = nd.fftn(X)
+    re = nd.real(y)
+    nd.sum(re * nd.Array(w)).backward()
+    g = X.grad().to_numpy()
+    ref = w.size * np.fft.ifftn(w.astype(np.complex128))
+    assert rel_l2(g, ref) < 1e-5
+    lz = LazyComplex(nd.Array(w))
+    assert not lz.materialised()
+    assert np.array_equal(lz.to_numpy(), w.astype(np.complex64)) and lz.materialised()
