@@ -155,7 +155,9 @@ class TrainStep:
         self.opt = nd.optim.Adam(self.params, lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8)
         self.reducer = None
         if world > 1:
-            self.reducer = ndist.GradAllReducer(self.params, overlap=os.environ.get("ENDIA_B200_DP_OVERLAP", "1") != "0")
+            # an all-reduce per parameter started from the backward walk; ENDIA_B200_DP_MODE=bucket sums
+            # all gradients with one all-reduce after the pass instead
+            self.reducer = ndist.GradAllReducer(self.params)
             self.opt.grad_scale = 1.0 / world   # global-mean loss = mean of the ranks' local means
         self.flat = ndist.flat_tensor
         self.feeder = None

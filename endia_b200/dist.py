@@ -37,33 +37,78 @@ def flat_tensor(arr):
 
 
 class GradAllReducer:
-    """Starts a sum all-reduce of a parameter's gradient the moment the backward walk has produced
-    it (last layer first), on the communicator's own stream, so that it overlaps the remaining
-    backward GEMMs; wait() joins them before the optimizer step. The mean over ranks is folded into
-    the optimizer's gradient scale instead of a separate pass."""
+    """Sums the parameters' gradients over the ranks before the optimizer step; the mean over ranks
+    is folded into the optimizer's gradient scale instead of a separate pass. Modes:
 
-    def __init__(self, params, group=None, overlap=True):
+    "overlap" (default) an all-reduce per parameter is started from a hook the moment the backward
+                        walk has produced its gradient (last layer first), on the communicator's
+                        stream, beside the remaining backward GEMMs.
+    "bucket"            after the backward pass the gradients are gathered into one flat buffer
+                        (a device copy of all of them, 0.07 ms for the 168 MB of c2), summed by ONE
+                        all-reduce, and the parameters' gradients become views of that buffer.
+    "serial"            an all-reduce per parameter after the backward pass.
+
+    Measured on the c2 step with 2 GPUs: overlap 4.21 ms, bucket 4.40-4.60 ms. (The persistent
+    GEMM kernels hold every SM, so a collective beside them waits for SMs and a GEMM launched
+    beside a collective runs on fewer; with short per-rank steps the bucket mode may win.)"""
+
+    def __init__(self, params, group=None, overlap=None, mode=None):
         self.params = list(params)
         self.group = group
-        self.overlap = overlap      # False: all-reduce only in wait(), after the backward pass
+        if mode is None:
+            mode = os.environ.get("ENDIA_B200_DP_MODE", "overlap") if overlap is None else (
+                "overlap" if overlap else "serial")
+        if mode not in ("bucket", "overlap", "serial"):
+            raise ValueError("GradAllReducer: unknown mode %r" % (mode,))
+        self.mode = mode
         self.pending = []
         self.deferred = []
+        self.flat = None
         for p in self.params:
             p.grad_hook = self._hook
 
     def _hook(self, param, grad):
+        if self.mode == "bucket":
+            return
         g = grad
         if not grad.is_contiguous():
             from .functional._utils import contiguous
             g = contiguous(grad)
             param.grad_(g)
-        if not self.overlap:
+        if self.mode == "serial":
             self.deferred.append(g)
             return
         self.pending.append(dist.all_reduce(flat_tensor(g), op=dist.ReduceOp.SUM, group=self.group,
                                             async_op=True))
 
+    def _reduce_bucket(self):
+        from . import _lib
+        from ._array import stream
+        from .functional._utils import contiguous
+        grads = [contiguous(p.grad()) for p in self.params]
+        total = sum(g.size() for g in grads)
+        if self.flat is None or self.flat.numel() != total:
+            self.flat = torch.empty(total, dtype=torch.float32, device=device())
+        off = 0
+        views = []
+        for p, g in zip(self.params, grads):
+            n = g.size()
+            piece = self.flat[off:off + n]
+            if n:
+                _lib.call("endia_b200_d2d", piece.data_ptr(), g.data_ptr(), 4 * n, stream())
+            v = Array(ArrayShape(g.shape()))
+            v.buf = piece
+            views.append(v)
+            off += n
+        if total:
+            dist.all_reduce(self.flat, op=dist.ReduceOp.SUM, group=self.group)
+        for p, v in zip(self.params, views):
+            p.grad_(v)
+
     def wait(self):
+        if self.mode == "bucket":
+            self._reduce_bucket()
+            return
         for g in self.deferred:
             self.pending.append(dist.all_reduce(flat_tensor(g), op=dist.ReduceOp.SUM, group=self.group,
                                                 async_op=True))

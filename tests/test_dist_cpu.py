@@ -96,7 +96,7 @@ def _reduce_worker(rank, world, port, ret):
     try:
         from endia_b200 import dist as ndist
         params = [_FakeParam() for _ in range(3)]
-        red = ndist.GradAllReducer(params)
+        red = ndist.GradAllReducer(params, mode="overlap")
         grads = [_FakeGrad(torch.full((5 + i,), float(rank + 1 + i))) for i in range(3)]
         # the backward walk reports gradients last layer first
         for p, g in reversed(list(zip(params, grads))):

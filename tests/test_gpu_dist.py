@@ -88,7 +88,7 @@ B = [nd.Array(b.copy(), requires_grad=True) for b in bs]
 params = [p for wb in zip(W, B) for p in wb]
 opt = nd.optim.Adam(params, lr=1e-3)
 opt.grad_scale = 1.0 / world
-red = ndist.GradAllReducer(params)
+red = ndist.GradAllReducer(params, mode=os.environ.get("DP_TEST_MODE", "overlap"))
 X, Y = nd.Array(x[lo:hi]), nd.Array(y[lo:hi])
 loss = nd.mse(nd.nn.mlp([X, None] + params, activation="tanh"), Y)
 loss.backward()
@@ -100,9 +100,11 @@ torch.distributed.destroy_process_group()
 '''
 
 
-def test_data_parallel_step_matches_single_gpu(nd, oracle, tmp_path):
-    """Two ranks, each on half of the batch, gradients all-reduced during the backward pass and
-    averaged inside Adam: the updated weights must equal the single-process result (oracle)."""
+@pytest.mark.parametrize("mode", ["overlap", "bucket"])
+def test_data_parallel_step_matches_single_gpu(nd, oracle, tmp_path, mode):
+    """Two ranks, each on half of the batch, gradients all-reduced (per parameter during the
+    backward pass, or as one flat bucket after it) and averaged inside Adam: the updated weights
+    must equal the single-process result (oracle)."""
     import torch
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
@@ -113,7 +115,8 @@ def test_data_parallel_step_matches_single_gpu(nd, oracle, tmp_path):
     s = socket.socket(); s.bind(("127.0.0.1", 0)); port = s.getsockname()[1]; s.close()
     out = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
                           "--master-addr", "127.0.0.1", "--master-port", str(port), str(script)],
-                         capture_output=True, text=True, timeout=300, env=dict(os.environ, NCCL_NVLS_ENABLE="0"))
+                         capture_output=True, text=True, timeout=300,
+                         env=dict(os.environ, NCCL_NVLS_ENABLE="0", DP_TEST_MODE=mode))
     assert out.returncode == 0, out.stdout + out.stderr
     Ws, bs, x, y = make_mlp_inputs([64, 256, 256, 32], 512, 0)
     oracle.config["mode"] = "fast"
