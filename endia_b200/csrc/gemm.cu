@@ -12,8 +12,9 @@ extern "C" {
 
 size_t endia_b200_gemm_colsum_scratch_bytes(int64_t M, int64_t N) {
   if (M <= 0 || N <= 0) return 0;
-  // One row of partial sums per 64-row tile covers every kernel's tile height (>= 64).
-  return sizeof(float) * (size_t)ceil_div(M, 64) * (size_t)N;
+  // One row of partial sums per 32 rows of C: the tensor-core epilogue writes one per warp (32
+  // rows), the FFMA kernel one per 128-row tile.
+  return sizeof(float) * (size_t)ceil_div(M, 32) * (size_t)N;
 }
 
 int endia_b200_gemm(int trans_a, int trans_b, int64_t M, int64_t N, int64_t K, const float *A,
@@ -75,7 +76,8 @@ int endia_b200_gemm(int trans_a, int trans_b, int64_t M, int64_t N, int64_t K, c
                "(M %lld N %lld K %lld batch %lld)", (long long)M, (long long)N, (long long)K,
                (long long)batch);
   }
-  int tile_m = 128;
+  // rows of C per partial column sum: 32 in the two-CTA tensor-core kernel, 128 in the FFMA kernel
+  int tile_m = (use_tc && colsum) ? 32 : 128;
   if (!use_tc && algo == ENDIA_B200_GEMM_AUTO && skinny_gemm_supported(p, trans_b, batch))
     return launch_gemm_skinny(p, trans_a, trans_b, s);
   if (use_tc) st = launch_gemm_tc(p, trans_a, trans_b, s);

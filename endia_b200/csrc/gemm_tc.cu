@@ -491,7 +491,8 @@ __device__ __forceinline__ void tc_epilogue_warp_bulk(uint32_t tmem_base, int q,
                                                       uint32_t buf, bool reduce, bool trace = false) {
   (void)trace;
   const uint32_t row_addr = tmem_base + ((uint32_t)(q * 32) << 16);
-  const bool plain = epi.alpha == 1.f && !epi.bias && !epi.act && !epi.dact && epi.beta == 0.f;
+  const bool plain = epi.alpha == 1.f && !epi.bias && !epi.act && !epi.dact && epi.beta == 0.f &&
+                     !epi.colsum_partial;
   const bool vec_epi = (!epi.bias || (reinterpret_cast<uintptr_t>(epi.bias) & 15) == 0) &&
                        (!epi.dact || ((reinterpret_cast<uintptr_t>(epi.dact_src) & 15) == 0 && epi.ld_dact % 4 == 0));
   uint32_t ra[32], rb[32];
@@ -524,6 +525,7 @@ __device__ __forceinline__ void tc_epilogue_warp_bulk(uint32_t tmem_base, int q,
     if (!plain) {
       __syncwarp();
       const int64_t n = nb + c4 * 4;
+      float4 cs = make_float4(0.f, 0.f, 0.f, 0.f);   // column sums of this lane's 8 rows
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
         const int r = rsub + 4 * i;
@@ -538,10 +540,26 @@ __device__ __forceinline__ void tc_epilogue_warp_bulk(uint32_t tmem_base, int q,
           float e[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
           for (int t = 0; t < 4; ++t)
-            if (n + t < N) e[t] = apply_epilogue(epi, e[t], m, n + t, cp + t);
+            e[t] = (n + t < N) ? apply_epilogue(epi, e[t], m, n + t, cp + t) : 0.f;
           v = make_float4(e[0], e[1], e[2], e[3]);
         }
+        cs.x += v.x; cs.y += v.y; cs.z += v.z; cs.w += v.w;
         sts128(a, v);
+      }
+      if (epi.colsum_partial) {
+        // the bias gradient: sum over the warp's 32 rows (the four lanes that share c4), one
+        // partial row per 32 rows of C, added up in a fixed order by colsum_finish_kernel
+        cs.x += __shfl_xor_sync(0xffffffffu, cs.x, 8);  cs.y += __shfl_xor_sync(0xffffffffu, cs.y, 8);
+        cs.z += __shfl_xor_sync(0xffffffffu, cs.z, 8);  cs.w += __shfl_xor_sync(0xffffffffu, cs.w, 8);
+        cs.x += __shfl_xor_sync(0xffffffffu, cs.x, 16); cs.y += __shfl_xor_sync(0xffffffffu, cs.y, 16);
+        cs.z += __shfl_xor_sync(0xffffffffu, cs.z, 16); cs.w += __shfl_xor_sync(0xffffffffu, cs.w, 16);
+        if (rsub == 0 && n < N && m0 + q * 32 < M) {
+          float *dstp = epi.colsum_partial + ((m0 + q * 32) >> 5) * N + n;
+          const float e[4] = {cs.x, cs.y, cs.z, cs.w};
+#pragma unroll
+          for (int t = 0; t < 4; ++t)
+            if (n + t < N) dstp[t] = e[t];
+        }
       }
     }
     fence_async_smem();
@@ -966,7 +984,9 @@ static bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 
 
 bool tc_gemm_supported(const GemmParams &p, int trans_a, int trans_b, int64_t batch, bool explicit_request) {
   (void)trans_a; (void)trans_b;
-  if (batch != 1 || p.epi.colsum_partial) return false;
+  if (batch != 1) return false;
+  // the fused column sum lives in the epilogue of the two-CTA kernel only
+  if (p.epi.colsum_partial && (p.N < 256 || !p.vec_c)) return false;
   // The tensor-core accumulator rounds toward zero on every add, a bias that grows linearly
   // with K (measured: -1.7e-5 of the result at K = 8192, -6.7e-5 at K = 32768). Longer
   // reductions stay on the FFMA kernel unless the caller asks for this one by name.
@@ -1085,7 +1105,7 @@ int launch_gemm_tc(const GemmParams &p, int trans_a, int trans_b, cudaStream_t s
   // is filled; the partial sums go through a work buffer and are added in a fixed order.
   int splits = 1;
   int scheme = p.scheme;
-  if (scheme == 0 || !p.scheme_forced) {
+  if ((scheme == 0 || !p.scheme_forced) && !p.epi.colsum_partial) {
     const int64_t ctas_wide = 2 * ceil_div(p.M, 256) * ceil_div(p.N, 256);
     const int64_t tiles = ceil_div(p.M, 128) * ceil_div(p.N, 128);
     const int64_t nkb32 = ceil_div(p.K, 32);
@@ -1101,7 +1121,7 @@ int launch_gemm_tc(const GemmParams &p, int trans_a, int trans_b, cudaStream_t s
     const char *e = getenv("ENDIA_B200_TC_BK");
     return (e && atoi(e) == 16) ? 16 : 32;
   }();
-  const bool pair = bn == 256 && ((bk == 32 && pair_mode()) || scheme == 1);
+  const bool pair = bn == 256 && ((bk == 32 && pair_mode()) || scheme == 1 || p.epi.colsum_partial);
   const bool bf16c = pair && scheme == 1;
   TcMaps maps;
   int st;
@@ -1175,7 +1195,7 @@ int launch_gemm_tc(const GemmParams &p, int trans_a, int trans_b, cudaStream_t s
   }
   // Halving K needs the bulk-store epilogue, a product that is linear in the accumulator and a
   // reduction long enough for the second pass over C to be cheap.
-  const bool linear_epi = !p.epi.bias && !p.epi.act && !p.epi.dact && p.epi.beta == 0.f;
+  const bool linear_epi = !p.epi.bias && !p.epi.act && !p.epi.dact && p.epi.beta == 0.f && !p.epi.colsum_partial;
   const int ksplit_max = (p.vec_c && linear_epi && p.K >= 4096 && ksplit_mode()) ? 2 : 1;
   if (bf16c) st = launch_pair_persistent<1>(maps, p, trans_a, trans_b, s, ksplit_max);
   else if (pair) st = launch_pair_persistent<0>(maps, p, trans_a, trans_b, s, ksplit_max);

@@ -122,6 +122,32 @@ def test_3xtf32_fused_epilogue(nd):
     assert max_rel(out, v) < 1e-4
 
 
+@pytest.mark.parametrize("algo_name", ["3xtf32", "tf32_bf16x2"])
+@pytest.mark.parametrize("M,N,K,tb", [(512, 384, 256, 1), (300, 260, 96, 0), (1024, 1024, 512, 1)])
+def test_tensor_core_epilogue_mask_and_bias_gradient(nd, M, N, K, tb, algo_name):
+    """dS = (dY . W^T) * act'(h) with the bias gradient colsum(dS) from the same launch: the
+    backward mask and the column reduction fused into the store of the dX product
+    (tanh_op.mojo:92, expand_op.mojo:121-126)."""
+    from endia_b200 import _lib
+    from endia_b200._array import alloc
+    algo = _lib.GEMM_3XTF32 if algo_name == "3xtf32" else _lib.GEMM_TF32_BF16X2
+    r = rng(M + N)
+    a = r.standard_normal((M, K)).astype(np.float32)
+    b = (r.standard_normal((N, K) if tb else (K, N)) * 0.1).astype(np.float32)
+    h = np.tanh(r.standard_normal((M, N))).astype(np.float32)
+    H, colsum = nd.Array(h), nd.Array([N])
+    scratch = alloc(_lib.lib.endia_b200_gemm_colsum_scratch_bytes(M, N) // 4 + 1)
+    epi = _lib.Epilogue()
+    epi.alpha, epi.beta = 1.0, 0.0
+    epi.dact, epi.dact_src, epi.ld_dact = _lib.ACT_TANH, H.data_ptr(), N
+    epi.colsum, epi.colsum_scratch = colsum.data_ptr(), scratch.data_ptr()
+    out = run_gemm(nd, a, b, 0, tb, algo, epi=epi)
+    bm = (b.T if tb else b).astype(np.float64)
+    v = (a.astype(np.float64) @ bm) * (1.0 - h.astype(np.float64) ** 2)
+    assert max_rel(out, v) < 1e-4
+    assert max_rel(colsum.to_numpy(), v.sum(0)) < 1e-4
+
+
 def test_3xtf32_long_k_error_growth(nd):
     """dW reduces over the batch: K = 8192 must still meet the gradient tolerance."""
     from endia_b200 import _lib
