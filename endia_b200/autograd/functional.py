@@ -34,6 +34,9 @@ def jacrev(arg, create_graph=False):
     for node in trace:
         for a in node.args_:
             pending[id(a)] = pending.get(id(a), 0) + 1
+    # (also left on the nodes for VJPs that fuse work across an edge only when it is the only one)
+    for node in trace:
+        node._consumers = pending.get(id(node), 0)
     prev = _state.create_graph
     _state.create_graph = bool(create_graph)
     try:

@@ -1,4 +1,6 @@
 """Process-wide switches read by the VJPs."""
+import os
+
 from .. import _lib
 
 # True while a backward pass runs with create_graph=True: VJPs then build differentiable
@@ -6,6 +8,9 @@ from .. import _lib
 create_graph = False
 # GEMM algorithm handed to endia_b200_gemm (AUTO = tcgen05 3xTF32 when the shape allows).
 gemm_algo = _lib.GEMM_AUTO
+# Let the dX product of a fused linear layer apply the lower layer's activation-derivative mask and
+# sum its bias gradient in its epilogue (ENDIA_B200_FUSE_MASK=1); off: a separate fused kernel.
+fuse_mask_into_dx = os.environ.get("ENDIA_B200_FUSE_MASK", "0") == "1"
 # Keep the tf32 low part of an op result beside it after its first use as a GEMM operand.
 cache_tf32_lo = True
 # Optional object with start(flops) / stop() called around every GEMM launch (benchmarks bracket

@@ -127,6 +127,29 @@ def test_c2_reduced_mlp_train_step(nd, oracle, act, fused):
     compare_steps(g, o)
 
 
+@pytest.mark.parametrize("act", ["tanh", "relu"])
+def test_c2_reduced_with_mask_fused_into_dx_product(nd, oracle, act, monkeypatch):
+    """The same step with the dX product of each layer applying the lower layer's activation
+    derivative and summing its bias gradient in its epilogue (state.fuse_mask_into_dx)."""
+    from endia_b200.autograd import state
+    monkeypatch.setattr(state, "fuse_mask_into_dx", True)
+    # the inputs of test_c2_reduced_mlp_train_step (relu's kink makes other draws flip single units)
+    Ws, bs, x, y = make_mlp_inputs([256, 512, 512, 512, 256], 384, 0, bias_zero=True)
+    oracle.config["mode"] = "fast"
+    try:
+        o = train_step(oracle, fwd_unfused(act), Ws, bs, x, y)
+    finally:
+        oracle.config["mode"] = "faithful"
+    launches0 = nd._lib.lib.endia_b200_launch_count()
+    g = train_step(nd, fwd_fused(act), Ws, bs, x, y)
+    fused_launches = nd._lib.lib.endia_b200_launch_count() - launches0
+    compare_steps(g, o)
+    monkeypatch.setattr(state, "fuse_mask_into_dx", False)
+    launches0 = nd._lib.lib.endia_b200_launch_count()
+    train_step(nd, fwd_fused(act), Ws, bs, x, y)
+    assert fused_launches < nd._lib.lib.endia_b200_launch_count() - launches0
+
+
 def second_order(L, Ws, bs, x, fused):
     W = [L.Array(w.copy(), requires_grad=True) for w in Ws]
     B = [L.Array(b.copy(), requires_grad=True) for b in bs]
