@@ -606,7 +606,7 @@ __device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity,
 template <bool A_MN, bool B_MN, int SCHEME>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(320, 1)
 gemm_tc2p_kernel(const __grid_constant__ TcMaps maps, const GemmParams p, int pairs_m, int tiles_n, int group_m,
-                 int ksplit) {
+                 int ksplit, int kseq) {
   constexpr int BN = 256, BNH = 128, BK = 32, STAGES = 3, EPI_WARPS = 8;
   extern __shared__ __align__(1024) uint8_t smem[];
   constexpr uint32_t A_BYTES = TC_BM * BK * 4;
@@ -747,19 +747,26 @@ gemm_tc2p_kernel(const __grid_constant__ TcMaps maps, const GemmParams p, int pa
       uint32_t it = 0;
       int j = 0;
       bool ok = true;
-      for (int t = pair_id; t < num_tiles && ok; t += num_pairs, ++j) {
-        // the epilogue warps of both CTAs have read the previous tile's accumulators
-        EB_TRACE(j, 0);
-        if (j > 0 && !mbar_wait_cluster(acc_empty, (uint32_t)(j - 1) & 1, 32)) break;
-        tc_fence_after();
-        EB_TRACE(j, 1);
+      // kseq > 1: a long reduction is cut into kseq runs; the accumulators are drained after each
+      // (the first run stores, the later ones add to C), which bounds the round-toward-zero bias
+      // of the accumulator adds by the length of one run.
+      for (int t = pair_id; t < num_tiles && ok; t += num_pairs) {
         int kb0, nkb;
         k_range(t, kb0, nkb);
-        for (int kb = 0; kb < nkb; ++kb, ++it) {
+        const int per_run = (nkb + kseq - 1) / kseq;
+        int kb = 0;
+        for (int run = 0; run < kseq && ok; ++run, ++j) {
+        // the epilogue warps of both CTAs have read the previous accumulators
+        EB_TRACE(j, 0);
+        if (j > 0 && !mbar_wait_cluster(acc_empty, (uint32_t)(j - 1) & 1, 32)) { ok = false; break; }
+        tc_fence_after();
+        EB_TRACE(j, 1);
+        const int kend = (run + 1) * per_run < nkb ? (run + 1) * per_run : nkb;
+        for (int kl = 0; kb < kend; ++kb, ++kl, ++it) {
           const int s = (int)(it % STAGES);
           if (!mbar_wait(full_bar(s), (it / STAGES) & 1, 33)) { ok = false; break; }
           tc_fence_after();
-          if (kb == 0) EB_TRACE(j, 2);
+          if (kl == 0) EB_TRACE(j, 2);
           const uint32_t st = smem_base + s * STAGE_BYTES;
           const uint32_t sb = st + 2 * A_BYTES;
           const uint64_t a_hi = tile_desc<A_MN, BK>(st), b_hi = tile_desc<B_MN, BK>(sb);
@@ -770,7 +777,7 @@ gemm_tc2p_kernel(const __grid_constant__ TcMaps maps, const GemmParams p, int pa
             for (int ks = 0; ks < BK / 8; ++ks) {
               const uint64_t ah = a_hi + ks * A_STEP, al = a_lo + ks * A_STEP;
               const uint64_t bh = b_hi + ks * B_STEP, bl = b_lo + ks * B_STEP;
-              const uint32_t acc = (kb | ks) ? 1u : 0u;
+              const uint32_t acc = (kl | ks) ? 1u : 0u;
               tc_mma_tf32_pair(tmem_base + BN, al, bh, idesc, acc);
               tc_mma_tf32_pair(tmem_base + BN, ah, bl, idesc, 1u);
               tc_mma_tf32_pair(tmem_base, ah, bh, idesc, acc);
@@ -782,18 +789,19 @@ gemm_tc2p_kernel(const __grid_constant__ TcMaps maps, const GemmParams p, int pa
             constexpr uint64_t A16_STEP = A_MN ? 128 : 2, B16_STEP = B_MN ? 128 : 2;
 #pragma unroll
             for (int ks = 0; ks < BK / 16; ++ks) {
-              const uint32_t acc = (kb | ks) ? 1u : 0u;
+              const uint32_t acc = (kl | ks) ? 1u : 0u;
               tc_mma_bf16_pair(tmem_base + BN, a16l + ks * A16_STEP, b16h + ks * B16_STEP, idesc16, acc);
               tc_mma_bf16_pair(tmem_base + BN, a16h + ks * A16_STEP, b16l + ks * B16_STEP, idesc16, 1u);
             }
 #pragma unroll
             for (int ks = 0; ks < BK / 8; ++ks)
-              tc_mma_tf32_pair(tmem_base, a_hi + ks * A_STEP, b_hi + ks * B_STEP, idesc, (kb | ks) ? 1u : 0u);
+              tc_mma_tf32_pair(tmem_base, a_hi + ks * A_STEP, b_hi + ks * B_STEP, idesc, (kl | ks) ? 1u : 0u);
           }
           tc_commit_pair(empty_bar(s));
         }
         tc_commit_pair(acc_full);   // also on the give-up path, so that the epilogue warps move on
         EB_TRACE(j, 3);
+        }
       }
     }
   } else {
@@ -801,16 +809,23 @@ gemm_tc2p_kernel(const __grid_constant__ TcMaps maps, const GemmParams p, int pa
     const int half = (warp - 2) >> 2;
     const uint32_t acc_empty_leader = map_to_cta(acc_empty, 0);
     int j = 0;
-    for (int t = pair_id; t < num_tiles; t += num_pairs, ++j) {
+    bool ok = true;
+    for (int t = pair_id; t < num_tiles && ok; t += num_pairs) {
       int m0, n0;
       tile_origin(t, m0, n0);
-      if (!mbar_wait(acc_full, (uint32_t)j & 1, 34)) break;
+      for (int run = 0; run < kseq; ++run, ++j) {
+      if (!mbar_wait(acc_full, (uint32_t)j & 1, 34)) { ok = false; break; }
       tc_fence_after();
       if (warp == 2 && lane == 0) EB_TRACE(j, 4);
+      if (run > 0) {
+        // this run is added to what the previous run of the same tile stored: that store must be complete
+        if (lane == 0) bulk_wait0();
+        __syncwarp();
+      }
       constexpr int CH = BN / 64;
       if (p.vec_c)
         tc_epilogue_warp_bulk<BN>(tmem_base, q, lane, half * CH, (half + 1) * CH, m0, n0, p.M, p.N, p.C, p.ldc,
-                                  p.epi, &maps.c, epi_base + (uint32_t)(warp - 2) * 4096u, ksplit > 1,
+                                  p.epi, &maps.c, epi_base + (uint32_t)(warp - 2) * 4096u, ksplit > 1 || run > 0,
                                   blockIdx.x == 0 && warp == 2 && lane == 0 && j == 1);
       else
         tc_epilogue_warp<BN, false>(tmem_base, q, lane, half * CH, (half + 1) * CH, m0, n0, p.M, p.N, p.C, p.ldc,
@@ -820,6 +835,7 @@ gemm_tc2p_kernel(const __grid_constant__ TcMaps maps, const GemmParams p, int pa
       if (warp == 2 && lane == 0) EB_TRACE(j, 5);
       if (warp == 9 && lane == 0) EB_TRACE(j, 6);
       if (lane == 0) mbar_arrive_cluster(acc_empty_leader);
+      }
     }
     if (lane == 0) bulk_wait0();   // the stores have left shared memory and are complete
   }
@@ -990,7 +1006,10 @@ bool tc_gemm_supported(const GemmParams &p, int trans_a, int trans_b, int64_t ba
   // The tensor-core accumulator rounds toward zero on every add, a bias that grows linearly
   // with K (measured: -1.7e-5 of the result at K = 8192, -6.7e-5 at K = 32768). Longer
   // reductions stay on the FFMA kernel unless the caller asks for this one by name.
-  if (p.K > 8192 && !explicit_request) return false;
+  // Linear epilogues on the two-CTA kernel are exempt: it drains the accumulators every 8192.
+  const bool runs_ok = p.N >= 256 && p.vec_c && !p.epi.bias && !p.epi.act && !p.epi.dact && p.epi.beta == 0.f &&
+                       !p.epi.colsum_partial;
+  if (p.K > 8192 && !explicit_request && !runs_ok) return false;
   if (!encode_fn()) return false;
   if (p.M < 128 || p.N < 128 || p.K < 32) return false;      // small products stay on the FFMA kernel
   if (p.M > (int64_t)1 << 30 || p.N > (int64_t)1 << 30 || p.K > (int64_t)1 << 30) return false;
@@ -1036,7 +1055,7 @@ static bool ksplit_mode() {
 // Persistent two-CTA kernel: as many CTA pairs as can be resident, each walking over its tiles.
 template <int SCHEME>
 static int launch_pair_persistent(const TcMaps &maps, const GemmParams &p, int trans_a, int trans_b,
-                                  cudaStream_t s, int ksplit_max) {
+                                  cudaStream_t s, int ksplit_max, int kseq) {
   constexpr size_t SMEM = (size_t)3 * (2 * TC_BM * 32 * 4 + 2 * 128 * 32 * 4) + 8 * 4096 + 1024 + 256;
   const int pairs_m = (int)ceil_div(p.M, 256), tiles_n = (int)ceil_div(p.N, 256);
   static const int group_env = []() { const char *e = getenv("ENDIA_B200_TC_GROUP_M"); return e ? atoi(e) : TC_GROUP_M; }();
@@ -1072,7 +1091,7 @@ static int launch_pair_persistent(const TcMaps &maps, const GemmParams &p, int t
     }                                                                                             \
     const int tiles = pairs_m * tiles_n;                                                          \
     int ksplit = 1;                                                                               \
-    if (ksplit_max >= 2 && tiles > max_pairs) {                                                   \
+    if (ksplit_max >= 2 && kseq == 1 && tiles > max_pairs) {                                                   \
       /* rounds of pairs with and without halving K, in units of half tiles */                    \
       const int r1 = 2 * ((tiles + max_pairs - 1) / max_pairs);                                   \
       const int r2 = (2 * tiles + max_pairs - 1) / max_pairs;                                     \
@@ -1084,7 +1103,7 @@ static int launch_pair_persistent(const TcMaps &maps, const GemmParams &p, int t
     }                                                                                             \
     const int items = tiles * ksplit;                                                             \
     const int pairs = items < max_pairs ? items : max_pairs;                                      \
-    kern<<<dim3((unsigned)(2 * pairs)), 320, SMEM, s>>>(maps, p, pairs_m, tiles_n, group_m, ksplit); \
+    kern<<<dim3((unsigned)(2 * pairs)), 320, SMEM, s>>>(maps, p, pairs_m, tiles_n, group_m, ksplit, kseq); \
   } while (0)
   if (trans_a && !trans_b) EB_TC2P_LAUNCH(true, true);
   else if (trans_a && trans_b) EB_TC2P_LAUNCH(true, false);
@@ -1105,7 +1124,7 @@ int launch_gemm_tc(const GemmParams &p, int trans_a, int trans_b, cudaStream_t s
   // is filled; the partial sums go through a work buffer and are added in a fixed order.
   int splits = 1;
   int scheme = p.scheme;
-  if ((scheme == 0 || !p.scheme_forced) && !p.epi.colsum_partial) {
+  if ((scheme == 0 || !p.scheme_forced) && !p.epi.colsum_partial && p.K <= 8192) {
     const int64_t ctas_wide = 2 * ceil_div(p.M, 256) * ceil_div(p.N, 256);
     const int64_t tiles = ceil_div(p.M, 128) * ceil_div(p.N, 128);
     const int64_t nkb32 = ceil_div(p.K, 32);
@@ -1197,8 +1216,10 @@ int launch_gemm_tc(const GemmParams &p, int trans_a, int trans_b, cudaStream_t s
   // reduction long enough for the second pass over C to be cheap.
   const bool linear_epi = !p.epi.bias && !p.epi.act && !p.epi.dact && p.epi.beta == 0.f && !p.epi.colsum_partial;
   const int ksplit_max = (p.vec_c && linear_epi && p.K >= 4096 && ksplit_mode()) ? 2 : 1;
-  if (bf16c) st = launch_pair_persistent<1>(maps, p, trans_a, trans_b, s, ksplit_max);
-  else if (pair) st = launch_pair_persistent<0>(maps, p, trans_a, trans_b, s, ksplit_max);
+  // Reductions longer than 8192 run as ceil(K / 8192) runs whose sums are added in order.
+  const int kseq = (pair && p.vec_c && linear_epi && p.K > 8192) ? (int)ceil_div(p.K, 8192) : 1;
+  if (bf16c) st = launch_pair_persistent<1>(maps, p, trans_a, trans_b, s, ksplit_max, kseq);
+  else if (pair) st = launch_pair_persistent<0>(maps, p, trans_a, trans_b, s, ksplit_max, kseq);
   else if (bn == 256 && bk == 16) st = launch_variant<256, 16, 4>(maps, p, trans_a, trans_b, s);
   else if (bn == 256) st = launch_variant<256, 32, 2>(maps, p, trans_a, trans_b, s);
   else if (bk == 16) st = launch_variant<128, 16, 6>(maps, q, trans_a, trans_b, s, splits);

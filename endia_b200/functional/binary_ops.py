@@ -150,12 +150,18 @@ def _batch_stride(a, batch):
 _LO_CACHE_MIN = 1 << 20
 
 
-def _tc_plan(M, N, K, nbatch, algo):
+def _tc_plan(M, N, K, nbatch, algo, linear=True):
     """Which operand parts the tcgen05 kernel that endia_b200_gemm will pick reads: "pair16" (bf16
     split, two-CTA kernel), "lo32" (fp32 low parts, 3xTF32 kernels) or None (FFMA / skinny kernels).
     A wrong guess only costs time: the kernel computes the parts it was not handed."""
-    if nbatch != 1 or algo == _lib.GEMM_FFMA or M < 128 or N < 128 or not 32 <= K <= 8192:
+    if nbatch != 1 or algo == _lib.GEMM_FFMA or M < 128 or N < 128 or K < 32:
         return None
+    if K > 8192:
+        # longer reductions run on the two-CTA kernel in runs of 8192 when nothing but alpha is
+        # fused into the store; otherwise on the FFMA kernel (unless the algorithm is named)
+        if N >= 256 and linear:
+            return "lo32" if algo == _lib.GEMM_3XTF32 else "pair16"
+        return None if algo == _lib.GEMM_AUTO else ("lo32" if algo == _lib.GEMM_3XTF32 or N < 256 else "pair16")
     if algo == _lib.GEMM_3XTF32 or N < 256:
         return "lo32"
     if algo == _lib.GEMM_AUTO:
@@ -223,7 +229,8 @@ def gemm_arrays(a, b, out, epi=None, algo=None):
         return
     # Operand parts kept beside an operand's storage are handed to the tensor-core kernel instead
     # of being recomputed per product.
-    plan = _tc_plan(M, N, K, nbatch, algo)
+    linear = epi is None or not (epi.bias or epi.act or epi.dact or epi.beta or epi.colsum)
+    plan = _tc_plan(M, N, K, nbatch, algo, linear)
     if plan is not None:
         pa, pb = _operand_parts_ptr(a, plan), _operand_parts_ptr(b, plan)
         if pa or pb:

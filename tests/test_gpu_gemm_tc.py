@@ -148,6 +148,30 @@ def test_tensor_core_epilogue_mask_and_bias_gradient(nd, M, N, K, tb, algo_name)
     assert max_rel(colsum.to_numpy(), v.sum(0)) < 1e-4
 
 
+@pytest.mark.parametrize("ta,tb,K", [(1, 0, 16384 + 96), (0, 1, 24576)])
+def test_auto_long_reduction_runs(nd, ta, tb, K):
+    """K > 8192 under GEMM_AUTO: the two-CTA kernel drains its accumulators every 8192 and adds
+    the runs in order into C, so the product is reproducible and as accurate as a short one."""
+    from endia_b200 import _lib
+    r = rng(K)
+    M, N = 384, 512
+    a = r.standard_normal((K, M) if ta else (M, K)).astype(np.float32)
+    b = r.standard_normal((N, K) if tb else (K, N)).astype(np.float32)
+    junk = np.full((M, N), -7e29, np.float32)
+    launches0 = _lib.lib.endia_b200_launch_count()
+    out = run_gemm(nd, a, b, ta, tb, _lib.GEMM_AUTO, c0=junk)
+    assert _lib.lib.endia_b200_launch_count() - launches0 <= 3      # two splits + one GEMM, no FFMA tiles
+    out2 = run_gemm(nd, a, b, ta, tb, _lib.GEMM_AUTO, c0=junk)
+    assert np.array_equal(out, out2)
+    am = (a.T if ta else a).astype(np.float64)
+    bm = (b.T if tb else b).astype(np.float64)
+    err = np.abs(out - am @ bm) / dot_scale(am, bm)
+    assert err.max() < 8e-6, err.max()
+    # the truncation bias of one long accumulation would show as a negative mean relative error
+    rel = (out - am @ bm) / np.maximum(np.abs(am @ bm), 1e-3 * dot_scale(am, bm))
+    assert abs(np.median(rel)) < 3e-5
+
+
 def test_3xtf32_long_k_error_growth(nd):
     """dW reduces over the batch: K = 8192 must still meet the gradient tolerance."""
     from endia_b200 import _lib

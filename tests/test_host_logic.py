@@ -64,7 +64,8 @@ def test_gemm_operand_parts_plan(monkeypatch):
     assert plan(256, 1024, 4096, 1, A) == "lo32"        # few tiles, long K: split-K 3xTF32 kernel
     assert plan(1024, 1024, 4096, 1, A) == "lo32"
     assert plan(4096, 128, 1024, 1, A) == "lo32"        # N < 256: one-CTA kernel
-    assert plan(4096, 4096, 16384, 1, A) is None        # K > 8192 stays on FFMA
+    assert plan(4096, 4096, 16384, 1, A) == "pair16"    # K > 8192: runs of 8192 on the two-CTA kernel
+    assert plan(4096, 4096, 16384, 1, A, linear=False) is None   # ... unless an epilogue is fused: FFMA
     assert plan(4096, 1, 1024, 1, A) is None and plan(64, 512, 512, 1, A) is None
     assert plan(8192, 4096, 4096, 2, A) is None         # batched products
     assert plan(8192, 4096, 4096, 1, _lib.GEMM_FFMA) is None
