@@ -20,6 +20,8 @@ def init_process_group():
         # larger groups keep NCCL's defaults and the full GEMM grid.
         os.environ.setdefault("NCCL_MAX_CTAS", "16")
         os.environ.setdefault("ENDIA_B200_TC_RESERVE_SMS", "16")
+    elif world > 2:
+        os.environ.setdefault("NCCL_MAX_CTAS", "64")   # the setting the 8-rank figure was measured with
     if world > 1 and not dist.is_initialized():
         backend = "nccl" if torch.cuda.is_available() else "gloo"
         if backend == "nccl":
