@@ -103,6 +103,7 @@ SIGNATURES = {
     "endia_b200_mse_fwd_bwd_noalloc": (C.c_int, [_vp, _vp, _i64, _f32, _vp, _vp, _vp]),
     "endia_b200_act_bwd_colsum_scratch_bytes": (_sz, [_i64, _i64]),
     "endia_b200_act_bwd_colsum": (C.c_int, [C.c_int, _vp, _vp, _vp, _vp, _i64, _i64, _vp, _vp]),
+    "endia_b200_act_bwd_colsum_parts": (C.c_int, [C.c_int, _vp, _vp, _vp, _vp, _i64, _i64, _vp, _vp, _vp]),
     "endia_b200_adam_step_multi": (C.c_int, [_i32, C.POINTER(_vp), C.POINTER(_vp), C.POINTER(_vp),
                                              C.POINTER(_vp), C.POINTER(_i64), _f32, _f32, _f32,
                                              _f32, _f32, _f32, _vp]),

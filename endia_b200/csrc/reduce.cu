@@ -2,6 +2,7 @@
 // Replaces ReduceAdd.__call__ (endia/functional/reduce_ops/reduce_add_op.mojo:65-210), which
 // accumulates sequentially in fp32, and the op chain of mse (loss_ops/mse_op.mojo:18-20).
 #include "common.cuh"
+#include <cuda_bf16.h>
 #include <mutex>
 
 namespace eb {
@@ -207,7 +208,7 @@ mse_partial_kernel(const float *pred, const float *target, int64_t n, float g2n,
 template <int VEC>
 __global__ void __launch_bounds__(256)
 act_bwd_colsum_kernel(int act, const float *a, const float *grad, float *ds, float *partial,
-                      int64_t M, int64_t N, int64_t rows_per_chunk) {
+                      int64_t M, int64_t N, int64_t rows_per_chunk, __nv_bfloat16 *hi16, __nv_bfloat16 *lo16) {
   const int64_t c = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * VEC;
   if (c >= N) return;
   const int64_t r0 = (int64_t)blockIdx.y * rows_per_chunk;
@@ -237,6 +238,21 @@ act_bwd_colsum_kernel(int act, const float *a, const float *grad, float *ds, flo
     if (ds) {
       if constexpr (VEC == 4) *reinterpret_cast<float4 *>(ds + r * N + c) = *reinterpret_cast<float4 *>(g);
       else ds[r * N + c] = g[0];
+    }
+    if constexpr (VEC == 4) {
+      if (hi16) {
+        // bf16(dS) and bf16(dS - tf32(dS)): the operand parts the GEMMs that consume dS read
+        float l[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) l[j] = g[j] - __uint_as_float(__float_as_uint(g[j]) & 0xFFFFE000u);
+        __nv_bfloat162 h01 = __floats2bfloat162_rn(g[0], g[1]), h23 = __floats2bfloat162_rn(g[2], g[3]);
+        __nv_bfloat162 l01 = __floats2bfloat162_rn(l[0], l[1]), l23 = __floats2bfloat162_rn(l[2], l[3]);
+        uint2 hv, lv;
+        hv.x = *reinterpret_cast<uint32_t *>(&h01); hv.y = *reinterpret_cast<uint32_t *>(&h23);
+        lv.x = *reinterpret_cast<uint32_t *>(&l01); lv.y = *reinterpret_cast<uint32_t *>(&l23);
+        *reinterpret_cast<uint2 *>(hi16 + r * N + c) = hv;
+        *reinterpret_cast<uint2 *>(lo16 + r * N + c) = lv;
+      }
     }
   }
   if (partial) {
@@ -446,6 +462,12 @@ size_t endia_b200_act_bwd_colsum_scratch_bytes(int64_t M, int64_t N) {
 
 int endia_b200_act_bwd_colsum(int act, const float *act_out, const float *grad, float *ds,
                               float *colsum, int64_t M, int64_t N, void *scratch, void *stream) {
+  return endia_b200_act_bwd_colsum_parts(act, act_out, grad, ds, colsum, M, N, scratch, nullptr, stream);
+}
+
+int endia_b200_act_bwd_colsum_parts(int act, const float *act_out, const float *grad, float *ds,
+                                    float *colsum, int64_t M, int64_t N, void *scratch, void *pair16,
+                                    void *stream) {
   int st = require_device();
   if (st) return st;
   EB_REQUIRE(M >= 0 && N >= 0, ENDIA_B200_EINVAL, "act_bwd_colsum: negative size");
@@ -461,12 +483,17 @@ int endia_b200_act_bwd_colsum(int act, const float *act_out, const float *grad, 
   float *partial = colsum ? static_cast<float *>(scratch) : nullptr;
   const bool vec = N % 4 == 0 && ((reinterpret_cast<uintptr_t>(grad) | reinterpret_cast<uintptr_t>(act_out) |
                                    reinterpret_cast<uintptr_t>(ds)) & 15) == 0;
+  EB_REQUIRE(!pair16 || (vec && (M * N) % 8 == 0 && (reinterpret_cast<uintptr_t>(pair16) & 15) == 0),
+             ENDIA_B200_EINVAL, "act_bwd_colsum: the bf16 parts need N %% 4 == 0, M*N %% 8 == 0 and aligned arrays");
+  __nv_bfloat16 *hi16 = static_cast<__nv_bfloat16 *>(pair16), *lo16 = hi16 ? hi16 + M * N : nullptr;
   if (vec) {
     dim3 grid((unsigned)ceil_div(N / 4, 256), (unsigned)chunks);
-    act_bwd_colsum_kernel<4><<<grid, 256, 0, s>>>(act, act_out, grad, act ? ds : nullptr, partial, M, N, rows);
+    act_bwd_colsum_kernel<4><<<grid, 256, 0, s>>>(act, act_out, grad, act ? ds : nullptr, partial, M, N, rows,
+                                                  hi16, lo16);
   } else {
     dim3 grid((unsigned)ceil_div(N, 256), (unsigned)chunks);
-    act_bwd_colsum_kernel<1><<<grid, 256, 0, s>>>(act, act_out, grad, act ? ds : nullptr, partial, M, N, rows);
+    act_bwd_colsum_kernel<1><<<grid, 256, 0, s>>>(act, act_out, grad, act ? ds : nullptr, partial, M, N, rows,
+                                                  nullptr, nullptr);
   }
   EB_LAUNCH_CHECK();
   if (colsum) {

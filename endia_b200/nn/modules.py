@@ -83,9 +83,21 @@ def linear(x, weight, bias=None, activation=None):
                 setup_shape_and_data(db)
             nbytes = _lib.lib.endia_b200_act_bwd_colsum_scratch_bytes(B, N) if need_db else 0
             scratch = alloc((nbytes + 3) // 4) if nbytes else None
-            _lib.call("endia_b200_act_bwd_colsum", act, out.data_ptr(), g.data_ptr(),
+            # dS feeds two products (dX and dW): when they run on the bf16-compensated kernel its
+            # operand parts are written in this pass instead of by a split kernel later
+            parts = None
+            if act and _state.cache_tf32_lo and (B * N) % 8 == 0 and B * N >= (1 << 20):
+                from ..functional.binary_ops import _tc_plan
+                if "pair16" in (_tc_plan(B, xp.shape()[1], N, 1, _state.gemm_algo),
+                                _tc_plan(xp.shape()[1], N, B, 1, _state.gemm_algo)):
+                    parts = alloc(B * N)
+            _lib.call("endia_b200_act_bwd_colsum_parts", act, out.data_ptr(), g.data_ptr(),
                       ds.data_ptr() if act else None, db.data_ptr() if need_db else None, B, N,
-                      scratch.data_ptr() if scratch is not None else None, stream())
+                      scratch.data_ptr() if scratch is not None else None,
+                      parts.data_ptr() if parts is not None else None, stream())
+            if parts is not None:
+                ds._pair16 = parts
+                ds._parts_ptr = ds.buf.data_ptr()
         else:
             ds = g
         res = []

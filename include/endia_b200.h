@@ -277,6 +277,13 @@ size_t endia_b200_act_bwd_colsum_scratch_bytes(int64_t M, int64_t N);
 int endia_b200_act_bwd_colsum(int act, const float *act_out, const float *grad, float *ds,
                               float *colsum, int64_t M, int64_t N, void *scratch, void *stream);
 
+/* The same, also writing the bf16 split of dS (endia_b200_bf16_split's layout, 4*M*N bytes at
+ * `pair16`, NULL = not written) that the TF32_BF16X2 products consuming dS read, in the same pass
+ * (needs act != NONE, N % 4 == 0, M*N % 8 == 0). */
+int endia_b200_act_bwd_colsum_parts(int act, const float *act_out, const float *grad, float *ds,
+                                    float *colsum, int64_t M, int64_t N, void *scratch, void *pair16,
+                                    void *stream);
+
 /* --------------------------------------------------------------- optimizer ---- */
 
 /* One fused Adam step over n_tensors parameter tensors (device pointers passed in HOST arrays):

@@ -330,3 +330,27 @@ def test_copy_strided_both_sides(nd):
     assert np.array_equal(b.to_numpy(), x.transpose(1, 0, 2))
     st = _lib.lib.endia_b200_copy_strided(view(a, [5, 9, 7], [63, 1, 9], 0).desc(), b.desc(), stream())
     assert st in (_lib.EINVAL, _lib.ESHAPE)
+
+
+def test_act_bwd_colsum_writes_operand_parts(nd):
+    """endia_b200_act_bwd_colsum_parts: dS, the bias gradient and the bf16 split of dS from one
+    pass; the split must equal what endia_b200_bf16_split makes of dS."""
+    import torch
+    from endia_b200 import _lib
+    from endia_b200._array import stream, alloc
+    r = rng(41)
+    M, N = 96, 256
+    h = np.tanh(r.standard_normal((M, N))).astype(np.float32)
+    g = r.standard_normal((M, N)).astype(np.float32)
+    H, G, DS, DB = nd.Array(h), nd.Array(g), nd.Array([M, N]), nd.Array([1, N])
+    scratch = alloc(_lib.lib.endia_b200_act_bwd_colsum_scratch_bytes(M, N) // 4 + 1)
+    parts, ref_parts = alloc(M * N), alloc(M * N)
+    _lib.call("endia_b200_act_bwd_colsum_parts", _lib.ACT_TANH, H.data_ptr(), G.data_ptr(), DS.data_ptr(),
+              DB.data_ptr(), M, N, scratch.data_ptr(), parts.data_ptr(), stream())
+    ds = g * (1.0 - h * h)
+    assert max_rel(DS.to_numpy(), ds) < 1e-6 and max_rel(DB.to_numpy(), ds.sum(0, keepdims=True)) < 1e-5
+    _lib.call("endia_b200_bf16_split", DS.data_ptr(), ref_parts.data_ptr(), M * N, stream())
+    assert torch.equal(parts.view(torch.int32), ref_parts.view(torch.int32))
+    st = _lib.lib.endia_b200_act_bwd_colsum_parts(_lib.ACT_TANH, H.data_ptr(), G.data_ptr(), DS.data_ptr(), None,
+                                                  3, 5, None, parts.data_ptr(), stream())
+    assert st == _lib.EINVAL
