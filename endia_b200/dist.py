@@ -65,7 +65,9 @@ class GradAllReducer:
         self.mode = mode
         self.pending = []
         self.deferred = []
+        self.small = []           # (param, grad) of small tensors, summed together in wait()
         self.flat = None
+        self.flat_small = None
         for p in self.params:
             p.grad_hook = self._hook
 
@@ -80,22 +82,33 @@ class GradAllReducer:
         if self.mode == "serial":
             self.deferred.append(g)
             return
+        if g.size() < self.SMALL and flat_tensor(g).is_cuda:
+            # bias-sized gradients: one collective for all of them instead of one each, whose
+            # latency would sit between the large ones on the communicator's stream
+            self.small.append((param, g))
+            return
         self.pending.append(dist.all_reduce(flat_tensor(g), op=dist.ReduceOp.SUM, group=self.group,
                                             async_op=True))
 
-    def _reduce_bucket(self):
+    SMALL = 1 << 16
+
+    def _reduce_bucket(self, params=None, grads=None, which="flat"):
         from . import _lib
         from ._array import stream
         from .functional._utils import contiguous
-        grads = [contiguous(p.grad()) for p in self.params]
+        if params is None:
+            params = self.params
+            grads = [contiguous(p.grad()) for p in params]
         total = sum(g.size() for g in grads)
-        if self.flat is None or self.flat.numel() != total:
-            self.flat = torch.empty(total, dtype=torch.float32, device=device())
+        flat = getattr(self, which)
+        if flat is None or flat.numel() != total:
+            flat = torch.empty(total, dtype=torch.float32, device=device())
+            setattr(self, which, flat)
         off = 0
         views = []
-        for p, g in zip(self.params, grads):
+        for p, g in zip(params, grads):
             n = g.size()
-            piece = self.flat[off:off + n]
+            piece = flat[off:off + n]
             if n:
                 _lib.call("endia_b200_d2d", piece.data_ptr(), g.data_ptr(), 4 * n, stream())
             v = Array(ArrayShape(g.shape()))
@@ -103,8 +116,8 @@ class GradAllReducer:
             views.append(v)
             off += n
         if total:
-            dist.all_reduce(self.flat, op=dist.ReduceOp.SUM, group=self.group)
-        for p, v in zip(self.params, views):
+            dist.all_reduce(flat, op=dist.ReduceOp.SUM, group=self.group)
+        for p, v in zip(params, views):
             p.grad_(v)
 
     def wait(self):
@@ -115,6 +128,9 @@ class GradAllReducer:
             self.pending.append(dist.all_reduce(flat_tensor(g), op=dist.ReduceOp.SUM, group=self.group,
                                                 async_op=True))
         self.deferred = []
+        if self.small:
+            self._reduce_bucket([p for p, _ in self.small], [g for _, g in self.small], "flat_small")
+            self.small = []
         for w in self.pending:
             w.wait()
         self.pending = []
