@@ -42,7 +42,7 @@ class GradAllReducer:
     """Sums the parameters' gradients over the ranks before the optimizer step; the mean over ranks
     is folded into the optimizer's gradient scale instead of a separate pass. Modes:
 
-    "overlap" (default) an all-reduce per parameter is started from a hook the moment the backward
+    "overlap"           an all-reduce per parameter is started from a hook the moment the backward
                         walk has produced its gradient (last layer first), on the communicator's
                         stream, beside the remaining backward GEMMs.
     "bucket"            after the backward pass the gradients are gathered into one flat buffer
@@ -50,15 +50,20 @@ class GradAllReducer:
                         all-reduce, and the parameters' gradients become views of that buffer.
     "serial"            an all-reduce per parameter after the backward pass.
 
-    Measured on the c2 step with 2 GPUs: overlap 4.21 ms, bucket 4.40-4.60 ms. (The persistent
-    GEMM kernels hold every SM, so a collective beside them waits for SMs and a GEMM launched
-    beside a collective runs on fewer; with short per-rank steps the bucket mode may win.)"""
+    Measured on the c2 step: 2 GPUs overlap 4.13-4.21 ms, bucket 4.40-4.60 ms; 8 GPUs overlap
+    2.08 ms, bucket 1.94 ms. The persistent GEMM kernels hold every SM, so a collective beside
+    them waits for SMs and a GEMM launched beside a collective runs on fewer; with the short
+    per-rank steps of 8 ranks one all-reduce after the pass costs less, so groups of 8 or more
+    default to "bucket", smaller ones to "overlap" (ENDIA_B200_DP_MODE overrides)."""
 
     def __init__(self, params, group=None, overlap=None, mode=None):
         self.params = list(params)
         self.group = group
         if mode is None:
-            mode = os.environ.get("ENDIA_B200_DP_MODE", "overlap") if overlap is None else (
+            default = "overlap"
+            if dist.is_initialized() and dist.get_world_size(group) >= 8:
+                default = "bucket"      # short per-rank steps: see the class comment
+            mode = os.environ.get("ENDIA_B200_DP_MODE", default) if overlap is None else (
                 "overlap" if overlap else "serial")
         if mode not in ("bucket", "overlap", "serial"):
             raise ValueError("GradAllReducer: unknown mode %r" % (mode,))
