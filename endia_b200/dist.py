@@ -15,9 +15,8 @@ def init_process_group():
     if world == 2:
         # The gradient all-reduce runs beside the backward GEMMs: with two ranks NCCL needs few
         # CTAs, so keep it to 16 and leave 16 SMs out of the persistent GEMM grid; neither then
-        # waits for the other's SMs (measured 5.21 -> 5.09 ms per c2 step). With 8 ranks the same
-        # limits make the all-reduce the bottleneck (3.12 ms against 2.08 ms without them), so
-        # larger groups keep NCCL's defaults and the full GEMM grid.
+        # waits for the other's SMs (measured 5.21 -> 5.09 ms per c2 step). Larger groups, whose
+        # all-reduce needs more of NCCL's CTAs, run without these limits.
         os.environ.setdefault("NCCL_MAX_CTAS", "16")
         os.environ.setdefault("ENDIA_B200_TC_RESERVE_SMS", "16")
     elif world > 2:
