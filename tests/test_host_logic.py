@@ -73,3 +73,22 @@ def test_gemm_operand_parts_plan(monkeypatch):
     assert plan(8192, 4096, 4096, 1, _lib.GEMM_TF32_BF16X2) == "pair16"
     monkeypatch.setenv("ENDIA_B200_TC_SCHEME", "3xtf32")
     assert plan(8192, 4096, 4096, 1, A) == "lo32"
+
+
+def test_bench_reference_arm_prints_contract_line():
+    """`bench.py --impl reference` needs no GPU: it times the CPU oracle on a bounded sample and
+    prints one JSON line with the keys the reference arm has to carry."""
+    import json
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    out = subprocess.run([sys.executable, os.path.join(root, "bench.py"), "--impl", "reference", "--steps", "1",
+                          "--warmup", "0", "--cpu-rows", "4"], capture_output=True, text=True, timeout=900, cwd=root)
+    assert out.returncode == 0, out.stderr[-2000:]
+    line = json.loads(out.stdout.strip().splitlines()[-1])
+    assert line["impl"] == "reference" and line["unit"] == "samples/s" and line["value"] > 0
+    assert line["higher_is_better"] is True and line["n_gpus"] == 1
+    assert line["cpu_baseline"]["kind"] in ("port", "reference") and line["cpu_baseline"]["cores"] >= 1
+    assert line["e2e"] == {"value": line["value"], "unit": "samples/s", "h2d_bytes_per_step": 0,
+                           "d2h_bytes_per_step": 0}
