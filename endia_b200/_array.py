@@ -50,6 +50,20 @@ def drop_operand_parts(arr):
     base._pair16 = None
 
 
+def await_pending(arr):
+    """Run and clear the completion callback a storage buffer carries, if any. An asynchronous
+    writer (the all-gather of a sharded optimizer step) leaves one on the array it is still
+    filling; every accessor of the device pointer calls this first, so a consumer on the compute
+    stream waits for exactly the arrays it reads and no others."""
+    base = getattr(arr, "base_", None)
+    if base is None:
+        base = arr
+    cb = getattr(base, "_pending", None)
+    if cb is not None:
+        base._pending = None
+        cb()
+
+
 def compute_stride(shape):
     """Row-major element strides (endia/utils/_array_shape.mojo:24-30)."""
     stride = [1] * len(shape)
@@ -177,6 +191,7 @@ class Array:
 
     def desc(self):
         """ctypes descriptor for the C ABI."""
+        await_pending(self)
         t = _CTensor()
         t.data = self.buf.data_ptr() if self.buf is not None and self.buf.numel() else None
         s = self.array_shape_
@@ -192,6 +207,7 @@ class Array:
 
     def data_ptr(self):
         """Device address of the first logical element."""
+        await_pending(self)
         w = 2 if self.is_complex_flag else 1
         return self.buf.data_ptr() + 4 * w * self.array_shape_.storage_offset
 
@@ -235,6 +251,7 @@ class Array:
     def to_numpy(self):
         """Copy to the host as float32 (or complex64) in logical order."""
         from .functional._utils import contiguous
+        await_pending(self)
         c = contiguous(self)
         n = c.size() * (2 if c.is_complex_flag else 1)
         off = c.array_shape_.storage_offset * (2 if c.is_complex_flag else 1)

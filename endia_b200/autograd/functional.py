@@ -27,6 +27,7 @@ def jacrev(arg, create_graph=False):
         seed = reshape(eye(out.size()), out.shape() + out.shape())
     else:
         seed = ones([last_dim])
+        seed._is_ones_seed = True   # lets a fused VJP skip the multiplication by one
     out.grad_(seed)
     # Number of graph edges into every node, so that a leaf's hook fires once its last
     # contribution has been accumulated.

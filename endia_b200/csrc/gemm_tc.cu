@@ -41,21 +41,6 @@ constexpr uint32_t TC_WAIT_LIMIT = 1u << 22;
 
 static __device__ int g_tc_status = 0;    // 0 ok, else the code of the first wait that gave up
 
-#ifdef EB_TC_TRACE
-// Debug build only: SM clock stamps of CTA 0 of the persistent kernel, 8 slots per tile.
-static __device__ long long g_tc_trace[16 * 8];
-#define EB_TRACE(tile, slot)                                                   \
-  do {                                                                         \
-    if (blockIdx.x == 0 && (tile) < 16) g_tc_trace[(tile) * 8 + (slot)] = clock64(); \
-  } while (0)
-#define EB_TRACE2(on, idx)                                                      \
-  do {                                                                         \
-    if ((on) && (idx) < 64) g_tc_trace[64 + (idx)] = clock64();                \
-  } while (0)
-#else
-#define EB_TRACE(tile, slot) do { } while (0)
-#define EB_TRACE2(on, idx) do { } while (0)
-#endif
 
 // ------------------------------------------------------------------------------- PTX helpers
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {
@@ -209,9 +194,7 @@ __device__ __forceinline__ float4 apply_epilogue4(const EpiParams &e, float4 acc
 template <int BN, bool DOUBLE_BUF = true>
 __device__ __forceinline__ void tc_epilogue_warp(uint32_t tmem_base, int q, int lane, int c_begin, int c_end,
                                                  int64_t m0, int64_t n0, int64_t M, int64_t N, float *Cout,
-                                                 int64_t ldc, const EpiParams &epi, bool vec_c, uint32_t buf,
-                                                 bool trace = false) {
-  (void)trace;
+                                                 int64_t ldc, const EpiParams &epi, bool vec_c, uint32_t buf) {
   const uint32_t row_addr = tmem_base + ((uint32_t)(q * 32) << 16);
   const bool vec_epi = vec_c && (!epi.bias || (reinterpret_cast<uintptr_t>(epi.bias) & 15) == 0) &&
                        (!epi.dact || ((reinterpret_cast<uintptr_t>(epi.dact_src) & 15) == 0 && epi.ld_dact % 4 == 0));
@@ -222,9 +205,7 @@ __device__ __forceinline__ void tc_epilogue_warp(uint32_t tmem_base, int q, int 
 #pragma unroll 1
   for (int c = c_begin; c < c_end; ++c) {
     const uint32_t bb = buf + (DOUBLE_BUF ? (uint32_t)(c & 1) * 4096u : 0u);
-    EB_TRACE2(trace, (c - c_begin) * 5 + 0);
     tc_wait_ld();
-    EB_TRACE2(trace, (c - c_begin) * 5 + 1);
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
       float4 v;
@@ -238,9 +219,7 @@ __device__ __forceinline__ void tc_epilogue_warp(uint32_t tmem_base, int q, int 
       tc_ld32(row_addr + (uint32_t)((c + 1) * 32), ra);
       tc_ld32(row_addr + (uint32_t)(BN + (c + 1) * 32), rb);
     }
-    EB_TRACE2(trace, (c - c_begin) * 5 + 2);
     __syncwarp();
-    EB_TRACE2(trace, (c - c_begin) * 5 + 3);
     const int64_t n = n0 + c * 32 + c4 * 4;
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
@@ -258,7 +237,6 @@ __device__ __forceinline__ void tc_epilogue_warp(uint32_t tmem_base, int q, int 
           if (n + t < N) cp[t] = apply_epilogue(epi, e[t], m, n + t, cp + t);
       }
     }
-    EB_TRACE2(trace, (c - c_begin) * 5 + 4);
     if (!DOUBLE_BUF) __syncwarp();   // the buffer is rewritten by the next chunk
   }
 }
@@ -488,8 +466,7 @@ template <int BN>
 __device__ __forceinline__ void tc_epilogue_warp_bulk(uint32_t tmem_base, int q, int lane, int c_begin, int c_end,
                                                       int64_t m0, int64_t n0, int64_t M, int64_t N, const float *Cout,
                                                       int64_t ldc, const EpiParams &epi, const CUtensorMap *cmap,
-                                                      uint32_t buf, bool reduce, bool trace = false) {
-  (void)trace;
+                                                      uint32_t buf, bool reduce) {
   const uint32_t row_addr = tmem_base + ((uint32_t)(q * 32) << 16);
   const bool plain = epi.alpha == 1.f && !epi.bias && !epi.act && !epi.dact && epi.beta == 0.f &&
                      !epi.colsum_partial;
@@ -501,12 +478,10 @@ __device__ __forceinline__ void tc_epilogue_warp_bulk(uint32_t tmem_base, int q,
   tc_ld32(row_addr + (uint32_t)(BN + c_begin * 32), rb);
 #pragma unroll 1
   for (int c = c_begin; c < c_end; ++c) {
-    EB_TRACE2(trace, (c - c_begin) * 5 + 0);
     tc_wait_ld();
     // the previous chunk's store has read the buffer
     if (lane == 0) bulk_wait_read0();
     __syncwarp();
-    EB_TRACE2(trace, (c - c_begin) * 5 + 1);
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
       float4 v;
@@ -520,7 +495,6 @@ __device__ __forceinline__ void tc_epilogue_warp_bulk(uint32_t tmem_base, int q,
       tc_ld32(row_addr + (uint32_t)((c + 1) * 32), ra);
       tc_ld32(row_addr + (uint32_t)(BN + (c + 1) * 32), rb);
     }
-    EB_TRACE2(trace, (c - c_begin) * 5 + 2);
     const int64_t nb = n0 + c * 32;
     if (!plain) {
       __syncwarp();
@@ -564,13 +538,11 @@ __device__ __forceinline__ void tc_epilogue_warp_bulk(uint32_t tmem_base, int q,
     }
     fence_async_smem();
     __syncwarp();
-    EB_TRACE2(trace, (c - c_begin) * 5 + 3);
     if (lane == 0 && nb < N && m0 + q * 32 < M) {
       if (reduce) tma_reduce_add_2d(cmap, buf, (int)nb, (int)(m0 + q * 32));
       else tma_store_2d(cmap, buf, (int)nb, (int)(m0 + q * 32));
       bulk_commit();
     }
-    EB_TRACE2(trace, (c - c_begin) * 5 + 4);
   }
 }
 
@@ -757,16 +729,13 @@ gemm_tc2p_kernel(const __grid_constant__ TcMaps maps, const GemmParams p, int pa
         int kb = 0;
         for (int run = 0; run < kseq && ok; ++run, ++j) {
         // the epilogue warps of both CTAs have read the previous accumulators
-        EB_TRACE(j, 0);
         if (j > 0 && !mbar_wait_cluster(acc_empty, (uint32_t)(j - 1) & 1, 32)) { ok = false; break; }
         tc_fence_after();
-        EB_TRACE(j, 1);
         const int kend = (run + 1) * per_run < nkb ? (run + 1) * per_run : nkb;
         for (int kl = 0; kb < kend; ++kb, ++kl, ++it) {
           const int s = (int)(it % STAGES);
           if (!mbar_wait(full_bar(s), (it / STAGES) & 1, 33)) { ok = false; break; }
           tc_fence_after();
-          if (kl == 0) EB_TRACE(j, 2);
           const uint32_t st = smem_base + s * STAGE_BYTES;
           const uint32_t sb = st + 2 * A_BYTES;
           const uint64_t a_hi = tile_desc<A_MN, BK>(st), b_hi = tile_desc<B_MN, BK>(sb);
@@ -800,7 +769,6 @@ gemm_tc2p_kernel(const __grid_constant__ TcMaps maps, const GemmParams p, int pa
           tc_commit_pair(empty_bar(s));
         }
         tc_commit_pair(acc_full);   // also on the give-up path, so that the epilogue warps move on
-        EB_TRACE(j, 3);
         }
       }
     }
@@ -816,7 +784,6 @@ gemm_tc2p_kernel(const __grid_constant__ TcMaps maps, const GemmParams p, int pa
       for (int run = 0; run < kseq; ++run, ++j) {
       if (!mbar_wait(acc_full, (uint32_t)j & 1, 34)) { ok = false; break; }
       tc_fence_after();
-      if (warp == 2 && lane == 0) EB_TRACE(j, 4);
       if (run > 0) {
         // this run is added to what the previous run of the same tile stored: that store must be complete
         if (lane == 0) bulk_wait0();
@@ -825,15 +792,12 @@ gemm_tc2p_kernel(const __grid_constant__ TcMaps maps, const GemmParams p, int pa
       constexpr int CH = BN / 64;
       if (p.vec_c)
         tc_epilogue_warp_bulk<BN>(tmem_base, q, lane, half * CH, (half + 1) * CH, m0, n0, p.M, p.N, p.C, p.ldc,
-                                  p.epi, &maps.c, epi_base + (uint32_t)(warp - 2) * 4096u, ksplit > 1 || run > 0,
-                                  blockIdx.x == 0 && warp == 2 && lane == 0 && j == 1);
+                                  p.epi, &maps.c, epi_base + (uint32_t)(warp - 2) * 4096u, ksplit > 1 || run > 0);
       else
         tc_epilogue_warp<BN, false>(tmem_base, q, lane, half * CH, (half + 1) * CH, m0, n0, p.M, p.N, p.C, p.ldc,
                                     p.epi, p.vec_c, epi_base + (uint32_t)(warp - 2) * 4096u);
       tc_fence_before();
       __syncwarp();
-      if (warp == 2 && lane == 0) EB_TRACE(j, 5);
-      if (warp == 9 && lane == 0) EB_TRACE(j, 6);
       if (lane == 0) mbar_arrive_cluster(acc_empty_leader);
       }
     }
@@ -1155,7 +1119,17 @@ int launch_gemm_tc(const GemmParams &p, int trans_a, int trans_b, cudaStream_t s
 
   // Operand parts: taken from the caller when provided (laid out like the operand's storage), else
   // computed into stream-ordered work buffers.
-  void *a_buf = nullptr, *b_buf = nullptr;
+  // (stream-ordered work buffers, released on every way out of this function)
+  struct WorkBuffers {
+    cudaStream_t s;
+    void *a = nullptr, *b = nullptr, *partial = nullptr;
+    ~WorkBuffers() {
+      if (a) cudaFreeAsync(a, s);
+      if (b) cudaFreeAsync(b, s);
+      if (partial) cudaFreeAsync(partial, s);
+    }
+  } work{s};
+  void *&a_buf = work.a, *&b_buf = work.b;
   if (bf16c) {
     // bf16(x) and bf16(x - tf32(x)), each [rows][ld16] bf16
     const int64_t a_ld16 = (a_cols + 7) / 8 * 8, b_ld16 = (b_cols + 7) / 8 * 8;
@@ -1200,11 +1174,10 @@ int launch_gemm_tc(const GemmParams &p, int trans_a, int trans_b, cudaStream_t s
     if ((st = make_map(&maps.b_lo, b_lo, b_cols, b_rows, b_lo_ld, b_bi, b_bo, trans_b == 0))) return st;
   }
   GemmParams q = p;
-  float *partial = nullptr;
   if (splits > 1) {
     q.ld_partial = (p.N + 3) / 4 * 4;
-    EB_CUDA(cudaMallocAsync(&partial, sizeof(float) * (size_t)splits * p.M * q.ld_partial, s));
-    q.partial = partial;
+    EB_CUDA(cudaMallocAsync(&work.partial, sizeof(float) * (size_t)splits * p.M * q.ld_partial, s));
+    q.partial = static_cast<float *>(work.partial);
   }
   if (pair && p.vec_c) {
     // output map: [M][N] floats with leading dimension ldc, boxes of 32 rows x 32 floats
@@ -1224,12 +1197,7 @@ int launch_gemm_tc(const GemmParams &p, int trans_a, int trans_b, cudaStream_t s
   else if (bn == 256) st = launch_variant<256, 32, 2>(maps, p, trans_a, trans_b, s);
   else if (bk == 16) st = launch_variant<128, 16, 6>(maps, q, trans_a, trans_b, s, splits);
   else st = launch_variant<128, 32, 3>(maps, q, trans_a, trans_b, s, splits);
-  if (splits > 1 && st == ENDIA_B200_OK) {
-    st = launch_splitk_finish(q, splits, s);
-    cudaFreeAsync(partial, s);
-  }
-  if (a_buf) EB_CUDA(cudaFreeAsync(a_buf, s));
-  if (b_buf) EB_CUDA(cudaFreeAsync(b_buf, s));
+  if (splits > 1 && st == ENDIA_B200_OK) st = launch_splitk_finish(q, splits, s);
   return st;
 }
 
@@ -1246,11 +1214,6 @@ int tc_status_and_clear(cudaStream_t s) {
 
 }  // namespace eb
 
-#ifdef EB_TC_TRACE
-extern "C" int endia_b200_debug_tc_trace(long long *out128) {
-  return cudaMemcpyFromSymbol(out128, eb::g_tc_trace, sizeof(long long) * 128) == cudaSuccess ? 0 : 1;
-}
-#endif
 
 extern "C" int endia_b200_has_tcgen05(void) { return eb::encode_fn() != nullptr ? 1 : 0; }
 

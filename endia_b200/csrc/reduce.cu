@@ -113,6 +113,17 @@ reduce_finish_kernel(const float *partial, float *out, int64_t n_out, int splits
   }
 }
 
+// out[0] = scale * sum of `count` partials, one CTA: thread t adds partial[t], partial[t + 256], ...
+// in that order and the CTA adds the 256 thread sums in a fixed tree, so the result does not depend
+// on timing. (A single thread walking thousands of partials costs more than the pass that made them.)
+__global__ void __launch_bounds__(256)
+scalar_finish_kernel(const float *partial, float *out, int count, float scale) {
+  float acc = 0.f;
+  for (int i = threadIdx.x; i < count; i += 256) acc += partial[i];
+  acc = block_sum(acc);
+  if (threadIdx.x == 0) out[0] = acc * scale;
+}
+
 // Layout [A, R, C] with C contiguous: dst[(a*chunks + chunk)*C + c] = sum over the chunk's rows.
 // VEC = 4: one thread owns 4 adjacent columns (128-bit loads).
 template <int VEC>
@@ -427,8 +438,11 @@ int endia_b200_reduce_add(const endia_b200_tensor *in, uint32_t axes_mask, float
   }
   EB_LAUNCH_CHECK();
   if (p.splits > 1) {
-    reduce_finish_kernel<<<grid_for(p.n_out, 256), 256, 0, s>>>(static_cast<const float *>(scratch),
-                                                                out, p.n_out, p.splits, 1.f);
+    if (p.n_out == 1)
+      scalar_finish_kernel<<<1, 256, 0, s>>>(static_cast<const float *>(scratch), out, p.splits, 1.f);
+    else
+      reduce_finish_kernel<<<grid_for(p.n_out, 256), 256, 0, s>>>(static_cast<const float *>(scratch),
+                                                                  out, p.n_out, p.splits, 1.f);
     EB_LAUNCH_CHECK();
   }
   return ENDIA_B200_OK;
@@ -450,7 +464,7 @@ int endia_b200_mse_fwd_bwd(const float *pred, const float *target, int64_t n, fl
   const float g2n = gscale * (inv_n + inv_n);
   mse_partial_kernel<<<ctas, 256, 0, s>>>(pred, target, n, g2n, dpred, static_cast<float *>(scratch));
   EB_LAUNCH_CHECK();
-  reduce_finish_kernel<<<1, 32, 0, s>>>(static_cast<const float *>(scratch), loss, 1, ctas, inv_n);
+  scalar_finish_kernel<<<1, 256, 0, s>>>(static_cast<const float *>(scratch), loss, ctas, inv_n);
   EB_LAUNCH_CHECK();
   return ENDIA_B200_OK;
 }
@@ -546,7 +560,7 @@ int endia_b200_mse_fwd_bwd_noalloc(const float *pred, const float *target, int64
   // Every partial slot in [0, ctas) is overwritten by this call, so nothing has to be cleared.
   mse_partial_kernel<<<ctas, 256, 0, s>>>(pred, target, n, g2n, dpred, scratch);
   EB_LAUNCH_CHECK();
-  reduce_finish_kernel<<<1, 32, 0, s>>>(scratch, loss, 1, ctas, inv_n);
+  scalar_finish_kernel<<<1, 256, 0, s>>>(scratch, loss, ctas, inv_n);
   EB_LAUNCH_CHECK();
   return ENDIA_B200_OK;
 }

@@ -6,21 +6,23 @@ import os
 import torch
 import torch.distributed as dist
 
-from ._array import Array, ArrayShape, device
+from ._array import Array, ArrayShape, device, await_pending
 
 
-def init_process_group():
-    """One process per GPU, launched by torchrun (RANK / LOCAL_RANK / WORLD_SIZE / MASTER_*)."""
+def init_process_group(nccl_max_ctas=None, gemm_reserve_sms=None):
+    """One process per GPU, launched by torchrun (RANK / LOCAL_RANK / WORLD_SIZE / MASTER_*).
+
+    A collective that runs beside the persistent GEMM kernels needs SMs of its own: the GEMM grid
+    otherwise holds all of them and NCCL's CTAs (or the GEMM's last CTA pairs) wait. The launcher
+    states both limits here, before NCCL and the GEMM read them: `nccl_max_ctas` becomes
+    NCCL_MAX_CTAS and `gemm_reserve_sms` the number of SMs left out of the persistent GEMM grid
+    (ENDIA_B200_TC_RESERVE_SMS); values already in the environment win, None sets nothing."""
     world = int(os.environ.get("WORLD_SIZE", "1"))
-    if world == 2:
-        # The gradient all-reduce runs beside the backward GEMMs: with two ranks NCCL needs few
-        # CTAs, so keep it to 16 and leave 16 SMs out of the persistent GEMM grid; neither then
-        # waits for the other's SMs (measured 5.21 -> 5.09 ms per c2 step). Larger groups, whose
-        # all-reduce needs more of NCCL's CTAs, run without these limits.
-        os.environ.setdefault("NCCL_MAX_CTAS", "16")
-        os.environ.setdefault("ENDIA_B200_TC_RESERVE_SMS", "16")
-    elif world > 2:
-        os.environ.setdefault("NCCL_MAX_CTAS", "64")   # the setting the 8-rank figure was measured with
+    if world > 1:
+        if nccl_max_ctas is not None:
+            os.environ.setdefault("NCCL_MAX_CTAS", str(int(nccl_max_ctas)))
+        if gemm_reserve_sms is not None:
+            os.environ.setdefault("ENDIA_B200_TC_RESERVE_SMS", str(int(gemm_reserve_sms)))
     if world > 1 and not dist.is_initialized():
         backend = "nccl" if torch.cuda.is_available() else "gloo"
         if backend == "nccl":
@@ -32,6 +34,7 @@ def init_process_group():
 
 def flat_tensor(arr):
     """torch view of an Array's contiguous storage (no copy)."""
+    await_pending(arr)
     w = 2 if arr.is_complex() else 1
     off = arr.storage_offset() * w
     return arr.buf[off:off + arr.size() * w]
@@ -144,6 +147,228 @@ class GradAllReducer:
             p.grad_hook = None
 
 
+class ShardedAdam:
+    """Adam for the batch-sharded training step with the optimizer sharded over the ranks: the sum of
+    the ranks' gradients and the replicated update of optim.Adam become
+
+      reduce-scatter   every large gradient is summed over the ranks the moment the backward walk
+                       has produced it (last layer first, beside the remaining backward GEMMs);
+                       rank r receives the r-th 1/P of it,
+      update           ONE multi-tensor launch over this rank's 1/P of every large parameter (its
+                       slices of m and v are the only optimizer state the rank holds) and over the
+                       small tensors (biases), whose gradients are summed by one all-reduce and
+                       updated on every rank,
+      all-gather       the updated slices are gathered in place into every rank's parameter,
+                       first layer first; a parameter carries a completion callback
+                       (_array.await_pending) until its gather is done, so the next forward pass
+                       waits layer by layer and the later gathers run beside it. The callback also
+                       rewrites the parameter's GEMM operand parts (one pass over the weights).
+
+    The arithmetic per element is optim.Adam's (endia/optim/adam.mojo:47-65) with the mean over
+    the ranks folded into the gradient scale; the bytes on NVLink are those of the all-reduce it
+    replaces, the optimizer pass and its state shrink by the number of ranks. `m` and `v` hold
+    slices for the large parameters (flat, 1/P of the elements) and whole arrays for the small."""
+    mode = "sharded"
+    SMALL = 1 << 16
+
+    def __init__(self, params, lr=0.001, beta1=0.9, beta2=0.999, eps=1e-8, group=None):
+        self.params = list(params)
+        self.lr, self.beta1, self.beta2, self.eps = lr, beta1, beta2, eps
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.t = 1.0
+        self.grad_scale = 1.0 / self.world
+        self.sharded = [self._shardable(p) for p in self.params]
+        self.g_slice = [torch.empty(p.size() // self.world, dtype=torch.float32, device=flat_tensor(p).device)
+                        if sh else None for p, sh in zip(self.params, self.sharded)]
+        self._m = self._v = None  # moments: allocated (zero) at the first step or first access
+        self.pending = []         # reduce-scatters in flight
+        self.small = []           # (index, gradient) of the replicated tensors of this pass
+        self.flat_small = None
+        self._ready = {}
+        for p in self.params:
+            p.grad_hook = self._hook
+
+    def _state(self):
+        if self._m is None:
+            shapes = [[p.size() // self.world] if sh else p.shape() for p, sh in zip(self.params, self.sharded)]
+            self._m = [Array(shape) for shape in shapes]
+            self._v = [Array(shape) for shape in shapes]
+        return self._m, self._v
+
+    @property
+    def m(self):
+        return self._state()[0]
+
+    @property
+    def v(self):
+        return self._state()[1]
+
+    def _reduce_scatter(self, out, inp):
+        """Asynchronous sum over the ranks of `inp`, this rank's 1/P of it into `out`."""
+        if dist.get_backend(self.group) != "gloo":
+            return dist.reduce_scatter_tensor(out, inp, op=dist.ReduceOp.SUM, group=self.group, async_op=True)
+        # gloo (CPU runs of the host logic) has no reduce-scatter: all-reduce a copy, keep the slice
+        tmp, k, r = inp.clone(), out.numel(), self.rank
+        work = dist.all_reduce(tmp, op=dist.ReduceOp.SUM, group=self.group, async_op=True)
+
+        class _Done:
+            def wait(self):
+                work.wait()
+                out.copy_(tmp[k * r:k * (r + 1)])
+        return _Done()
+
+    def _shardable(self, p):
+        return (self.world > 1 and p.size() >= self.SMALL and p.size() % self.world == 0 and p.is_contiguous()
+                and not p.is_complex())
+
+    def _index(self, param):
+        for i, p in enumerate(self.params):
+            if p is param:
+                return i
+        raise KeyError("ShardedAdam: unknown parameter")
+
+    def _hook(self, param, grad):
+        from .functional._utils import contiguous
+        i = self._index(param)
+        g = contiguous(grad)
+        if g is not grad:
+            param.grad_(g)
+        if not self.sharded[i]:
+            self.small.append((i, g))
+            return
+        self.pending.append(self._reduce_scatter(self.g_slice[i], flat_tensor(g)))
+        self._ready[i] = True
+
+    def wait(self):
+        """Nothing to do before step(): kept so that the step reads like the replicated one."""
+
+    def detach(self):
+        for p in self.params:
+            p.grad_hook = None
+
+    def reset_state(self):
+        from . import _lib
+        from ._array import stream
+        self.t = 1.0
+        for i, p in enumerate(self.params):
+            for st in (self.m[i], self.v[i]):
+                if not self.sharded[i]:
+                    st.array_shape_ = ArrayShape(p.shape())
+                if st.size():
+                    _lib.call("endia_b200_memset0", st.data_ptr(), st.size() * 4, stream())
+
+    def step(self):
+        import ctypes as C
+        from . import _lib
+        from ._array import stream, alloc
+        from .functional._utils import contiguous, broadcast_shapes
+        n = len(self.params)
+        # gradients that no hook has seen (a parameter outside the graph): zeros, like Array.grad()
+        seen_small = {i for i, _ in self.small}
+        for i, p in enumerate(self.params):
+            if self.sharded[i] and not self._ready.get(i):
+                self._hook(p, p.grad())
+            elif not self.sharded[i] and i not in seen_small:
+                self.small.append((i, contiguous(p.grad())))
+        small = dict(self.small)
+        if self.world > 1 and small:
+            # the bias-sized gradients: one collective for all of them
+            idx = sorted(small)
+            total = sum(small[i].size() for i in idx)
+            if self.flat_small is None or self.flat_small.numel() != total:
+                self.flat_small = torch.empty(total, dtype=torch.float32, device=flat_tensor(self.params[idx[0]]).device)
+            off = 0
+            views = {}
+            for i in idx:
+                k = small[i].size()
+                piece = self.flat_small[off:off + k]
+                piece.copy_(flat_tensor(small[i]))
+                v = Array(ArrayShape(small[i].shape()))
+                v.buf = piece
+                views[i] = v
+                off += k
+            dist.all_reduce(self.flat_small, op=dist.ReduceOp.SUM, group=self.group)
+            for i in idx:
+                self.params[i].grad_(views[i])
+            small = views
+        for w in self.pending:
+            w.wait()
+        self.pending = []
+        P, G, M, V, numel = [], [], [], [], []
+        for i, p in enumerate(self.params):
+            if self.sharded[i]:
+                k = p.size() // self.world
+                P.append(p.data_ptr() + 4 * k * self.rank)
+                G.append(self.g_slice[i].data_ptr())
+                numel.append(k)
+            else:
+                g = small[i]
+                if g.size() != p.size():
+                    raise _lib.EndiaError(_lib.ESHAPE, "Adam: gradient %s does not match parameter %s" % (
+                        g.shape(), p.shape()))
+                P.append(p.data_ptr())
+                G.append(g.data_ptr())
+                numel.append(p.size())
+                shp = broadcast_shapes(self.m[i].shape(), g.shape())     # (1, N) for a bias, as in optim.Adam
+                self.m[i].array_shape_ = ArrayShape(shp)
+                self.v[i].array_shape_ = ArrayShape(shp)
+            M.append(self.m[i].data_ptr())
+            V.append(self.v[i].data_ptr())
+        arr = lambda xs: (C.c_void_p * n)(*xs)
+        _lib.call("endia_b200_adam_step_multi", n, arr(P), arr(G), arr(M), arr(V), (C.c_int64 * n)(*numel),
+                  self.lr, self.beta1, self.beta2, self.eps, self.t, self.grad_scale, stream())
+        # gather the updated slices, first layer first; consumers wait per parameter
+        for i, p in enumerate(self.params):
+            p._tf32_lo = None
+            if not self.sharded[i]:
+                p._pair16 = None
+                continue
+            k = p.size() // self.world
+            full = flat_tensor(p)
+            work = dist.all_gather_into_tensor(full, full[k * self.rank:k * (self.rank + 1)], group=self.group,
+                                               async_op=True)
+            wants_parts = p.ndim() == 2 and p.size() % 8 == 0 and p.size() >= 128 * 128
+            if wants_parts and getattr(p, "_pair16", None) is None:
+                p._pair16 = alloc(p.size())
+            if not wants_parts:
+                p._pair16 = None
+            p._parts_ptr = None      # the parts are stale until the callback has rewritten them
+            p._pending = self._completion(p, work, wants_parts)
+        self._ready = {}
+        self.small = []
+        self.t += 1.0
+
+    @staticmethod
+    def _completion(p, work, wants_parts):
+        def done():
+            from . import _lib
+            from ._array import stream
+            work.wait()              # the compute stream waits for this parameter's gather
+            if wants_parts:
+                _lib.call("endia_b200_bf16_split", p.buf.data_ptr(), p._pair16.data_ptr(), p.size(), stream())
+                p._parts_ptr = p.buf.data_ptr()
+        return done
+
+
+def data_parallel_adam(params, lr=0.001, beta1=0.9, beta2=0.999, eps=1e-8, group=None, mode=None):
+    """Optimizer and gradient exchange for a batch-sharded training step: (optimizer, reducer). The
+    step calls reducer.wait() after backward() and optimizer.step() after that. Modes
+    (ENDIA_B200_DP_MODE overrides): "sharded" (default: ShardedAdam, reduce-scatter + 1/P update +
+    all-gather) or one of GradAllReducer's replicated modes "overlap", "bucket", "serial"."""
+    from .optim import Adam
+    if mode is None:
+        mode = os.environ.get("ENDIA_B200_DP_MODE", "sharded")
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    if mode == "sharded":
+        opt = ShardedAdam(params, lr, beta1, beta2, eps, group)
+        return opt, opt
+    opt = Adam(params, lr=lr, beta1=beta1, beta2=beta2, eps=eps)
+    opt.grad_scale = 1.0 / world     # global-mean loss = mean of the ranks' local means
+    return opt, GradAllReducer(params, group, mode=mode)
+
+
 # ---------------------------------------------------------------------------------------------
 # Slab-decomposed N-D FFT: the array is split along axis 0 over the ranks; the transform over the
 # trailing axes is local, one all-to-all re-splits the array along axis 1 so that axis 0 becomes
@@ -216,52 +441,130 @@ class PeerBuffers:
     """One device buffer per rank, mapped into every rank of the machine through CUDA IPC, plus
     the stream-ordered barrier that orders the ranks' accesses (a one-element NCCL all-reduce:
     when it completes on a rank, every rank has reached that point of its stream). A rank writes
-    into the others' buffers with endia_b200_copy_strided (plain stores over NVLink)."""
+    into the others' buffers with endia_b200_copy_strided (plain stores over NVLink).
+
+    Creation is collective and every step of it ends in an agreement (an all-reduce of a success
+    flag that every rank reaches whether its own step worked or not), so a failure on one rank -
+    an allocation that does not fit, a peer that cannot be mapped - makes ALL ranks release what
+    they hold and use the NCCL all-to-all instead; no rank is left inside a collective alone."""
 
     _cache = {}
+
+    # the four device primitives (class attributes so that a host-side test can stand in for them)
+    @staticmethod
+    def _ipc_alloc(nbytes):
+        import ctypes as C
+        from . import _lib
+        local, handle = C.c_void_p(), (C.c_ubyte * 64)()
+        _lib.call("endia_b200_ipc_alloc", int(nbytes), C.byref(local), handle)
+        return local.value, bytes(handle)
+
+    @staticmethod
+    def _ipc_open(handle):
+        import ctypes as C
+        from . import _lib
+        p = C.c_void_p()
+        _lib.call("endia_b200_ipc_open", (C.c_ubyte * 64).from_buffer_copy(handle), C.byref(p))
+        return p.value
+
+    @staticmethod
+    def _ipc_close(ptr):
+        from . import _lib
+        _lib.call("endia_b200_ipc_close", ptr)
+
+    @staticmethod
+    def _ipc_free(ptr):
+        from . import _lib
+        _lib.call("endia_b200_ipc_free", ptr)
+
+    @staticmethod
+    def _flag_device(group):
+        return device() if dist.get_backend(group) == "nccl" else torch.device("cpu")
+
+    @classmethod
+    def _agree(cls, ok, group):
+        """True when `ok` holds on every rank (a collective: every rank must call it)."""
+        flag = torch.tensor([1.0 if ok else 0.0], device=cls._flag_device(group))
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=group)
+        return float(flag.item()) > 0.0
 
     @classmethod
     def get(cls, nbytes, group=None):
         """Buffers of at least nbytes, created collectively on first use and reused; None when the
-        ranks cannot map each other's memory (the exchange then goes through NCCL)."""
+        ranks cannot map each other's memory (the exchange then goes through NCCL). Every rank of
+        the group must call this with the same nbytes."""
         key = id(group)
         cur = cls._cache.get(key)
         if cur is not None and (cur is False or cur.nbytes >= nbytes):
             return cur or None
-        try:
-            made = cls(nbytes, group)
-        except Exception as exc:   # e.g. no peer access between the devices
-            if os.environ.get("ENDIA_B200_DEBUG"):
-                print("endia_b200: peer buffers unavailable (%s); using NCCL all-to-all" % exc)
-            made = False
-        # every rank must take the same path
-        flag = torch.tensor([1.0 if made else 0.0], device=device())
-        dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=group)
-        if float(flag.item()) == 0.0:
-            made = False
-        cls._cache[key] = made
-        return made or None
+        if cur:
+            cur.close()          # replaced by larger buffers (all ranks take this branch together)
+        made = cls._create(int(nbytes), group)
+        cls._cache[key] = made if made is not None else False
+        return made
 
-    def __init__(self, nbytes, group=None):
-        import ctypes as C
-        from . import _lib
-        self.nbytes, self.group = int(nbytes), group
-        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
-        local = C.c_void_p()
-        handle = (C.c_ubyte * 64)()
-        _lib.call("endia_b200_ipc_alloc", self.nbytes, C.byref(local), handle)
-        handles = [None] * self.world
-        dist.all_gather_object(handles, bytes(handle), group=group)
+    @classmethod
+    def release(cls, group=None):
+        """Unmap and free the group's buffers (collective); the next get() creates new ones."""
+        cur = cls._cache.pop(id(group), None)
+        if cur:
+            cur.close()
+
+    @classmethod
+    def _create(cls, nbytes, group):
+        debug = os.environ.get("ENDIA_B200_DEBUG")
+        rank, world = dist.get_rank(group), dist.get_world_size(group)
+        local, handle, why = None, b"", None
+        try:
+            local, handle = cls._ipc_alloc(nbytes)
+        except Exception as exc:          # e.g. the buffer does not fit on this rank's device
+            why = exc
+        if not cls._agree(local is not None, group):
+            if local is not None:
+                cls._ipc_free(local)
+            if debug:
+                print("endia_b200: peer buffers unavailable (allocation: %s); using NCCL all-to-all" % (why,))
+            return None
+        handles = [None] * world
+        dist.all_gather_object(handles, handle, group=group)
+        ptrs, opened = [None] * world, []
+        try:
+            for r, h in enumerate(handles):
+                if r == rank:
+                    ptrs[r] = local
+                else:
+                    ptrs[r] = cls._ipc_open(h)
+                    opened.append(ptrs[r])
+        except Exception as exc:          # e.g. no peer access between the devices
+            why = exc
+        if not cls._agree(why is None, group):
+            for p in opened:
+                cls._ipc_close(p)
+            dist.barrier(group=group)     # every rank has unmapped before any rank frees
+            cls._ipc_free(local)
+            if debug:
+                print("endia_b200: peer buffers unavailable (mapping: %s); using NCCL all-to-all" % (why,))
+            return None
+        self = cls.__new__(cls)
+        self.nbytes, self.group, self.rank, self.world = nbytes, group, rank, world
+        self.ptrs = ptrs
+        self._flag = torch.zeros(1, device=cls._flag_device(group))
+        self.closed = False
+        return self
+
+    def close(self):
+        """Collective: unmap the peers' buffers, wait until every rank has, free the own buffer."""
+        if self.closed:
+            return
+        self.closed = True
+        if torch.cuda.is_available():
+            torch.cuda.synchronize()
+        for r, p in enumerate(self.ptrs):
+            if r != self.rank:
+                self._ipc_close(p)
+        dist.barrier(group=self.group)
+        self._ipc_free(self.ptrs[self.rank])
         self.ptrs = []
-        for r, h in enumerate(handles):
-            if r == self.rank:
-                self.ptrs.append(local.value)
-            else:
-                p = C.c_void_p()
-                hb = (C.c_ubyte * 64).from_buffer_copy(h)
-                _lib.call("endia_b200_ipc_open", hb, C.byref(p))
-                self.ptrs.append(p.value)
-        self._flag = torch.zeros(1, device=device())
 
     def barrier(self):
         dist.all_reduce(self._flag, group=self.group)

@@ -15,6 +15,15 @@ class Adam:
         self.v = [Array(p.shape()) for p in self.params]
         self.grad_scale = 1.0  # folded into the gradient read (1/world_size under data parallelism)
 
+    def reset_state(self):
+        """Zero moments with the parameters' shapes and t = 1, as after construction."""
+        self.t = 1.0
+        for i, p in enumerate(self.params):
+            for st in (self.m[i], self.v[i]):
+                st.array_shape_ = ArrayShape(p.shape())
+                if st.size():
+                    _lib.call("endia_b200_memset0", st.data_ptr(), st.size() * 4, stream())
+
     def step(self):
         n = len(self.params)
         grads = []

@@ -1,12 +1,12 @@
 """Single-kernel cases through the C ABI, timed with CUDA events: the unit for micro-benchmarks and
 for profiler captures (one kernel, a few launches, a few hundred MB on the device).
 
-  python -m endia_b200.kernel_cases gemm --m 4096 --n 4096 --k 4096 --ta 0 --tb 0 --algo auto
-  python -m endia_b200.kernel_cases fft --batch 32 --n 1048576
-  python -m endia_b200.kernel_cases fftn --shape 256,256,256
-  python -m endia_b200.kernel_cases ew --rows 8192 --cols 4096
-  python -m endia_b200.kernel_cases adam --numel 41956352
-  python -m endia_b200.kernel_cases actbwd --rows 8192 --cols 4096
+  python kernel_bench.py gemm --m 4096 --n 4096 --k 4096 --ta 0 --tb 0 --algo auto
+  python kernel_bench.py fft --batch 32 --n 1048576
+  python kernel_bench.py fftn --shape 256,256,256
+  python kernel_bench.py ew --rows 8192 --cols 4096
+  python kernel_bench.py adam --numel 41956352
+  python kernel_bench.py actbwd --rows 8192 --cols 4096
 
 Each case prints one JSON line: average milliseconds per call over --reps calls after --warmup,
 and the achieved rate on the algorithmic bytes or flops of the call.
@@ -14,13 +14,16 @@ and the achieved rate on the algorithmic bytes or flops of the call.
 import argparse
 import ctypes as C
 import json
+import os
+import sys
 
 import numpy as np
 import torch
 
-import endia_b200 as nd
-from endia_b200 import _lib
-from endia_b200._array import alloc, stream
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+import endia_b200 as nd  # noqa: E402
+from endia_b200 import _lib  # noqa: E402
+from endia_b200._array import alloc, stream  # noqa: E402
 
 
 def _time(fn, warmup, reps, flush=None):

@@ -30,11 +30,13 @@ _LIB = os.path.join(_HERE, "_build", "liboracle.so")
 
 config = {
     "mode": "faithful",       # "faithful": reference loop order, fp32, 1 thread. "fast": f64 accumulation, all cores
+                              # (large products through numpy's float64 BLAS); checked against faithful mode
     "nelts": 16,              # SIMD width of the matmul/reduce partial sums: simdwidthof[float32]*2 on AVX2
                               # (endia/utils/aliases.mojo:20-21)
     "square_T_quirk": False,  # True reproduces matmul_fwd's handling of a transposed view of a SQUARE
                               # matrix (matmul_op.mojo:111-129): `g @ W.T()` is then evaluated as `g @ W`
     "fft_threads": 1,
+    "blas_min_flops": 2.0e9,  # fast mode: products of at least this many flops go through numpy's float64 BLAS
 }
 
 
@@ -549,7 +551,12 @@ def matmul(a, b):  # matmul_op.mojo:36-90 (shape), 93-254 (fwd), 257-284 (vjp)
         if cplx:
             lib().oracle_matmul_c64(_ptr(xb[i]), _ptr(bb[i]), _ptr(ob[i]), M, N, K, config["nelts"])
         elif config["mode"] == "fast":
-            lib().oracle_matmul_fast(_ptr(xb[i]), _ptr(bb[i]), _ptr(ob[i]), M, N, K)
+            if 2.0 * M * N * K >= config["blas_min_flops"]:
+                # the same product, float64 throughout, through numpy's BLAS: what makes the
+                # full-size configurations checkable in seconds
+                ob[i][...] = np.matmul(xb[i].astype(np.float64), bb[i].astype(np.float64).T).astype(np.float32)
+            else:
+                lib().oracle_matmul_fast(_ptr(xb[i]), _ptr(bb[i]), _ptr(ob[i]), M, N, K)
         else:
             lib().oracle_matmul_f32(_ptr(xb[i]), _ptr(bb[i]), _ptr(ob[i]), M, N, K, config["nelts"])
 

@@ -118,3 +118,121 @@ def test_gradient_allreducer_two_ranks_gloo():
         ret = m.dict()
         mp.spawn(_reduce_worker, args=(world, port, ret), nprocs=world, join=True)
         assert dict(ret) == {0: True, 1: True}
+
+
+def _peer_worker(rank, world, port, fail, ret):
+    """Host-injected failures of the peer-buffer set-up: the four device primitives are stood in
+    by fakes that record their calls; `fail` names the step that fails and on which rank."""
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from endia_b200 import dist as ndist
+        calls = []
+        PB = ndist.PeerBuffers
+        PB._cache.clear()
+
+        def alloc(nbytes):
+            if fail == ("alloc", rank):
+                raise MemoryError("injected: the buffer does not fit")
+            calls.append("alloc")
+            return 1000 + rank, bytes([rank]) * 64
+
+        def open_(handle):
+            if fail == ("open", rank):
+                raise RuntimeError("injected: no peer access")
+            calls.append("open%d" % handle[0])
+            return 2000 + handle[0]
+        PB._ipc_alloc = staticmethod(alloc)
+        PB._ipc_open = staticmethod(open_)
+        PB._ipc_close = staticmethod(lambda p: calls.append("close%d" % p))
+        PB._ipc_free = staticmethod(lambda p: calls.append("free%d" % p))
+        got = PB.get(4096)
+        again = PB.get(4096)            # the outcome is remembered: no second collective attempt
+        state = "none" if got is None else "ok"
+        if got is not None:
+            assert again is got and got.ptrs[rank] == 1000 + rank and got.ptrs[1 - rank] == 2000 + (1 - rank)
+            bigger = PB.get(8192)       # replaced collectively: the old ones are unmapped and freed
+            assert bigger is not got and got.closed and bigger.nbytes == 8192
+            PB.release()
+            assert bigger.closed and PB._cache == {}
+        ret[rank] = (state, again is None if got is None else True, list(calls))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("fail", [None, ("alloc", 1), ("open", 0)])
+def test_peer_buffers_all_ranks_agree_on_failure(fail):
+    """One rank's allocation or mapping fails (injected on the host): every rank must end up on the
+    fallback path, having released what it held, with no rank left inside a collective."""
+    world = 2
+    port = _free_port()
+    with mp.Manager() as m:
+        ret = m.dict()
+        mp.spawn(_peer_worker, args=(world, port, fail, ret), nprocs=world, join=True)
+        out = dict(ret)
+    if fail is None:
+        for r in range(2):
+            state, same, calls = out[r]
+            assert state == "ok" and same
+            assert calls == ["alloc", "open%d" % (1 - r), "close%d" % (2001 - r), "free%d" % (1000 + r),
+                             "alloc", "open%d" % (1 - r), "close%d" % (2001 - r), "free%d" % (1000 + r)]
+        return
+    assert out[0][0] == out[1][0] == "none" and out[0][1] and out[1][1]
+    if fail[0] == "alloc":
+        assert out[0][2] == ["alloc", "free1000"] and out[1][2] == []        # the healthy rank frees its buffer
+    else:
+        assert out[0][2] == ["alloc", "free1000"]                           # rank 0 mapped nothing
+        assert out[1][2] == ["alloc", "open0", "close2000", "free1001"]     # rank 1 unmaps, then frees
+
+
+class _FakeArray(_FakeGrad):
+    """A parameter as ShardedAdam's host logic sees it."""
+
+    def __init__(self, t):
+        super().__init__(t)
+        self.grad_hook = None
+        self.g = None
+
+    def shape(self):
+        return list(self.buf.shape)
+
+    def grad_(self, g):
+        self.g = g
+
+
+def _sharded_worker(rank, world, port, ret):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from endia_b200 import dist as ndist
+        big, small = 1 << 16, 300
+        params = [_FakeArray(torch.zeros(big)), _FakeArray(torch.zeros(small)), _FakeArray(torch.zeros(2 * big))]
+        opt = ndist.ShardedAdam(params)
+        assert opt.sharded == [True, False, True] and opt.grad_scale == 1.0 / world
+        assert [None if g is None else g.numel() for g in opt.g_slice] == [big // world, None, 2 * big // world]
+        grads = [_FakeGrad(torch.arange(p.size(), dtype=torch.float32) * (rank + 1)) for p in params]
+        for p, g in reversed(list(zip(params, grads))):     # the backward walk: last layer first
+            p.grad_hook(p, g)
+        assert len(opt.pending) == 2 and [i for i, _ in opt.small] == [1]
+        for w in opt.pending:
+            w.wait()
+        scale = sum(r + 1 for r in range(world))
+        ok = True
+        for i in (0, 2):
+            k = params[i].size() // world
+            want = torch.arange(params[i].size(), dtype=torch.float32)[k * rank:k * (rank + 1)] * scale
+            ok = ok and torch.equal(opt.g_slice[i], want)
+        ret[rank] = bool(ok)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_sharded_adam_reduce_scatter_two_ranks_gloo():
+    """Host logic of the sharded optimizer: which tensors are sharded, and that the hook's
+    reduce-scatter leaves rank r with the r-th slice of the summed gradient."""
+    world = 2
+    port = _free_port()
+    with mp.Manager() as m:
+        ret = m.dict()
+        mp.spawn(_sharded_worker, args=(world, port, ret), nprocs=world, join=True)
+        assert dict(ret) == {0: True, 1: True}

@@ -136,6 +136,75 @@ def test_data_parallel_step_matches_single_gpu(nd, oracle, tmp_path, mode):
             assert np.abs(a - p_ref).max() <= 2.5e-3
 
 
+_SHARDED_WORKER = r'''
+import os, sys, numpy as np, torch
+sys.path.insert(0, %(root)r)
+sys.path.insert(0, os.path.join(%(root)r, "tests"))
+import endia_b200 as nd
+from endia_b200 import dist as ndist
+from test_gpu_mlp import make_mlp_inputs
+rank, world = ndist.init_process_group()
+nd._array.device()
+dims, batch = [64, 512, 512, 32], 512
+Ws, bs, x, y = make_mlp_inputs(dims, batch, 0)
+lo, hi = rank * batch // world, (rank + 1) * batch // world
+W = [nd.Array(w.copy(), requires_grad=True) for w in Ws]
+B = [nd.Array(b.copy(), requires_grad=True) for b in bs]
+params = [p for wb in zip(W, B) for p in wb]
+opt, red = ndist.data_parallel_adam(params, lr=1e-3, mode="sharded")
+assert opt.sharded == [False, False, True, False, False, False], opt.sharded
+X, Y = nd.Array(x[lo:hi]), nd.Array(y[lo:hi])
+losses = []
+for step in range(3):
+    loss = nd.mse(nd.nn.mlp([X, None] + params, activation="tanh"), Y)
+    loss.backward()
+    red.wait()
+    opt.step()
+    loss.zero_grad()
+    losses.append(float(loss.to_numpy()[0]))
+assert opt.m[2].shape() == [512 * 512 // world] and opt.m[3].shape() == [1, 512]
+np.savez(os.path.join(%(out)r, "rank%%d.npz" %% rank), *([p.to_numpy() for p in params] + [np.array(losses)]))
+torch.distributed.destroy_process_group()
+'''
+
+
+def test_sharded_adam_matches_single_gpu(nd, oracle, tmp_path):
+    """Two ranks, each on half of the batch, three steps with the sharded optimizer (reduce-scatter
+    of the large gradients, 1/P Adam update, all-gather of the updated slices consumed layer by
+    layer by the next forward pass): parameters and the mean of the ranks' losses must equal the
+    single-process result (oracle)."""
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    from test_gpu_mlp import make_mlp_inputs, train_step, fwd_unfused
+    script = tmp_path / "sharded_worker.py"
+    script.write_text(_SHARDED_WORKER % {"root": ROOT, "out": str(tmp_path)})
+    s = socket.socket(); s.bind(("127.0.0.1", 0)); port = s.getsockname()[1]; s.close()
+    out = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
+                          "--master-addr", "127.0.0.1", "--master-port", str(port), str(script)],
+                         capture_output=True, text=True, timeout=300, env=dict(os.environ, NCCL_NVLS_ENABLE="0"))
+    assert out.returncode == 0, out.stdout + out.stderr
+    Ws, bs, x, y = make_mlp_inputs([64, 512, 512, 32], 512, 0)
+    oracle.config["mode"] = "fast"
+    try:
+        ref = train_step(oracle, fwd_unfused("tanh"), Ws, bs, x, y, steps=3)
+    finally:
+        oracle.config["mode"] = "faithful"
+    n = len(ref["params"])
+    got = [np.load(tmp_path / ("rank%d.npz" % rank)) for rank in range(2)]
+    mean_loss = 0.5 * (got[0]["arr_%d" % n][-1] + got[1]["arr_%d" % n][-1])
+    assert abs(mean_loss - ref["loss"][0]) <= 1e-4 * abs(ref["loss"][0])
+    for i in range(n):
+        p_ref = ref["params"][i]
+        a0, a1 = got[0]["arr_%d" % i], got[1]["arr_%d" % i]
+        assert np.array_equal(a0, a1)                  # every rank holds the same gathered weights
+        # Adam's first steps move a weight by about lr whatever the gradient's size, so an entry whose
+        # gradient changes sign within rounding differs by up to the step length
+        assert np.abs(a0 - p_ref).max() <= 3 * 2.5e-3
+        close = np.abs(a0 - p_ref) <= 1e-4 * np.maximum(np.abs(p_ref), np.sqrt(np.mean(p_ref ** 2)))
+        assert close.mean() > 0.999, (i, close.mean())
+
+
 _ABI_COMM_WORKER = r'''
 import os, sys, ctypes as C, numpy as np
 sys.path.insert(0, %(root)r)
@@ -216,3 +285,32 @@ def test_c_abi_collectives_single_rank(nd):
     assert np.array_equal(Y.to_numpy(), x) and np.array_equal(Z.to_numpy(), x)
     assert _lib.lib.endia_b200_allreduce_sum_f32(None, X.data_ptr(), Y.data_ptr(), 5000, stream()) == _lib.EINVAL
     _lib.call("endia_b200_comm_destroy", comm)
+
+
+def test_sharded_adam_single_rank_equals_adam(nd):
+    """Without a process group ShardedAdam has nothing to shard: three steps must give optim.Adam's
+    parameters and moments bit for bit (same kernel, same state shapes)."""
+    from endia_b200.dist import data_parallel_adam
+    from test_gpu_mlp import make_mlp_inputs
+    Ws, bs, x, y = make_mlp_inputs([32, 300, 8], 64, 3)
+
+    def run(make_opt):
+        W = [nd.Array(w.copy(), requires_grad=True) for w in Ws]
+        B = [nd.Array(b.copy(), requires_grad=True) for b in bs]
+        params = [p for wb in zip(W, B) for p in wb]
+        opt, red = make_opt(params)
+        X, Y = nd.Array(x), nd.Array(y)
+        for _ in range(3):
+            loss = nd.mse(nd.nn.mlp([X, None] + params, activation="relu"), Y)
+            loss.backward()
+            if red is not None:
+                red.wait()
+            opt.step()
+            loss.zero_grad()
+        return [p.to_numpy() for p in params], [m.to_numpy() for m in opt.m], [m.shape() for m in opt.m], opt.t
+
+    a = run(lambda params: data_parallel_adam(params, lr=1e-3, mode="sharded"))
+    b = run(lambda params: (nd.optim.Adam(params, lr=1e-3), None))
+    assert a[2] == b[2] and a[3] == b[3] == 4.0
+    for u, v in zip(a[0] + a[1], b[0] + b[1]):
+        assert np.array_equal(u, v)

@@ -117,8 +117,8 @@ def test_c4_full_size_identities(nd):
 
 
 def test_c5_full_size_identities(nd):
-    """c5 at full size (512^3): gradient identity d/dx sum(real(fftn(x)) w) = N ifftn(w) on sampled
-    lines, the inverse round trip, and linearity of the transform."""
+    """c5 at full size (512^3), forward only: the inverse round trip, one output line against a
+    float64 evaluation and the DC term (the VJP at this size: test_gpu_full_size.py)."""
     r = rng(0)
     shape = (512, 512, 512)
     z = crandn(r, shape)

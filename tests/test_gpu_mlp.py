@@ -1,13 +1,15 @@
 """GPU parity of the training-step path (MLP forward, backward, Adam; second order with
 create_graph) against the CPU oracle: config c1 at full size, c2 and c3 at reduced sizes with the
-oracle and at full size through size-independent identities."""
+oracle and at full size through size-independent identities (the full-size steps against the
+oracle: test_gpu_full_size.py)."""
 import numpy as np
 import pytest
 
 from conftest import rng, max_rel
 
 pytestmark = pytest.mark.gpu
-TOL = 1e-4  # max relative error on gradients and updated weights (fp32; GEMMs are 3xTF32 or FFMA)
+TOL = 1e-4  # max relative error on gradients and updated weights (fp32; GEMMs run the default tensor-core
+            # scheme, one tf32 MMA + two bf16 correction MMAs per product, 3xTF32 for N < 256, or FFMA)
 
 
 def make_mlp_inputs(dims, batch, seed, bias_zero=False, x_dist="normal", out_dim=None):
@@ -420,3 +422,39 @@ def test_captured_step_replays_double_backward(nd):
     loss_e2, grads_e2 = step()
     for a, b in zip(got2, [loss_e2.to_numpy()] + [g.to_numpy() for g in grads_e2]):
         assert np.array_equal(a, b)
+
+
+def test_fused_mse_forward_and_vjps(nd, oracle):
+    """mse as one fused kernel (loss_ops/mse_op.mojo:18-20): seeded directly, scaled by a later
+    op (the VJP then multiplies by the incoming gradient), with a target that needs a gradient,
+    through a transposed (non-contiguous) prediction (op composition), and under create_graph."""
+    r = rng(41)
+    p = r.standard_normal((37, 21)).astype(np.float32)
+    t = r.standard_normal((37, 21)).astype(np.float32)
+
+    def run(L, scale, tgrad, transposed, second):
+        P = L.Array(p.T.copy() if transposed else p, requires_grad=True)
+        T = L.Array(t, requires_grad=tgrad)
+        loss = L.mse(P.T() if transposed else P, T)
+        if scale:
+            loss = loss * 3.0
+        if second:
+            g = L.grad(outs=[loss], inputs=[P], create_graph=True)[0]
+            loss2 = L.sum(g * g)
+            g2 = L.grad(outs=[loss2], inputs=[P])[0]
+            return [loss.to_numpy(), g.to_numpy(), g2.to_numpy()]
+        loss.backward()
+        out = [loss.to_numpy(), P.grad().to_numpy()]
+        if tgrad:
+            out.append(T.grad().to_numpy())
+        return out
+
+    for case in [(False, False, False, False), (True, False, False, False), (True, True, False, False),
+                 (False, False, True, False), (True, False, False, True)]:
+        got, ref = run(nd, *case), run(oracle, *case)
+        for a, b in zip(got, ref):
+            assert a.shape == b.shape and max_rel(a, b) < 1e-5, case
+    launches0 = nd._lib.lib.endia_b200_launch_count()
+    P, T = nd.Array(p, requires_grad=True), nd.Array(t)
+    nd.mse(P, T).backward()
+    assert nd._lib.lib.endia_b200_launch_count() - launches0 <= 4   # fill of the seed, two mse kernels

@@ -71,6 +71,32 @@ def test_matmul_fwd_and_grad_vs_torch(oracle, mode):
     assert mean_rel(B.grad().v[0], tb.grad.numpy(), 1e-6) < 1e-4
 
 
+def test_fast_mode_engines_agree_with_faithful(oracle):
+    """Fast mode (what checks the full-size configurations) computes the same product as the
+    reference's loop: its C loop with float64 sums and, above config["blas_min_flops"], numpy's float64
+    BLAS product both agree with the faithful float32 loop to float32 rounding of the terms."""
+    eo = oracle
+    r = rng(7)
+    a = r.standard_normal((96, 200)).astype(np.float32)
+    b = r.standard_normal((200, 64)).astype(np.float32)
+    faithful = eo.matmul(eo.Array(a), eo.Array(b)).v
+    old = eo.config["blas_min_flops"]
+    try:
+        eo.config["mode"] = "fast"
+        c_loop = eo.matmul(eo.Array(a), eo.Array(b)).v
+        eo.config["blas_min_flops"] = 0.0
+        blas = eo.matmul(eo.Array(a), eo.Array(b)).v
+        blas_t = eo.matmul(eo.Array(a), eo.Array(np.ascontiguousarray(b.T)).T()).v
+    finally:
+        eo.config["mode"] = "faithful"
+        eo.config["blas_min_flops"] = old
+    exact = a.astype(np.float64) @ b.astype(np.float64)
+    scale = np.abs(a).astype(np.float64) @ np.abs(b).astype(np.float64)
+    assert np.array_equal(c_loop, exact.astype(np.float32)) or (np.abs(c_loop - exact) / scale).max() < 1e-7
+    assert (np.abs(blas - exact) / scale).max() < 1e-7 and np.array_equal(blas, blas_t)
+    assert (np.abs(faithful - exact) / scale).max() < 2e-6
+
+
 def test_square_weight_quirk_switch(oracle):
     eo = oracle
     r = rng(2)
