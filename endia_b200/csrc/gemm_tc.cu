@@ -466,10 +466,14 @@ template <int BN>
 __device__ __forceinline__ void tc_epilogue_warp_bulk(uint32_t tmem_base, int q, int lane, int c_begin, int c_end,
                                                       int64_t m0, int64_t n0, int64_t M, int64_t N, const float *Cout,
                                                       int64_t ldc, const EpiParams &epi, const CUtensorMap *cmap,
-                                                      uint32_t buf, bool reduce) {
+                                                      uint32_t buf, bool reduce, bool raw = false,
+                                                      bool pre_add = false) {
+  // raw: this is a partial run of a reduction whose epilogue is not linear: the bare sums are
+  // stored (or added); pre_add: the last run of such a reduction, which adds what the earlier runs
+  // left in C before it applies the epilogue.
   const uint32_t row_addr = tmem_base + ((uint32_t)(q * 32) << 16);
-  const bool plain = epi.alpha == 1.f && !epi.bias && !epi.act && !epi.dact && epi.beta == 0.f &&
-                     !epi.colsum_partial;
+  const bool plain = raw || (epi.alpha == 1.f && !epi.bias && !epi.act && !epi.dact && epi.beta == 0.f &&
+                             !epi.colsum_partial && !pre_add);
   const bool vec_epi = (!epi.bias || (reinterpret_cast<uintptr_t>(epi.bias) & 15) == 0) &&
                        (!epi.dact || ((reinterpret_cast<uintptr_t>(epi.dact_src) & 15) == 0 && epi.ld_dact % 4 == 0));
   uint32_t ra[32], rb[32];
@@ -509,12 +513,16 @@ __device__ __forceinline__ void tc_epilogue_warp_bulk(uint32_t tmem_base, int q,
         float4 v = lds128(a);
         const float *cp = Cout + m * ldc + n;
         if (n + 4 <= N) {
+          if (pre_add) {
+            const float4 c = __ldcg(reinterpret_cast<const float4 *>(cp));
+            v.x += c.x; v.y += c.y; v.z += c.z; v.w += c.w;
+          }
           v = apply_epilogue4(epi, v, m, n, cp, vec_epi);
         } else {
           float e[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
           for (int t = 0; t < 4; ++t)
-            e[t] = (n + t < N) ? apply_epilogue(epi, e[t], m, n + t, cp + t) : 0.f;
+            e[t] = (n + t < N) ? apply_epilogue(epi, e[t] + (pre_add ? __ldcg(cp + t) : 0.f), m, n + t, cp + t) : 0.f;
           v = make_float4(e[0], e[1], e[2], e[3]);
         }
         cs.x += v.x; cs.y += v.y; cs.z += v.z; cs.w += v.w;
@@ -578,7 +586,7 @@ __device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity,
 template <bool A_MN, bool B_MN, int SCHEME>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(320, 1)
 gemm_tc2p_kernel(const __grid_constant__ TcMaps maps, const GemmParams p, int pairs_m, int tiles_n, int group_m,
-                 int ksplit, int kseq) {
+                 int ksplit, int kseq, int kseq_raw) {
   constexpr int BN = 256, BNH = 128, BK = 32, STAGES = 3, EPI_WARPS = 8;
   extern __shared__ __align__(1024) uint8_t smem[];
   constexpr uint32_t A_BYTES = TC_BM * BK * 4;
@@ -719,9 +727,11 @@ gemm_tc2p_kernel(const __grid_constant__ TcMaps maps, const GemmParams p, int pa
       uint32_t it = 0;
       int j = 0;
       bool ok = true;
-      // kseq > 1: a long reduction is cut into kseq runs; the accumulators are drained after each
+      // kseq > 1: the reduction is cut into kseq runs; the accumulators are drained after each
       // (the first run stores, the later ones add to C), which bounds the round-toward-zero bias
-      // of the accumulator adds by the length of one run.
+      // of the accumulator adds by the length of one run. With an epilogue that is not linear in
+      // the accumulator (kseq_raw) the earlier runs leave bare sums in C and the last run adds
+      // them to its own before the epilogue.
       for (int t = pair_id; t < num_tiles && ok; t += num_pairs) {
         int kb0, nkb;
         k_range(t, kb0, nkb);
@@ -790,9 +800,12 @@ gemm_tc2p_kernel(const __grid_constant__ TcMaps maps, const GemmParams p, int pa
         __syncwarp();
       }
       constexpr int CH = BN / 64;
+      const bool last_run = run == kseq - 1;
+      const bool raw = kseq_raw && !last_run, pre_add = kseq_raw && last_run && kseq > 1;
+      const bool reduce = kseq_raw ? (run > 0 && !last_run) : (ksplit > 1 || run > 0);
       if (p.vec_c)
         tc_epilogue_warp_bulk<BN>(tmem_base, q, lane, half * CH, (half + 1) * CH, m0, n0, p.M, p.N, p.C, p.ldc,
-                                  p.epi, &maps.c, epi_base + (uint32_t)(warp - 2) * 4096u, ksplit > 1 || run > 0);
+                                  p.epi, &maps.c, epi_base + (uint32_t)(warp - 2) * 4096u, reduce, raw, pre_add);
       else
         tc_epilogue_warp<BN, false>(tmem_base, q, lane, half * CH, (half + 1) * CH, m0, n0, p.M, p.N, p.C, p.ldc,
                                     p.epi, p.vec_c, epi_base + (uint32_t)(warp - 2) * 4096u);
@@ -970,9 +983,10 @@ bool tc_gemm_supported(const GemmParams &p, int trans_a, int trans_b, int64_t ba
   // The tensor-core accumulator rounds toward zero on every add, a bias that grows linearly
   // with K (measured: -1.7e-5 of the result at K = 8192, -6.7e-5 at K = 32768). Longer
   // reductions stay on the FFMA kernel unless the caller asks for this one by name.
-  // Linear epilogues on the two-CTA kernel are exempt: it drains the accumulators every 8192.
-  const bool runs_ok = p.N >= 256 && p.vec_c && !p.epi.bias && !p.epi.act && !p.epi.dact && p.epi.beta == 0.f &&
-                       !p.epi.colsum_partial;
+  // The two-CTA kernel is exempt where it can cut the reduction into short runs (see
+  // launch_gemm_tc): a linear epilogue, or any epilogue with beta == 0.
+  const bool linear = !p.epi.bias && !p.epi.act && !p.epi.dact && p.epi.beta == 0.f && !p.epi.colsum_partial;
+  const bool runs_ok = p.N >= 256 && p.vec_c && (linear || p.epi.beta == 0.f);
   if (p.K > 8192 && !explicit_request && !runs_ok) return false;
   if (!encode_fn()) return false;
   if (p.M < 128 || p.N < 128 || p.K < 32) return false;      // small products stay on the FFMA kernel
@@ -1019,7 +1033,7 @@ static bool ksplit_mode() {
 // Persistent two-CTA kernel: as many CTA pairs as can be resident, each walking over its tiles.
 template <int SCHEME>
 static int launch_pair_persistent(const TcMaps &maps, const GemmParams &p, int trans_a, int trans_b,
-                                  cudaStream_t s, int ksplit_max, int kseq) {
+                                  cudaStream_t s, int ksplit_max, int run_k, int kseq_raw) {
   constexpr size_t SMEM = (size_t)3 * (2 * TC_BM * 32 * 4 + 2 * 128 * 32 * 4) + 8 * 4096 + 1024 + 256;
   const int pairs_m = (int)ceil_div(p.M, 256), tiles_n = (int)ceil_div(p.N, 256);
   static const int group_env = []() { const char *e = getenv("ENDIA_B200_TC_GROUP_M"); return e ? atoi(e) : TC_GROUP_M; }();
@@ -1055,7 +1069,7 @@ static int launch_pair_persistent(const TcMaps &maps, const GemmParams &p, int t
     }                                                                                             \
     const int tiles = pairs_m * tiles_n;                                                          \
     int ksplit = 1;                                                                               \
-    if (ksplit_max >= 2 && kseq == 1 && tiles > max_pairs) {                                                   \
+    if (ksplit_max >= 2 && tiles > max_pairs) {                                                   \
       /* rounds of pairs with and without halving K, in units of half tiles */                    \
       const int r1 = 2 * ((tiles + max_pairs - 1) / max_pairs);                                   \
       const int r2 = (2 * tiles + max_pairs - 1) / max_pairs;                                     \
@@ -1067,7 +1081,10 @@ static int launch_pair_persistent(const TcMaps &maps, const GemmParams &p, int t
     }                                                                                             \
     const int items = tiles * ksplit;                                                             \
     const int pairs = items < max_pairs ? items : max_pairs;                                      \
-    kern<<<dim3((unsigned)(2 * pairs)), 320, SMEM, s>>>(maps, p, pairs_m, tiles_n, group_m, ksplit, kseq); \
+    /* runs of at most run_k along K per work item (run_k = 0: one run) */                        \
+    const int kseq = run_k > 0 ? (int)ceil_div(ceil_div(p.K, ksplit), run_k) : 1;                 \
+    kern<<<dim3((unsigned)(2 * pairs)), 320, SMEM, s>>>(maps, p, pairs_m, tiles_n, group_m, ksplit,  \
+                                                        kseq < 1 ? 1 : kseq, kseq > 1 ? kseq_raw : 0); \
   } while (0)
   if (trans_a && !trans_b) EB_TC2P_LAUNCH(true, true);
   else if (trans_a && trans_b) EB_TC2P_LAUNCH(true, false);
@@ -1189,10 +1206,17 @@ int launch_gemm_tc(const GemmParams &p, int trans_a, int trans_b, cudaStream_t s
   // reduction long enough for the second pass over C to be cheap.
   const bool linear_epi = !p.epi.bias && !p.epi.act && !p.epi.dact && p.epi.beta == 0.f && !p.epi.colsum_partial;
   const int ksplit_max = (p.vec_c && linear_epi && p.K >= 4096 && ksplit_mode()) ? 2 : 1;
-  // Reductions longer than 8192 run as ceil(K / 8192) runs whose sums are added in order.
-  const int kseq = (pair && p.vec_c && linear_epi && p.K > 8192) ? (int)ceil_div(p.K, 8192) : 1;
-  if (bf16c) st = launch_pair_persistent<1>(maps, p, trans_a, trans_b, s, ksplit_max, kseq);
-  else if (pair) st = launch_pair_persistent<0>(maps, p, trans_a, trans_b, s, ksplit_max, kseq);
+  // The tensor-core accumulator rounds toward zero, a bias that grows with the number of adds
+  // into one accumulator: the reduction runs as ceil(K / run_k) runs whose sums are added in
+  // order in fp32 (round to nearest). An epilogue that is linear in the accumulator is applied
+  // per run; any other (bias, activation, mask, column sums) needs beta == 0, because the runs
+  // before the last keep their bare sums in C.
+  static const int run_k_env = []() { const char *e = getenv("ENDIA_B200_TC_RUN_K"); return e ? atoi(e) : 2048; }();
+  const bool runs_ok = pair && p.vec_c && (linear_epi || p.epi.beta == 0.f);
+  const int run_k = runs_ok ? (run_k_env > 0 ? (run_k_env + 31) / 32 * 32 : 0) : 0;
+  const int kseq_raw = linear_epi ? 0 : 1;
+  if (bf16c) st = launch_pair_persistent<1>(maps, p, trans_a, trans_b, s, ksplit_max, run_k, kseq_raw);
+  else if (pair) st = launch_pair_persistent<0>(maps, p, trans_a, trans_b, s, ksplit_max, run_k, kseq_raw);
   else if (bn == 256 && bk == 16) st = launch_variant<256, 16, 4>(maps, p, trans_a, trans_b, s);
   else if (bn == 256) st = launch_variant<256, 32, 2>(maps, p, trans_a, trans_b, s);
   else if (bk == 16) st = launch_variant<128, 16, 6>(maps, q, trans_a, trans_b, s, splits);

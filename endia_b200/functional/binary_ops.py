@@ -157,8 +157,8 @@ def _tc_plan(M, N, K, nbatch, algo, linear=True):
     if nbatch != 1 or algo == _lib.GEMM_FFMA or M < 128 or N < 128 or K < 32:
         return None
     if K > 8192:
-        # longer reductions run on the two-CTA kernel in runs of 8192 when nothing but alpha is
-        # fused into the store; otherwise on the FFMA kernel (unless the algorithm is named)
+        # longer reductions run on the two-CTA kernel, which cuts them into short runs, unless the
+        # epilogue accumulates into C (beta); otherwise on the FFMA kernel (unless the algorithm is named)
         if N >= 256 and linear:
             return "lo32" if algo == _lib.GEMM_3XTF32 else "pair16"
         return None if algo == _lib.GEMM_AUTO else ("lo32" if algo == _lib.GEMM_3XTF32 or N < 256 else "pair16")
@@ -229,7 +229,7 @@ def gemm_arrays(a, b, out, epi=None, algo=None):
         return
     # Operand parts kept beside an operand's storage are handed to the tensor-core kernel instead
     # of being recomputed per product.
-    linear = epi is None or not (epi.bias or epi.act or epi.dact or epi.beta or epi.colsum)
+    linear = epi is None or not epi.beta     # (the kernel's short accumulation runs need beta == 0)
     plan = _tc_plan(M, N, K, nbatch, algo, linear)
     if plan is not None:
         pa, pb = _operand_parts_ptr(a, plan), _operand_parts_ptr(b, plan)
