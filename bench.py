@@ -267,6 +267,13 @@ class FFTStep:
         self.h2d_bytes = int(self.x_host.numel() * 8) * world
         self.d2h_bytes = 4 * world
         self.last_y = None
+        # One rank: the step is a handful of launches whose host cost (op nodes, graph walk) is
+        # comparable to the transforms themselves at c4's size, so it is replayed as one CUDA graph
+        # (the library's CapturedStep), like c3. ENDIA_B200_BENCH_GRAPH=0 enqueues it op by op.
+        self.captured = None
+        if world == 1 and os.environ.get("ENDIA_B200_BENCH_GRAPH", "1") != "0":
+            from endia_b200.utils.general import CapturedStep
+            self.captured = CapturedStep(self._eager)
 
     @staticmethod
     def crandn(r, shape):
@@ -286,6 +293,14 @@ class FFTStep:
         from endia_b200.dist import flat_tensor
         if host_io:
             flat_tensor(self.X).copy_(torch.view_as_real(self.x_host).reshape(-1), non_blocking=True)
+        dx = self.captured() if self.captured is not None else self._eager()
+        if host_io:
+            self.loss_host.copy_(flat_tensor(self.last_loss), non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+        return dx
+
+    def _eager(self):
+        nd = self.nd
         if self.workload == "c4":
             y = nd.fft(self.X)
             loss = nd.sum(nd.square(nd.to_abs(y))) * (1.0 / (1 << 20))
@@ -300,9 +315,6 @@ class FFTStep:
         dx = self.X.grad()
         loss.zero_grad()
         self.last_y, self.last_loss = y, loss
-        if host_io:
-            self.loss_host.copy_(flat_tensor(loss), non_blocking=True)
-            torch.cuda.current_stream().synchronize()
         return dx
 
 
@@ -909,6 +921,17 @@ def bench_fft(ctx, name, steps, warmup, with_cpu=True, with_parity=True):
     work = FFTStep(ctx.nd, ctx.torch, name, ctx.rank if name == "c5" else 0, world)
     t = timed_region(ctx, work, steps, warmup, e2e_steps=min(steps, 5))
     parity = c5_parity(ctx, work) if (world > 1 and with_parity) else None
+    if work.captured is not None:
+        # a replayed graph has no per-call events: the transform calls are timed in three steps
+        # enqueued op by op (CUDA events around each endia_b200_fft_c2c_fused call)
+        timer = CallTimer(ctx.torch)
+        ctx.nd.config.fft_timer = timer
+        for _ in range(3):
+            work._eager()
+        ctx.torch.cuda.synchronize()
+        ctx.nd.config.fft_timer = None
+        t["n_calls"], t["call_work"], t["call_ms"] = timer.summary()
+        t["call_steps"] = 3
     if ctx.rank != 0:
         return None
     pk = ctx.pk
@@ -923,10 +946,17 @@ def bench_fft(ctx, name, steps, warmup, with_cpu=True, with_parity=True):
             "e2e": {"value": work.alg_bytes / (t["ms_e2e_step"] / 1000.0) / 1e9, "unit": "GB/s",
                     "h2d_bytes_per_step": work.h2d_bytes, "d2h_bytes_per_step": work.d2h_bytes},
             "gpu_launches": t["launches"], "host_enqueue_ms_per_step": t["host_ms_step"],
+            "implementation": {
+                "launch": ("one CUDA graph per step (%d kernels); ENDIA_B200_BENCH_GRAPH=0 runs it op by op"
+                           % work.captured.launches_per_replay) if work.captured is not None else "op by op",
+                "fusion": "loss term summed in the last pass of the forward transform, its gradient folded into "
+                          "the scale of the VJP transform (ENDIA_B200_FFT_FUSE=0: every op a pass of its own)"},
             "roofline": {"bound": "hbm", "achieved": ach, "peak": hbm * world, "unit": "GB/s",
                          "frac": ach / (hbm * world) if hbm else None, "traffic": None,
-                         "kernel": "fft calls (%d, %.1f%% of the step); algorithmic bytes = one read + one write "
-                                   "of the array per transform" % (t["n_calls"], 100.0 * t["call_ms"] / (ms * steps)),
+                         "kernel": "fft calls (%d per step, %.3f ms per step); algorithmic bytes = one read + one "
+                                   "write of the array per transform" % (
+                                       t["n_calls"] // t.get("call_steps", steps),
+                                       t["call_ms"] / t.get("call_steps", steps)),
                          "path_frac": path / (hbm * world),
                          "path_note": "value / peak: the whole forward+VJP on its 4S algorithmic bytes",
                          "peak_note": "%s hbm_gbs (copy)%s" % (pk["source"], " x %d GPUs" % world if world > 1 else "")}}

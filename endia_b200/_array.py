@@ -64,6 +64,30 @@ def await_pending(arr):
         cb()
 
 
+def watch_input(src, node):
+    """Remember that `node`, an array whose kernel is still deferred (it has pending() and runs the
+    kernel on access of `buf`), will read `src`'s storage."""
+    import weakref
+    base = src.base()
+    readers = base.__dict__.setdefault("_pending_readers", [])
+    readers[:] = [r for r in readers if r() is not None and r().pending()]
+    readers.append(weakref.ref(node))
+
+
+def flush_readers(dst):
+    """Enqueue every deferred kernel that still has to read `dst`'s storage; every in-place writer
+    of an array's storage calls this first, so that a deferred result is that of the contents it
+    was created from."""
+    base = dst.base()
+    readers = base.__dict__.get("_pending_readers")
+    if readers:
+        base._pending_readers = []
+        for r in readers:
+            node = r()
+            if node is not None and node.pending():
+                node.buf   # noqa: B018  (runs the kernel)
+
+
 def compute_stride(shape):
     """Row-major element strides (endia/utils/_array_shape.mojo:24-30)."""
     stride = [1] * len(shape)

@@ -51,6 +51,18 @@ class Epilogue(C.Structure):
     ]
 
 
+class FftFusion(C.Structure):
+    """Mirror of `endia_b200_fft_fusion`."""
+    _fields_ = [
+        ("scale_dev", C.c_void_p),
+        ("reduce", C.c_int32),
+        ("reduce_w", C.c_void_p),
+        ("reduce_out", C.c_void_p),
+        ("reduce_scale", C.c_float),
+        ("reduce_scratch", C.c_void_p),
+    ]
+
+
 # status codes
 OK, EINVAL, ECUDA, ENODEV, ENOMEM, ESHAPE, EPOW2, ETIMEOUT, ELIMIT = 0, -1, -2, -3, -4, -5, -6, -7, -8
 ACT_NONE, ACT_RELU, ACT_TANH, ACT_SIGMOID = 0, 1, 2, 3
@@ -118,6 +130,10 @@ SIGNATURES = {
                                   [_vp, _i32, _f32, _f32, _f32, _f32, _f32, _vp]),
     "endia_b200_fft_scratch_bytes": (_sz, [_TP, C.POINTER(_i32), _i32]),
     "endia_b200_fft_c2c": (C.c_int, [_TP, _TP, C.POINTER(_i32), _i32, C.c_int, _f32, _vp, _vp]),
+    "endia_b200_fft_fusion_scratch_bytes": (_sz, []),
+    "endia_b200_fft_c2c_fused": (C.c_int, [_TP, _TP, C.POINTER(_i32), _i32, C.c_int, _f32, _vp,
+                                           C.POINTER(FftFusion), _vp]),
+    "endia_b200_fft_loss_term": (C.c_int, [_TP, C.c_int, _vp, _vp, _f32, _vp, _vp]),
     "endia_b200_sgd_step_multi": (C.c_int, [_i32, C.POINTER(_vp), C.POINTER(_vp), C.POINTER(_vp),
                                             C.POINTER(_i64), _f32, _f32, _f32, _f32, _vp]),
     "endia_b200_rmsprop_step_multi": (C.c_int, [_i32, C.POINTER(_vp), C.POINTER(_vp), C.POINTER(_vp),

@@ -18,3 +18,7 @@ cache_tf32_lo = True
 gemm_timer = None
 # Same hook around every FFT call: start(algorithmic_bytes) / stop().
 fft_timer = None
+# Ops of the FFT loss chains (fft -> abs -> real -> square -> sum, fft -> real -> * w -> sum) return
+# deferred arrays so that the loss term and its gradient are folded into the transforms
+# (functional/_deferred.py); ENDIA_B200_FFT_FUSE=0 runs every op eagerly.
+defer_fft_chains = os.environ.get("ENDIA_B200_FFT_FUSE", "1") != "0"

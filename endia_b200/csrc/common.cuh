@@ -75,6 +75,9 @@ inline bool is_contiguous(const endia_b200_tensor *t) {
 }
 int check_tensor(const endia_b200_tensor *t, const char *what);
 
+// out[0] = scale * (sum of `count` floats at `partial`), one CTA, fixed summation order (reduce.cu).
+int launch_scalar_finish(const float *partial, float *out, int count, float scale, cudaStream_t s);
+
 // Grid size for a grid-stride kernel: enough CTAs to fill the machine a few times over.
 inline int grid_for(int64_t work_items, int threads, int ctas_per_sm = 8) {
   int64_t want = ceil_div(work_items, threads);

@@ -36,7 +36,29 @@ struct FftParams {
   const float2 *tw_hi, *tw_lo;
   int lo_bits;
   int in_real;                   // `in` points at floats (one per element): the imaginary part is 0
+  // Work fused into the LAST pass of a transform (all zero otherwise):
+  const float *scale_dev;        // a device scalar multiplied into `scale`
+  int red_mode;                  // 1: sum |y|^2, 2: sum real(y) * red_w[index of y], over the stored values y
+  const float *red_w;
+  float *red_partial;            // one partial sum per CTA
 };
+
+// Sum over the CTA of `v` (blockDim.x a multiple of 32); valid in thread 0.
+__device__ __forceinline__ float fft_block_sum(float v) {
+  __shared__ float part[32];
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  if (lane == 0) part[w] = v;
+  __syncthreads();
+  float r = 0.f;
+  if (w == 0) {
+    r = lane < (int)((blockDim.x + 31) >> 5) ? part[lane] : 0.f;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) r += __shfl_xor_sync(0xffffffffu, r, o);
+  }
+  return r;
+}
 
 // Element `idx` (in elements from `base`) of the input, which is complex or, with `real`, real.
 __device__ __forceinline__ float2 load_in(const float2 *base, int64_t idx, int real) {
@@ -147,6 +169,8 @@ __global__ void __launch_bounds__(1024, 1) fft_tile_kernel(const __grid_constant
   const int tid = threadIdx.x, nthr = blockDim.x;
   const int T = P.T, LS = T + 1, N = P.N;
   const int total = T * N;
+  const float scale = P.scale_dev ? P.scale * __ldg(P.scale_dev) : P.scale;
+  float red = 0.f;
   for (int64_t tile = blockIdx.x; tile < P.n_tiles; tile += gridDim.x) {
     const int64_t o = tile / P.tiles_per_outer;
     const int64_t line0 = (tile - o * P.tiles_per_outer) * T;
@@ -196,11 +220,18 @@ __global__ void __launch_bounds__(1024, 1) fft_tile_kernel(const __grid_constant
         v = cmul(v, cmul(__ldg(P.tw_hi + (q >> P.lo_bits)),
                          __ldg(P.tw_lo + (q & ((int64_t(1) << P.lo_bits) - 1)))));
       }
-      v.x *= P.scale; v.y *= P.scale;
+      v.x *= scale; v.y *= scale;
       if (P.conj_out) v.y = -v.y;
-      dst[(int64_t)t * P.out_line_stride + (int64_t)j * P.out_elem_stride] = v;
+      const int64_t at = (int64_t)t * P.out_line_stride + (int64_t)j * P.out_elem_stride;
+      dst[at] = v;
+      if (P.red_mode == 1) red += v.x * v.x + v.y * v.y;
+      else if (P.red_mode == 2) red += v.x * __ldg(P.red_w + (dst - P.out) + at);
     }
     __syncthreads();
+  }
+  if (P.red_mode) {
+    red = fft_block_sum(red);
+    if (tid == 0) P.red_partial[blockIdx.x] = red;
   }
 }
 
@@ -229,9 +260,13 @@ struct FastParams {
   int conj_in, conj_out;
   float scale;
   int in_real;                   // as in FftParams
+  const float *scale_dev;        // as in FftParams (last pass only)
+  const float *red_w;
+  float *red_partial;
 };
 
 enum { FAST_COL = 0, FAST_ROW = 1, FAST_COL_STAGED_IN = 2 };
+enum { RED_NONE = 0, RED_ABS2 = 1, RED_RE_W = 2 };
 
 template <int LOGN, int MODE, int T>
 __device__ __forceinline__ int fast_phys(int j, int t) {
@@ -253,13 +288,19 @@ __device__ __forceinline__ int fast_phys(int j, int t) {
 __device__ __forceinline__ float2 fast_bigtw(const FastParams &P, int q) {
   return cmul(__ldg(P.tw_hi + (q >> P.lo_bits)), __ldg(P.tw_lo + (q & ((1 << P.lo_bits) - 1))));
 }
-__device__ __forceinline__ void fast_store(const FastParams &P, float2 *dst, int j, float2 v) {
-  v.x *= P.scale; v.y *= P.scale;
+// Store of output point j of the line at `dst`; RED accumulates the loss term of the stored value
+// (`wl` = the line of red_w that lies under `dst`).
+template <int RED>
+__device__ __forceinline__ void fast_store(const FastParams &P, float2 *dst, int j, float2 v, float sc,
+                                           float &red, const float *wl) {
+  v.x *= sc; v.y *= sc;
   if (P.conj_out) v.y = -v.y;
   dst[(int64_t)j * P.out_elem] = v;
+  if constexpr (RED == RED_ABS2) red += v.x * v.x + v.y * v.y;
+  if constexpr (RED == RED_RE_W) red += v.x * __ldg(wl + (int64_t)j * P.out_elem);
 }
 
-template <int LOGN, int MODE, bool TW, int T, bool REAL>
+template <int LOGN, int MODE, bool TW, int T, bool REAL, int RED = RED_NONE>
 __global__ void __launch_bounds__((T << LOGN) / 16, 16384 / (T << LOGN))
 fft_fast_kernel(const __grid_constant__ FastParams P) {
   constexpr int N = 1 << LOGN, NT = T * N / 16, Q = N / 16, R3 = N / 256;
@@ -271,11 +312,14 @@ fft_fast_kernel(const __grid_constant__ FastParams P) {
   const int i0 = MODE == FAST_ROW ? tid % Q : (tid >> LOGT);
   for (int q = tid; q < N; q += NT) tws[q] = __ldg(P.tw + q);
   __syncthreads();
+  const float sc = P.scale_dev ? P.scale * __ldg(P.scale_dev) : P.scale;
+  float red = 0.f;
   for (int64_t tile = blockIdx.x; tile < P.n_tiles; tile += gridDim.x) {
     const int64_t o = tile / P.tiles_per_outer;
     const int line0 = (int)(tile - o * P.tiles_per_outer) * T;
     const int line = line0 + t;
     float2 *dst = P.out + o * P.out_outer + (int64_t)line * P.out_line;
+    const float *wl = RED == RED_RE_W ? P.red_w + (dst - P.out) : nullptr;
     float2 u[16];
     if constexpr (MODE == FAST_COL_STAGED_IN) {
       // contiguous lines: a warp reads 32 consecutive points of one line, the swizzle makes the
@@ -329,7 +373,7 @@ fft_fast_kernel(const __grid_constant__ FastParams P) {
         for (int r = 0; r < 16; ++r) { u[r] = cmul(u[r], w); w = cmul(w, step); }
       }
 #pragma unroll
-      for (int r = 0; r < 16; ++r) fast_store(P, dst, i0 + 16 * r, u[r]);
+      for (int r = 0; r < 16; ++r) fast_store<RED>(P, dst, i0 + 16 * r, u[r], sc, red, wl);
     } else {
       __syncthreads();
 #pragma unroll
@@ -353,11 +397,29 @@ fft_fast_kernel(const __grid_constant__ FastParams P) {
           for (int r = 0; r < R3; ++r) { v[r] = cmul(v[r], w); w = cmul(w, step); }
         }
 #pragma unroll
-        for (int r = 0; r < R3; ++r) fast_store(P, dst, i + r * 256, v[r]);
+        for (int r = 0; r < R3; ++r) fast_store<RED>(P, dst, i + r * 256, v[r], sc, red, wl);
       }
     }
     __syncthreads();
   }
+  if constexpr (RED != RED_NONE) {
+    red = fft_block_sum(red);
+    if (tid == 0) P.red_partial[blockIdx.x] = red;
+  }
+}
+
+// Standalone form of the fused loss term, for transforms whose last pass has no fused variant:
+// one pass over the stored result.
+__global__ void __launch_bounds__(256) fft_reduce_kernel(const float2 *y, const float *w, int64_t n, int mode,
+                                                         float *partial) {
+  float red = 0.f;
+  const int64_t step = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += step) {
+    const float2 v = y[i];
+    red += mode == RED_ABS2 ? v.x * v.x + v.y * v.y : v.x * __ldg(w + i);
+  }
+  red = fft_block_sum(red);
+  if (threadIdx.x == 0) partial[blockIdx.x] = red;
 }
 
 // ------------------------------------------------------------------ host side
@@ -414,13 +476,25 @@ static int pick_T(int N) {
   return T;
 }
 
-template <int LOGN, int MODE, bool TW, int T, bool REAL>
-static int launch_fast_variant(FastParams F, int64_t lines_per_outer, int64_t n_outer, cudaStream_t s) {
+constexpr int FFT_RED_MAX_PARTIALS = 4096;   // CTAs of a last pass never exceed this
+
+// What the last pass of a transform does besides the transform (see endia_b200_fft_fusion).
+struct LastPass {
+  const float *scale_dev = nullptr;
+  int red_mode = RED_NONE;
+  const float *red_w = nullptr;
+  float *red_partial = nullptr;
+  int n_partials = 0;            // out: CTAs that wrote a partial sum (0: the pass had no fused variant)
+};
+
+template <int LOGN, int MODE, bool TW, int T, bool REAL, int RED = RED_NONE>
+static int launch_fast_variant(FastParams F, int64_t lines_per_outer, int64_t n_outer, cudaStream_t s,
+                               LastPass *lp = nullptr) {
   constexpr int N = 1 << LOGN;
   constexpr size_t SMEM = sizeof(float2) * (size_t)N * (T + 1);   // T lines of data + the twiddle table
   F.tiles_per_outer = lines_per_outer / T;
   F.n_tiles = F.tiles_per_outer * n_outer;
-  auto kern = fft_fast_kernel<LOGN, MODE, TW, T, REAL>;
+  auto kern = fft_fast_kernel<LOGN, MODE, TW, T, REAL, RED>;
   static bool attr = false;
   if (!attr) {
     EB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM));
@@ -429,35 +503,64 @@ static int launch_fast_variant(FastParams F, int64_t lines_per_outer, int64_t n_
   const int per_sm = 16384 / (T * N);   // 1024 threads (16 points each) per SM
   const int64_t cap = (int64_t)(sm_count() > 0 ? sm_count() : 148) * per_sm;
   const int grid = (int)(F.n_tiles < cap ? F.n_tiles : cap);
+  if (lp) {
+    F.scale_dev = lp->scale_dev;
+    if constexpr (RED != RED_NONE) {
+      F.red_w = lp->red_w; F.red_partial = lp->red_partial;
+      lp->n_partials = grid;
+    }
+  }
   kern<<<grid, T * N / 16, SMEM, s>>>(F);
   EB_LAUNCH_CHECK();
   return ENDIA_B200_OK;
 }
 
+// The variants that can end a transform exist with the fused loss terms as well (complex source,
+// no four-step twiddle: that pass is never the last).
+template <int LOGN, int MODE, int T>
+static int launch_fast_last(const FastParams &F, int64_t lpo, int64_t no, cudaStream_t s, LastPass *lp) {
+  const int red = lp ? lp->red_mode : RED_NONE;
+  if (red == RED_ABS2) return launch_fast_variant<LOGN, MODE, false, T, false, RED_ABS2>(F, lpo, no, s, lp);
+  if (red == RED_RE_W) return launch_fast_variant<LOGN, MODE, false, T, false, RED_RE_W>(F, lpo, no, s, lp);
+  return launch_fast_variant<LOGN, MODE, false, T, false>(F, lpo, no, s, lp);
+}
+
 template <int LOGN, bool REAL>
-static int launch_fast_nr(const FastParams &F, bool tw, int64_t lpo, int64_t no, cudaStream_t s) {
+static int launch_fast_nr(const FastParams &F, bool tw, int64_t lpo, int64_t no, cudaStream_t s, LastPass *lp) {
   const bool row_in = F.in_elem == 1, row_out = F.out_elem == 1;
-  if (row_in && row_out) return launch_fast_variant<LOGN, FAST_ROW, false, 8, REAL>(F, lpo, no, s);
+  if (row_in && row_out) {
+    if constexpr (!REAL) return launch_fast_last<LOGN, FAST_ROW, 8>(F, lpo, no, s, lp);
+    return launch_fast_variant<LOGN, FAST_ROW, false, 8, REAL>(F, lpo, no, s, lp);
+  }
   // 16 lines per tile give 128-byte segments on the strided side; they fit next to 2 CTAs per SM
-  // for lines up to 512 points (and, with one 1024-thread CTA per SM, for 1024 points).
+  // for lines up to 512 points (and, with one 1024-thread CTA per SM, for 1024 points: measured
+  // faster than two 512-thread CTAs of 8 lines, whose segments are 64 bytes).
   static const int wide_max = []() { const char *e = getenv("ENDIA_B200_FFT_WIDE_MAX"); return e ? atoi(e) : 1024; }();
   if constexpr (LOGN <= 10) {
     if ((1 << LOGN) <= wide_max && lpo % 16 == 0) {
-      if (row_in) return launch_fast_variant<LOGN, FAST_COL_STAGED_IN, false, 16, REAL>(F, lpo, no, s);
-      return tw ? launch_fast_variant<LOGN, FAST_COL, true, 16, REAL>(F, lpo, no, s)
-                : launch_fast_variant<LOGN, FAST_COL, false, 16, REAL>(F, lpo, no, s);
+      if (row_in) {
+        if constexpr (!REAL) return launch_fast_last<LOGN, FAST_COL_STAGED_IN, 16>(F, lpo, no, s, lp);
+        return launch_fast_variant<LOGN, FAST_COL_STAGED_IN, false, 16, REAL>(F, lpo, no, s, lp);
+      }
+      if (tw) return launch_fast_variant<LOGN, FAST_COL, true, 16, REAL>(F, lpo, no, s, lp);
+      if constexpr (!REAL) return launch_fast_last<LOGN, FAST_COL, 16>(F, lpo, no, s, lp);
+      return launch_fast_variant<LOGN, FAST_COL, false, 16, REAL>(F, lpo, no, s, lp);
     }
   }
-  if (row_in) return launch_fast_variant<LOGN, FAST_COL_STAGED_IN, false, 8, REAL>(F, lpo, no, s);
-  return tw ? launch_fast_variant<LOGN, FAST_COL, true, 8, REAL>(F, lpo, no, s)
-            : launch_fast_variant<LOGN, FAST_COL, false, 8, REAL>(F, lpo, no, s);
+  if (row_in) {
+    if constexpr (!REAL) return launch_fast_last<LOGN, FAST_COL_STAGED_IN, 8>(F, lpo, no, s, lp);
+    return launch_fast_variant<LOGN, FAST_COL_STAGED_IN, false, 8, REAL>(F, lpo, no, s, lp);
+  }
+  if (tw) return launch_fast_variant<LOGN, FAST_COL, true, 8, REAL>(F, lpo, no, s, lp);
+  if constexpr (!REAL) return launch_fast_last<LOGN, FAST_COL, 8>(F, lpo, no, s, lp);
+  return launch_fast_variant<LOGN, FAST_COL, false, 8, REAL>(F, lpo, no, s, lp);
 }
 
 template <int LOGN>
-static int launch_fast_n(const FastParams &F, bool tw, int64_t lpo, int64_t no, cudaStream_t s) {
+static int launch_fast_n(const FastParams &F, bool tw, int64_t lpo, int64_t no, cudaStream_t s, LastPass *lp) {
   // a real source (read with a zero imaginary part) has kernels of its own, so that the complex
   // ones keep their register budget
-  return F.in_real ? launch_fast_nr<LOGN, true>(F, tw, lpo, no, s) : launch_fast_nr<LOGN, false>(F, tw, lpo, no, s);
+  return F.in_real ? launch_fast_nr<LOGN, true>(F, tw, lpo, no, s, lp) : launch_fast_nr<LOGN, false>(F, tw, lpo, no, s, lp);
 }
 
 // Supported combinations: strided in and out (optionally with the four-step twiddle), contiguous
@@ -468,12 +571,12 @@ static bool fast_supported(int64_t in_elem, int64_t out_elem, bool tw) {
   return !row_out;
 }
 
-static int launch_fast(const FastParams &F, int N, bool tw, int64_t lpo, int64_t no, cudaStream_t s) {
+static int launch_fast(const FastParams &F, int N, bool tw, int64_t lpo, int64_t no, cudaStream_t s, LastPass *lp) {
   switch (N) {
-    case 256: return launch_fast_n<8>(F, tw, lpo, no, s);
-    case 512: return launch_fast_n<9>(F, tw, lpo, no, s);
-    case 1024: return launch_fast_n<10>(F, tw, lpo, no, s);
-    default: return launch_fast_n<11>(F, tw, lpo, no, s);
+    case 256: return launch_fast_n<8>(F, tw, lpo, no, s, lp);
+    case 512: return launch_fast_n<9>(F, tw, lpo, no, s, lp);
+    case 1024: return launch_fast_n<10>(F, tw, lpo, no, s, lp);
+    default: return launch_fast_n<11>(F, tw, lpo, no, s, lp);
   }
 }
 
@@ -486,7 +589,9 @@ struct Pass {
   int64_t big_n;  // > 0: four-step twiddle W_big^(j*line) at the store
 };
 
-static int launch_pass(const Pass &ps, const float2 *in, float2 *out, cudaStream_t s, bool in_real = false) {
+// `lp` is given for the last pass of a transform only.
+static int launch_pass(const Pass &ps, const float2 *in, float2 *out, cudaStream_t s, bool in_real = false,
+                       LastPass *lp = nullptr) {
   FftParams P{};
   P.in = in; P.out = out; P.N = ps.N;
   P.in_real = in_real ? 1 : 0;
@@ -518,7 +623,7 @@ static int launch_pass(const Pass &ps, const float2 *in, float2 *out, cudaStream
       if ((st = twiddle_table(ps.big_n, int64_t(1) << F.lo_bits, int64_t(1) << (lb - F.lo_bits), 2,
                               &F.tw_hi))) return st;
     }
-    return launch_fast(F, ps.N, ps.big_n > 0, ps.lines_per_outer, ps.n_outer, s);
+    return launch_fast(F, ps.N, ps.big_n > 0, ps.lines_per_outer, ps.n_outer, s, lp);
   }
   if (ps.big_n > 0) {
     const int lb = ilog2(ps.big_n);
@@ -532,12 +637,20 @@ static int launch_pass(const Pass &ps, const float2 *in, float2 *out, cudaStream
   const size_t smem = sizeof(float2) * (size_t)ps.N * (P.T + 1);
   static bool attr_set = false;
   if (!attr_set) {
+    // (the kernel also has 128 bytes of static shared memory for its block sum)
     EB_CUDA(cudaFuncSetAttribute(fft_tile_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 227 * 1024));
+                                 227 * 1024 - 1024));
     attr_set = true;
   }
   int64_t cap = (int64_t)(sm_count() > 0 ? sm_count() : 148) * 4;
   int grid = (int)(P.n_tiles < cap ? P.n_tiles : cap);
+  if (lp) {
+    P.scale_dev = lp->scale_dev;
+    if (lp->red_mode) {
+      P.red_mode = lp->red_mode; P.red_w = lp->red_w; P.red_partial = lp->red_partial;
+      lp->n_partials = grid;
+    }
+  }
   fft_tile_kernel<<<grid, threads, smem, s>>>(P);
   EB_LAUNCH_CHECK();
   return ENDIA_B200_OK;
@@ -617,11 +730,53 @@ size_t endia_b200_fft_scratch_bytes(const endia_b200_tensor *in, const int32_t *
   return bytes;
 }
 
+size_t endia_b200_fft_fusion_scratch_bytes(void) { return sizeof(float) * FFT_RED_MAX_PARTIALS; }
+
+int endia_b200_fft_loss_term(const endia_b200_tensor *y, int reduce, const float *reduce_w, float *reduce_out,
+                             float reduce_scale, void *reduce_scratch, void *stream) {
+  int st = require_device();
+  if (st) return st;
+  if ((st = check_tensor(y, "fft_loss_term: y"))) return st;
+  EB_REQUIRE(y->is_complex && is_contiguous(y), ENDIA_B200_EINVAL, "fft_loss_term: y must be contiguous complex");
+  EB_REQUIRE(reduce == RED_ABS2 || reduce == RED_RE_W, ENDIA_B200_EINVAL, "fft_loss_term: unknown reduction %d", reduce);
+  EB_REQUIRE(reduce_out && reduce_scratch && (reduce != RED_RE_W || reduce_w), ENDIA_B200_EINVAL,
+             "fft_loss_term: NULL pointer");
+  cudaStream_t s = as_stream(stream);
+  const int64_t total = numel(y);
+  if (total == 0) {
+    EB_CUDA(cudaMemsetAsync(reduce_out, 0, sizeof(float), s));
+    return ENDIA_B200_OK;
+  }
+  const int ctas = grid_for(total, 256, 8);
+  fft_reduce_kernel<<<ctas, 256, 0, s>>>(reinterpret_cast<const float2 *>(y->data) + y->offset, reduce_w, total, reduce,
+                                         static_cast<float *>(reduce_scratch));
+  EB_LAUNCH_CHECK();
+  return launch_scalar_finish(static_cast<float *>(reduce_scratch), reduce_out, ctas, reduce_scale, s);
+}
+
 int endia_b200_fft_c2c(const endia_b200_tensor *in, const endia_b200_tensor *out,
                        const int32_t *dims, int32_t n_dims, int inverse, float scale, void *scratch,
                        void *stream) {
+  return endia_b200_fft_c2c_fused(in, out, dims, n_dims, inverse, scale, scratch, nullptr, stream);
+}
+
+int endia_b200_fft_c2c_fused(const endia_b200_tensor *in, const endia_b200_tensor *out,
+                             const int32_t *dims, int32_t n_dims, int inverse, float scale, void *scratch,
+                             const endia_b200_fft_fusion *fusion, void *stream) {
   int st = require_device();
   if (st) return st;
+  LastPass lp;
+  const bool fused = fusion != nullptr;
+  if (fused) {
+    EB_REQUIRE(fusion->reduce >= 0 && fusion->reduce <= 2, ENDIA_B200_EINVAL, "fft: unknown reduction %d", fusion->reduce);
+    EB_REQUIRE(!fusion->reduce || (fusion->reduce_out && fusion->reduce_scratch), ENDIA_B200_EINVAL,
+               "fft: the fused reduction needs reduce_out and reduce_scratch");
+    EB_REQUIRE(fusion->reduce != 2 || fusion->reduce_w, ENDIA_B200_EINVAL, "fft: reduce = 2 needs reduce_w");
+    lp.scale_dev = fusion->scale_dev;
+    lp.red_mode = fusion->reduce;
+    lp.red_w = fusion->reduce_w;
+    lp.red_partial = static_cast<float *>(fusion->reduce_scratch);
+  }
   if ((st = check_tensor(in, "fft: in"))) return st;
   if ((st = check_tensor(out, "fft: out"))) return st;
   // A real `in` (contiguous) is read as complex with a zero imaginary part by the first pass.
@@ -640,8 +795,24 @@ int endia_b200_fft_c2c(const endia_b200_tensor *in, const endia_b200_tensor *out
   EB_REQUIRE(!need_scratch || scratch, ENDIA_B200_EINVAL,
              "fft: scratch of endia_b200_fft_scratch_bytes() bytes is required");
   const int64_t total = numel(in);
-  if (total == 0) return ENDIA_B200_OK;
   cudaStream_t s = as_stream(stream);
+  if (total == 0) {
+    if (fused && fusion->reduce) EB_CUDA(cudaMemsetAsync(fusion->reduce_out, 0, sizeof(float), s));
+    return ENDIA_B200_OK;
+  }
+  // After the last pass: add up the per-CTA partial sums, or, where that pass had no fused variant
+  // (or ran as several launches), take the loss term in one more pass over the result.
+  int last_launches = 0;
+  auto finish_reduction = [&]() -> int {
+    if (!fused || !fusion->reduce) return ENDIA_B200_OK;
+    float2 *y = reinterpret_cast<float2 *>(out->data) + out->offset;
+    if (lp.n_partials == 0 || last_launches != 1) {
+      lp.n_partials = grid_for(total, 256, 8);
+      fft_reduce_kernel<<<lp.n_partials, 256, 0, s>>>(y, lp.red_w, total, lp.red_mode, lp.red_partial);
+      EB_LAUNCH_CHECK();
+    }
+    return launch_scalar_finish(lp.red_partial, fusion->reduce_out, lp.n_partials, fusion->reduce_scale, s);
+  };
   const float2 *src = real_in ? reinterpret_cast<const float2 *>(static_cast<const float *>(in->data) + in->offset)
                               : reinterpret_cast<const float2 *>(in->data) + in->offset;
   float2 *dst = reinterpret_cast<float2 *>(out->data) + out->offset;
@@ -653,7 +824,9 @@ int endia_b200_fft_c2c(const endia_b200_tensor *in, const endia_b200_tensor *out
   if (axes.empty()) {
     // Nothing to transform: out = scale * in (the inverse of a length-1 transform is itself).
     Pass ps{1, 1, total, 0, 1, 1, 0, 1, 1, 0, 0, scale, 0};
-    return launch_pass(ps, src, dst, s, real_in);
+    ++last_launches;
+    if ((st = launch_pass(ps, src, dst, s, real_in, fused ? &lp : nullptr))) return st;
+    return finish_reduction();
   }
   // Innermost axis first: its pass reads `in` in long contiguous runs.
   for (size_t a = axes.size(); a-- > 0;) {
@@ -672,7 +845,8 @@ int endia_b200_fft_c2c(const endia_b200_tensor *in, const endia_b200_tensor *out
         ps.in_outer = ps.out_outer = ai.n * ai.inner; ps.in_line = ps.out_line = 1;
         ps.in_elem = ps.out_elem = ai.inner;
       }
-      if ((st = launch_pass(ps, src, dst, s, real_in))) return st;
+      if (last) ++last_launches;
+      if ((st = launch_pass(ps, src, dst, s, real_in, (fused && last) ? &lp : nullptr))) return st;
     } else {
       int n1, n2;
       split_len(ai.n, n1, n2);
@@ -698,13 +872,14 @@ int endia_b200_fft_c2c(const endia_b200_tensor *in, const endia_b200_tensor *out
         pb.in_outer = pb.out_outer = ai.n; pb.in_line = n2; pb.in_elem = 1;
         pb.out_line = 1; pb.out_elem = n1;
         pb.conj_in = 0; pb.conj_out = cout; pb.scale = sc; pb.big_n = 0;
-        if ((st = launch_pass(pb, tmp, dst + g0 * ai.n, s))) return st;
+        if (last) ++last_launches;
+        if ((st = launch_pass(pb, tmp, dst + g0 * ai.n, s, false, (fused && last) ? &lp : nullptr))) return st;
       }
     }
     src = dst;
     real_in = false;
   }
-  return ENDIA_B200_OK;
+  return finish_reduction();
 }
 
 }  // extern "C"

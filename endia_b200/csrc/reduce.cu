@@ -370,6 +370,12 @@ static int make_plan(const endia_b200_tensor *in, uint32_t axes_mask, RedPlan &p
   return ENDIA_B200_OK;
 }
 
+int launch_scalar_finish(const float *partial, float *out, int count, float scale, cudaStream_t s) {
+  scalar_finish_kernel<<<1, 256, 0, s>>>(partial, out, count, scale);
+  EB_LAUNCH_CHECK();
+  return ENDIA_B200_OK;
+}
+
 static int mse_ctas(int64_t n) {
   int64_t c = ceil_div(n, 256 * 16);
   if (c > 1024) c = 1024;

@@ -262,9 +262,11 @@ class ShardedAdam:
     def step(self):
         import ctypes as C
         from . import _lib
-        from ._array import stream, alloc
+        from ._array import stream, alloc, flush_readers
         from .functional._utils import contiguous, broadcast_shapes
         n = len(self.params)
+        for p in self.params:
+            flush_readers(p)
         # gradients that no hook has seen (a parameter outside the graph): zeros, like Array.grad()
         seen_small = {i for i, _ in self.small}
         for i, p in enumerate(self.params):

@@ -19,12 +19,21 @@ def setup_shape_and_data(curr):
 
 
 def op_array(array_shape, args, name, callable, vjp=None, jvp=None, is_view=False, meta_data=None,
-             is_complex_p=False, kwargs=None):
+             is_complex_p=False, kwargs=None, deferred=None, root=None, w=None):
     """Create the result node of an op and run its forward (functional/_utils.mojo:208-316).
 
     requires_grad is the OR over the args and the complex flag is the OR over the args (or
-    forced); graph edges and the VJP are stored only when a gradient can flow (:262-272)."""
-    curr = Array(array_shape)
+    forced); graph edges and the VJP are stored only when a gradient can flow (:262-272).
+    `deferred` names the node's place in one of the FFT loss chains (functional/_deferred.py): the
+    forward then runs when the result's storage is first asked for."""
+    from ..autograd import state as _state
+    if deferred is not None and _state.defer_fft_chains:
+        from ._deferred import Deferred
+        curr = Deferred(array_shape)
+        curr.kind, curr.root, curr.w = deferred, root, w
+    else:
+        deferred = None
+        curr = Array(array_shape)
     curr.name = name
     curr.is_view = is_view
     curr.meta_data = list(meta_data) if meta_data else []
@@ -34,7 +43,10 @@ def op_array(array_shape, args, name, callable, vjp=None, jvp=None, is_view=Fals
         curr.args_ = list(args)
         curr.vjp_ = vjp
         curr.jvp_ = jvp
-    callable(curr, args)
+    if deferred is not None:
+        curr._thunk = lambda: callable(curr, args)
+    else:
+        callable(curr, args)
     return curr
 
 
@@ -95,6 +107,8 @@ def copy_into(src, dst):
     if not dst.is_contiguous():
         raise _lib.EndiaError(_lib.EINVAL, "in-place update of a non-contiguous view is not supported")
     s = contiguous(src)
+    from .._array import flush_readers
+    flush_readers(dst)        # deferred kernels that read the old contents run first
     w = 2 if dst.is_complex() else 1
     if s.is_complex() != dst.is_complex():
         raise _lib.EndiaError(_lib.EINVAL, "in-place update: complex flag mismatch")

@@ -25,7 +25,16 @@ def binary_op_array(arg0, arg1, name, opcode, vjp):
     args (binary_ops/_utils.mojo:57-90)."""
     shape = broadcast_shapes(arg0.shape(), arg1.shape())
     a0, a1 = expand(arg0, shape), expand(arg1, shape)
-    return op_array(ArrayShape(shape), [a0, a1], name, _binary_call(opcode), vjp=vjp)
+    defer = {}
+    if opcode == _lib.BIN_MUL:
+        # real(fftn(x)) * w with a plain real w of the same shape: see _deferred.py
+        from ._deferred import is_pending, Deferred
+        for u, v in ((a0, a1), (a1, a0)):
+            if is_pending(u, "re") and not isinstance(v, Deferred) and not v.is_complex() \
+                    and not v.requires_grad() and v.is_contiguous() and v.shape() == u.shape():
+                defer = {"deferred": "rew", "root": u.root, "w": v}
+                break
+    return op_array(ArrayShape(shape), [a0, a1], name, _binary_call(opcode), vjp=vjp, **defer)
 
 
 def _zero():

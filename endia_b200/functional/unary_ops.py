@@ -13,8 +13,8 @@ def _unary_call(opcode):
     return call
 
 
-def unary_op_array(arg0, name, opcode, vjp):
-    return op_array(ArrayShape(arg0.shape()), [arg0], name, _unary_call(opcode), vjp=vjp)
+def unary_op_array(arg0, name, opcode, vjp, **defer):
+    return op_array(ArrayShape(arg0.shape()), [arg0], name, _unary_call(opcode), vjp=vjp, **defer)
 
 
 def _fused(opcode, a, b):
@@ -76,6 +76,9 @@ def _square_vjp(primals, grad, out):
 
 
 def square(arg0):
+    from ._deferred import is_pending
+    if is_pending(arg0, "absr"):       # square(to_abs(fft(x))): see _deferred.py
+        return unary_op_array(arg0, "square", _lib.UN_SQUARE, _square_vjp, deferred="abs2", root=arg0.root)
     return unary_op_array(arg0, "square", _lib.UN_SQUARE, _square_vjp)
 
 
@@ -102,6 +105,9 @@ def _abs_vjp(primals, grad, out):
 
 
 def abs(arg0):
+    from ._deferred import is_pending
+    if is_pending(arg0, "fft"):
+        return unary_op_array(arg0, "abs", _lib.UN_ABS, _abs_vjp, deferred="abs", root=arg0)
     return unary_op_array(arg0, "abs", _lib.UN_ABS, _abs_vjp)
 
 

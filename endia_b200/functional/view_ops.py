@@ -211,7 +211,13 @@ def real(arg0):
         if not _state.create_graph and not grad.is_complex():
             return [LazyComplex(contiguous(grad))]   # complex(grad, 0), written only if read as such
         return [make_complex(grad, expand(Array([1]), grad.shape()))]
-    res = op_array(shape, [arg0], "real", _view_call, vjp=vjp, is_view=True)
+    from ._deferred import is_pending
+    defer = {}
+    if is_pending(arg0, "abs"):
+        defer = {"deferred": "absr", "root": arg0.root}
+    elif is_pending(arg0, "fft"):
+        defer = {"deferred": "re", "root": arg0}
+    res = op_array(shape, [arg0], "real", _view_call, vjp=vjp, is_view=True, **defer)
     res.is_complex_flag = False
     return res
 

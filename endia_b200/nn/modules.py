@@ -3,7 +3,7 @@ epilogue adds the bias and applies the activation; its VJP is one fused mask+bia
 and two GEMMs that read transposed operands in place. With create_graph=True the VJP is the
 reference's composition of differentiable ops instead, so higher-order gradients work."""
 from .. import _lib
-from .._array import Array, ArrayShape, alloc, stream, drop_operand_parts
+from .._array import Array, ArrayShape, alloc, stream, drop_operand_parts, flush_readers
 from ..autograd import state as _state
 from ..functional import init_ops
 from ..functional._utils import op_array, setup_shape_and_data, contiguous
@@ -252,6 +252,8 @@ class SmallMLPStep:
             raise _lib.EndiaError(_lib.ESHAPE, "fused_train_step: x / target do not match the network")
         opt = self.optimizer
         if opt is not None:
+            for p in self.weights + self.biases:
+                flush_readers(p)
             st = self._fn(self.L, self.c_dims, batch, self.act, x.data_ptr(), target.data_ptr(), self.p_W, self.p_b,
                           self.p_gW, self.p_gb, self.p_mW, self.p_vW, self.p_mb, self.p_vb, self.loss.data_ptr(), 1,
                           opt.lr, opt.beta1, opt.beta2, opt.eps, opt.t, stream())

@@ -25,9 +25,11 @@ class Adam:
                     _lib.call("endia_b200_memset0", st.data_ptr(), st.size() * 4, stream())
 
     def step(self):
+        from .._array import flush_readers
         n = len(self.params)
         grads = []
         for p in self.params:
+            flush_readers(p)
             if not p.is_contiguous():
                 raise _lib.EndiaError(_lib.EINVAL, "Adam: parameters must be contiguous arrays")
             grads.append(contiguous(p.grad()))  # zeros when no gradient is stored (_array.mojo:695-698)

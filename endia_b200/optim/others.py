@@ -5,7 +5,7 @@ gradient is (1, N), so the velocity / cache of a bias becomes (1, N)."""
 import ctypes as C
 
 from .. import _lib
-from .._array import Array, ArrayShape, stream, drop_operand_parts
+from .._array import Array, ArrayShape, stream, drop_operand_parts, flush_readers
 from ..functional._utils import contiguous, broadcast_shapes
 
 
@@ -20,6 +20,7 @@ class _FusedOptimizer:
         n = len(self.params)
         grads = []
         for p in self.params:
+            flush_readers(p)
             if not p.is_contiguous():
                 raise _lib.EndiaError(_lib.EINVAL, "optimizer: parameters must be contiguous arrays")
             g = contiguous(p.grad())   # zeros when no gradient is stored (_array.mojo:695-698)

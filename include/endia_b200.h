@@ -365,6 +365,37 @@ int endia_b200_fft_c2c(const endia_b200_tensor *in, const endia_b200_tensor *out
                        const int32_t *dims, int32_t n_dims, int inverse, float scale,
                        void *scratch, void *stream);
 
+/* The same transform with work fused into its last pass, so that a loss on the result and the
+ * gradient that flows back into the VJP transform cost no passes of their own:
+ *   scale_dev     (optional) device scalar multiplied into `scale` when the last pass runs: the
+ *                 incoming gradient of a loss, folded into the VJP transform
+ *   reduce = 1    reduce_out[0] = reduce_scale * sum |y|^2          the chain
+ *                 sum(square(to_abs(y))) (abs_op.mojo:114-157, real_op.mojo:43-52,
+ *                 square_op.mojo:117-119, sum_op.mojo:35-62)
+ *   reduce = 2    reduce_out[0] = reduce_scale * sum real(y) * reduce_w   the chain
+ *                 sum(real(y) * w) (real_op.mojo:43-52, mul_op.mojo, sum_op.mojo:35-62);
+ *                 reduce_w: contiguous float array of the output's shape
+ * over the stored output y (after `scale`). The sum is deterministic: one partial per CTA of the
+ * last pass in `reduce_scratch` (endia_b200_fft_fusion_scratch_bytes() bytes), added in a fixed
+ * order. Where the last pass has no fused form the loss term takes one more pass over `out`.
+ * `fusion` = NULL is endia_b200_fft_c2c. */
+typedef struct endia_b200_fft_fusion {
+  const float *scale_dev;
+  int32_t reduce;
+  const float *reduce_w;
+  float *reduce_out;
+  float reduce_scale;
+  void *reduce_scratch;
+} endia_b200_fft_fusion;
+size_t endia_b200_fft_fusion_scratch_bytes(void);
+int endia_b200_fft_c2c_fused(const endia_b200_tensor *in, const endia_b200_tensor *out,
+                             const int32_t *dims, int32_t n_dims, int inverse, float scale,
+                             void *scratch, const endia_b200_fft_fusion *fusion, void *stream);
+/* The same loss term (reduce = 1 or 2, as above) in one pass over a contiguous complex array `y`
+ * that exists already. */
+int endia_b200_fft_loss_term(const endia_b200_tensor *y, int reduce, const float *reduce_w,
+                             float *reduce_out, float reduce_scale, void *reduce_scratch, void *stream);
+
 /* ------------------------------------------------------------- collectives ---- */
 
 /* One NCCL communicator per (process, device); libnccl.so.2 is opened at first use

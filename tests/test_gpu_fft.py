@@ -194,3 +194,133 @@ def test_real_vjp_gradient_stays_lazy_into_fft(nd):
     lz = LazyComplex(nd.Array(w))
     assert not lz.materialised()
     assert np.array_equal(lz.to_numpy(), w.astype(np.complex64)) and lz.materialised()
+
+
+@pytest.mark.parametrize("shape,dims,real_src", [
+    ((8, 65536), [1], False),          # four-step: the last pass reads rows and writes strided
+    ((2, 1 << 20), [1], False),        # two 1024-point passes (the c4 passes)
+    ((16, 1024), [1], False),          # contiguous rows in and out
+    ((512, 32, 16), [0], False),       # strided axis, 512-point lines
+    ((64, 128, 256), [0, 1, 2], False),  # last pass on the generic tile kernel (64-point lines)
+    ((512, 512, 4), [0, 1], False),
+    ((8, 2048), [1], True),            # real source: loss term in a pass of its own
+    ((6, 40), [], False),              # nothing to transform
+])
+def test_fused_fft_entry_point(nd, shape, dims, real_src):
+    """endia_b200_fft_c2c_fused: the result equals the plain transform's (times the device scale),
+    and both loss terms equal float64 sums over it, whichever kernel runs the last pass."""
+    import ctypes as C
+    from endia_b200 import _lib
+    from endia_b200._array import stream, alloc
+    r = rng(len(shape) + shape[-1])
+    x = r.standard_normal(shape).astype(np.float32) if real_src else crandn(r, shape)
+    w = r.uniform(-1, 1, shape).astype(np.float32)
+    X, W = nd.Array(x), nd.Array(w)
+    Y0, Y1 = nd.Array(list(shape), is_complex=True), nd.Array(list(shape), is_complex=True)
+    G, L = nd.Array(np.array([0.75], np.float32)), nd.Array([1])
+    cd = (C.c_int32 * max(len(dims), 1))(*dims)
+    nb = _lib.lib.endia_b200_fft_scratch_bytes(X.desc(), cd, len(dims))
+    scratch = alloc(nb // 4 + 1) if nb else None
+    sp = scratch.data_ptr() if scratch is not None else None
+    keep = alloc(_lib.lib.endia_b200_fft_fusion_scratch_bytes() // 4)
+    for inverse in (0, 1):
+        _lib.call("endia_b200_fft_c2c", X.desc(), Y0.desc(), cd, len(dims), inverse, 0.5, sp, stream())
+        y0 = Y0.to_numpy().astype(np.complex128)
+        for mode in (1, 2):
+            f = _lib.FftFusion()
+            f.scale_dev, f.reduce, f.reduce_scale = G.data_ptr(), mode, 2.0
+            f.reduce_w, f.reduce_out, f.reduce_scratch = W.data_ptr(), L.data_ptr(), keep.data_ptr()
+            _lib.call("endia_b200_fft_c2c_fused", X.desc(), Y1.desc(), cd, len(dims), inverse, 0.5, sp,
+                      C.byref(f), stream())
+            y1 = Y1.to_numpy().astype(np.complex128)
+            assert rel_l2(y1, 0.75 * y0) < 1e-6
+            want = 2.0 * (np.sum(np.abs(y1) ** 2) if mode == 1 else np.sum(y1.real * w))
+            scale = 2.0 * (np.sum(np.abs(y1) ** 2) if mode == 1 else np.sqrt(np.sum((y1.real * w) ** 2)) * 10)
+            assert abs(L.to_numpy()[0] - want) <= 1e-5 * scale, (inverse, mode)
+            _lib.call("endia_b200_fft_loss_term", Y1.desc(), mode, W.data_ptr(), L.data_ptr(), 2.0, keep.data_ptr(),
+                      stream())
+            assert abs(L.to_numpy()[0] - want) <= 1e-5 * scale
+    st = _lib.lib.endia_b200_fft_loss_term(X.desc() if real_src else Y1.desc(), 3, None, L.data_ptr(), 1.0,
+                                           keep.data_ptr(), stream())
+    assert st == _lib.EINVAL
+
+
+def _fft_programs():
+    def c4(L, z, w):
+        X = L.Array(z, requires_grad=True)
+        y = L.fft(X)
+        loss = L.sum(L.square(L.to_abs(y))) * (1.0 / z.shape[-1])
+        loss.backward()
+        return y, X, loss
+
+    def c5(L, z, w):
+        X = L.Array(z, requires_grad=True)
+        y = L.fftn(X)
+        loss = L.sum(L.real(y) * L.Array(w))
+        loss.backward()
+        return y, X, loss
+
+    def c5_mean_inverse(L, z, w):
+        X = L.Array(z, requires_grad=True)
+        y = L.ifftn(X, [0, -1])
+        loss = L.mean(L.Array(w) * L.real(y)) * 3.0
+        loss.backward()
+        return y, X, loss
+    return {"c4": c4, "c5": c5, "c5_mean_inverse": c5_mean_inverse}
+
+
+@pytest.mark.parametrize("prog", ["c4", "c5", "c5_mean_inverse"])
+@pytest.mark.parametrize("shape", [(4, 4096), (16, 64, 256), (2, 1 << 17)])
+def test_fft_loss_chains_fused_equal_eager(nd, prog, shape, monkeypatch):
+    """The two loss chains with their kernels folded into the transforms (the default) against the
+    same program run op by op (state.defer_fft_chains off): result, loss and gradient agree, and the
+    fused form launches only the transforms and the two finishing sums."""
+    from endia_b200.autograd import state
+    r = rng(sum(shape))
+    z, w = crandn(r, shape), r.uniform(-1, 1, shape).astype(np.float32)
+    f = _fft_programs()[prog]
+    count = nd._lib.lib.endia_b200_launch_count
+    monkeypatch.setattr(state, "defer_fft_chains", False)
+    n0 = count()
+    y0, X0, l0 = f(nd, z, w)
+    eager_launches = count() - n0
+    monkeypatch.setattr(state, "defer_fft_chains", True)
+    n0 = count()
+    y1, X1, l1 = f(nd, z, w)
+    fused_launches = count() - n0
+    assert fused_launches <= eager_launches - 3, (fused_launches, eager_launches)
+    assert rel_l2(y1.to_numpy(), y0.to_numpy()) < 1e-6
+    assert rel_l2(X1.grad().to_numpy(), X0.grad().to_numpy()) < 1e-6
+    ref = abs(l0.to_numpy()[0]) if prog == "c4" else np.abs(y0.to_numpy()).max()
+    assert abs(l1.to_numpy()[0] - l0.to_numpy()[0]) <= 1e-5 * max(ref, abs(l0.to_numpy()[0]))
+
+
+def test_deferred_fft_results_behave_like_arrays(nd, oracle):
+    """A deferred transform or chain member gives its values whenever they are asked for: before or
+    after the fused loss, through two losses on one transform (the lazily scaled gradient is then
+    written out and added), under create_graph, and after its input was rewritten in place."""
+    r = rng(77)
+    z, w = crandn(r, (8, 512)), r.uniform(-1, 1, (8, 512)).astype(np.float32)
+    X = nd.Array(z, requires_grad=True)
+    y = nd.fft(X)
+    a = nd.to_abs(y)
+    loss = nd.sum(nd.square(a)) + nd.sum(nd.real(y) * nd.Array(w))
+    assert rel_l2(a.to_numpy(), np.abs(np.fft.fft(z.astype(np.complex128)))) < TOL   # asked for after the fused sum
+    loss.backward()
+    Xo = oracle.Array(z, requires_grad=True)
+    yo = oracle.fft(Xo)
+    lo = oracle.sum(oracle.square(oracle.to_abs(yo))) + oracle.sum(oracle.real(yo) * oracle.Array(w))
+    lo.backward()
+    assert rel_l2(X.grad().to_numpy(), Xo.grad().to_numpy()) < TOL
+    assert abs(loss.to_numpy()[0] - lo.to_numpy()[0]) <= 1e-5 * abs(lo.to_numpy()[0])
+    # create_graph: the fused node's VJP is the composition of differentiable ops
+    X2 = nd.Array(z, requires_grad=True)
+    l2 = nd.sum(nd.square(nd.to_abs(nd.fft(X2))))
+    g = nd.grad(outs=[l2], inputs=[X2], create_graph=True)[0]
+    assert rel_l2(g.to_numpy(), 2 * 512 * z) < TOL
+    # an in-place update of the input runs the pending transform first
+    X3 = nd.Array(z)
+    y3 = nd.fft(X3)
+    X3 -= nd.Array(np.ones((8, 512), np.complex64))
+    assert rel_l2(y3.to_numpy(), np.fft.fft(z.astype(np.complex128))) < TOL
+    assert rel_l2(nd.fft(X3).to_numpy(), np.fft.fft(z.astype(np.complex128) - 1)) < TOL
