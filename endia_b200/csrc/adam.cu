@@ -23,6 +23,7 @@ struct AdamArgs {
   int n;
   float lr, b1, b2, eps, omb1, omb2, c1, c2, gscale;
   // SGD: b1 = momentum, b2 = weight decay. RMSprop: b1 = alpha, omb1 = 1 - alpha. Adagrad: lr, eps.
+  const float *t_dev;            // Adam: the step count lives on the device (c1, c2 are formed there)
 };
 
 enum { OPT_ADAM = 0, OPT_SGD = 1, OPT_SGD_MOMENTUM = 2, OPT_RMSPROP = 3, OPT_ADAGRAD = 4 };
@@ -31,12 +32,13 @@ __device__ __forceinline__ float tf32_lo(float x) {
   return x - __uint_as_float(__float_as_uint(x) & 0xFFFFE000u);
 }
 
-__device__ __forceinline__ void adam_one(float &p, float g, float &m, float &v, const AdamArgs &a) {
+__device__ __forceinline__ void adam_one(float &p, float g, float &m, float &v, const AdamArgs &a, float c1,
+                                         float c2) {
   g *= a.gscale;
   m = a.b1 * m + a.omb1 * g;           // adam.mojo:49-51
   v = a.b2 * v + (a.omb2 * g) * g;     // adam.mojo:52-56, (1-b2)*g*g left to right
-  const float mhat = m / a.c1;         // adam.mojo:57-58
-  const float vhat = v / a.c2;
+  const float mhat = m / c1;           // adam.mojo:57-58
+  const float vhat = v / c2;
   p = p - (a.lr * mhat) / (sqrtf(vhat) + a.eps);  // adam.mojo:61-63
 }
 
@@ -97,7 +99,17 @@ __global__ void __launch_bounds__(256) opt_kernel(const __grid_constant__ AdamAr
   }
 }
 
+// t_dev[0] += 1: the step count of a step that is replayed from a CUDA graph advances on the device.
+__global__ void adam_bump_kernel(float *t_dev) { t_dev[0] += 1.f; }
+
 __global__ void __launch_bounds__(256) adam_kernel(const __grid_constant__ AdamArgs a) {
+  float c1 = a.c1, c2 = a.c2;
+  if (a.t_dev) {
+    // 1 - beta^t with the power correctly rounded to fp32 (evaluated in double), as the host forms it
+    const double t = (double)__ldg(a.t_dev);
+    c1 = 1.f - (float)pow((double)a.b1, t);
+    c2 = 1.f - (float)pow((double)a.b2, t);
+  }
   const int64_t total = a.chunk_start[a.n];
   for (int64_t c = blockIdx.x; c < total; c += gridDim.x) {
     int t = 0;
@@ -117,8 +129,8 @@ __global__ void __launch_bounds__(256) adam_kernel(const __grid_constant__ AdamA
         float4 gg = __ldg(reinterpret_cast<const float4 *>(g + i));
         float4 mm = *reinterpret_cast<float4 *>(m + i);
         float4 vv = *reinterpret_cast<float4 *>(v + i);
-        adam_one(pp.x, gg.x, mm.x, vv.x, a); adam_one(pp.y, gg.y, mm.y, vv.y, a);
-        adam_one(pp.z, gg.z, mm.z, vv.z, a); adam_one(pp.w, gg.w, mm.w, vv.w, a);
+        adam_one(pp.x, gg.x, mm.x, vv.x, a, c1, c2); adam_one(pp.y, gg.y, mm.y, vv.y, a, c1, c2);
+        adam_one(pp.z, gg.z, mm.z, vv.z, a, c1, c2); adam_one(pp.w, gg.w, mm.w, vv.w, a, c1, c2);
         *reinterpret_cast<float4 *>(p + i) = pp;
         *reinterpret_cast<float4 *>(m + i) = mm;
         *reinterpret_cast<float4 *>(v + i) = vv;
@@ -138,7 +150,7 @@ __global__ void __launch_bounds__(256) adam_kernel(const __grid_constant__ AdamA
         }
       }
       for (int64_t i = v1 + threadIdx.x; i < e1; i += 256) {
-        adam_one(p[i], g[i], m[i], v[i], a);
+        adam_one(p[i], g[i], m[i], v[i], a, c1, c2);
         if (lo && !a.lo_is_bf16) {
           lo[i] = tf32_lo(p[i]);
         } else if (lo) {
@@ -149,7 +161,7 @@ __global__ void __launch_bounds__(256) adam_kernel(const __grid_constant__ AdamA
       }
     } else {
       for (int64_t i = e0 + threadIdx.x; i < e1; i += 256) {
-        adam_one(p[i], g[i], m[i], v[i], a);
+        adam_one(p[i], g[i], m[i], v[i], a, c1, c2);
         if (lo && !a.lo_is_bf16) {
           lo[i] = tf32_lo(p[i]);
         } else if (lo) {
@@ -168,13 +180,14 @@ using namespace eb;
 
 static int adam_launch(int32_t n_tensors, float *const *params, const float *const *grads, float *const *m,
                        float *const *v, float *const *p_lo, int lo_is_bf16, const int64_t *numel, float lr,
-                       float beta1, float beta2, float eps, float t, float grad_scale, void *stream) {
+                       float beta1, float beta2, float eps, float t, float grad_scale, void *stream,
+                       float *t_dev = nullptr) {
   int st = require_device();
   if (st) return st;
   EB_REQUIRE(n_tensors >= 0, ENDIA_B200_EINVAL, "adam: negative tensor count");
   if (n_tensors == 0) return ENDIA_B200_OK;
   EB_REQUIRE(params && grads && m && v && numel, ENDIA_B200_EINVAL, "adam: NULL argument array");
-  EB_REQUIRE(t >= 1.f, ENDIA_B200_EINVAL, "adam: step count t starts at 1 (adam.mojo:40)");
+  EB_REQUIRE(t_dev || t >= 1.f, ENDIA_B200_EINVAL, "adam: step count t starts at 1 (adam.mojo:40)");
   for (int i0 = 0; i0 < n_tensors; i0 += ADAM_MAX_TENSORS) {
     AdamArgs a{};
     a.n = 0;
@@ -201,13 +214,28 @@ static int adam_launch(int32_t n_tensors, float *const *params, const float *con
     a.omb2 = 1.f - beta2;
     a.c1 = 1.f - powf(beta1, t);
     a.c2 = 1.f - powf(beta2, t);
+    a.t_dev = t_dev;
     int64_t total = a.chunk_start[a.n];
     int64_t cap = (int64_t)(sm_count() > 0 ? sm_count() : 148) * 8;
     int grid = (int)(total < cap ? total : cap);
     adam_kernel<<<grid, 256, 0, as_stream(stream)>>>(a);
     EB_LAUNCH_CHECK();
   }
+  if (t_dev) {
+    adam_bump_kernel<<<1, 1, 0, as_stream(stream)>>>(t_dev);
+    EB_LAUNCH_CHECK();
+  }
   return ENDIA_B200_OK;
+}
+
+extern "C" int endia_b200_adam_step_multi_graph(int32_t n_tensors, float *const *params,
+                                                const float *const *grads, float *const *m,
+                                                float *const *v, void *const *p16, const int64_t *numel,
+                                                float lr, float beta1, float beta2, float eps, float *t_dev,
+                                                float grad_scale, void *stream) {
+  EB_REQUIRE(t_dev != nullptr, ENDIA_B200_EINVAL, "adam: t_dev is NULL");
+  return adam_launch(n_tensors, params, grads, m, v, reinterpret_cast<float *const *>(p16), 1, numel, lr, beta1,
+                     beta2, eps, 1.f, grad_scale, stream, t_dev);
 }
 
 extern "C" int endia_b200_adam_step_multi_lo(int32_t n_tensors, float *const *params,

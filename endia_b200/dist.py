@@ -158,11 +158,15 @@ class ShardedAdam:
                        slices of m and v are the only optimizer state the rank holds) and over the
                        small tensors (biases), whose gradients are summed by one all-reduce and
                        updated on every rank,
-      all-gather       the updated slices are gathered in place into every rank's parameter,
-                       first layer first; a parameter carries a completion callback
-                       (_array.await_pending) until its gather is done, so the next forward pass
-                       waits layer by layer and the later gathers run beside it. The callback also
-                       rewrites the parameter's GEMM operand parts (one pass over the weights).
+      all-gather       the updated slices are gathered in place into every rank's parameter when
+                       the parameters are next used: after step() a sharded parameter carries a
+                       completion callback (_array.await_pending); the first one that runs starts
+                       the gathers of all of them (first layer first) on the communicator's
+                       stream, and each consumer waits for its own parameter only, so the forward
+                       pass runs beside the later gathers. The callback also rewrites the
+                       parameter's GEMM operand parts (one pass over the weights). A step is
+                       thereby self-contained (gathers, forward, backward, reduce-scatters,
+                       update), which is what lets it be captured as one CUDA graph.
 
     The arithmetic per element is optim.Adam's (endia/optim/adam.mojo:47-65) with the mean over
     the ranks folded into the gradient scale; the bytes on NVLink are those of the all-reduce it
@@ -187,6 +191,8 @@ class ShardedAdam:
         self.small = []           # (index, gradient) of the replicated tensors of this pass
         self.flat_small = None
         self._ready = {}
+        self._gathers = None      # all-gathers of the last step, once launched
+        self._t_dev = None
         for p in self.params:
             p.grad_hook = self._hook
 
@@ -252,6 +258,8 @@ class ShardedAdam:
         from . import _lib
         from ._array import stream
         self.t = 1.0
+        if self._t_dev is not None:
+            _lib.call("endia_b200_fill", self._t_dev.data_ptr(), 1, 0, 1.0, 0.0, stream())
         for i, p in enumerate(self.params):
             for st in (self.m[i], self.v[i]):
                 if not self.sharded[i]:
@@ -298,6 +306,8 @@ class ShardedAdam:
         for w in self.pending:
             w.wait()
         self.pending = []
+        for p in self.params:       # a gather of the last step that no consumer has waited for
+            await_pending(p)
         P, G, M, V, numel = [], [], [], [], []
         for i, p in enumerate(self.params):
             if self.sharded[i]:
@@ -319,39 +329,87 @@ class ShardedAdam:
             M.append(self.m[i].data_ptr())
             V.append(self.v[i].data_ptr())
         arr = lambda xs: (C.c_void_p * n)(*xs)
-        _lib.call("endia_b200_adam_step_multi", n, arr(P), arr(G), arr(M), arr(V), (C.c_int64 * n)(*numel),
-                  self.lr, self.beta1, self.beta2, self.eps, self.t, self.grad_scale, stream())
-        # gather the updated slices, first layer first; consumers wait per parameter
+        t_dev = getattr(self, "_t_dev", None)
+        if t_dev is not None:
+            _lib.call("endia_b200_adam_step_multi_graph", n, arr(P), arr(G), arr(M), arr(V), None,
+                      (C.c_int64 * n)(*numel), self.lr, self.beta1, self.beta2, self.eps, t_dev.data_ptr(),
+                      self.grad_scale, stream())
+        else:
+            _lib.call("endia_b200_adam_step_multi", n, arr(P), arr(G), arr(M), arr(V), (C.c_int64 * n)(*numel),
+                      self.lr, self.beta1, self.beta2, self.eps, self.t, self.grad_scale, stream())
+        # The updated slices are gathered when the parameters are next used (first layer first):
+        # every sharded parameter carries a completion callback until then.
         for i, p in enumerate(self.params):
             p._tf32_lo = None
             if not self.sharded[i]:
                 p._pair16 = None
                 continue
-            k = p.size() // self.world
-            full = flat_tensor(p)
-            work = dist.all_gather_into_tensor(full, full[k * self.rank:k * (self.rank + 1)], group=self.group,
-                                               async_op=True)
             wants_parts = p.ndim() == 2 and p.size() % 8 == 0 and p.size() >= 128 * 128
             if wants_parts and getattr(p, "_pair16", None) is None:
                 p._pair16 = alloc(p.size())
             if not wants_parts:
                 p._pair16 = None
             p._parts_ptr = None      # the parts are stale until the callback has rewritten them
-            p._pending = self._completion(p, work, wants_parts)
+            p._pending = self._completion(i, wants_parts)
+        self._gathers = None
         self._ready = {}
         self.small = []
-        self.t += 1.0
+        if not (torch.cuda.is_available() and torch.cuda.is_current_stream_capturing()):
+            self.t += 1.0     # (a step being captured is not run; after_replay counts its replays)
 
-    @staticmethod
-    def _completion(p, work, wants_parts):
+    def _launch_gathers(self):
+        """All-gather of every sharded parameter's updated slices, in parameter order, on the
+        communicator's stream (in place: rank r's slice is already where it belongs)."""
+        if self._gathers is not None:
+            return
+        self._gathers = {}
+        for i, p in enumerate(self.params):
+            if not self.sharded[i]:
+                continue
+            k = p.size() // self.world
+            full = p.buf[:p.size()]
+            self._gathers[i] = dist.all_gather_into_tensor(full, full[k * self.rank:k * (self.rank + 1)],
+                                                           group=self.group, async_op=True)
+
+    def _completion(self, i, wants_parts):
+        p = self.params[i]
+
         def done():
             from . import _lib
             from ._array import stream
-            work.wait()              # the compute stream waits for this parameter's gather
+            self._launch_gathers()
+            self._gathers[i].wait()          # the compute stream waits for this parameter's gather only
             if wants_parts:
                 _lib.call("endia_b200_bf16_split", p.buf.data_ptr(), p._pair16.data_ptr(), p.size(), stream())
                 p._parts_ptr = p.buf.data_ptr()
         return done
+
+    def sync(self):
+        """Complete every parameter on this rank now (collective: every rank calls it). After a
+        step a sharded parameter is whole on a rank once its gather has run, which the next use
+        of the parameter on ALL ranks starts; code that reads parameters on one rank only calls
+        this first."""
+        for p in self.params:
+            await_pending(p)
+
+    # ---- steps replayed from a CUDA graph (utils.CapturedStep(..., optimizers=[self])) -----------
+    def begin_capture(self):
+        from .functional.init_ops import full
+        self._t_dev = full([1], self.t)
+
+    def end_capture(self):
+        self._t_dev = None
+
+    def after_replay(self):
+        """A replayed step has run the update on the device; the host-side state follows: the step
+        count, and the completion callbacks of the sharded parameters (the gathers of the new
+        slices are the first thing the next replay, or the next use on the host, does)."""
+        self.t += 1.0
+        for i, p in enumerate(self.params):
+            if self.sharded[i]:
+                p._parts_ptr = None
+                p._pending = self._completion(i, getattr(p, "_pair16", None) is not None)
+        self._gathers = None
 
 
 def data_parallel_adam(params, lr=0.001, beta1=0.9, beta2=0.999, eps=1e-8, group=None, mode=None):

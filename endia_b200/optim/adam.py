@@ -15,9 +15,25 @@ class Adam:
         self.v = [Array(p.shape()) for p in self.params]
         self.grad_scale = 1.0  # folded into the gradient read (1/world_size under data parallelism)
 
+    # ---- steps replayed from a CUDA graph (utils.CapturedStep(..., optimizers=[self])) -----------
+    def begin_capture(self):
+        """The step count moves to a device float (a host value would be frozen in the graph); called
+        by CapturedStep before it captures."""
+        from ..functional.init_ops import full
+        self._t_dev = full([1], self.t)
+
+    def end_capture(self):
+        """Steps enqueued op by op again (the host count is kept current by after_replay)."""
+        self._t_dev = None
+
+    def after_replay(self):
+        self.t += 1.0
+
     def reset_state(self):
         """Zero moments with the parameters' shapes and t = 1, as after construction."""
         self.t = 1.0
+        if getattr(self, "_t_dev", None) is not None:
+            _lib.call("endia_b200_fill", self._t_dev.data_ptr(), 1, 0, 1.0, 0.0, stream())
         for i, p in enumerate(self.params):
             for st in (self.m[i], self.v[i]):
                 st.array_shape_ = ArrayShape(p.shape())
@@ -58,12 +74,19 @@ class Adam:
                 p._pair16 = None
                 parts.append(None)
         P16 = (C.c_void_p * n)(*parts)
-        _lib.call("endia_b200_adam_step_multi_bf16", n, P, G, M, V, P16, numel, self.lr, self.beta1, self.beta2,
-                  self.eps, self.t, self.grad_scale, stream())
+        t_dev = getattr(self, "_t_dev", None)
+        if t_dev is not None:
+            _lib.call("endia_b200_adam_step_multi_graph", n, P, G, M, V, P16, numel, self.lr, self.beta1,
+                      self.beta2, self.eps, t_dev.data_ptr(), self.grad_scale, stream())
+        else:
+            _lib.call("endia_b200_adam_step_multi_bf16", n, P, G, M, V, P16, numel, self.lr, self.beta1,
+                      self.beta2, self.eps, self.t, self.grad_scale, stream())
         # m and v take the broadcast shape of (state, grad): a bias gradient is (1, N), so the
         # moments become (1, N) while the parameter keeps (N) (adam.mojo:49-56, expand_op.mojo:121-126).
         for i, g in enumerate(grads):
             shp = broadcast_shapes(self.m[i].shape(), g.shape())
             self.m[i].array_shape_ = ArrayShape(shp)
             self.v[i].array_shape_ = ArrayShape(shp)
-        self.t += 1.0
+        import torch
+        if not torch.cuda.is_current_stream_capturing():
+            self.t += 1.0     # (a step being captured is not run; after_replay counts its replays)

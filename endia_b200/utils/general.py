@@ -98,18 +98,30 @@ class CapturedStep:
     to the ~25 us of host work per launch (the create_graph=True double-backward step has about
     110 launches) becomes GPU-bound this way."""
 
-    def __init__(self, fn, warmup=2):
+    def __init__(self, fn, warmup=2, optimizers=()):
+        """`optimizers`: the optimizers whose step() runs inside fn. Their step count changes from
+        step to step, so it moves to the device for the capture (begin_capture / end_capture) and
+        the host copy is advanced after every replay (after_replay)."""
         import torch
         from .._array import device
         device()
+        self.optimizers = list(optimizers)
         for _ in range(warmup):
             fn()
         torch.cuda.synchronize()
         from .. import _lib
+        for opt in self.optimizers:
+            opt.begin_capture()
+        torch.cuda.synchronize()
         before = _lib.lib.endia_b200_launch_count()
         self.graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(self.graph):
-            self.out = fn()
+        try:
+            with torch.cuda.graph(self.graph):
+                self.out = fn()
+        except BaseException:
+            for opt in self.optimizers:
+                opt.end_capture()
+            raise
         torch.cuda.synchronize()
         # kernels of this library inside the graph (endia_b200_launch_count only sees enqueues)
         self.launches_per_replay = int(_lib.lib.endia_b200_launch_count() - before)
@@ -118,4 +130,12 @@ class CapturedStep:
     def __call__(self):
         self.graph.replay()
         self.replays += 1
+        for opt in self.optimizers:
+            opt.after_replay()
         return self.out
+
+    def release(self):
+        """Back to op-by-op steps: the optimizers count on the host again."""
+        for opt in self.optimizers:
+            opt.end_capture()
+        self.optimizers = []
