@@ -6,6 +6,6 @@ from ._lib import EndiaError
 from ._array import Array, Tensor, ndarray, ArrayShape
 from .functional import *  # noqa: F401,F403
 from .functional import sum, abs, pow, complex  # noqa: F401  (shadow builtins on purpose, as Endia does)
-from .autograd.functional import backward, jacrev, grad, jacobian, hessian, value_and_grad, Callable
+from .autograd.functional import backward, jacrev, grad, jacobian, hessian, value_and_grad, Callable, jvp
 from . import nn, optim
 from .autograd import state as config

@@ -68,9 +68,11 @@ OK, EINVAL, ECUDA, ENODEV, ENOMEM, ESHAPE, EPOW2, ETIMEOUT, ELIMIT = 0, -1, -2, 
 ACT_NONE, ACT_RELU, ACT_TANH, ACT_SIGMOID = 0, 1, 2, 3
 GEMM_AUTO, GEMM_FFMA, GEMM_3XTF32, GEMM_TF32_BF16X2 = 0, 1, 2, 3
 (UN_COPY, UN_NEG, UN_RELU, UN_TANH, UN_SIGMOID, UN_SQUARE, UN_SQRT, UN_ABS, UN_SIGN, UN_CONJ,
- UN_EXP, UN_LOG, UN_SIN, UN_COS, UN_RECIPROCAL) = range(15)
+ UN_EXP, UN_LOG, UN_SIN, UN_COS, UN_RECIPROCAL, UN_SINH, UN_COSH, UN_TAN, UN_ASIN, UN_ACOS,
+ UN_ATAN) = range(21)
 (BIN_ADD, BIN_SUB, BIN_MUL, BIN_DIV, BIN_POW, BIN_GREATER, BIN_RELU_BWD, BIN_TANH_BWD,
- BIN_SIGMOID_BWD, BIN_COMPLEX, BIN_ABS_BWD, BIN_SQUARE_BWD) = range(12)
+ BIN_SIGMOID_BWD, BIN_COMPLEX, BIN_ABS_BWD, BIN_SQUARE_BWD, BIN_GREATER_EQUAL, BIN_LESS,
+ BIN_LESS_EQUAL, BIN_EQUAL, BIN_NOT_EQUAL) = range(17)
 
 _vp, _i64, _i32, _f32, _sz = C.c_void_p, C.c_int64, C.c_int32, C.c_float, C.c_size_t
 _TP = C.POINTER(Tensor)
@@ -84,7 +86,9 @@ SIGNATURES = {
     "endia_b200_has_tcgen05": (C.c_int, []),
     "endia_b200_launch_count": (C.c_uint64, []),
     "endia_b200_device_status": (C.c_int, [_vp]),
+    "endia_b200_selftest_wait_timeout": (C.c_int, [_i32, _vp]),
     "endia_b200_malloc": (C.c_int, [C.POINTER(_vp), _sz, _vp]),
+    "endia_b200_set_malloc_quota": (C.c_int, [_sz]),
     "endia_b200_free": (C.c_int, [_vp, _vp]),
     "endia_b200_memset0": (C.c_int, [_vp, _sz, _vp]),
     "endia_b200_h2d": (C.c_int, [_vp, _vp, _sz, _vp]),
@@ -110,6 +114,7 @@ SIGNATURES = {
     "endia_b200_eye": (C.c_int, [_vp, _i64, _vp]),
     "endia_b200_reduce_scratch_bytes": (_sz, [_TP, C.c_uint32]),
     "endia_b200_reduce_add": (C.c_int, [_TP, C.c_uint32, _vp, _vp, _vp]),
+    "endia_b200_reduce_mul": (C.c_int, [_TP, C.c_uint32, _vp, _vp, _vp]),
     "endia_b200_mse_scratch_bytes": (_sz, [_i64]),
     "endia_b200_mse_fwd_bwd": (C.c_int, [_vp, _vp, _i64, _f32, _vp, _vp, _vp, _vp]),
     "endia_b200_mse_fwd_bwd_noalloc": (C.c_int, [_vp, _vp, _i64, _f32, _vp, _vp, _vp]),

@@ -63,6 +63,28 @@ def jacrev(arg, create_graph=False):
         reset_node_id_recursive(out)
 
 
+def jvp(out, inputs, tangents):
+    """Forward mode: the tangent of `out` for the given tangents of `inputs`, by one walk over the
+    graph in evaluation order that calls every node's `jvp` rule (the slot the reference's ops fill,
+    e.g. tanh_op.mojo:56-73; the reference has no driver that calls them). Nodes that do not depend
+    on `inputs` have a zero tangent."""
+    from ..functional.init_ops import zeros_like
+    tan = {id(x): t for x, t in zip(inputs, tangents)}
+    for node in top_order(out):
+        node.id = -1
+        if id(node) in tan or not node.args_:
+            continue
+        ts = [tan.get(id(a)) for a in node.args_]
+        if all(t is None for t in ts):
+            continue
+        if node.jvp_ is None:
+            raise ValueError("jvp: op %r has no forward-mode rule" % (node.name,))
+        ts = [t if t is not None else zeros_like(a) for t, a in zip(ts, node.args_)]
+        tan[id(node)] = node.jvp_(node.args_, ts)
+    res = tan.get(id(out))
+    return res if res is not None else zeros_like(out)
+
+
 def grad(outs=None, inputs=None, retain_grads=True, create_graph=False, argnums=(-1,)):
     """Two forms, as in the reference:
       grad(outs=[...], inputs=[...], retain_grads, create_graph) -> list of gradient Arrays

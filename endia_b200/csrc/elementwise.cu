@@ -45,6 +45,12 @@ __device__ __forceinline__ float un_real(float x) {
   if constexpr (OP == ENDIA_B200_UN_SIN) return sinf(x);
   if constexpr (OP == ENDIA_B200_UN_COS) return cosf(x);
   if constexpr (OP == ENDIA_B200_UN_RECIPROCAL) return 1.f / x;
+  if constexpr (OP == ENDIA_B200_UN_SINH) return sinhf(x);                // sinh_op.mojo:108
+  if constexpr (OP == ENDIA_B200_UN_COSH) return coshf(x);                // cosh_op.mojo:109
+  if constexpr (OP == ENDIA_B200_UN_TAN) return tanf(x);                  // tan_op.mojo:101
+  if constexpr (OP == ENDIA_B200_UN_ASIN) return asinf(x);                // asin_op.mojo:103
+  if constexpr (OP == ENDIA_B200_UN_ACOS) return acosf(x);                // acos_op.mojo:111
+  if constexpr (OP == ENDIA_B200_UN_ATAN) return atanf(x);                // atan_op.mojo:105
   return x;
 }
 
@@ -63,6 +69,11 @@ __device__ __forceinline__ float bin_real(float a, float b) {
     return u * cosf(3.14159265358979323846f * b);
   }
   if constexpr (OP == ENDIA_B200_BIN_GREATER) return a > b ? 1.f : 0.f;  // greater_op.mojo:55-60
+  if constexpr (OP == ENDIA_B200_BIN_GREATER_EQUAL) return a >= b ? 1.f : 0.f;   // greater_equal_op.mojo
+  if constexpr (OP == ENDIA_B200_BIN_LESS) return a < b ? 1.f : 0.f;             // less_op.mojo
+  if constexpr (OP == ENDIA_B200_BIN_LESS_EQUAL) return a <= b ? 1.f : 0.f;      // less_equal_op.mojo
+  if constexpr (OP == ENDIA_B200_BIN_EQUAL) return a == b ? 1.f : 0.f;           // equal_op.mojo
+  if constexpr (OP == ENDIA_B200_BIN_NOT_EQUAL) return a != b ? 1.f : 0.f;       // not_equal_op.mojo
   if constexpr (OP == ENDIA_B200_BIN_RELU_BWD) return a > 0.f ? b : 0.f;  // relu_op.mojo:95
   if constexpr (OP == ENDIA_B200_BIN_TANH_BWD) {                          // tanh_op.mojo:92
     float t = tanhf(a);
@@ -113,6 +124,21 @@ __device__ __forceinline__ c32 un_cplx(c32 z) {
   if constexpr (OP == ENDIA_B200_UN_RECIPROCAL) {
     float d = z.re * z.re + z.im * z.im;
     r.re = z.re / d; r.im = -z.im / d;
+  }
+  if constexpr (OP == ENDIA_B200_UN_SINH) {   // sinh_op.mojo:108-109
+    r.re = sinhf(z.re) * cosf(z.im); r.im = coshf(z.re) * sinf(z.im);
+  }
+  if constexpr (OP == ENDIA_B200_UN_COSH) {   // cosh_op.mojo:109-110
+    r.re = coshf(z.re) * cosf(z.im); r.im = sinhf(z.re) * sinf(z.im);
+  }
+  // tan, acos and atan act on the real part and give a zero imaginary part, asin uses the
+  // reference's own pair of formulas (tan_op.mojo:101-102, acos_op.mojo:111-112,
+  // atan_op.mojo:105-106, asin_op.mojo:103-104)
+  if constexpr (OP == ENDIA_B200_UN_TAN) { r.re = tanf(z.re); r.im = 0.f; }
+  if constexpr (OP == ENDIA_B200_UN_ACOS) { r.re = acosf(z.re); r.im = 0.f; }
+  if constexpr (OP == ENDIA_B200_UN_ATAN) { r.re = atanf(z.re); r.im = 0.f; }
+  if constexpr (OP == ENDIA_B200_UN_ASIN) {
+    r.re = asinf(z.re) * coshf(z.im); r.im = -acosf(z.re) * sinhf(z.im);
   }
   return r;
 }
@@ -374,6 +400,8 @@ int endia_b200_ew_unary(int op, const endia_b200_tensor *in, const endia_b200_te
     EB_CASE(ENDIA_B200_UN_SQRT) EB_CASE(ENDIA_B200_UN_ABS) EB_CASE(ENDIA_B200_UN_SIGN)
     EB_CASE(ENDIA_B200_UN_CONJ) EB_CASE(ENDIA_B200_UN_EXP) EB_CASE(ENDIA_B200_UN_LOG)
     EB_CASE(ENDIA_B200_UN_SIN) EB_CASE(ENDIA_B200_UN_COS) EB_CASE(ENDIA_B200_UN_RECIPROCAL)
+    EB_CASE(ENDIA_B200_UN_SINH) EB_CASE(ENDIA_B200_UN_COSH) EB_CASE(ENDIA_B200_UN_TAN)
+    EB_CASE(ENDIA_B200_UN_ASIN) EB_CASE(ENDIA_B200_UN_ACOS) EB_CASE(ENDIA_B200_UN_ATAN)
 #undef EB_CASE
   }
   return ENDIA_B200_EINVAL;
@@ -413,6 +441,8 @@ int endia_b200_ew_binary(int op, const endia_b200_tensor *a, const endia_b200_te
     EB_CASE(ENDIA_B200_BIN_RELU_BWD) EB_CASE(ENDIA_B200_BIN_TANH_BWD)
     EB_CASE(ENDIA_B200_BIN_SIGMOID_BWD) EB_CASE(ENDIA_B200_BIN_COMPLEX)
     EB_CASE(ENDIA_B200_BIN_ABS_BWD) EB_CASE(ENDIA_B200_BIN_SQUARE_BWD)
+    EB_CASE(ENDIA_B200_BIN_GREATER_EQUAL) EB_CASE(ENDIA_B200_BIN_LESS) EB_CASE(ENDIA_B200_BIN_LESS_EQUAL)
+    EB_CASE(ENDIA_B200_BIN_EQUAL) EB_CASE(ENDIA_B200_BIN_NOT_EQUAL)
 #undef EB_CASE
   }
   return ENDIA_B200_EINVAL;

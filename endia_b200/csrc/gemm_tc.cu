@@ -62,11 +62,23 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 // Bounded wait: false (and the status flag set) when the phase never completes.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int code) {
-  for (uint32_t it = 0; it < TC_WAIT_LIMIT; ++it)
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int code,
+                                          uint32_t limit = TC_WAIT_LIMIT) {
+  for (uint32_t it = 0; it < limit; ++it)
     if (mbar_try_wait(bar, parity)) return true;
   atomicCAS(&g_tc_status, 0, code);
   return false;
+}
+
+// Self-test of the give-up path: one thread waits, with the wait above and a limit of `polls`, on a
+// barrier that nothing ever arrives at. The wait runs out, records code 99 and the kernel returns.
+__global__ void wait_selftest_kernel(uint32_t polls) {
+  __shared__ __align__(8) uint64_t bar;
+  if (threadIdx.x == 0) {
+    mbar_init(smem_u32(&bar), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    mbar_wait(smem_u32(&bar), 0, 99, polls);
+  }
 }
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, uint32_t bar,
                                             int c0, int c1) {
@@ -1240,6 +1252,15 @@ int tc_status_and_clear(cudaStream_t s) {
 
 
 extern "C" int endia_b200_has_tcgen05(void) { return eb::encode_fn() != nullptr ? 1 : 0; }
+
+extern "C" int endia_b200_selftest_wait_timeout(int32_t polls, void *stream) {
+  int st = eb::require_device();
+  if (st) return st;
+  EB_REQUIRE(polls >= 1 && polls <= (1 << 20), ENDIA_B200_EINVAL, "selftest_wait_timeout: polls must be in [1, 2^20]");
+  eb::wait_selftest_kernel<<<1, 32, 0, eb::as_stream(stream)>>>((uint32_t)polls);
+  EB_LAUNCH_CHECK();
+  return ENDIA_B200_OK;
+}
 
 extern "C" int endia_b200_device_status(void *stream) {
   int st = eb::require_device();

@@ -18,6 +18,7 @@ struct RedParams {
   int64_t n_out, n_red;
   int splits;
   int64_t red_per_split;
+  int mul;              // 1: product instead of sum (reduce_mul_op.mojo)
 };
 
 __device__ __forceinline__ int64_t offs(const int64_t *shape, const int64_t *stride, int n,
@@ -53,6 +54,27 @@ __device__ __forceinline__ float block_sum(float v) {
   return r;
 }
 
+// Product over the warp / the CTA, same shape as the sums above.
+__device__ __forceinline__ float warp_prod(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v *= __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float block_prod(float v) {
+  __shared__ float warp_part[32];
+  v = warp_prod(v);
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  __syncthreads();
+  if (lane == 0) warp_part[w] = v;
+  __syncthreads();
+  float r = 1.f;
+  if (w == 0) {
+    r = lane < (int)(blockDim.x >> 5) ? warp_part[lane] : 1.f;
+    r = warp_prod(r);
+  }
+  return r;
+}
+
 // GROUP threads cooperate on one (output element, split): GROUP = 256 (a CTA), 32 (a warp) or 1.
 template <int GROUP>
 __global__ void __launch_bounds__(256) reduce_generic_kernel(RedParams p) {
@@ -63,8 +85,17 @@ __global__ void __launch_bounds__(256) reduce_generic_kernel(RedParams p) {
   for (int64_t gbase = (int64_t)blockIdx.x * groups_per_cta; gbase < n_groups;
        gbase += (int64_t)gridDim.x * groups_per_cta) {
     const int64_t g = gbase + g_in_cta;
-    float acc = 0.f;
-    if (g < n_groups) {
+    float acc = p.mul ? 1.f : 0.f;
+    if (g < n_groups && p.mul) {
+      const int64_t o = g / p.splits;
+      const int s = (int)(g - o * p.splits);
+      const int64_t base = offs(p.kshape, p.kstride, p.nk, o);
+      const int64_t r0 = (int64_t)s * p.red_per_split;
+      int64_t r1 = r0 + p.red_per_split;
+      if (r1 > p.n_red) r1 = p.n_red;
+      for (int64_t r = r0 + t_in_g; r < r1; r += GROUP)
+        acc *= p.in[base + offs(p.rshape, p.rstride, p.nr, r)];
+    } else if (g < n_groups) {
       const int64_t o = g / p.splits;
       const int s = (int)(g - o * p.splits);
       const int64_t base = offs(p.kshape, p.kstride, p.nk, o);
@@ -91,10 +122,10 @@ __global__ void __launch_bounds__(256) reduce_generic_kernel(RedParams p) {
       }
     }
     if constexpr (GROUP == 256) {
-      acc = block_sum(acc);
+      acc = p.mul ? block_prod(acc) : block_sum(acc);
       if (threadIdx.x == 0 && g < n_groups) p.dst[g] = acc;
     } else if constexpr (GROUP == 32) {
-      acc = warp_sum(acc);
+      acc = p.mul ? warp_prod(acc) : warp_sum(acc);
       if (t_in_g == 0 && g < n_groups) p.dst[g] = acc;
     } else {
       if (g < n_groups) p.dst[g] = acc;
@@ -102,13 +133,13 @@ __global__ void __launch_bounds__(256) reduce_generic_kernel(RedParams p) {
   }
 }
 
-// out[o] = sum_s partial[o*splits + s], sequential in s.
+// out[o] = sum_s partial[o*splits + s] (or the product, mul = 1), sequential in s.
 __global__ void __launch_bounds__(256)
-reduce_finish_kernel(const float *partial, float *out, int64_t n_out, int splits, float scale) {
+reduce_finish_kernel(const float *partial, float *out, int64_t n_out, int splits, float scale, int mul = 0) {
   const int64_t step = (int64_t)gridDim.x * blockDim.x;
   for (int64_t o = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; o < n_out; o += step) {
-    float acc = 0.f;
-    for (int s = 0; s < splits; ++s) acc += partial[o * splits + s];
+    float acc = mul ? 1.f : 0.f;
+    for (int s = 0; s < splits; ++s) acc = mul ? acc * partial[o * splits + s] : acc + partial[o * splits + s];
     out[o] = acc * scale;
   }
 }
@@ -312,7 +343,7 @@ struct RedPlan {
   size_t scratch_bytes;
 };
 
-static int make_plan(const endia_b200_tensor *in, uint32_t axes_mask, RedPlan &pl) {
+static int make_plan(const endia_b200_tensor *in, uint32_t axes_mask, RedPlan &pl, bool generic_only = false) {
   int st = check_tensor(in, "reduce_add: in");
   if (st) return st;
   // Float view of the input: complex arrays get an extra kept (re, im) dim.
@@ -349,8 +380,8 @@ static int make_plan(const endia_b200_tensor *in, uint32_t axes_mask, RedPlan &p
   pl.colsum = false;
   pl.scratch_bytes = 0;
   // Column-sum fast path: one reduced dim, innermost kept dim contiguous and inside it.
-  if (p.nr == 1 && p.nk >= 1 && p.nk <= 2 && p.kstride[p.nk - 1] == 1 && p.kshape[p.nk - 1] >= 32 &&
-      p.n_red > 1) {
+  if (!generic_only && p.nr == 1 && p.nk >= 1 && p.nk <= 2 && p.kstride[p.nk - 1] == 1 &&
+      p.kshape[p.nk - 1] >= 32 && p.n_red > 1) {
     pl.C = p.kshape[p.nk - 1];
     pl.R = p.rshape[0]; pl.r_stride = p.rstride[0];
     pl.A = p.nk == 2 ? p.kshape[0] : 1;
@@ -409,23 +440,40 @@ using namespace eb;
 extern "C" {
 
 size_t endia_b200_reduce_scratch_bytes(const endia_b200_tensor *in, uint32_t axes_mask) {
-  RedPlan pl;
-  if (make_plan(in, axes_mask, pl)) return 0;
-  return pl.scratch_bytes;
+  // (enough for the sum and for the product, which always takes the generic kernel)
+  RedPlan pl, pg;
+  if (make_plan(in, axes_mask, pl) || make_plan(in, axes_mask, pg, true)) return 0;
+  return pl.scratch_bytes > pg.scratch_bytes ? pl.scratch_bytes : pg.scratch_bytes;
 }
+
+static int reduce_impl(const endia_b200_tensor *in, uint32_t axes_mask, float *out, void *scratch,
+                       void *stream, int mul);
 
 int endia_b200_reduce_add(const endia_b200_tensor *in, uint32_t axes_mask, float *out, void *scratch,
                           void *stream) {
+  return reduce_impl(in, axes_mask, out, scratch, stream, 0);
+}
+
+int endia_b200_reduce_mul(const endia_b200_tensor *in, uint32_t axes_mask, float *out, void *scratch,
+                          void *stream) {
+  EB_REQUIRE(in && !in->is_complex, ENDIA_B200_EINVAL, "reduce_mul: real arrays only");
+  return reduce_impl(in, axes_mask, out, scratch, stream, 1);
+}
+
+static int reduce_impl(const endia_b200_tensor *in, uint32_t axes_mask, float *out, void *scratch,
+                       void *stream, int mul) {
   int st = require_device();
   if (st) return st;
   RedPlan pl;
-  if ((st = make_plan(in, axes_mask, pl))) return st;
+  if ((st = make_plan(in, axes_mask, pl, mul != 0))) return st;
+  pl.p.mul = mul;
   if (pl.p.n_out == 0) return ENDIA_B200_OK;
   EB_REQUIRE(out != nullptr, ENDIA_B200_EINVAL, "reduce_add: out is NULL");
   EB_REQUIRE(pl.scratch_bytes == 0 || scratch != nullptr, ENDIA_B200_EINVAL,
              "reduce_add: %zu bytes of scratch are required", pl.scratch_bytes);
   cudaStream_t s = as_stream(stream);
   if (pl.p.n_red == 0) {
+    if (mul) return endia_b200_fill(out, pl.p.n_out, 0, 1.f, 0.f, stream);     // the empty product
     EB_CUDA(cudaMemsetAsync(out, 0, sizeof(float) * pl.p.n_out, s));
     return ENDIA_B200_OK;
   }
@@ -463,11 +511,11 @@ int endia_b200_reduce_add(const endia_b200_tensor *in, uint32_t axes_mask, float
   }
   EB_LAUNCH_CHECK();
   if (p.splits > 1) {
-    if (p.n_out == 1)
+    if (p.n_out == 1 && !mul)
       scalar_finish_kernel<<<1, 256, 0, s>>>(static_cast<const float *>(scratch), out, p.splits, 1.f);
     else
       reduce_finish_kernel<<<grid_for(p.n_out, 256), 256, 0, s>>>(static_cast<const float *>(scratch),
-                                                                  out, p.n_out, p.splits, 1.f);
+                                                                  out, p.n_out, p.splits, 1.f, mul);
     EB_LAUNCH_CHECK();
   }
   return ENDIA_B200_OK;

@@ -2,6 +2,8 @@
 // The reference keeps every Array in host memory (endia/_array/_array.mojo:125-131); these
 // entry points are what a device-resident Node needs instead.
 #include "common.cuh"
+#include <mutex>
+#include <unordered_map>
 #include <string.h>
 #include <atomic>
 
@@ -102,12 +104,31 @@ const char *endia_b200_last_error(void) { return g_err; }
 int endia_b200_version(void) { return 1000; }
 uint64_t endia_b200_launch_count(void) { return eb::launches(); }
 
+// Bytes handed out by endia_b200_malloc and not yet freed, and the optional quota on them.
+static std::mutex g_alloc_mutex;
+static std::unordered_map<void *, size_t> g_alloc_sizes;
+static size_t g_alloc_live = 0, g_alloc_quota = 0;
+
+int endia_b200_set_malloc_quota(size_t bytes) {
+  std::lock_guard<std::mutex> lock(g_alloc_mutex);
+  g_alloc_quota = bytes;
+  return ENDIA_B200_OK;
+}
+
 int endia_b200_malloc(void **ptr, size_t bytes, void *stream) {
   EB_REQUIRE(ptr != nullptr, ENDIA_B200_EINVAL, "malloc: ptr is NULL");
   int st = require_device();
   if (st) return st;
   *ptr = nullptr;
   if (bytes == 0) return ENDIA_B200_OK;
+  {
+    std::lock_guard<std::mutex> lock(g_alloc_mutex);
+    if (g_alloc_quota && g_alloc_live + bytes > g_alloc_quota) {
+      set_error("device allocation of %zu bytes refused: %zu bytes are live and the quota is %zu", bytes,
+                g_alloc_live, g_alloc_quota);
+      return ENDIA_B200_ENOMEM;
+    }
+  }
   cudaError_t e = cudaMallocAsync(ptr, bytes, as_stream(stream));
   if (e == cudaErrorMemoryAllocation) {
     cudaGetLastError();
@@ -115,10 +136,21 @@ int endia_b200_malloc(void **ptr, size_t bytes, void *stream) {
     return ENDIA_B200_ENOMEM;
   }
   EB_CUDA(e);
+  std::lock_guard<std::mutex> lock(g_alloc_mutex);
+  g_alloc_sizes[*ptr] = bytes;
+  g_alloc_live += bytes;
   return ENDIA_B200_OK;
 }
 int endia_b200_free(void *ptr, void *stream) {
   if (!ptr) return ENDIA_B200_OK;
+  {
+    std::lock_guard<std::mutex> lock(g_alloc_mutex);
+    auto it = g_alloc_sizes.find(ptr);
+    if (it != g_alloc_sizes.end()) {
+      g_alloc_live -= it->second;
+      g_alloc_sizes.erase(it);
+    }
+  }
   EB_CUDA(cudaFreeAsync(ptr, as_stream(stream)));
   return ENDIA_B200_OK;
 }

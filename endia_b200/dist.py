@@ -9,14 +9,16 @@ import torch.distributed as dist
 from ._array import Array, ArrayShape, device, await_pending
 
 
-def init_process_group(nccl_max_ctas=None, gemm_reserve_sms=None):
+def init_process_group(nccl_max_ctas=None, gemm_reserve_sms=None, timeout_s=None):
     """One process per GPU, launched by torchrun (RANK / LOCAL_RANK / WORLD_SIZE / MASTER_*).
 
     A collective that runs beside the persistent GEMM kernels needs SMs of its own: the GEMM grid
     otherwise holds all of them and NCCL's CTAs (or the GEMM's last CTA pairs) wait. The launcher
     states both limits here, before NCCL and the GEMM read them: `nccl_max_ctas` becomes
     NCCL_MAX_CTAS and `gemm_reserve_sms` the number of SMs left out of the persistent GEMM grid
-    (ENDIA_B200_TC_RESERVE_SMS); values already in the environment win, None sets nothing."""
+    (ENDIA_B200_TC_RESERVE_SMS); values already in the environment win, None sets nothing.
+    `timeout_s` bounds the rendezvous and every later collective: a rank that never joins (or that
+    has left) then ends the others' wait with an exception instead of a hang."""
     world = int(os.environ.get("WORLD_SIZE", "1"))
     if world > 1:
         if nccl_max_ctas is not None:
@@ -25,10 +27,14 @@ def init_process_group(nccl_max_ctas=None, gemm_reserve_sms=None):
             os.environ.setdefault("ENDIA_B200_TC_RESERVE_SMS", str(int(gemm_reserve_sms)))
     if world > 1 and not dist.is_initialized():
         backend = "nccl" if torch.cuda.is_available() else "gloo"
+        kw = {}
+        if timeout_s is not None:
+            import datetime
+            kw["timeout"] = datetime.timedelta(seconds=float(timeout_s))
         if backend == "nccl":
-            dist.init_process_group(backend, device_id=device())
+            dist.init_process_group(backend, device_id=device(), **kw)
         else:
-            dist.init_process_group(backend)
+            dist.init_process_group(backend, **kw)
     return (dist.get_rank(), dist.get_world_size()) if dist.is_initialized() else (0, 1)
 
 

@@ -20,7 +20,7 @@ def _binary_call(opcode):
     return call
 
 
-def binary_op_array(arg0, arg1, name, opcode, vjp):
+def binary_op_array(arg0, arg1, name, opcode, vjp, jvp=None):
     """Expand both args to the broadcast shape (views), then register the op on the expanded
     args (binary_ops/_utils.mojo:57-90)."""
     shape = broadcast_shapes(arg0.shape(), arg1.shape())
@@ -34,7 +34,7 @@ def binary_op_array(arg0, arg1, name, opcode, vjp):
                     and not v.requires_grad() and v.is_contiguous() and v.shape() == u.shape():
                 defer = {"deferred": "rew", "root": u.root, "w": v}
                 break
-    return op_array(ArrayShape(shape), [a0, a1], name, _binary_call(opcode), vjp=vjp, **defer)
+    return op_array(ArrayShape(shape), [a0, a1], name, _binary_call(opcode), vjp=vjp, jvp=jvp, **defer)
 
 
 def _zero():
@@ -71,24 +71,37 @@ def _pow_vjp(primals, grad, out):  # pow_op.mojo:109-115
     return [lhs, rhs]
 
 
+# Forward-mode rules (the `jvp` slot of each op: add_op.mojo, sub_op.mojo, mul_op.mojo, div_op.mojo,
+# pow_op.mojo, matmul_op.mojo): tangents in, tangent out.
+def _div_jvp(p, t):
+    return sub(div(t[0], p[1]), div(mul(p[0], t[1]), mul(p[1], p[1])))
+
+
+def _pow_jvp(p, t):
+    from .unary_ops import log
+    out = pow_to(p[0], p[1])
+    return add(mul(mul(t[0], p[1]), div(out, p[0])), mul(mul(t[1], out), log(p[0])))
+
+
 def add(arg0, arg1):
-    return binary_op_array(arg0, arg1, "add", _lib.BIN_ADD, _add_vjp)
+    return binary_op_array(arg0, arg1, "add", _lib.BIN_ADD, _add_vjp, jvp=lambda p, t: add(t[0], t[1]))
 
 
 def sub(arg0, arg1):
-    return binary_op_array(arg0, arg1, "sub", _lib.BIN_SUB, _sub_vjp)
+    return binary_op_array(arg0, arg1, "sub", _lib.BIN_SUB, _sub_vjp, jvp=lambda p, t: sub(t[0], t[1]))
 
 
 def mul(arg0, arg1):
-    return binary_op_array(arg0, arg1, "mul", _lib.BIN_MUL, _mul_vjp)
+    return binary_op_array(arg0, arg1, "mul", _lib.BIN_MUL, _mul_vjp,
+                           jvp=lambda p, t: add(mul(t[0], p[1]), mul(p[0], t[1])))
 
 
 def div(arg0, arg1):
-    return binary_op_array(arg0, arg1, "div", _lib.BIN_DIV, _div_vjp)
+    return binary_op_array(arg0, arg1, "div", _lib.BIN_DIV, _div_vjp, jvp=_div_jvp)
 
 
 def pow_to(arg0, arg1):
-    return binary_op_array(arg0, arg1, "pow_to", _lib.BIN_POW, _pow_vjp)
+    return binary_op_array(arg0, arg1, "pow_to", _lib.BIN_POW, _pow_vjp, jvp=_pow_jvp)
 
 
 pow = pow_to
@@ -277,4 +290,5 @@ def matmul(arg0, arg1):
     batch, shape = _matmul_shape(arg0.shape(), arg1.shape())
     a0 = expand(arg0, batch + arg0.shape()[-2:], ignore_axes=(-2, -1))
     a1 = expand(arg1, batch + arg1.shape()[-2:], ignore_axes=(-2, -1))
-    return op_array(ArrayShape(shape), [a0, a1], "matmul", _matmul_call, vjp=_matmul_vjp)
+    return op_array(ArrayShape(shape), [a0, a1], "matmul", _matmul_call, vjp=_matmul_vjp,
+                    jvp=lambda p, t: add(matmul(t[0], p[1]), matmul(p[0], t[1])))

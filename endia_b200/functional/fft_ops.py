@@ -183,6 +183,7 @@ def _fft_node(x, dims, norm, inverse):
             run_fft(src, res, d, not inverse, scale * factor, scale_dev=scale_dev)
         return [res]
     res = op_array(ArrayShape(x.shape()), [x], "ifftn" if inverse else "fftn", call, vjp=vjp,
+                   jvp=lambda p, t: (ifftn if inverse else fftn)(t[0], dims_l, norm),     # the transform is linear
                    meta_data=encode_fft_params(dims_l, norm), is_complex_p=True, deferred="fft")
     if isinstance(res, Deferred) and res.pending():
         res._fft_args = (x, d, inverse, scale)

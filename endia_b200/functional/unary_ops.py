@@ -13,8 +13,13 @@ def _unary_call(opcode):
     return call
 
 
-def unary_op_array(arg0, name, opcode, vjp, **defer):
-    return op_array(ArrayShape(arg0.shape()), [arg0], name, _unary_call(opcode), vjp=vjp, **defer)
+def unary_op_array(arg0, name, opcode, vjp, jvp=None, **defer):
+    return op_array(ArrayShape(arg0.shape()), [arg0], name, _unary_call(opcode), vjp=vjp, jvp=jvp, **defer)
+
+
+def _m(a, b):
+    from .binary_ops import mul
+    return mul(a, b)
 
 
 def _fused(opcode, a, b):
@@ -23,7 +28,8 @@ def _fused(opcode, a, b):
 
 
 def neg(arg0):
-    return unary_op_array(arg0, "neg", _lib.UN_NEG, lambda p, g, o: [neg(g)])  # neg_op.mojo:91
+    return unary_op_array(arg0, "neg", _lib.UN_NEG, lambda p, g, o: [neg(g)],     # neg_op.mojo:91
+                          jvp=lambda p, t: neg(t[0]))
 
 
 def _relu_vjp(primals, grad, out):
@@ -38,7 +44,10 @@ def _relu_vjp(primals, grad, out):
 def relu(arg0):
     if arg0.is_complex():
         raise _lib.EndiaError(_lib.EINVAL, "Warning: Relu does not support complex numbers")  # relu_op.mojo:51-52
-    return unary_op_array(arg0, "relu", _lib.UN_RELU, _relu_vjp)
+    def jvp(p, t):
+        from .comparison_ops import greater
+        return _m(greater(p[0], Array([p[0].shape()[-1]])), t[0])
+    return unary_op_array(arg0, "relu", _lib.UN_RELU, _relu_vjp, jvp=jvp)
 
 
 def _tanh_vjp(primals, grad, out):
@@ -50,7 +59,8 @@ def _tanh_vjp(primals, grad, out):
 
 
 def tanh(arg0):
-    return unary_op_array(arg0, "tanh", _lib.UN_TANH, _tanh_vjp)
+    return unary_op_array(arg0, "tanh", _lib.UN_TANH, _tanh_vjp,
+                          jvp=lambda p, t: _m(1.0 - square(tanh(p[0])), t[0]))        # tanh_op.mojo:56-73
 
 
 def _sigmoid_vjp(primals, grad, out):
@@ -64,7 +74,10 @@ def _sigmoid_vjp(primals, grad, out):
 def sigmoid(arg0):
     if arg0.is_complex():
         raise _lib.EndiaError(_lib.EINVAL, "Warning: Sigmoid does not support complex numbers")  # sigmoid_op.mojo:49-50
-    return unary_op_array(arg0, "sigmoid", _lib.UN_SIGMOID, _sigmoid_vjp)
+    def jvp(p, t):
+        sg = sigmoid(p[0])
+        return _m(_m(sg, 1.0 - sg), t[0])
+    return unary_op_array(arg0, "sigmoid", _lib.UN_SIGMOID, _sigmoid_vjp, jvp=jvp)
 
 
 def _square_vjp(primals, grad, out):
@@ -79,16 +92,18 @@ def square(arg0):
     from ._deferred import is_pending
     if is_pending(arg0, "absr"):       # square(to_abs(fft(x))): see _deferred.py
         return unary_op_array(arg0, "square", _lib.UN_SQUARE, _square_vjp, deferred="abs2", root=arg0.root)
-    return unary_op_array(arg0, "square", _lib.UN_SQUARE, _square_vjp)
+    return unary_op_array(arg0, "square", _lib.UN_SQUARE, _square_vjp, jvp=lambda p, t: _m(2.0 * p[0], t[0]))
 
 
 def sqrt(arg0):
     from .binary_ops import div
-    return unary_op_array(arg0, "sqrt", _lib.UN_SQRT, lambda p, g, o: [div(g, 2.0 * sqrt(p[0]))])  # sqrt_op.mojo:91
+    return unary_op_array(arg0, "sqrt", _lib.UN_SQRT, lambda p, g, o: [div(g, 2.0 * sqrt(p[0]))],  # sqrt_op.mojo:91
+                          jvp=lambda p, t: div(t[0], 2.0 * sqrt(p[0])))
 
 
 def conj(arg0):
-    return unary_op_array(arg0, "conj", _lib.UN_CONJ, lambda p, g, o: [conj(g)])  # conj_op.mojo
+    return unary_op_array(arg0, "conj", _lib.UN_CONJ, lambda p, g, o: [conj(g)],  # conj_op.mojo
+                          jvp=lambda p, t: conj(t[0]))
 
 
 def sign(arg0):
@@ -108,7 +123,7 @@ def abs(arg0):
     from ._deferred import is_pending
     if is_pending(arg0, "fft"):
         return unary_op_array(arg0, "abs", _lib.UN_ABS, _abs_vjp, deferred="abs", root=arg0)
-    return unary_op_array(arg0, "abs", _lib.UN_ABS, _abs_vjp)
+    return unary_op_array(arg0, "abs", _lib.UN_ABS, _abs_vjp, jvp=lambda p, t: _m(sign(p[0]), t[0]))
 
 
 def to_abs(arg0):
@@ -119,25 +134,71 @@ def to_abs(arg0):
 
 def exp(arg0):
     from .binary_ops import mul
-    return unary_op_array(arg0, "exp", _lib.UN_EXP, lambda p, g, o: [mul(exp(p[0]), g)])
+    return unary_op_array(arg0, "exp", _lib.UN_EXP, lambda p, g, o: [mul(exp(p[0]), g)],
+                          jvp=lambda p, t: mul(exp(p[0]), t[0]))
 
 
 def log(arg0):
     from .binary_ops import div
-    return unary_op_array(arg0, "log", _lib.UN_LOG, lambda p, g, o: [div(g, p[0])])  # log_op.mojo:91
+    return unary_op_array(arg0, "log", _lib.UN_LOG, lambda p, g, o: [div(g, p[0])],  # log_op.mojo:91
+                          jvp=lambda p, t: div(t[0], p[0]))
 
 
 def sin(arg0):
     from .binary_ops import mul
-    return unary_op_array(arg0, "sin", _lib.UN_SIN, lambda p, g, o: [mul(cos(p[0]), g)])
+    return unary_op_array(arg0, "sin", _lib.UN_SIN, lambda p, g, o: [mul(cos(p[0]), g)],
+                          jvp=lambda p, t: mul(cos(p[0]), t[0]))
 
 
 def cos(arg0):
     from .binary_ops import mul
-    return unary_op_array(arg0, "cos", _lib.UN_COS, lambda p, g, o: [mul(neg(sin(p[0])), g)])
+    return unary_op_array(arg0, "cos", _lib.UN_COS, lambda p, g, o: [mul(neg(sin(p[0])), g)],
+                          jvp=lambda p, t: mul(neg(sin(p[0])), t[0]))
 
 
 def reciprocal(arg0):
     from .binary_ops import div
     return unary_op_array(arg0, "reciprocal", _lib.UN_RECIPROCAL,
-                          lambda p, g, o: [div(neg(g), square(p[0]))])
+                          lambda p, g, o: [div(neg(g), square(p[0]))],
+                          jvp=lambda p, t: div(neg(t[0]), square(p[0])))
+
+
+def sinh(arg0):
+    """vjp cosh(x) * grad (sinh_op.mojo:68, 88)."""
+    return unary_op_array(arg0, "sinh", _lib.UN_SINH, lambda p, g, o: [_m(cosh(p[0]), g)],
+                          jvp=lambda p, t: _m(cosh(p[0]), t[0]))
+
+
+def cosh(arg0):
+    """vjp sinh(x) * grad (cosh_op.mojo:69, 89)."""
+    return unary_op_array(arg0, "cosh", _lib.UN_COSH, lambda p, g, o: [_m(sinh(p[0]), g)],
+                          jvp=lambda p, t: _m(sinh(p[0]), t[0]))
+
+
+def tan(arg0):
+    """vjp grad * (1 + out^2) (tan_op.mojo:81). The jvp is (1 + tan(x)^2) * dx; the reference's line
+    `1 + square(tan(x)) * dx` (tan_op.mojo:65) binds the product first."""
+    return unary_op_array(arg0, "tan", _lib.UN_TAN, lambda p, g, o: [_m(g, 1.0 + square(o))],
+                          jvp=lambda p, t: _m(1.0 + square(tan(p[0])), t[0]))
+
+
+def asin(arg0):
+    """vjp grad / sqrt(1 - x^2) (asin_op.mojo:83); the jvp is the same factor (the reference writes
+    1 / cos(x), asin_op.mojo:67, which is the derivative of another function)."""
+    from .binary_ops import div
+    return unary_op_array(arg0, "asin", _lib.UN_ASIN, lambda p, g, o: [div(g, sqrt(1.0 - square(p[0])))],
+                          jvp=lambda p, t: div(t[0], sqrt(1.0 - square(p[0]))))
+
+
+def acos(arg0):
+    """vjp -grad / sqrt(1 - x^2) (acos_op.mojo:71, 91)."""
+    from .binary_ops import div
+    return unary_op_array(arg0, "acos", _lib.UN_ACOS, lambda p, g, o: [div(neg(g), sqrt(1.0 - square(p[0])))],
+                          jvp=lambda p, t: div(neg(t[0]), sqrt(1.0 - square(p[0]))))
+
+
+def atan(arg0):
+    """vjp grad / (1 + x^2) (atan_op.mojo:69, 85)."""
+    from .binary_ops import div
+    return unary_op_array(arg0, "atan", _lib.UN_ATAN, lambda p, g, o: [div(g, 1.0 + square(p[0]))],
+                          jvp=lambda p, t: div(t[0], 1.0 + square(p[0])))

@@ -53,8 +53,9 @@ def expand(arg0, array_shape, ignore_axes=()):
     if arg0.ndim() == len(target):
         if all(i in ignore or a == t for i, (a, t) in enumerate(zip(arg0.shape(), target))):
             return arg0
+    ig = tuple(ignore_axes)
     return op_array(_expand_shape(arg0, target, ignore_axes), [arg0], "brdcst", _view_call,
-                    vjp=_expand_vjp, is_view=True)
+                    vjp=_expand_vjp, is_view=True, jvp=lambda p, t: expand(t[0], target, ig))
 
 
 broadcast_to = expand
@@ -81,7 +82,8 @@ def permute(arg0, axis):
     shape = ArrayShape([sh[p] for p in perm], [st[p] for p in perm], arg0.storage_offset())
     ax = list(axis)
     return op_array(shape, [arg0], "permute", _view_call,
-                    vjp=lambda primals, grad, out: [permute_inv(grad, ax)], is_view=True)
+                    vjp=lambda primals, grad, out: [permute_inv(grad, ax)], is_view=True,
+                    jvp=lambda p, t: permute(t[0], ax))
 
 
 def permute_inv(arg0, axis):
@@ -94,7 +96,8 @@ def permute_inv(arg0, axis):
         stride[p] = st[i]
     ax = list(axis)
     return op_array(ArrayShape(shape, stride, arg0.storage_offset()), [arg0], "permute_inv", _view_call,
-                    vjp=lambda primals, grad, out: [permute(grad, ax)], is_view=True)
+                    vjp=lambda primals, grad, out: [permute(grad, ax)], is_view=True,
+                    jvp=lambda p, t: permute_inv(t[0], ax))
 
 
 def transpose(arg0, axis1=-1, axis2=-2):
@@ -124,7 +127,8 @@ def squeeze(arg0):
     keep = [i for i in range(len(sh)) if i not in axes]
     shape = ArrayShape([sh[i] for i in keep], [st[i] for i in keep], arg0.storage_offset())
     return op_array(shape, [arg0], "squeeze", _view_call,
-                    vjp=lambda primals, grad, out: [unsqueeze(grad, axes)], is_view=True)
+                    vjp=lambda primals, grad, out: [unsqueeze(grad, axes)], is_view=True,
+                    jvp=lambda p, t: squeeze(t[0]))
 
 
 def unsqueeze(arg0, axis):
@@ -151,7 +155,8 @@ def unsqueeze(arg0, axis):
             if stride[i] == -1:
                 stride[i] = stride[i + 1]
     return op_array(ArrayShape(shape, stride, arg0.storage_offset()), [arg0], "unsqueeze", _view_call,
-                    vjp=lambda primals, grad, out: [squeeze(grad)], is_view=True)
+                    vjp=lambda primals, grad, out: [squeeze(grad)], is_view=True,
+                    jvp=lambda p, t: unsqueeze(t[0], axis))
 
 
 # --------------------------------------------------------------------------- reshape
@@ -173,7 +178,8 @@ def reshape(arg0, shape):
     src = contiguous_op(arg0)
     prim_shape = arg0.shape()
     return op_array(ArrayShape(shape, compute_stride(shape), src.storage_offset()), [src], "reshape",
-                    _view_call, vjp=lambda primals, grad, out: [reshape(grad, prim_shape)], is_view=True)
+                    _view_call, vjp=lambda primals, grad, out: [reshape(grad, prim_shape)], is_view=True,
+                    jvp=lambda p, t: reshape(t[0], shape))
 
 
 view = reshape
@@ -192,7 +198,7 @@ def contiguous_op(arg0):
         c = contiguous(args[0])
         curr.buf = c.buf
     return op_array(ArrayShape(arg0.shape()), [arg0], "contiguous", fwd,
-                    vjp=lambda primals, grad, out: [grad])
+                    vjp=lambda primals, grad, out: [grad], jvp=lambda p, t: t[0])
 
 
 # ------------------------------------------------------------------------ real / imag
@@ -217,7 +223,7 @@ def real(arg0):
         defer = {"deferred": "absr", "root": arg0.root}
     elif is_pending(arg0, "fft"):
         defer = {"deferred": "re", "root": arg0}
-    res = op_array(shape, [arg0], "real", _view_call, vjp=vjp, is_view=True, **defer)
+    res = op_array(shape, [arg0], "real", _view_call, vjp=vjp, is_view=True, jvp=lambda p, t: real(t[0]), **defer)
     res.is_complex_flag = False
     return res
 

@@ -120,7 +120,16 @@ def linear(x, weight, bias=None, activation=None):
         if bias is not None:
             res.append(db if need_db else zero)
         return res
-    res = op_array(ArrayShape([B, N]), args, "linear", call, vjp=vjp)
+    def jvp(primals, tangents):
+        # act'(out) * (dx @ W + x @ dW + db), from the ops the layer stands for
+        z = matmul(primals[0], primals[1])
+        dz = add(matmul(tangents[0], primals[1]), matmul(primals[0], tangents[1]))
+        if bias is not None:
+            z, dz = add(z, primals[2]), add(dz, tangents[2])
+        if not act:
+            return dz
+        return _act_bwd_graph(act, _ACT_FNS[act](z), dz)
+    res = op_array(ArrayShape([B, N]), args, "linear", call, vjp=vjp, jvp=jvp)
     res._lin_act = act
     res._lin_bias = bias
     return res

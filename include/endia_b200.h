@@ -75,11 +75,21 @@ int endia_b200_has_tcgen05(void);
  * wait on barriers never spin without a limit; a wait that runs out records a code, lets the
  * kernel drain and return, and is reported here. */
 int endia_b200_device_status(void *stream);
+/* Self-test of that give-up path: launches one small kernel whose only wait (the library's bounded
+ * barrier wait, limited to `polls` polls, at most 2^20) is on a barrier that nothing arrives at. The
+ * wait runs out, the kernel returns, and the next endia_b200_device_status reports
+ * ENDIA_B200_ETIMEOUT once; the context stays usable. */
+int endia_b200_selftest_wait_timeout(int32_t polls, void *stream);
 
 /* Stream-ordered device memory. Replaces UnsafePointer.alloc/free + memset_zero in
  * Node.__init__/__del__ (endia/_array/_array.mojo:127-128, 177-179) and
  * setup_shape_and_data (endia/functional/_utils.mojo:319-326). */
 int endia_b200_malloc(void **ptr, size_t bytes, void *stream);
+/* Upper bound on the bytes endia_b200_malloc may have live at one time (0 = none, the default). A
+ * request beyond it fails with ENDIA_B200_ENOMEM before the driver is asked: the budget of a host
+ * that shares the device, and the way a caller's out-of-memory handling is exercised without
+ * exhausting a GPU. */
+int endia_b200_set_malloc_quota(size_t bytes);
 int endia_b200_free(void *ptr, void *stream);
 int endia_b200_memset0(void *ptr, size_t bytes, void *stream);
 int endia_b200_h2d(void *dst_dev, const void *src_host, size_t bytes, void *stream);
@@ -195,6 +205,8 @@ enum {
   ENDIA_B200_UN_SQUARE, ENDIA_B200_UN_SQRT, ENDIA_B200_UN_ABS, ENDIA_B200_UN_SIGN,
   ENDIA_B200_UN_CONJ, ENDIA_B200_UN_EXP, ENDIA_B200_UN_LOG, ENDIA_B200_UN_SIN,
   ENDIA_B200_UN_COS, ENDIA_B200_UN_RECIPROCAL,
+  ENDIA_B200_UN_SINH, ENDIA_B200_UN_COSH, ENDIA_B200_UN_TAN, ENDIA_B200_UN_ASIN, ENDIA_B200_UN_ACOS,
+  ENDIA_B200_UN_ATAN,        /* unary_ops/{sinh,cosh,tan,asin,acos,atan}_op.mojo */
   ENDIA_B200_UN_COUNT
 };
 enum {
@@ -208,6 +220,9 @@ enum {
                                   init_ops.mojo:419-433)                                      */
   ENDIA_B200_BIN_ABS_BWD,      /* out = a/|a| * b            Abs.vjp sign(x)*grad, abs_op.mojo:93          */
   ENDIA_B200_BIN_SQUARE_BWD,   /* out = 2*a*b                Square.vjp, square_op.mojo:96                 */
+  /* the other comparisons of comparison_ops/: 1.0 / 0.0, real operands */
+  ENDIA_B200_BIN_GREATER_EQUAL, ENDIA_B200_BIN_LESS, ENDIA_B200_BIN_LESS_EQUAL, ENDIA_B200_BIN_EQUAL,
+  ENDIA_B200_BIN_NOT_EQUAL,
   ENDIA_B200_BIN_COUNT
 };
 
@@ -241,6 +256,11 @@ int endia_b200_eye(float *dst, int64_t n, void *stream);
  * that is 0). Replaces ReduceAdd.__call__ (endia/functional/reduce_ops/reduce_add_op.mojo:65-210). */
 size_t endia_b200_reduce_scratch_bytes(const endia_b200_tensor *in, uint32_t axes_mask);
 int endia_b200_reduce_add(const endia_b200_tensor *in, uint32_t axes_mask, float *out,
+                          void *scratch, void *stream);
+
+/* The same with a product instead of a sum (ReduceMul.__call__,
+ * endia/functional/reduce_ops/reduce_mul_op.mojo); real arrays only. Same scratch size. */
+int endia_b200_reduce_mul(const endia_b200_tensor *in, uint32_t axes_mask, float *out,
                           void *scratch, void *stream);
 
 /* Fused mean-squared-error forward and backward on contiguous [n] buffers:

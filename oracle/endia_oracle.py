@@ -459,6 +459,53 @@ def exp(a):
                   lambda p, g, o: [mul(exp(p[0]), g)])
 
 
+def sin(a):  # sin_op.mojo
+    return _unary(a, "sin", np.sin, lambda r, i: (np.sin(r) * np.cosh(i), np.cos(r) * np.sinh(i)),
+                  lambda p, g, o: [mul(cos(p[0]), g)])
+
+
+def cos(a):  # cos_op.mojo
+    return _unary(a, "cos", np.cos, lambda r, i: (np.cos(r) * np.cosh(i), -np.sin(r) * np.sinh(i)),
+                  lambda p, g, o: [mul(neg(sin(p[0])), g)])
+
+
+def sinh(a):  # sinh_op.mojo:88, 108-109
+    return _unary(a, "sinh", np.sinh, lambda r, i: (np.sinh(r) * np.cos(i), np.cosh(r) * np.sin(i)),
+                  lambda p, g, o: [mul(cosh(p[0]), g)])
+
+
+def cosh(a):  # cosh_op.mojo:89, 109-110
+    return _unary(a, "cosh", np.cosh, lambda r, i: (np.cosh(r) * np.cos(i), np.sinh(r) * np.sin(i)),
+                  lambda p, g, o: [mul(sinh(p[0]), g)])
+
+
+def tan(a):  # tan_op.mojo:81, 101-102 (complex input: real part only)
+    return _unary(a, "tan", np.tan, lambda r, i: (np.tan(r), np.zeros_like(r)),
+                  lambda p, g, o: [mul(g, 1 + square(o))])
+
+
+def asin(a):  # asin_op.mojo:83, 103-104
+    return _unary(a, "asin", np.arcsin, lambda r, i: (np.arcsin(r) * np.cosh(i), -np.arccos(r) * np.sinh(i)),
+                  lambda p, g, o: [div(g, sqrt(1 - square(p[0])))])
+
+
+def acos(a):  # acos_op.mojo:91, 111-112
+    return _unary(a, "acos", np.arccos, lambda r, i: (np.arccos(r), np.zeros_like(r)),
+                  lambda p, g, o: [div(neg(g), sqrt(1 - square(p[0])))])
+
+
+def atan(a):  # atan_op.mojo:85, 105-106
+    return _unary(a, "atan", np.arctan, lambda r, i: (np.arctan(r), np.zeros_like(r)),
+                  lambda p, g, o: [div(g, 1 + square(p[0]))])
+
+
+def reciprocal(a):  # reciprocal_op.mojo
+    def cplx(r, i):
+        d = r * r + i * i
+        return r / d, -i / d
+    return _unary(a, "reciprocal", lambda x: f32(1) / x, cplx, lambda p, g, o: [div(neg(g), square(p[0]))])
+
+
 def conj(a):  # conj_op.mojo:29-63
     return _unary(a, "conj", lambda x: x, lambda r, i: (r, -i), lambda p, g, o: [conj(g)])
 
@@ -509,6 +556,36 @@ def mean(a, axes=None, keepdims=False):  # mean_op.mojo:35-65
     divisor = float(np.float32(a.size() / res.size()))
     out = res / divisor
     return out if keepdims else squeeze(out)
+
+
+def reduce_mul(a, axis):  # reduce_ops/reduce_mul_op.mojo (forward); the VJP is the product's derivative,
+    # expand(grad * out) / x: the reference's own VJP hands the expanded gradient on unchanged (:238-255)
+    nd = a.ndim()
+    axes = sorted(set(x + nd if x < 0 else x for x in axis))
+    x = contiguous(a)
+    val = np.prod(x, axis=tuple(axes), keepdims=True, dtype=np.float32) if axes else x.copy()
+    return op_array(val.astype(np.float32), [a], "reduce_mul",
+                    lambda p, g, o: [div(expand(mul(g, o), p[0].shape()), p[0])])
+
+
+def prod(a):  # prod_op.mojo
+    return squeeze(reduce_mul(a, list(range(a.ndim()))))
+
+
+def variance(a, axes=None, unbiased=True, keepdims=False):  # variance_op.mojo:65-79
+    if axes is None:
+        axes = list(range(a.ndim()))
+    res = reduce_add(a, axes)
+    n = float(np.float32(a.size() / res.size()))
+    divisor = n - 1.0 if unbiased else n
+    mean_res = res / n
+    diff = a - mean_res
+    var = reduce_add(diff * diff, axes) / divisor
+    return var if keepdims else squeeze(var)
+
+
+def std(a, axes=None, unbiased=True, keepdims=False):  # std_op.mojo
+    return sqrt(variance(a, axes, unbiased, keepdims))
 
 
 def mse(pred, target):  # loss_ops/mse_op.mojo:18-20

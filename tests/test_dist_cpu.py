@@ -236,3 +236,29 @@ def test_sharded_adam_reduce_scatter_two_ranks_gloo():
         ret = m.dict()
         mp.spawn(_sharded_worker, args=(world, port, ret), nprocs=world, join=True)
         assert dict(ret) == {0: True, 1: True}
+
+
+def _lonely_worker(port, ret):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK="0", WORLD_SIZE="2")
+    from endia_b200 import dist as ndist
+    import time
+    t0 = time.time()
+    try:
+        ndist.init_process_group(timeout_s=3)
+        ret["outcome"] = "joined"
+    except Exception as exc:      # the rendezvous timed out
+        ret["outcome"] = type(exc).__name__
+    ret["seconds"] = time.time() - t0
+
+
+def test_rendezvous_with_a_missing_rank_times_out():
+    """Host-side failure injection: rank 1 of 2 never starts. With a timeout the other rank's
+    init_process_group ends with an exception after about that long instead of waiting for ever."""
+    port = _free_port()
+    with mp.Manager() as m:
+        ret = m.dict()
+        p = mp.get_context("spawn").Process(target=_lonely_worker, args=(port, ret))
+        p.start()
+        p.join(60)
+        assert not p.is_alive()
+        assert ret["outcome"] != "joined" and ret["seconds"] < 30, dict(ret)

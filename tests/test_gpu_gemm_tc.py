@@ -293,3 +293,22 @@ def test_accumulator_truncation_bias_is_bounded_by_the_run_length(nd, algo_name)
     bias_epi = np.mean((out[rows] - ref) / ref)
     print("mean relative error of a same-sign sum, K = 8192: plain %.2e, with epilogue %.2e" % (bias_plain, bias_epi))
     assert abs(bias_plain) < 2e-5 and abs(bias_epi) < 2e-5
+
+
+def test_bounded_wait_gives_up_and_the_context_stays_usable(nd):
+    """A device-side wait that can never complete (a barrier nothing arrives at, limited to a
+    thousand polls) runs out: the kernel returns, endia_b200_device_status reports ETIMEOUT exactly
+    once, and a tensor-core product afterwards is still correct."""
+    from endia_b200 import _lib
+    from endia_b200._array import stream
+    assert _lib.lib.endia_b200_device_status(stream()) == 0
+    _lib.call("endia_b200_selftest_wait_timeout", 1000, stream())
+    assert _lib.lib.endia_b200_device_status(stream()) == _lib.ETIMEOUT
+    assert b"wait" in _lib.lib.endia_b200_last_error()
+    assert _lib.lib.endia_b200_device_status(stream()) == 0            # reported once, then cleared
+    assert _lib.lib.endia_b200_selftest_wait_timeout(0, stream()) == _lib.EINVAL
+    r = rng(5)
+    a = r.standard_normal((256, 128)).astype(np.float32)
+    b = r.standard_normal((128, 256)).astype(np.float32)
+    out = run_gemm(nd, a, b, 0, 0, _lib.GEMM_TF32_BF16X2)
+    assert max_rel(out, a.astype(np.float64) @ b.astype(np.float64)) < 2e-5

@@ -458,3 +458,69 @@ def test_fused_mse_forward_and_vjps(nd, oracle):
     P, T = nd.Array(p, requires_grad=True), nd.Array(t)
     nd.mse(P, T).backward()
     assert nd._lib.lib.endia_b200_launch_count() - launches0 <= 4   # fill of the seed, two mse kernels
+
+
+@pytest.mark.parametrize("opt_name", ["Adam", "SGD", "RMSprop"])
+def test_checkpoint_resume_is_bit_exact(nd, tmp_path, opt_name):
+    """utils.checkpoint: parameters and optimizer state (Adam's m, v, t with the (1, N) moment shapes
+    of the biases) saved after step k; a fresh network that loads them reproduces step k+1 bit for
+    bit, weights, state and loss."""
+    from endia_b200.utils import checkpoint
+    Ws, bs, x, y = make_mlp_inputs([16, 256, 256, 8], 128, 9)
+    X, Y = nd.Array(x), nd.Array(y)
+
+    def make():
+        W = [nd.Array(w.copy(), requires_grad=True) for w in Ws]
+        B = [nd.Array(b.copy(), requires_grad=True) for b in bs]
+        params = [p for wb in zip(W, B) for p in wb]
+        kw = {"Adam": {}, "SGD": {"momentum": 0.9, "lr": 0.05}, "RMSprop": {}}[opt_name]
+        return params, getattr(nd.optim, opt_name)(params, **kw)
+
+    def step(params, opt):
+        loss = nd.mse(nd.nn.mlp([X, None] + params, activation="tanh"), Y)
+        loss.backward()
+        opt.step()
+        loss.zero_grad()
+        return loss.to_numpy()
+
+    params, opt = make()
+    for _ in range(3):
+        step(params, opt)
+    manifest = checkpoint.save(str(tmp_path / "run"), params, opt)
+    assert manifest["optimizer"]["type"] == opt_name and len(manifest["tensors"]) >= 2 * len(params)
+    want_loss = step(params, opt)
+    want = [p.to_numpy() for p in params]
+    params2, opt2 = make()
+    checkpoint.load(str(tmp_path / "run"), params2, opt2)
+    if opt_name == "Adam":
+        assert opt2.t == 4.0 and opt2.m[1].shape() == [1, 256]
+    got_loss = step(params2, opt2)
+    assert np.array_equal(got_loss, want_loss)
+    for a, b in zip([p.to_numpy() for p in params2], want):
+        assert np.array_equal(a, b)
+    state = "m" if opt_name == "Adam" else ("velocity" if opt_name == "SGD" else "cache")
+    for a, b in zip(getattr(opt2, state), getattr(opt, state)):
+        assert np.array_equal(a.to_numpy(), b.to_numpy())
+    with pytest.raises(nd.EndiaError):
+        checkpoint.load(str(tmp_path / "run"), params2[:-1] + [nd.Array([3])], opt2)
+
+
+def test_torch_bridges(nd):
+    """utils.array_conversions (to_torch / from_torch / is_close, array_conversions.mojo:21-135)."""
+    import torch
+    from endia_b200.utils import array_conversions as ac
+    r = rng(12)
+    x = r.standard_normal((5, 7)).astype(np.float32)
+    z = (r.standard_normal((3, 4)) + 1j * r.standard_normal((3, 4))).astype(np.complex64)
+    X = nd.Array(x, requires_grad=True)
+    t = ac.to_torch(X)
+    assert t.is_cuda and t.requires_grad and np.array_equal(t.detach().cpu().numpy(), x)
+    assert np.array_equal(ac.to_torch(X.T()).detach().cpu().numpy(), x.T)
+    tz = ac.to_torch(nd.Array(z))
+    assert tz.dtype == torch.complex64 and np.array_equal(tz.cpu().numpy(), z)
+    back = ac.from_torch(torch.from_numpy(z))
+    assert back.is_complex() and back.shape() == [3, 4] and np.array_equal(back.to_numpy(), z)
+    assert ac.is_close(nd.tanh(X), torch.tanh(torch.from_numpy(x)))
+    view = ac.to_torch(X, copy=False)
+    view.mul_(2.0)
+    assert np.array_equal(X.to_numpy(), 2 * x)

@@ -29,7 +29,8 @@ def check(results, tol=TOL):
             assert max_rel(g, o) < tol, max_rel(g, o)
 
 
-UNARY = ["neg", "relu", "tanh", "sigmoid", "square", "exp", "conj"]
+UNARY = ["neg", "relu", "tanh", "sigmoid", "square", "exp", "conj", "sin", "cos", "sinh", "cosh", "atan",
+         "reciprocal"]
 
 
 @pytest.mark.parametrize("name", UNARY)
@@ -41,6 +42,98 @@ def test_unary_fwd_grad(nd, oracle, name):
         L.sum(y).backward()
         return [y, X.grad()]
     check(both(nd, oracle, prog, x))
+
+
+@pytest.mark.parametrize("name", ["tan", "asin", "acos"])
+def test_unary_bounded_domain(nd, oracle, name):
+    x = rng(21).uniform(-0.9, 0.9, (2, 30, 40)).astype(np.float32)
+
+    def prog(L, X):
+        y = getattr(L, name)(X)
+        L.sum(y * y).backward()
+        return [y, X.grad()]
+    check(both(nd, oracle, prog, x))
+
+
+@pytest.mark.parametrize("name", ["sinh", "cosh", "tan", "asin", "acos", "atan", "sin", "cos", "reciprocal"])
+def test_unary_catalogue_complex(nd, oracle, name):
+    """The complex forms the reference defines for these ops (tan, acos, atan act on the real part;
+    asin_op.mojo:103-104 has its own pair of formulas)."""
+    r = rng(22)
+    z = (r.uniform(-0.8, 0.8, (5, 17)) + 1j * r.uniform(-0.8, 0.8, (5, 17))).astype(np.complex64)
+
+    def prog(L, Z):
+        return [getattr(L, name)(Z)]
+    check(both(nd, oracle, prog, z), 1e-5)
+
+
+@pytest.mark.parametrize("shape,axes", [((6, 7, 8), [1]), ((128, 40), [0]), ((3, 5000), [1]), ((4, 33), [0, 1])])
+def test_variance_std_prod(nd, oracle, shape, axes):
+    """variance / std (variance_op.mojo:65-79, std_op.mojo) and reduce_mul / prod with their VJPs."""
+    x = rng(23).uniform(0.9, 1.1, shape).astype(np.float32)
+
+    def prog(L, X):
+        v = L.variance(X, axes)
+        sd = L.std(X, axes, unbiased=False, keepdims=True)
+        p = L.reduce_mul(X, axes)
+        L.sum(v).backward()
+        gv = X.grad()
+        X.remove_grad()
+        L.sum(p).backward()
+        return [v, sd, p, gv, X.grad(), L.prod(X) if X.size() < 300 else p]
+    check(both(nd, oracle, prog, x))
+
+
+def test_comparison_ops(nd):
+    a = np.array([[1.0, 2.0, 3.0], [3.0, 2.0, 1.0]], np.float32)
+    b = np.array([2.0, 2.0, 2.0], np.float32)
+    A, B = nd.Array(a), nd.Array(b)
+    for name, fn in [("greater", np.greater), ("greater_equal", np.greater_equal), ("less", np.less),
+                     ("less_equal", np.less_equal), ("equal", np.equal), ("not_equal", np.not_equal)]:
+        got = getattr(nd, name)(A, B)
+        assert got.shape() == [2, 3] and not got.requires_grad()
+        assert np.array_equal(got.to_numpy(), fn(a, b).astype(np.float32)), name
+
+
+def test_forward_mode_matches_reverse_mode(nd):
+    """nd.jvp walks the graph forward through every op's jvp rule; for random tangents t and
+    cotangents g the two modes must agree on <g, J t> (a chain of elementwise ops, broadcasting,
+    reductions, views, a matmul and a fused linear layer; then a transform of a complex array)."""
+    r = rng(24)
+    x = r.uniform(0.3, 0.9, (6, 8)).astype(np.float32)
+    w = r.standard_normal((8, 5)).astype(np.float32)
+    b = r.standard_normal(5).astype(np.float32)
+
+    def f(X, W, Bv):
+        h = nd.nn.linear(nd.tanh(X) * nd.sinh(X) + nd.sqrt(X) / nd.exp(X), W, Bv, "sigmoid")
+        h = nd.matmul(h, W.T()) - nd.atan(X) + nd.reduce_add(nd.square(X), [1])
+        z = nd.reshape(nd.permute(h, [1, 0]), [2, 4, 6])
+        return nd.squeeze(z * z), nd.mean(nd.log(X) + nd.cos(X) * nd.asin(X), [0])
+
+    X, W, Bv = (nd.Array(v, requires_grad=True) for v in (x, w, b))
+    outs = f(X, W, Bv)
+    tx, tw, tb = (r.standard_normal(v.shape).astype(np.float32) for v in (x, w, b))
+    for out in outs:
+        g = r.standard_normal(out.shape()).astype(np.float32)
+        jt = nd.jvp(out, [X, W, Bv], [nd.Array(tx), nd.Array(tw), nd.Array(tb)]).to_numpy()
+        for p in (X, W, Bv):
+            p.remove_grad()
+        nd.sum(out * nd.Array(g)).backward()
+        lhs = float(np.sum(jt.astype(np.float64) * g))
+        rhs = sum(float(np.sum(p.grad().to_numpy().reshape(t.shape).astype(np.float64) * t))
+                  for p, t in ((X, tx), (W, tw), (Bv, tb)))
+        assert abs(lhs - rhs) <= 1e-4 * max(abs(lhs), abs(rhs), 1.0), (lhs, rhs)
+    # y = real(fftn(z)) for complex z: <g, Re F t> = Re <F^H g, t>, and FFTN.vjp returns F^H g
+    z = (r.standard_normal((4, 16)) + 1j * r.standard_normal((4, 16))).astype(np.complex64)
+    t = (r.standard_normal((4, 16)) + 1j * r.standard_normal((4, 16))).astype(np.complex64)
+    g = r.standard_normal((4, 16)).astype(np.float32)
+    Z = nd.Array(z, requires_grad=True)
+    y = nd.real(nd.fftn(Z))
+    jt = nd.jvp(y, [Z], [nd.Array(t)]).to_numpy()
+    nd.sum(y * nd.Array(g)).backward()
+    lhs = float(np.sum(jt.astype(np.float64) * g))
+    rhs = float(np.real(np.vdot(Z.grad().to_numpy().astype(np.complex128), t.astype(np.complex128))))
+    assert abs(lhs - rhs) <= 1e-4 * max(abs(lhs), abs(rhs), 1.0), (lhs, rhs)
 
 
 @pytest.mark.parametrize("name", ["sqrt", "abs", "log", "sign"])
@@ -354,3 +447,26 @@ def test_act_bwd_colsum_writes_operand_parts(nd):
     st = _lib.lib.endia_b200_act_bwd_colsum_parts(_lib.ACT_TANH, H.data_ptr(), G.data_ptr(), DS.data_ptr(), None,
                                                   3, 5, None, parts.data_ptr(), stream())
     assert st == _lib.EINVAL
+
+
+def test_malloc_quota_refuses_without_exhausting_the_device(nd):
+    """Host-injected out-of-memory: with a quota set, endia_b200_malloc refuses a request that
+    would exceed it (ENOMEM, message with the figures), frees give the room back, and an absurd
+    request without a quota fails cleanly with the same status."""
+    from endia_b200 import _lib
+    from endia_b200._array import stream
+    lib = _lib.lib
+    a, b = C.c_void_p(), C.c_void_p()
+    _lib.call("endia_b200_set_malloc_quota", 1 << 20)
+    try:
+        _lib.call("endia_b200_malloc", C.byref(a), 600 << 10, stream())
+        assert lib.endia_b200_malloc(C.byref(b), 600 << 10, stream()) == _lib.ENOMEM
+        assert b.value is None and b"quota" in lib.endia_b200_last_error()
+        _lib.call("endia_b200_free", a, stream())
+        _lib.call("endia_b200_malloc", C.byref(b), 600 << 10, stream())
+        _lib.call("endia_b200_free", b, stream())
+    finally:
+        _lib.call("endia_b200_set_malloc_quota", 0)
+    assert lib.endia_b200_malloc(C.byref(a), 1 << 50, stream()) == _lib.ENOMEM
+    x = nd.Array(np.ones(8, np.float32))
+    assert x.to_numpy().sum() == 8.0          # the context is intact

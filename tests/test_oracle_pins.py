@@ -116,7 +116,9 @@ def test_square_weight_quirk_switch(oracle):
 
 
 UNARY = [("relu", torch.relu), ("tanh", torch.tanh), ("sigmoid", torch.sigmoid),
-         ("square", torch.square), ("neg", torch.neg), ("exp", torch.exp)]
+         ("square", torch.square), ("neg", torch.neg), ("exp", torch.exp),
+         ("sin", torch.sin), ("cos", torch.cos), ("sinh", torch.sinh), ("cosh", torch.cosh),
+         ("atan", torch.atan), ("reciprocal", torch.reciprocal)]
 
 
 @pytest.mark.parametrize("name,tfn", UNARY)
@@ -131,6 +133,47 @@ def test_unary_fwd_and_grad_vs_torch(oracle, name, tfn):
     tout = tfn(tx)
     tout.sum().backward()
     assert mean_rel(out.v, tout.detach().numpy(), 1e-6) < 1e-4
+    assert mean_rel(X.grad().v, tx.grad.numpy(), 1e-6) < 1e-4
+
+
+@pytest.mark.parametrize("name,tfn", [("tan", torch.tan), ("asin", torch.asin), ("acos", torch.acos)])
+def test_bounded_domain_unary_vs_torch(oracle, name, tfn):
+    """tan / asin / acos on (-0.9, 0.9) (tests/test_endia/test_functional/test_unary_ops/)."""
+    eo = oracle
+    x = rng(4).uniform(-0.9, 0.9, (2, 30, 40)).astype(np.float32)
+    X = eo.Array(x, requires_grad=True)
+    out = getattr(eo, name)(X)
+    eo.sum(out).backward()
+    tx = torch.tensor(x, requires_grad=True)
+    tfn(tx).sum().backward()
+    assert mean_rel(out.v, tfn(tx).detach().numpy(), 1e-6) < 1e-4
+    assert mean_rel(X.grad().v, tx.grad.numpy(), 1e-6) < 1e-4
+
+
+def test_variance_std_prod_vs_torch(oracle):
+    """reduce_ops/variance_op.mojo:65-79, std_op.mojo, reduce_mul_op.mojo / prod_op.mojo, forward and grad."""
+    eo = oracle
+    x = rng(5).uniform(0.5, 1.5, (6, 7, 8)).astype(np.float32)
+    for unbiased in (True, False):
+        X = eo.Array(x, requires_grad=True)
+        v = eo.variance(X, [1], unbiased=unbiased)
+        sd = eo.std(X, [0, 2], unbiased=unbiased, keepdims=True)
+        eo.sum(v).backward()
+        tx = torch.tensor(x, requires_grad=True)
+        tv = tx.var(1, unbiased=unbiased)
+        tv.sum().backward()
+        assert v.shape() == [6, 8] and sd.shape() == [1, 7, 1]
+        assert mean_rel(v.v, tv.detach().numpy(), 1e-6) < 1e-4
+        assert mean_rel(X.grad().v, tx.grad.numpy(), 1e-6) < 1e-4
+        assert mean_rel(sd.v, tx.std((0, 2), unbiased=unbiased, keepdim=True).detach().numpy(), 1e-6) < 1e-4
+    X = eo.Array(x, requires_grad=True)
+    p = eo.reduce_mul(X, [1])
+    eo.sum(p).backward()
+    tx = torch.tensor(x, requires_grad=True)
+    tp = tx.prod(1, keepdim=True)
+    tp.sum().backward()
+    assert p.shape() == [6, 1, 8] and eo.prod(X).shape() == [1]
+    assert mean_rel(p.v, tp.detach().numpy(), 1e-6) < 1e-4
     assert mean_rel(X.grad().v, tx.grad.numpy(), 1e-6) < 1e-4
 
 
