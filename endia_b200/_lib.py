@@ -132,7 +132,7 @@ SIGNATURES = {
                                                   _f32, _f32, _f32, _f32, _vp]),
     "endia_b200_adam_step_multi_graph": (C.c_int, [_i32, C.POINTER(_vp), C.POINTER(_vp), C.POINTER(_vp),
                                                    C.POINTER(_vp), C.POINTER(_vp), C.POINTER(_i64), _f32, _f32,
-                                                   _f32, _f32, _vp, _f32, _vp]),
+                                                   _f32, _f32, _vp, _i32, _f32, _vp]),
     "endia_b200_bf16_split": (C.c_int, [_vp, _vp, _i64, _vp]),
     "endia_b200_mlp_small_step": (C.c_int, [_i32, C.POINTER(_i32), _i32, _i32, _vp, _vp] + [C.POINTER(_vp)] * 8 +
                                   [_vp, _i32, _f32, _f32, _f32, _f32, _f32, _vp]),

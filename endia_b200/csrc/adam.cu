@@ -181,7 +181,7 @@ using namespace eb;
 static int adam_launch(int32_t n_tensors, float *const *params, const float *const *grads, float *const *m,
                        float *const *v, float *const *p_lo, int lo_is_bf16, const int64_t *numel, float lr,
                        float beta1, float beta2, float eps, float t, float grad_scale, void *stream,
-                       float *t_dev = nullptr) {
+                       float *t_dev = nullptr, bool bump = true) {
   int st = require_device();
   if (st) return st;
   EB_REQUIRE(n_tensors >= 0, ENDIA_B200_EINVAL, "adam: negative tensor count");
@@ -221,7 +221,7 @@ static int adam_launch(int32_t n_tensors, float *const *params, const float *con
     adam_kernel<<<grid, 256, 0, as_stream(stream)>>>(a);
     EB_LAUNCH_CHECK();
   }
-  if (t_dev) {
+  if (t_dev && bump) {
     adam_bump_kernel<<<1, 1, 0, as_stream(stream)>>>(t_dev);
     EB_LAUNCH_CHECK();
   }
@@ -232,10 +232,17 @@ extern "C" int endia_b200_adam_step_multi_graph(int32_t n_tensors, float *const 
                                                 const float *const *grads, float *const *m,
                                                 float *const *v, void *const *p16, const int64_t *numel,
                                                 float lr, float beta1, float beta2, float eps, float *t_dev,
-                                                float grad_scale, void *stream) {
+                                                int32_t advance, float grad_scale, void *stream) {
   EB_REQUIRE(t_dev != nullptr, ENDIA_B200_EINVAL, "adam: t_dev is NULL");
+  if (n_tensors == 0 && advance) {      // only the count: the tensors of this step went in earlier calls
+    int st = require_device();
+    if (st) return st;
+    adam_bump_kernel<<<1, 1, 0, as_stream(stream)>>>(t_dev);
+    EB_LAUNCH_CHECK();
+    return ENDIA_B200_OK;
+  }
   return adam_launch(n_tensors, params, grads, m, v, reinterpret_cast<float *const *>(p16), 1, numel, lr, beta1,
-                     beta2, eps, 1.f, grad_scale, stream, t_dev);
+                     beta2, eps, 1.f, grad_scale, stream, t_dev, advance != 0);
 }
 
 extern "C" int endia_b200_adam_step_multi_lo(int32_t n_tensors, float *const *params,

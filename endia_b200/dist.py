@@ -155,50 +155,58 @@ class GradAllReducer:
 
 class ShardedAdam:
     """Adam for the batch-sharded training step with the optimizer sharded over the ranks: the sum of
-    the ranks' gradients and the replicated update of optim.Adam become
+    the ranks' gradients and the replicated update of optim.Adam become, per large parameter,
 
-      reduce-scatter   every large gradient is summed over the ranks the moment the backward walk
-                       has produced it (last layer first, beside the remaining backward GEMMs);
-                       rank r receives the r-th 1/P of it,
-      update           ONE multi-tensor launch over this rank's 1/P of every large parameter (its
-                       slices of m and v are the only optimizer state the rank holds) and over the
-                       small tensors (biases), whose gradients are summed by one all-reduce and
-                       updated on every rank,
-      all-gather       the updated slices are gathered in place into every rank's parameter when
-                       the parameters are next used: after step() a sharded parameter carries a
-                       completion callback (_array.await_pending); the first one that runs starts
-                       the gathers of all of them (first layer first) on the communicator's
-                       stream, and each consumer waits for its own parameter only, so the forward
-                       pass runs beside the later gathers. The callback also rewrites the
-                       parameter's GEMM operand parts (one pass over the weights). A step is
-                       thereby self-contained (gathers, forward, backward, reduce-scatters,
-                       update), which is what lets it be captured as one CUDA graph.
+      reduce-scatter   the gradient is summed over the ranks the moment the backward walk has
+                       produced it (last layer first); rank r receives the r-th 1/P of it,
+      update           Adam on this rank's 1/P of the parameter (its slices of m and v are the only
+                       optimizer state the rank holds),
+      all-gather       the updated slices are gathered in place into every rank's parameter, and the
+                       parameter's GEMM operand parts are rewritten (one pass over the weights).
 
-    The arithmetic per element is optim.Adam's (endia/optim/adam.mojo:47-65) with the mean over
-    the ranks folded into the gradient scale; the bytes on NVLink are those of the all-reduce it
-    replaces, the optimizer pass and its state shrink by the number of ranks. `m` and `v` hold
+    pipelined=True (default): the three steps of a layer run as a chain on a side stream of their own
+    as soon as the layer's gradient exists, beside the backward pass of the layers below, so that
+    only the first layer's chain is left when the walk ends; step() updates the bias-sized tensors
+    (one all-reduce, replicated update), joins the chains and advances t. The update of a parameter
+    therefore starts DURING backward(): every backward() must be followed by one step().
+    pipelined=False: backward() only starts the reduce-scatters; step() runs ONE multi-tensor
+    update, and the gathers start when the parameters are next used (each consumer waits for its own
+    parameter: the next forward pass runs beside the later gathers).
+
+    Either way a step is self-contained (every collective it starts is consumed inside it or at the
+    next use of the parameters), which lets it be captured as one CUDA graph. The arithmetic per
+    element is optim.Adam's (endia/optim/adam.mojo:47-65) with the mean over the ranks folded into
+    the gradient scale; the bytes on NVLink are those of the all-reduce it replaces. `m` and `v` hold
     slices for the large parameters (flat, 1/P of the elements) and whole arrays for the small."""
     mode = "sharded"
     SMALL = 1 << 16
 
-    def __init__(self, params, lr=0.001, beta1=0.9, beta2=0.999, eps=1e-8, group=None):
+    def __init__(self, params, lr=0.001, beta1=0.9, beta2=0.999, eps=1e-8, group=None, pipelined=None):
         self.params = list(params)
         self.lr, self.beta1, self.beta2, self.eps = lr, beta1, beta2, eps
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        if pipelined is None:
+            pipelined = os.environ.get("ENDIA_B200_DP_PIPELINE", "1") != "0"
+        self.pipelined = bool(pipelined) and self.world > 1 and torch.cuda.is_available() \
+            and dist.get_backend(group) == "nccl"
         self.t = 1.0
         self.grad_scale = 1.0 / self.world
         self.sharded = [self._shardable(p) for p in self.params]
         self.g_slice = [torch.empty(p.size() // self.world, dtype=torch.float32, device=flat_tensor(p).device)
                         if sh else None for p, sh in zip(self.params, self.sharded)]
         self._m = self._v = None  # moments: allocated (zero) at the first step or first access
-        self.pending = []         # reduce-scatters in flight
+        self.pending = []         # reduce-scatters in flight (not pipelined)
         self.small = []           # (index, gradient) of the replicated tensors of this pass
         self.flat_small = None
         self._ready = {}
-        self._gathers = None      # all-gathers of the last step, once launched
+        self._gathers = None      # all-gathers of the last step, once launched (not pipelined)
+        self._chains = {}         # index -> side stream whose chain of this pass is in flight (pipelined)
+        self._streams = {}
         self._t_dev = None
+        if self.pipelined:
+            self._state()         # zeroed on the compute stream now: the layers' side streams start from it
         for p in self.params:
             p.grad_hook = self._hook
 
@@ -241,8 +249,49 @@ class ShardedAdam:
                 return i
         raise KeyError("ShardedAdam: unknown parameter")
 
+    def _wants_parts(self, p):
+        return p.ndim() == 2 and p.size() % 8 == 0 and p.size() >= 128 * 128
+
+    def _adam(self, indices, grads, stream_ptr, advance):
+        """One multi-tensor launch over the listed parameters: this rank's slice of a sharded one
+        (gradient = its reduce-scatter result), the whole of a replicated one (gradient from `grads`)."""
+        import ctypes as C
+        from . import _lib
+        from .functional._utils import broadcast_shapes
+        P, G, M, V, numel = [], [], [], [], []
+        for i in indices:
+            p = self.params[i]
+            if self.sharded[i]:
+                k = p.size() // self.world
+                P.append(p.buf.data_ptr() + 4 * k * self.rank)
+                G.append(self.g_slice[i].data_ptr())
+                numel.append(k)
+            else:
+                g = grads[i]
+                if g.size() != p.size():
+                    raise _lib.EndiaError(_lib.ESHAPE, "Adam: gradient %s does not match parameter %s" % (
+                        g.shape(), p.shape()))
+                P.append(p.data_ptr())
+                G.append(g.data_ptr())
+                numel.append(p.size())
+                shp = broadcast_shapes(self.m[i].shape(), g.shape())     # (1, N) for a bias, as in optim.Adam
+                self.m[i].array_shape_ = ArrayShape(shp)
+                self.v[i].array_shape_ = ArrayShape(shp)
+            M.append(self.m[i].data_ptr())
+            V.append(self.v[i].data_ptr())
+        n = len(P)
+        arr = lambda xs: (C.c_void_p * max(n, 1))(*xs)
+        if self._t_dev is not None:
+            _lib.call("endia_b200_adam_step_multi_graph", n, arr(P), arr(G), arr(M), arr(V), None,
+                      (C.c_int64 * max(n, 1))(*numel), self.lr, self.beta1, self.beta2, self.eps,
+                      self._t_dev.data_ptr(), 1 if advance else 0, self.grad_scale, stream_ptr)
+        elif n:
+            _lib.call("endia_b200_adam_step_multi", n, arr(P), arr(G), arr(M), arr(V), (C.c_int64 * n)(*numel),
+                      self.lr, self.beta1, self.beta2, self.eps, self.t, self.grad_scale, stream_ptr)
+
     def _hook(self, param, grad):
         from .functional._utils import contiguous
+        from ._array import flush_readers
         i = self._index(param)
         g = contiguous(grad)
         if g is not grad:
@@ -250,8 +299,39 @@ class ShardedAdam:
         if not self.sharded[i]:
             self.small.append((i, g))
             return
-        self.pending.append(self._reduce_scatter(self.g_slice[i], flat_tensor(g)))
         self._ready[i] = True
+        rs = self._reduce_scatter(self.g_slice[i], flat_tensor(g))
+        if not self.pipelined:
+            self.pending.append(rs)
+            return
+        # the layer's chain on its own stream: reduce-scatter -> update of the slice -> all-gather ->
+        # operand parts. The layer's own VJP products (the last readers of the old weights in this
+        # pass) are on the compute stream ahead of the reduce-scatter, which the chain waits for.
+        from . import _lib
+        from ._array import alloc
+        flush_readers(param)
+        side = self._streams.get(i)
+        if side is None:
+            side = self._streams[i] = torch.cuda.Stream(device=flat_tensor(param).device)
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            rs.wait()
+            self._adam([i], None, side.cuda_stream, advance=False)
+            k = param.size() // self.world
+            full = param.buf[:param.size()]
+            ag = dist.all_gather_into_tensor(full, full[k * self.rank:k * (self.rank + 1)], group=self.group,
+                                             async_op=True)
+            ag.wait()
+            param._tf32_lo = None
+            if self._wants_parts(param):
+                if getattr(param, "_pair16", None) is None:
+                    param._pair16 = alloc(param.size())
+                _lib.call("endia_b200_bf16_split", param.buf.data_ptr(), param._pair16.data_ptr(), param.size(),
+                          side.cuda_stream)
+                param._parts_ptr = param.buf.data_ptr()
+            else:
+                param._pair16 = None
+        self._chains[i] = side
 
     def wait(self):
         """Nothing to do before step(): kept so that the step reads like the replicated one."""
@@ -274,11 +354,8 @@ class ShardedAdam:
                     _lib.call("endia_b200_memset0", st.data_ptr(), st.size() * 4, stream())
 
     def step(self):
-        import ctypes as C
-        from . import _lib
         from ._array import stream, alloc, flush_readers
-        from .functional._utils import contiguous, broadcast_shapes
-        n = len(self.params)
+        from .functional._utils import contiguous
         for p in self.params:
             flush_readers(p)
         # gradients that no hook has seen (a parameter outside the graph): zeros, like Array.grad()
@@ -309,58 +386,42 @@ class ShardedAdam:
             for i in idx:
                 self.params[i].grad_(views[i])
             small = views
-        for w in self.pending:
-            w.wait()
-        self.pending = []
-        for p in self.params:       # a gather of the last step that no consumer has waited for
-            await_pending(p)
-        P, G, M, V, numel = [], [], [], [], []
-        for i, p in enumerate(self.params):
-            if self.sharded[i]:
-                k = p.size() // self.world
-                P.append(p.data_ptr() + 4 * k * self.rank)
-                G.append(self.g_slice[i].data_ptr())
-                numel.append(k)
-            else:
-                g = small[i]
-                if g.size() != p.size():
-                    raise _lib.EndiaError(_lib.ESHAPE, "Adam: gradient %s does not match parameter %s" % (
-                        g.shape(), p.shape()))
-                P.append(p.data_ptr())
-                G.append(g.data_ptr())
-                numel.append(p.size())
-                shp = broadcast_shapes(self.m[i].shape(), g.shape())     # (1, N) for a bias, as in optim.Adam
-                self.m[i].array_shape_ = ArrayShape(shp)
-                self.v[i].array_shape_ = ArrayShape(shp)
-            M.append(self.m[i].data_ptr())
-            V.append(self.v[i].data_ptr())
-        arr = lambda xs: (C.c_void_p * n)(*xs)
-        t_dev = getattr(self, "_t_dev", None)
-        if t_dev is not None:
-            _lib.call("endia_b200_adam_step_multi_graph", n, arr(P), arr(G), arr(M), arr(V), None,
-                      (C.c_int64 * n)(*numel), self.lr, self.beta1, self.beta2, self.eps, t_dev.data_ptr(),
-                      self.grad_scale, stream())
+        capturing = torch.cuda.is_available() and torch.cuda.is_current_stream_capturing()
+        if self.pipelined:
+            # the replicated tensors here (and the step count), then the layers' chains join
+            self._adam(sorted(small), small, stream(), advance=True)
+            for i in small:
+                self.params[i]._tf32_lo = None
+                self.params[i]._pair16 = None
+            main = torch.cuda.current_stream()
+            for side in self._chains.values():
+                main.wait_stream(side)
+            self._chains = {}
         else:
-            _lib.call("endia_b200_adam_step_multi", n, arr(P), arr(G), arr(M), arr(V), (C.c_int64 * n)(*numel),
-                      self.lr, self.beta1, self.beta2, self.eps, self.t, self.grad_scale, stream())
-        # The updated slices are gathered when the parameters are next used (first layer first):
-        # every sharded parameter carries a completion callback until then.
-        for i, p in enumerate(self.params):
-            p._tf32_lo = None
-            if not self.sharded[i]:
-                p._pair16 = None
-                continue
-            wants_parts = p.ndim() == 2 and p.size() % 8 == 0 and p.size() >= 128 * 128
-            if wants_parts and getattr(p, "_pair16", None) is None:
-                p._pair16 = alloc(p.size())
-            if not wants_parts:
-                p._pair16 = None
-            p._parts_ptr = None      # the parts are stale until the callback has rewritten them
-            p._pending = self._completion(i, wants_parts)
-        self._gathers = None
+            for w in self.pending:
+                w.wait()
+            self.pending = []
+            for p in self.params:       # a gather of the last step that no consumer has waited for
+                await_pending(p)
+            self._adam(list(range(len(self.params))), small, stream(), advance=True)
+            # The updated slices are gathered when the parameters are next used (first layer first):
+            # every sharded parameter carries a completion callback until then.
+            for i, p in enumerate(self.params):
+                p._tf32_lo = None
+                if not self.sharded[i]:
+                    p._pair16 = None
+                    continue
+                wants = self._wants_parts(p)
+                if wants and getattr(p, "_pair16", None) is None:
+                    p._pair16 = alloc(p.size())
+                if not wants:
+                    p._pair16 = None
+                p._parts_ptr = None      # the parts are stale until the callback has rewritten them
+                p._pending = self._completion(i, wants)
+            self._gathers = None
         self._ready = {}
         self.small = []
-        if not (torch.cuda.is_available() and torch.cuda.is_current_stream_capturing()):
+        if not capturing:
             self.t += 1.0     # (a step being captured is not run; after_replay counts its replays)
 
     def _launch_gathers(self):
@@ -391,10 +452,10 @@ class ShardedAdam:
         return done
 
     def sync(self):
-        """Complete every parameter on this rank now (collective: every rank calls it). After a
-        step a sharded parameter is whole on a rank once its gather has run, which the next use
+        """Complete every parameter on this rank now (collective: every rank calls it). Without the
+        pipeline a sharded parameter is whole on a rank once its gather has run, which the next use
         of the parameter on ALL ranks starts; code that reads parameters on one rank only calls
-        this first."""
+        this first. (With the pipeline step() leaves the parameters complete.)"""
         for p in self.params:
             await_pending(p)
 
@@ -408,9 +469,12 @@ class ShardedAdam:
 
     def after_replay(self):
         """A replayed step has run the update on the device; the host-side state follows: the step
-        count, and the completion callbacks of the sharded parameters (the gathers of the new
-        slices are the first thing the next replay, or the next use on the host, does)."""
+        count and, without the pipeline, the completion callbacks of the sharded parameters (the
+        gathers of the new slices are the first thing the next replay, or the next use on the host,
+        does)."""
         self.t += 1.0
+        if self.pipelined:
+            return
         for i, p in enumerate(self.params):
             if self.sharded[i]:
                 p._parts_ptr = None

@@ -77,7 +77,7 @@ class Adam:
         t_dev = getattr(self, "_t_dev", None)
         if t_dev is not None:
             _lib.call("endia_b200_adam_step_multi_graph", n, P, G, M, V, P16, numel, self.lr, self.beta1,
-                      self.beta2, self.eps, t_dev.data_ptr(), self.grad_scale, stream())
+                      self.beta2, self.eps, t_dev.data_ptr(), 1, self.grad_scale, stream())
         else:
             _lib.call("endia_b200_adam_step_multi_bf16", n, P, G, M, V, P16, numel, self.lr, self.beta1,
                       self.beta2, self.eps, self.t, self.grad_scale, stream())

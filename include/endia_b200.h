@@ -352,11 +352,13 @@ int endia_b200_adam_step_multi_bf16(int32_t n_tensors, float *const *params, con
 /* endia_b200_adam_step_multi_bf16 for a step that is replayed from a CUDA graph, where a host value
  * of t would be frozen at capture: t is read from t_dev[0] (a device float, >= 1) when the kernel
  * runs, the bias corrections 1 - beta^t are formed on the device (the power in double, rounded to
- * fp32), and a second one-thread launch adds 1 to t_dev[0]. `p16` may be NULL or hold NULL entries. */
+ * fp32), and, with `advance` != 0, a second one-thread launch adds 1 to t_dev[0] (a step whose
+ * tensors go in several calls advances with the last one; n_tensors = 0 only advances).
+ * `p16` may be NULL or hold NULL entries. */
 int endia_b200_adam_step_multi_graph(int32_t n_tensors, float *const *params, const float *const *grads,
                                      float *const *m, float *const *v, void *const *p16,
                                      const int64_t *numel, float lr, float beta1, float beta2, float eps,
-                                     float *t_dev, float grad_scale, void *stream);
+                                     float *t_dev, int32_t advance, float grad_scale, void *stream);
 
 /* The other optimizers of the reference as single multi-tensor launches, same conventions as
  * endia_b200_adam_step_multi (flat numel per tensor, gradients multiplied by grad_scale first):
