@@ -48,6 +48,7 @@ class Epilogue(C.Structure):
         ("b_lo", C.c_void_p),
         ("a16", C.c_void_p),
         ("b16", C.c_void_p),
+        ("c16", C.c_void_p),
     ]
 
 

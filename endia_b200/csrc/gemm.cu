@@ -48,6 +48,12 @@ int endia_b200_gemm(int trans_a, int trans_b, int64_t M, int64_t N, int64_t K, c
     p.epi.ld_dact = epi->ld_dact;
     p.a_lo = epi->a_lo; p.b_lo = epi->b_lo;
     p.a16 = epi->a16; p.b16 = epi->b16;
+    if (epi->c16) {
+      EB_REQUIRE(batch == 1 && ldc == N && (M * N) % 8 == 0 && aligned16(C) && aligned16(epi->c16), ENDIA_B200_EINVAL,
+                 "gemm: c16 needs batch == 1, ldc == N, M*N %% 8 == 0 and 16-byte aligned C and c16");
+      p.epi.c16 = epi->c16;
+      p.epi.c16_lo = M * N;
+    }
     EB_REQUIRE(epi->act >= 0 && epi->act <= ENDIA_B200_ACT_SIGMOID && epi->dact >= 0 &&
                    epi->dact <= ENDIA_B200_ACT_SIGMOID, ENDIA_B200_EINVAL, "gemm: unknown activation");
     EB_REQUIRE(epi->dact == 0 || (epi->dact_src && epi->ld_dact >= N), ENDIA_B200_EINVAL,
@@ -78,11 +84,24 @@ int endia_b200_gemm(int trans_a, int trans_b, int64_t M, int64_t N, int64_t K, c
   }
   // rows of C per partial column sum: 32 in the two-CTA tensor-core kernel, 128 in the FFMA kernel
   int tile_m = (use_tc && colsum) ? 32 : 128;
-  if (!use_tc && algo == ENDIA_B200_GEMM_AUTO && skinny_gemm_supported(p, trans_b, batch))
-    return launch_gemm_skinny(p, trans_a, trans_b, s);
-  if (use_tc) st = launch_gemm_tc(p, trans_a, trans_b, s);
-  else st = launch_gemm_ffma(p, trans_a, trans_b, batch, s);
+  bool c16_written = false;
+  void *c16 = p.epi.c16;
+  if (!use_tc && algo == ENDIA_B200_GEMM_AUTO && skinny_gemm_supported(p, trans_b, batch)) {
+    p.epi.c16 = nullptr;
+    if ((st = launch_gemm_skinny(p, trans_a, trans_b, s))) return st;
+    if (c16) return launch_bf16_split(C, c16, static_cast<char *>(c16) + 2 * M * N, 1, M * N, M * N, M * N, s);
+    return ENDIA_B200_OK;
+  }
+  if (use_tc) {
+    st = launch_gemm_tc(p, trans_a, trans_b, s, &c16_written);
+  } else {
+    p.epi.c16 = nullptr;
+    st = launch_gemm_ffma(p, trans_a, trans_b, batch, s);
+  }
   if (st) return st;
+  if (c16 && !c16_written &&      // a kernel without that epilogue ran: one pass over C
+      (st = launch_bf16_split(C, c16, static_cast<char *>(c16) + 2 * M * N, 1, M * N, M * N, M * N, s)))
+    return st;
   if (colsum) return launch_colsum_finish(p.epi.colsum_partial, colsum, N, (int)ceil_div(M, tile_m), 1, s);
   return ENDIA_B200_OK;
 }

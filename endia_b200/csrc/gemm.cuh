@@ -11,6 +11,10 @@ struct EpiParams {
   const float *dact_src;
   int64_t ld_dact;
   float *colsum_partial;  // [row tiles (x batch), N] partial column sums, or NULL
+  // optional: the bf16 split of the stored values (bf16(c) at c16[m*ldc + n], bf16(c - tf32(c)) at
+  // c16[c16_lo + m*ldc + n], in bf16 elements), written by the two-CTA kernel's epilogue
+  void *c16;
+  int64_t c16_lo;
 };
 
 struct GemmParams {
@@ -77,7 +81,7 @@ int launch_splitk_finish(const GemmParams &p, int splits, cudaStream_t s);
 // tcgen05 3xTF32 path: true when the shape/alignment is one it handles.
 bool tc_gemm_supported(const GemmParams &p, int trans_a, int trans_b, int64_t batch,
                        bool explicit_request);
-int launch_gemm_tc(const GemmParams &p, int trans_a, int trans_b, cudaStream_t s);
+int launch_gemm_tc(const GemmParams &p, int trans_a, int trans_b, cudaStream_t s, bool *c16_written = nullptr);
 // Scheme GEMM_AUTO uses on the two-CTA kernel (1 unless ENDIA_B200_TC_SCHEME=3xtf32).
 int tc_default_scheme();
 

@@ -479,37 +479,48 @@ __device__ __forceinline__ void tc_epilogue_warp_bulk(uint32_t tmem_base, int q,
                                                       int64_t m0, int64_t n0, int64_t M, int64_t N, const float *Cout,
                                                       int64_t ldc, const EpiParams &epi, const CUtensorMap *cmap,
                                                       uint32_t buf, bool reduce, bool raw = false,
-                                                      bool pre_add = false) {
+                                                      bool pre_add = false, bool with_corr = true) {
+  // with_corr = false: a run before the last one: the correction accumulator keeps running (its
+  // truncation is 2^-11 of the main one's) and only the main accumulator is drained.
   // raw: this is a partial run of a reduction whose epilogue is not linear: the bare sums are
   // stored (or added); pre_add: the last run of such a reduction, which adds what the earlier runs
   // left in C before it applies the epilogue.
   const uint32_t row_addr = tmem_base + ((uint32_t)(q * 32) << 16);
   const bool plain = raw || (epi.alpha == 1.f && !epi.bias && !epi.act && !epi.dact && epi.beta == 0.f &&
-                             !epi.colsum_partial && !pre_add);
+                             !epi.colsum_partial && !pre_add && !epi.c16);
   const bool vec_epi = (!epi.bias || (reinterpret_cast<uintptr_t>(epi.bias) & 15) == 0) &&
                        (!epi.dact || ((reinterpret_cast<uintptr_t>(epi.dact_src) & 15) == 0 && epi.ld_dact % 4 == 0));
   uint32_t ra[32], rb[32];
   const int c4 = lane & 7, rsub = lane >> 3;
   tc_ld32(row_addr + (uint32_t)(c_begin * 32), ra);
-  tc_ld32(row_addr + (uint32_t)(BN + c_begin * 32), rb);
+  if (with_corr) tc_ld32(row_addr + (uint32_t)(BN + c_begin * 32), rb);
 #pragma unroll 1
   for (int c = c_begin; c < c_end; ++c) {
     tc_wait_ld();
     // the previous chunk's store has read the buffer
     if (lane == 0) bulk_wait_read0();
     __syncwarp();
+    if (with_corr) {
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      float4 v;
-      v.x = __uint_as_float(ra[4 * j + 0]) + __uint_as_float(rb[4 * j + 0]);
-      v.y = __uint_as_float(ra[4 * j + 1]) + __uint_as_float(rb[4 * j + 1]);
-      v.z = __uint_as_float(ra[4 * j + 2]) + __uint_as_float(rb[4 * j + 2]);
-      v.w = __uint_as_float(ra[4 * j + 3]) + __uint_as_float(rb[4 * j + 3]);
-      sts128(buf + (uint32_t)lane * 128u + (uint32_t)((j ^ (lane & 7)) * 16), v);
+      for (int j = 0; j < 8; ++j) {
+        float4 v;
+        v.x = __uint_as_float(ra[4 * j + 0]) + __uint_as_float(rb[4 * j + 0]);
+        v.y = __uint_as_float(ra[4 * j + 1]) + __uint_as_float(rb[4 * j + 1]);
+        v.z = __uint_as_float(ra[4 * j + 2]) + __uint_as_float(rb[4 * j + 2]);
+        v.w = __uint_as_float(ra[4 * j + 3]) + __uint_as_float(rb[4 * j + 3]);
+        sts128(buf + (uint32_t)lane * 128u + (uint32_t)((j ^ (lane & 7)) * 16), v);
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float4 v = make_float4(__uint_as_float(ra[4 * j + 0]), __uint_as_float(ra[4 * j + 1]),
+                                     __uint_as_float(ra[4 * j + 2]), __uint_as_float(ra[4 * j + 3]));
+        sts128(buf + (uint32_t)lane * 128u + (uint32_t)((j ^ (lane & 7)) * 16), v);
+      }
     }
     if (c + 1 < c_end) {   // in flight while this chunk is finished and stored
       tc_ld32(row_addr + (uint32_t)((c + 1) * 32), ra);
-      tc_ld32(row_addr + (uint32_t)(BN + (c + 1) * 32), rb);
+      if (with_corr) tc_ld32(row_addr + (uint32_t)(BN + (c + 1) * 32), rb);
     }
     const int64_t nb = n0 + c * 32;
     if (!plain) {
@@ -539,6 +550,30 @@ __device__ __forceinline__ void tc_epilogue_warp_bulk(uint32_t tmem_base, int q,
         }
         cs.x += v.x; cs.y += v.y; cs.z += v.z; cs.w += v.w;
         sts128(a, v);
+        if (epi.c16) {
+          // the operand parts of the stored values, for the products that will read C
+          __nv_bfloat16 *h16 = static_cast<__nv_bfloat16 *>(epi.c16) + m * ldc + n, *l16 = h16 + epi.c16_lo;
+          const float e[4] = {v.x, v.y, v.z, v.w};
+          if (n + 4 <= N) {
+            const __nv_bfloat162 h01 = __floats2bfloat162_rn(e[0], e[1]), h23 = __floats2bfloat162_rn(e[2], e[3]);
+            const __nv_bfloat162 l01 = __floats2bfloat162_rn(e[0] - __uint_as_float(__float_as_uint(e[0]) & 0xFFFFE000u),
+                                                             e[1] - __uint_as_float(__float_as_uint(e[1]) & 0xFFFFE000u));
+            const __nv_bfloat162 l23 = __floats2bfloat162_rn(e[2] - __uint_as_float(__float_as_uint(e[2]) & 0xFFFFE000u),
+                                                             e[3] - __uint_as_float(__float_as_uint(e[3]) & 0xFFFFE000u));
+            uint2 hv, lv;
+            hv.x = *reinterpret_cast<const uint32_t *>(&h01); hv.y = *reinterpret_cast<const uint32_t *>(&h23);
+            lv.x = *reinterpret_cast<const uint32_t *>(&l01); lv.y = *reinterpret_cast<const uint32_t *>(&l23);
+            *reinterpret_cast<uint2 *>(h16) = hv;
+            *reinterpret_cast<uint2 *>(l16) = lv;
+          } else {
+#pragma unroll
+            for (int t = 0; t < 4; ++t)
+              if (n + t < N) {
+                h16[t] = __float2bfloat16_rn(e[t]);
+                l16[t] = __float2bfloat16_rn(e[t] - __uint_as_float(__float_as_uint(e[t]) & 0xFFFFE000u));
+              }
+          }
+        }
       }
       if (epi.colsum_partial) {
         // the bias gradient: sum over the warp's 32 rows (the four lanes that share c4), one
@@ -769,7 +804,8 @@ gemm_tc2p_kernel(const __grid_constant__ TcMaps maps, const GemmParams p, int pa
               const uint64_t ah = a_hi + ks * A_STEP, al = a_lo + ks * A_STEP;
               const uint64_t bh = b_hi + ks * B_STEP, bl = b_lo + ks * B_STEP;
               const uint32_t acc = (kl | ks) ? 1u : 0u;
-              tc_mma_tf32_pair(tmem_base + BN, al, bh, idesc, acc);
+              // (the correction accumulator runs on over the runs of a work item)
+              tc_mma_tf32_pair(tmem_base + BN, al, bh, idesc, (run | kl | ks) ? 1u : 0u);
               tc_mma_tf32_pair(tmem_base + BN, ah, bl, idesc, 1u);
               tc_mma_tf32_pair(tmem_base, ah, bh, idesc, acc);
             }
@@ -780,7 +816,7 @@ gemm_tc2p_kernel(const __grid_constant__ TcMaps maps, const GemmParams p, int pa
             constexpr uint64_t A16_STEP = A_MN ? 128 : 2, B16_STEP = B_MN ? 128 : 2;
 #pragma unroll
             for (int ks = 0; ks < BK / 16; ++ks) {
-              const uint32_t acc = (kl | ks) ? 1u : 0u;
+              const uint32_t acc = (run | kl | ks) ? 1u : 0u;   // (runs on over the runs of a work item)
               tc_mma_bf16_pair(tmem_base + BN, a16l + ks * A16_STEP, b16h + ks * B16_STEP, idesc16, acc);
               tc_mma_bf16_pair(tmem_base + BN, a16h + ks * A16_STEP, b16l + ks * B16_STEP, idesc16, 1u);
             }
@@ -817,7 +853,8 @@ gemm_tc2p_kernel(const __grid_constant__ TcMaps maps, const GemmParams p, int pa
       const bool reduce = kseq_raw ? (run > 0 && !last_run) : (ksplit > 1 || run > 0);
       if (p.vec_c)
         tc_epilogue_warp_bulk<BN>(tmem_base, q, lane, half * CH, (half + 1) * CH, m0, n0, p.M, p.N, p.C, p.ldc,
-                                  p.epi, &maps.c, epi_base + (uint32_t)(warp - 2) * 4096u, reduce, raw, pre_add);
+                                  p.epi, &maps.c, epi_base + (uint32_t)(warp - 2) * 4096u, reduce, raw, pre_add,
+                                  last_run);
       else
         tc_epilogue_warp<BN, false>(tmem_base, q, lane, half * CH, (half + 1) * CH, m0, n0, p.M, p.N, p.C, p.ldc,
                                     p.epi, p.vec_c, epi_base + (uint32_t)(warp - 2) * 4096u);
@@ -1107,7 +1144,9 @@ static int launch_pair_persistent(const TcMaps &maps, const GemmParams &p, int t
   return ENDIA_B200_OK;
 }
 
-int launch_gemm_tc(const GemmParams &p, int trans_a, int trans_b, cudaStream_t s) {
+int launch_gemm_tc(const GemmParams &p_in, int trans_a, int trans_b, cudaStream_t s, bool *c16_written) {
+  GemmParams p = p_in;
+  if (c16_written) *c16_written = false;
   // Operand geometry in memory: A is [M, K] (K-major) or [K, M] (MN-major); B is [K, N] (MN-major,
   // the row-major weight of `x @ W`) or [N, K] (K-major).
   const int64_t a_rows = trans_a ? p.K : p.M, a_cols = trans_a ? p.M : p.K;
@@ -1216,7 +1255,12 @@ int launch_gemm_tc(const GemmParams &p, int trans_a, int trans_b, cudaStream_t s
   }
   // Halving K needs the bulk-store epilogue, a product that is linear in the accumulator and a
   // reduction long enough for the second pass over C to be cheap.
-  const bool linear_epi = !p.epi.bias && !p.epi.act && !p.epi.dact && p.epi.beta == 0.f && !p.epi.colsum_partial;
+  // The operand parts of C are written by the bulk-store epilogue of the two-CTA kernel only (from
+  // the final values, so the epilogue then counts as not linear); elsewhere the caller splits C.
+  if (!(pair && p.vec_c)) p.epi.c16 = nullptr;
+  if (c16_written) *c16_written = p.epi.c16 != nullptr;
+  const bool linear_epi = !p.epi.bias && !p.epi.act && !p.epi.dact && p.epi.beta == 0.f && !p.epi.colsum_partial &&
+                          !p.epi.c16;
   const int ksplit_max = (p.vec_c && linear_epi && p.K >= 4096 && ksplit_mode()) ? 2 : 1;
   // The tensor-core accumulator rounds toward zero, a bias that grows with the number of adds
   // into one accumulator: the reduction runs as ceil(K / run_k) runs whose sums are added in

@@ -53,7 +53,19 @@ def linear(x, weight, bias=None, activation=None):
         epi.alpha, epi.beta, epi.act = 1.0, 0.0, act
         if bias is not None:
             epi.bias = contiguous(a[2]).data_ptr()
+        # The layer's output feeds two products (the next layer's forward and its weight gradient):
+        # when those run on the bf16-compensated kernel, this product's epilogue writes their
+        # operand parts instead of a split kernel later.
+        parts = None
+        if _state.cache_tf32_lo and curr.requires_grad_flag and (B * N) % 8 == 0 and B * N >= (1 << 20):
+            from ..functional.binary_ops import _tc_plan
+            if _tc_plan(B, N, N, 1, _state.gemm_algo) == "pair16":
+                parts = alloc(B * N)
+                epi.c16 = parts.data_ptr()
         gemm_arrays(a[0], a[1], curr, epi=epi)
+        if parts is not None:
+            curr._pair16 = parts
+            curr._parts_ptr = curr.buf.data_ptr()
 
     def vjp(primals, grad, out):
         xp, wp = primals[0], primals[1]

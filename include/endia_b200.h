@@ -158,6 +158,11 @@ typedef struct endia_b200_epilogue {
    * inside the call. */
   const void *a16;
   const void *b16;
+  /* Optional output: the bf16 split of the stored C (endia_b200_bf16_split's layout for the [M, N]
+   * array; needs batch == 1, ldc == N, M*N a multiple of 8), for the products that will read C as an
+   * operand. Written by the two-CTA kernel's epilogue from the values it stores; when another
+   * kernel runs the call ends with one split pass over C, so the parts are valid either way. */
+  void *c16;
 } endia_b200_epilogue;
 
 size_t endia_b200_gemm_colsum_scratch_bytes(int64_t M, int64_t N);

@@ -36,7 +36,7 @@ def test_struct_layout_matches_header():
     from endia_b200 import _lib
     assert C.sizeof(_lib.Tensor) == 8 + 64 + 64 + 8 + 4 + 4
     assert _lib.Tensor.offset.offset == 136
-    assert C.sizeof(_lib.Epilogue) == 88
+    assert C.sizeof(_lib.Epilogue) == 96
 
 
 def test_no_cpu_fallback():

@@ -312,3 +312,30 @@ def test_bounded_wait_gives_up_and_the_context_stays_usable(nd):
     b = r.standard_normal((128, 256)).astype(np.float32)
     out = run_gemm(nd, a, b, 0, 0, _lib.GEMM_TF32_BF16X2)
     assert max_rel(out, a.astype(np.float64) @ b.astype(np.float64)) < 2e-5
+
+
+@pytest.mark.parametrize("M,N,K,algo_name", [(512, 512, 4096, "tf32_bf16x2"), (300, 520, 96, "3xtf32"),
+                                             (256, 128, 64, "3xtf32"), (64, 40, 16, "ffma")])
+def test_epilogue_writes_operand_parts_of_the_output(nd, M, N, K, algo_name):
+    """epi.c16: the bf16 split of the stored C (what the products that read C as an operand need)
+    comes out of the same call, from the two-CTA kernel's epilogue (first two cases: two
+    accumulation runs with the bare-sum round trip, and a single run) or from a split pass where
+    another kernel runs; bit for bit what endia_b200_bf16_split gives on the output."""
+    import torch
+    from endia_b200 import _lib
+    from endia_b200._array import stream, alloc
+    algo = {"3xtf32": _lib.GEMM_3XTF32, "tf32_bf16x2": _lib.GEMM_TF32_BF16X2, "ffma": _lib.GEMM_FFMA}[algo_name]
+    r = rng(M + K)
+    a = r.standard_normal((M, K)).astype(np.float32)
+    b = (r.standard_normal((K, N)) / np.sqrt(K)).astype(np.float32)
+    bias = r.standard_normal(N).astype(np.float32)
+    A, B, BIAS, Cd = nd.Array(a), nd.Array(b), nd.Array(bias), nd.Array([M, N])
+    parts, want = alloc(M * N), alloc(M * N)
+    epi = _lib.Epilogue()
+    epi.alpha, epi.beta, epi.bias, epi.act, epi.c16 = 1.0, 0.0, BIAS.data_ptr(), _lib.ACT_TANH, parts.data_ptr()
+    _lib.call("endia_b200_gemm", 0, 0, M, N, K, A.data_ptr(), K, B.data_ptr(), N, Cd.data_ptr(), N, 1, 0, 0, 0,
+              C.byref(epi), algo, stream())
+    _lib.call("endia_b200_bf16_split", Cd.data_ptr(), want.data_ptr(), M * N, stream())
+    assert torch.equal(parts.view(torch.int32), want.view(torch.int32))
+    ref = np.tanh(a.astype(np.float64) @ b.astype(np.float64) + bias)
+    assert max_rel(Cd.to_numpy(), ref) < 6e-5
