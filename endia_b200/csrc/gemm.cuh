@@ -27,6 +27,7 @@ struct GemmParams {
   // split-K: partial[split][M][ld_partial] receives the raw sums of each K range
   float *partial;
   int64_t ld_partial;
+  int64_t partial_rows;   // rows per slice of `partial` (0: M)
   // optional precomputed tf32 low parts, laid out like A / B
   const float *a_lo, *b_lo;
   // optional precomputed bf16 splits of the operands' storage (endia_b200_bf16_split)

@@ -479,7 +479,9 @@ __device__ __forceinline__ void tc_epilogue_warp_bulk(uint32_t tmem_base, int q,
                                                       int64_t m0, int64_t n0, int64_t M, int64_t N, const float *Cout,
                                                       int64_t ldc, const EpiParams &epi, const CUtensorMap *cmap,
                                                       uint32_t buf, bool reduce, bool raw = false,
-                                                      bool pre_add = false, bool with_corr = true) {
+                                                      bool pre_add = false, bool with_corr = true,
+                                                      int64_t row_off = 0) {
+  // row_off: added to the row coordinate of the stores (the slice of a split-K work buffer).
   // with_corr = false: a run before the last one: the correction accumulator keeps running (its
   // truncation is 2^-11 of the main one's) and only the main accumulator is drained.
   // raw: this is a partial run of a reduction whose epilogue is not linear: the bare sums are
@@ -594,8 +596,8 @@ __device__ __forceinline__ void tc_epilogue_warp_bulk(uint32_t tmem_base, int q,
     fence_async_smem();
     __syncwarp();
     if (lane == 0 && nb < N && m0 + q * 32 < M) {
-      if (reduce) tma_reduce_add_2d(cmap, buf, (int)nb, (int)(m0 + q * 32));
-      else tma_store_2d(cmap, buf, (int)nb, (int)(m0 + q * 32));
+      if (reduce) tma_reduce_add_2d(cmap, buf, (int)nb, (int)(m0 + q * 32 + row_off));
+      else tma_store_2d(cmap, buf, (int)nb, (int)(m0 + q * 32 + row_off));
       bulk_commit();
     }
   }
@@ -633,7 +635,7 @@ __device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity,
 template <bool A_MN, bool B_MN, int SCHEME>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(320, 1)
 gemm_tc2p_kernel(const __grid_constant__ TcMaps maps, const GemmParams p, int pairs_m, int tiles_n, int group_m,
-                 int ksplit, int kseq, int kseq_raw) {
+                 int ksplit, int kseq, int kseq_raw, int part_rows) {
   constexpr int BN = 256, BNH = 128, BK = 32, STAGES = 3, EPI_WARPS = 8;
   extern __shared__ __align__(1024) uint8_t smem[];
   constexpr uint32_t A_BYTES = TC_BM * BK * 4;
@@ -651,7 +653,9 @@ gemm_tc2p_kernel(const __grid_constant__ TcMaps maps, const GemmParams p, int pa
   const int num_pairs = (int)(gridDim.x >> 1), pair_id = (int)(blockIdx.x >> 1);
   // Work items: every tile once per K range (ksplit = 2 halves the reduction so that a tile count
   // that fills the last round of pairs badly is balanced; the halves are then added into a zeroed
-  // C by the copy engine, and two addends give the same sum in either order).
+  // C by the copy engine, and two addends give the same sum in either order). part_rows > 0: any
+  // number of K ranges; range r stores its bare sums to rows [r * part_rows, ...) of the work buffer
+  // behind maps.c, and splitk_finish_kernel adds the ranges in order and applies the epilogue.
   const int num_tiles = pairs_m * tiles_n * ksplit;
   const int tiles_mn = pairs_m * tiles_n;
   const int nkb_all = (int)((p.K + BK - 1) / BK);
@@ -849,12 +853,14 @@ gemm_tc2p_kernel(const __grid_constant__ TcMaps maps, const GemmParams p, int pa
       }
       constexpr int CH = BN / 64;
       const bool last_run = run == kseq - 1;
-      const bool raw = kseq_raw && !last_run, pre_add = kseq_raw && last_run && kseq > 1;
-      const bool reduce = kseq_raw ? (run > 0 && !last_run) : (ksplit > 1 || run > 0);
-      if (p.vec_c)
+      const bool raw = part_rows ? true : (kseq_raw && !last_run);
+      const bool pre_add = part_rows ? false : (kseq_raw && last_run && kseq > 1);
+      const bool reduce = part_rows ? run > 0 : (kseq_raw ? (run > 0 && !last_run) : (ksplit > 1 || run > 0));
+      const int64_t row_off = part_rows ? (int64_t)(t / tiles_mn) * part_rows : 0;
+      if (p.vec_c || part_rows)
         tc_epilogue_warp_bulk<BN>(tmem_base, q, lane, half * CH, (half + 1) * CH, m0, n0, p.M, p.N, p.C, p.ldc,
                                   p.epi, &maps.c, epi_base + (uint32_t)(warp - 2) * 4096u, reduce, raw, pre_add,
-                                  last_run);
+                                  last_run, row_off);
       else
         tc_epilogue_warp<BN, false>(tmem_base, q, lane, half * CH, (half + 1) * CH, m0, n0, p.M, p.N, p.C, p.ldc,
                                     p.epi, p.vec_c, epi_base + (uint32_t)(warp - 2) * 4096u);
@@ -873,20 +879,54 @@ gemm_tc2p_kernel(const __grid_constant__ TcMaps maps, const GemmParams p, int pa
   }
 }
 
-// Second stage of split-K: C = epilogue(sum over the splits, in order).
+// Second stage of split-K: C = epilogue(sum over the splits, in order). The loads of eight splits
+// are issued together; with VEC a thread takes four consecutive columns.
+template <bool VEC>
 __global__ void __launch_bounds__(256) splitk_finish_kernel(GemmParams p, int splits) {
-  const int64_t total = p.M * p.N;
+  constexpr int W = VEC ? 4 : 1;
+  const int64_t NW = (p.N + W - 1) / W, total = p.M * NW;
+  const bool narrow = total < ((int64_t)1 << 31);
   const int64_t step = (int64_t)gridDim.x * blockDim.x;
+  const int64_t slice = (p.partial_rows ? p.partial_rows : p.M) * p.ld_partial;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += step) {
-    const int64_t m = i / p.N, n = i - m * p.N;
-    float v = 0.f;
-    for (int s = 0; s < splits; ++s) v += p.partial[((int64_t)s * p.M + m) * p.ld_partial + n];
-    p.C[m * p.ldc + n] = apply_epilogue(p.epi, v, m, n, p.C + m * p.ldc + n);
+    const int64_t m = narrow ? (int64_t)((uint32_t)i / (uint32_t)NW) : i / NW;
+    const int64_t n = (i - m * NW) * W;
+    const float *src = p.partial + m * p.ld_partial + n;
+    float v[W];
+#pragma unroll
+    for (int j = 0; j < W; ++j) v[j] = 0.f;
+    for (int s0 = 0; s0 < splits; s0 += 8) {
+      float t[8][W];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        if (s0 + u < splits) {
+          if (VEC) {
+            const float4 q = __ldcs(reinterpret_cast<const float4 *>(src + (int64_t)(s0 + u) * slice));
+            t[u][0] = q.x; t[u][W > 1 ? 1 : 0] = q.y; t[u][W > 2 ? 2 : 0] = q.z; t[u][W > 3 ? 3 : 0] = q.w;
+          } else {
+            t[u][0] = __ldcs(src + (int64_t)(s0 + u) * slice);
+          }
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 8; ++u)
+        if (s0 + u < splits)
+#pragma unroll
+          for (int j = 0; j < W; ++j) v[j] += t[u][j];
+    }
+    float *c = p.C + m * p.ldc + n;
+#pragma unroll
+    for (int j = 0; j < W; ++j) v[j] = apply_epilogue(p.epi, v[j], m, n + j, c + j);
+    if (VEC) *reinterpret_cast<float4 *>(c) = make_float4(v[0], v[W > 1 ? 1 : 0], v[W > 2 ? 2 : 0], v[W > 3 ? 3 : 0]);
+    else c[0] = v[0];
   }
 }
 
 int launch_splitk_finish(const GemmParams &p, int splits, cudaStream_t s) {
-  splitk_finish_kernel<<<grid_for(p.M * p.N, 256), 256, 0, s>>>(p, splits);
+  const bool vec = p.vec_c && p.N % 4 == 0 && p.ld_partial % 4 == 0 &&
+                   (reinterpret_cast<uintptr_t>(p.partial) & 15) == 0;
+  if (vec) splitk_finish_kernel<true><<<grid_for(p.M * (p.N / 4), 256), 256, 0, s>>>(p, splits);
+  else splitk_finish_kernel<false><<<grid_for(p.M * p.N, 256), 256, 0, s>>>(p, splits);
   EB_LAUNCH_CHECK();
   return ENDIA_B200_OK;
 }
@@ -1074,6 +1114,23 @@ static bool pair_mode() {
   return on;
 }
 
+// K ranges as work items of the two-CTA kernel when a product has few tiles (ENDIA_B200_TC_PAIR_SPLIT=0: off)
+static bool pair_split_mode() {
+  static const bool on = []() { const char *e = getenv("ENDIA_B200_TC_PAIR_SPLIT"); return !(e && atoi(e) == 0); }();
+  return on;
+}
+
+// CTA pairs the persistent kernel runs with (SM pairs minus the reserve for concurrent kernels).
+static int pair_capacity() {
+  static const int cap = []() {
+    const int sms = sm_count() > 0 ? sm_count() : 148;
+    const char *rs = getenv("ENDIA_B200_TC_RESERVE_SMS");
+    const int c = sms / 2 - (rs ? atoi(rs) / 2 : 0);
+    return c >= 8 ? c : 8;
+  }();
+  return cap;
+}
+
 static bool ksplit_mode() {
   static const bool on = []() { const char *e = getenv("ENDIA_B200_TC_KSPLIT"); return !(e && atoi(e) == 0); }();
   return on;
@@ -1082,7 +1139,9 @@ static bool ksplit_mode() {
 // Persistent two-CTA kernel: as many CTA pairs as can be resident, each walking over its tiles.
 template <int SCHEME>
 static int launch_pair_persistent(const TcMaps &maps, const GemmParams &p, int trans_a, int trans_b,
-                                  cudaStream_t s, int ksplit_max, int run_k, int kseq_raw) {
+                                  cudaStream_t s, int ksplit_max, int run_k, int kseq_raw, int part_splits) {
+  // part_splits >= 2: that many K ranges per tile, each with its slice of the work buffer behind
+  // maps.c (pairs_m * 256 rows per slice)
   constexpr size_t SMEM = (size_t)3 * (2 * TC_BM * 32 * 4 + 2 * 128 * 32 * 4) + 8 * 4096 + 1024 + 256;
   const int pairs_m = (int)ceil_div(p.M, 256), tiles_n = (int)ceil_div(p.N, 256);
   static const int group_env = []() { const char *e = getenv("ENDIA_B200_TC_GROUP_M"); return e ? atoi(e) : TC_GROUP_M; }();
@@ -1118,13 +1177,15 @@ static int launch_pair_persistent(const TcMaps &maps, const GemmParams &p, int t
     }                                                                                             \
     const int tiles = pairs_m * tiles_n;                                                          \
     int ksplit = 1;                                                                               \
-    if (ksplit_max >= 2 && tiles > max_pairs) {                                                   \
+    if (part_splits >= 2) {                                                                       \
+      ksplit = part_splits;                                                                       \
+    } else if (ksplit_max >= 2 && tiles > max_pairs) {                                                   \
       /* rounds of pairs with and without halving K, in units of half tiles */                    \
       const int r1 = 2 * ((tiles + max_pairs - 1) / max_pairs);                                   \
       const int r2 = (2 * tiles + max_pairs - 1) / max_pairs;                                     \
       if (r2 * 100 <= r1 * 95) ksplit = 2;                                                        \
     }                                                                                             \
-    if (ksplit > 1) {                                                                             \
+    if (ksplit > 1 && part_splits < 2) {                                                          \
       if (p.ldc == p.N) EB_CUDA(cudaMemsetAsync(p.C, 0, sizeof(float) * p.M * p.N, s));           \
       else EB_CUDA(cudaMemset2DAsync(p.C, sizeof(float) * p.ldc, 0, sizeof(float) * p.N, p.M, s)); \
     }                                                                                             \
@@ -1133,7 +1194,8 @@ static int launch_pair_persistent(const TcMaps &maps, const GemmParams &p, int t
     /* runs of at most run_k along K per work item (run_k = 0: one run) */                        \
     const int kseq = run_k > 0 ? (int)ceil_div(ceil_div(p.K, ksplit), run_k) : 1;                 \
     kern<<<dim3((unsigned)(2 * pairs)), 320, SMEM, s>>>(maps, p, pairs_m, tiles_n, group_m, ksplit,  \
-                                                        kseq < 1 ? 1 : kseq, kseq > 1 ? kseq_raw : 0); \
+                                                        kseq < 1 ? 1 : kseq, kseq > 1 ? kseq_raw : 0,   \
+                                                        part_splits >= 2 ? pairs_m * 256 : 0);        \
   } while (0)
   if (trans_a && !trans_b) EB_TC2P_LAUNCH(true, true);
   else if (trans_a && trans_b) EB_TC2P_LAUNCH(true, false);
@@ -1154,17 +1216,27 @@ int launch_gemm_tc(const GemmParams &p_in, int trans_a, int trans_b, cudaStream_
   int bn = p.N >= 256 ? 256 : 128;
   // Few output tiles and a long reduction: split K over CTAs (128 x 128 tiles) so that the machine
   // is filled; the partial sums go through a work buffer and are added in a fixed order.
-  int splits = 1;
+  // N >= 256: the two-CTA kernel takes K ranges as extra work items (part_splits), each with its
+  // own slice of a work buffer; N < 256: the one-CTA kernel, 128 x 128 tiles (splits).
+  int splits = 1, part_splits = 1;
   int scheme = p.scheme;
-  if ((scheme == 0 || !p.scheme_forced) && !p.epi.colsum_partial && p.K <= 8192) {
-    const int64_t ctas_wide = 2 * ceil_div(p.M, 256) * ceil_div(p.N, 256);
+  if (bn == 256 && !p.epi.colsum_partial && p.K >= 2048 && pair_split_mode()) {
+    const int64_t tiles = ceil_div(p.M, 256) * ceil_div(p.N, 256);
+    const int64_t cap = pair_capacity();
+    if (2 * tiles <= cap) {
+      int64_t sp = cap / tiles;
+      if (sp > p.K / 512) sp = p.K / 512;
+      if (sp > 16) sp = 16;
+      if (sp >= 2) part_splits = (int)sp;
+    }
+  } else if (bn == 128 && (scheme == 0 || !p.scheme_forced) && !p.epi.colsum_partial && p.K <= 8192) {
     const int64_t tiles = ceil_div(p.M, 128) * ceil_div(p.N, 128);
     const int64_t nkb32 = ceil_div(p.K, 32);
-    if ((bn == 128 ? tiles : ctas_wide) < 100 && nkb32 >= 16) {
+    if (tiles < 100 && nkb32 >= 16) {
       int64_t sp = 148 / tiles;
       if (sp > nkb32 / 8) sp = nkb32 / 8;
       if (sp > 16) sp = 16;
-      if (sp >= 2) { splits = (int)sp; bn = 128; scheme = 0; }
+      if (sp >= 2) { splits = (int)sp; scheme = 0; }
     }
   }
   // k-block depth of the one-CTA kernel: 32 floats per stage, or 16 with a deeper ring.
@@ -1247,7 +1319,17 @@ int launch_gemm_tc(const GemmParams &p_in, int trans_a, int trans_b, cudaStream_
     EB_CUDA(cudaMallocAsync(&work.partial, sizeof(float) * (size_t)splits * p.M * q.ld_partial, s));
     q.partial = static_cast<float *>(work.partial);
   }
-  if (pair && p.vec_c) {
+  if (!pair) part_splits = 1;
+  if (part_splits >= 2) {
+    // work buffer [part_splits][rows of whole tiles][N]: the kernel stores bare sums, the finishing
+    // kernel adds the slices in order and applies the epilogue
+    q.ld_partial = (p.N + 3) / 4 * 4;
+    q.partial_rows = ceil_div(p.M, 256) * 256;
+    EB_CUDA(cudaMallocAsync(&work.partial, sizeof(float) * (size_t)part_splits * q.partial_rows * q.ld_partial, s));
+    q.partial = static_cast<float *>(work.partial);
+    if ((st = make_map(&maps.c, q.partial, p.N, (int64_t)part_splits * q.partial_rows, q.ld_partial, 32, 32, false)))
+      return st;
+  } else if (pair && p.vec_c) {
     // output map: [M][N] floats with leading dimension ldc, boxes of 32 rows x 32 floats
     if ((st = make_map(&maps.c, p.C, p.N, p.M, p.ldc, 32, 32, false))) return st;
   } else {
@@ -1257,7 +1339,7 @@ int launch_gemm_tc(const GemmParams &p_in, int trans_a, int trans_b, cudaStream_
   // reduction long enough for the second pass over C to be cheap.
   // The operand parts of C are written by the bulk-store epilogue of the two-CTA kernel only (from
   // the final values, so the epilogue then counts as not linear); elsewhere the caller splits C.
-  if (!(pair && p.vec_c)) p.epi.c16 = nullptr;
+  if (!(pair && p.vec_c) || part_splits >= 2) p.epi.c16 = nullptr;
   if (c16_written) *c16_written = p.epi.c16 != nullptr;
   const bool linear_epi = !p.epi.bias && !p.epi.act && !p.epi.dact && p.epi.beta == 0.f && !p.epi.colsum_partial &&
                           !p.epi.c16;
@@ -1268,16 +1350,17 @@ int launch_gemm_tc(const GemmParams &p_in, int trans_a, int trans_b, cudaStream_
   // per run; any other (bias, activation, mask, column sums) needs beta == 0, because the runs
   // before the last keep their bare sums in C.
   static const int run_k_env = []() { const char *e = getenv("ENDIA_B200_TC_RUN_K"); return e ? atoi(e) : 2048; }();
-  const bool runs_ok = pair && p.vec_c && (linear_epi || p.epi.beta == 0.f);
+  const bool runs_ok = pair && (part_splits >= 2 || (p.vec_c && (linear_epi || p.epi.beta == 0.f)));
   const int run_k = runs_ok ? (run_k_env > 0 ? (run_k_env + 31) / 32 * 32 : 0) : 0;
   const int kseq_raw = linear_epi ? 0 : 1;
-  if (bf16c) st = launch_pair_persistent<1>(maps, p, trans_a, trans_b, s, ksplit_max, run_k, kseq_raw);
-  else if (pair) st = launch_pair_persistent<0>(maps, p, trans_a, trans_b, s, ksplit_max, run_k, kseq_raw);
+  if (bf16c) st = launch_pair_persistent<1>(maps, p, trans_a, trans_b, s, ksplit_max, run_k, kseq_raw, part_splits);
+  else if (pair) st = launch_pair_persistent<0>(maps, p, trans_a, trans_b, s, ksplit_max, run_k, kseq_raw, part_splits);
   else if (bn == 256 && bk == 16) st = launch_variant<256, 16, 4>(maps, p, trans_a, trans_b, s);
   else if (bn == 256) st = launch_variant<256, 32, 2>(maps, p, trans_a, trans_b, s);
   else if (bk == 16) st = launch_variant<128, 16, 6>(maps, q, trans_a, trans_b, s, splits);
   else st = launch_variant<128, 32, 3>(maps, q, trans_a, trans_b, s, splits);
   if (splits > 1 && st == ENDIA_B200_OK) st = launch_splitk_finish(q, splits, s);
+  if (part_splits >= 2 && st == ENDIA_B200_OK) st = launch_splitk_finish(q, part_splits, s);
   return st;
 }
 

@@ -186,13 +186,8 @@ def _tc_plan(M, N, K, nbatch, algo, linear=True):
         return None if algo == _lib.GEMM_AUTO else ("lo32" if algo == _lib.GEMM_3XTF32 or N < 256 else "pair16")
     if algo == _lib.GEMM_3XTF32 or N < 256:
         return "lo32"
-    if algo == _lib.GEMM_AUTO:
-        if os.environ.get("ENDIA_B200_TC_SCHEME", "")[:1] in ("3", "0"):
-            return "lo32"
-        wide = 2 * (-(-M // 256)) * (-(-N // 256))
-        tiles = (-(-M // 128)) * (-(-N // 128))
-        if wide < 100 and K >= 512 and min(148 // tiles, K // 256, 16) >= 2:
-            return "lo32"      # few tiles, long K: the split-K 3xTF32 kernel
+    if algo == _lib.GEMM_AUTO and os.environ.get("ENDIA_B200_TC_SCHEME", "")[:1] in ("3", "0"):
+        return "lo32"
     return "pair16"
 
 

@@ -150,8 +150,9 @@ def test_tensor_core_epilogue_mask_and_bias_gradient(nd, M, N, K, tb, algo_name)
 
 @pytest.mark.parametrize("ta,tb,K", [(1, 0, 16384 + 96), (0, 1, 24576)])
 def test_auto_long_reduction_runs(nd, ta, tb, K):
-    """K > 8192 under GEMM_AUTO: the two-CTA kernel drains its accumulators every 8192 and adds
-    the runs in order into C, so the product is reproducible and as accurate as a short one."""
+    """K > 8192 under GEMM_AUTO: the two-CTA kernel drains its accumulators after runs of 2048 and
+    adds the runs (and the K ranges of a product with few tiles) in order, so the product is
+    reproducible and as accurate as a short one."""
     from endia_b200 import _lib
     r = rng(K)
     M, N = 384, 512
@@ -160,7 +161,8 @@ def test_auto_long_reduction_runs(nd, ta, tb, K):
     junk = np.full((M, N), -7e29, np.float32)
     launches0 = _lib.lib.endia_b200_launch_count()
     out = run_gemm(nd, a, b, ta, tb, _lib.GEMM_AUTO, c0=junk)
-    assert _lib.lib.endia_b200_launch_count() - launches0 <= 3      # two splits + one GEMM, no FFMA tiles
+    # two splits + one GEMM (K ranges as work items) + the kernel that adds the ranges; no FFMA tiles
+    assert _lib.lib.endia_b200_launch_count() - launches0 <= 4
     out2 = run_gemm(nd, a, b, ta, tb, _lib.GEMM_AUTO, c0=junk)
     assert np.array_equal(out, out2)
     am = (a.T if ta else a).astype(np.float64)
@@ -339,3 +341,32 @@ def test_epilogue_writes_operand_parts_of_the_output(nd, M, N, K, algo_name):
     assert torch.equal(parts.view(torch.int32), want.view(torch.int32))
     ref = np.tanh(a.astype(np.float64) @ b.astype(np.float64) + bias)
     assert max_rel(Cd.to_numpy(), ref) < 6e-5
+
+
+@pytest.mark.parametrize("algo_name", ["auto", "3xtf32", "tf32_bf16x2"])
+@pytest.mark.parametrize("M,N,K,ta,tb", [(1024, 1024, 4096, 1, 0), (256, 1024, 4096, 1, 0), (4096, 256, 2048, 0, 1),
+                                         (300, 260, 2048 + 32, 0, 0), (300, 259, 2048, 0, 1),
+                                         (520, 300, 8192 + 64, 1, 1)])
+def test_few_tiles_long_reduction_takes_k_ranges(nd, M, N, K, ta, tb, algo_name):
+    """A product with few 256 x 256 tiles and K >= 2048 runs on the two-CTA kernel with K ranges as
+    extra work items; their bare sums are added in order by the finishing kernel, which applies the
+    whole epilogue (here alpha, bias, tanh and accumulation into C). Same bits on every run."""
+    from endia_b200 import _lib
+    algo = {"auto": _lib.GEMM_AUTO, "3xtf32": _lib.GEMM_3XTF32, "tf32_bf16x2": _lib.GEMM_TF32_BF16X2}[algo_name]
+    r = rng(M + N + K)
+    a = r.standard_normal((K, M) if ta else (M, K)).astype(np.float32)
+    b = (r.standard_normal((N, K) if tb else (K, N)) / np.sqrt(K)).astype(np.float32)
+    bias = r.standard_normal(N).astype(np.float32)
+    c0 = r.standard_normal((M, N)).astype(np.float32)
+    am = (a.T if ta else a).astype(np.float64)
+    bm = (b.T if tb else b).astype(np.float64)
+    out = run_gemm(nd, a, b, ta, tb, algo)
+    assert max_rel(out, am @ bm) < 4e-5
+    BIAS = nd.Array(bias)
+    epi = _lib.Epilogue()
+    epi.alpha, epi.beta, epi.bias, epi.act = 0.5, 2.0, BIAS.data_ptr(), _lib.ACT_TANH
+    want = np.tanh(0.5 * (am @ bm) + bias) + 2.0 * c0
+    out1 = run_gemm(nd, a, b, ta, tb, algo, epi=epi, c0=c0)
+    out2 = run_gemm(nd, a, b, ta, tb, algo, epi=epi, c0=c0)
+    assert max_rel(out1, want) < 4e-5
+    assert np.array_equal(out1, out2)

@@ -369,10 +369,12 @@ def test_empty_arrays(nd):
 
 @pytest.mark.parametrize("ta,tb", [(0, 0), (0, 1), (1, 0), (1, 1)])
 @pytest.mark.parametrize("M,N,K", [(300, 1, 257), (300, 5, 64), (129, 70, 1), (64, 100, 3), (1, 1024, 4096),
-                                   (3, 300, 200), (1024, 1, 4096)])
+                                   (3, 300, 200), (1024, 1, 4096), (4096, 1, 1024), (4096, 1024, 1),
+                                   (8, 1024, 512), (4100, 4, 1028), (512, 8, 96), (2, 260, 4100), (700, 2, 8)])
 def test_gemm_degenerate_shapes_with_epilogue(nd, ta, tb, M, N, K):
-    """N <= 8 and K <= 8 take the one-pass kernels under GEMM_AUTO; bias, activation, mask and
-    accumulation are fused there as well."""
+    """N <= 8, M <= 8 and K <= 8 take the one-pass kernels under GEMM_AUTO (rows, tall and outer
+    product forms, with and without 16-byte accesses and K ranges over CTAs); bias, activation,
+    mask and accumulation are fused there as well."""
     from endia_b200 import _lib
     from endia_b200._array import stream
     r = rng(21)

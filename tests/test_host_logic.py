@@ -61,8 +61,8 @@ def test_gemm_operand_parts_plan(monkeypatch):
     for M, N, K in [(8192, 4096, 1024), (8192, 4096, 4096), (8192, 1024, 4096), (4096, 4096, 8192),
                     (1024, 4096, 8192), (4096, 1024, 256)]:
         assert plan(M, N, K, 1, A) == "pair16", (M, N, K)
-    assert plan(256, 1024, 4096, 1, A) == "lo32"        # few tiles, long K: split-K 3xTF32 kernel
-    assert plan(1024, 1024, 4096, 1, A) == "lo32"
+    assert plan(256, 1024, 4096, 1, A) == "pair16"      # few tiles, long K: K ranges on the two-CTA kernel
+    assert plan(1024, 1024, 4096, 1, A) == "pair16"
     assert plan(4096, 128, 1024, 1, A) == "lo32"        # N < 256: one-CTA kernel
     assert plan(4096, 4096, 16384, 1, A) == "pair16"    # K > 8192: runs of 8192 on the two-CTA kernel
     assert plan(4096, 4096, 16384, 1, A, linear=False) is None   # ... unless an epilogue is fused: FFMA
