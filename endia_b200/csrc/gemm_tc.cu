@@ -111,6 +111,14 @@ __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
         "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
       : "r"(taddr) : "memory");
 }
+__device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr) : "memory");
+}
 __device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 // Shared-memory matrix descriptor (descriptor version 1): start address, leading and stride byte
@@ -469,60 +477,89 @@ __device__ __forceinline__ uint64_t tile_desc16(uint32_t addr) {
   return MN_MAJOR ? smem_desc(addr, 4096, 1024, 2) : smem_desc(addr, 16, 512, 4);
 }
 
-// Epilogue of one warp of the persistent kernel: like tc_epilogue_warp, but the finished
-// [32 x 32] chunk leaves shared memory through a bulk tensor store issued by one lane (the
-// register path of 128-bit stores drains a tile several times slower). The fused epilogue
-// runs in place on the shared-memory chunk with eight lanes along each row, so that its reads
-// of the activation source, the bias and C are coalesced; a plain product skips that pass.
+// Epilogue of one warp of the persistent kernel, in two steps. tc_epilogue_drain moves the warp's
+// 32 rows x 128 columns (the sum of the two accumulators) from tensor memory into registers; the
+// caller then hands the accumulators back to the MMA issuer, so that the next tile's products run
+// while tc_epilogue_warp_bulk finishes this one: chunk by chunk of [32 x 32] through the warp's
+// shared-memory buffer and out with a bulk tensor store issued by one lane (the register path of
+// 128-bit stores drains a tile several times slower). The fused epilogue runs in place on the
+// shared-memory chunk with eight lanes along each row, so that its reads of the activation
+// source, the bias and C are coalesced; a plain product skips that pass.
+// with_corr = false: a run before the last one: the correction accumulator keeps running (its
+// truncation is 2^-11 of the main one's) and only the main accumulator is drained.
+__device__ __forceinline__ void tc_stage_chunk(uint32_t buf, int lane, const uint32_t (&v)[32]) {
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const float4 x = make_float4(__uint_as_float(v[4 * j + 0]), __uint_as_float(v[4 * j + 1]),
+                                 __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3]));
+    sts128(buf + (uint32_t)lane * 128u + (uint32_t)((j ^ (lane & 7)) * 16), x);
+  }
+}
+
+// (the first chunk goes straight to the warp's shared-memory buffer, the other three stay in
+// registers: 96 values per lane)
 template <int BN>
-__device__ __forceinline__ void tc_epilogue_warp_bulk(uint32_t tmem_base, int q, int lane, int c_begin, int c_end,
-                                                      int64_t m0, int64_t n0, int64_t M, int64_t N, const float *Cout,
-                                                      int64_t ldc, const EpiParams &epi, const CUtensorMap *cmap,
-                                                      uint32_t buf, bool reduce, bool raw = false,
-                                                      bool pre_add = false, bool with_corr = true,
-                                                      int64_t row_off = 0) {
+__device__ __forceinline__ void tc_epilogue_drain(uint32_t tmem_base, int q, int lane, int c_begin, bool with_corr,
+                                                  uint32_t buf, uint32_t (&v1)[32], uint32_t (&v2)[32],
+                                                  uint32_t (&v3)[32]) {
+  const uint32_t row_addr = tmem_base + ((uint32_t)(q * 32) << 16);
+  uint32_t rb[16];
+#define EB_ADD_CORR(C, V)                                                                  \
+  if (with_corr) {                                                                         \
+    _Pragma("unroll") for (int h = 0; h < 2; ++h) {                                        \
+      tc_ld16(row_addr + (uint32_t)(BN + (c_begin + C) * 32 + 16 * h), rb);                \
+      tc_wait_ld();                                                                        \
+      _Pragma("unroll") for (int j = 0; j < 16; ++j)                                       \
+        V[16 * h + j] = __float_as_uint(__uint_as_float(V[16 * h + j]) + __uint_as_float(rb[j])); \
+    }                                                                                      \
+  }
+  {
+    uint32_t v0[32];
+    tc_ld32(row_addr + (uint32_t)((c_begin + 0) * 32), v0);
+    // the last store of the previous tile has read the buffer
+    if (lane == 0) bulk_wait_read0();
+    __syncwarp();
+    tc_wait_ld();
+    EB_ADD_CORR(0, v0)
+    tc_stage_chunk(buf, lane, v0);
+  }
+  tc_ld32(row_addr + (uint32_t)((c_begin + 1) * 32), v1);
+  tc_ld32(row_addr + (uint32_t)((c_begin + 2) * 32), v2);
+  tc_ld32(row_addr + (uint32_t)((c_begin + 3) * 32), v3);
+  tc_wait_ld();
+  EB_ADD_CORR(1, v1)
+  EB_ADD_CORR(2, v2)
+  EB_ADD_CORR(3, v3)
+#undef EB_ADD_CORR
+}
+
+__device__ __forceinline__ void tc_epilogue_warp_bulk(const uint32_t (&v1)[32], const uint32_t (&v2)[32],
+                                                      const uint32_t (&v3)[32], int q,
+                                                      int lane, int c_begin, int64_t m0, int64_t n0, int64_t M,
+                                                      int64_t N, const float *Cout, int64_t ldc,
+                                                      const EpiParams &epi, const CUtensorMap *cmap, uint32_t buf,
+                                                      bool reduce, bool raw, bool pre_add, int64_t row_off) {
   // row_off: added to the row coordinate of the stores (the slice of a split-K work buffer).
-  // with_corr = false: a run before the last one: the correction accumulator keeps running (its
-  // truncation is 2^-11 of the main one's) and only the main accumulator is drained.
   // raw: this is a partial run of a reduction whose epilogue is not linear: the bare sums are
   // stored (or added); pre_add: the last run of such a reduction, which adds what the earlier runs
   // left in C before it applies the epilogue.
-  const uint32_t row_addr = tmem_base + ((uint32_t)(q * 32) << 16);
   const bool plain = raw || (epi.alpha == 1.f && !epi.bias && !epi.act && !epi.dact && epi.beta == 0.f &&
                              !epi.colsum_partial && !pre_add && !epi.c16);
   const bool vec_epi = (!epi.bias || (reinterpret_cast<uintptr_t>(epi.bias) & 15) == 0) &&
                        (!epi.dact || ((reinterpret_cast<uintptr_t>(epi.dact_src) & 15) == 0 && epi.ld_dact % 4 == 0));
-  uint32_t ra[32], rb[32];
   const int c4 = lane & 7, rsub = lane >> 3;
-  tc_ld32(row_addr + (uint32_t)(c_begin * 32), ra);
-  if (with_corr) tc_ld32(row_addr + (uint32_t)(BN + c_begin * 32), rb);
 #pragma unroll 1
-  for (int c = c_begin; c < c_end; ++c) {
-    tc_wait_ld();
-    // the previous chunk's store has read the buffer
-    if (lane == 0) bulk_wait_read0();
-    __syncwarp();
-    if (with_corr) {
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        float4 v;
-        v.x = __uint_as_float(ra[4 * j + 0]) + __uint_as_float(rb[4 * j + 0]);
-        v.y = __uint_as_float(ra[4 * j + 1]) + __uint_as_float(rb[4 * j + 1]);
-        v.z = __uint_as_float(ra[4 * j + 2]) + __uint_as_float(rb[4 * j + 2]);
-        v.w = __uint_as_float(ra[4 * j + 3]) + __uint_as_float(rb[4 * j + 3]);
-        sts128(buf + (uint32_t)lane * 128u + (uint32_t)((j ^ (lane & 7)) * 16), v);
+  for (int ci = 0; ci < 4; ++ci) {
+    const int c = c_begin + ci;
+    if (ci > 0) {   // (chunk 0 was staged by tc_epilogue_drain)
+      // the previous chunk's store has read the buffer
+      if (lane == 0) bulk_wait_read0();
+      __syncwarp();
+      switch (ci) {
+        case 1: tc_stage_chunk(buf, lane, v1); break;
+        case 2: tc_stage_chunk(buf, lane, v2); break;
+        default: tc_stage_chunk(buf, lane, v3); break;
       }
-    } else {
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const float4 v = make_float4(__uint_as_float(ra[4 * j + 0]), __uint_as_float(ra[4 * j + 1]),
-                                     __uint_as_float(ra[4 * j + 2]), __uint_as_float(ra[4 * j + 3]));
-        sts128(buf + (uint32_t)lane * 128u + (uint32_t)((j ^ (lane & 7)) * 16), v);
-      }
-    }
-    if (c + 1 < c_end) {   // in flight while this chunk is finished and stored
-      tc_ld32(row_addr + (uint32_t)((c + 1) * 32), ra);
-      if (with_corr) tc_ld32(row_addr + (uint32_t)(BN + (c + 1) * 32), rb);
     }
     const int64_t nb = n0 + c * 32;
     if (!plain) {
@@ -607,7 +644,8 @@ __device__ __forceinline__ void tc_epilogue_warp_bulk(uint32_t tmem_base, int q,
 // One CTA pair per SM pair walks over the 256 x 256 tiles t = pair, pair + pairs, ... The ring of
 // operand stages runs on across tile boundaries, so the loads of the next tile are in flight while
 // the epilogue warps drain tensor memory; the MMA issuer only waits until every epilogue warp of
-// both CTAs has read the accumulators ("acc_empty") before it overwrites them. What is saved per
+// both CTAs has read the accumulators into registers ("acc_empty") before it overwrites them: the
+// fused epilogue and the stores of a tile run beside the products of the next one. What is saved per
 // tile: the CTA launch, the tensor-memory allocation, the barrier set-up and the empty pipeline.
 // The epilogue warps have 4 KB of shared memory each of their own (the stages are never free).
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {
@@ -846,27 +884,35 @@ gemm_tc2p_kernel(const __grid_constant__ TcMaps maps, const GemmParams p, int pa
       for (int run = 0; run < kseq; ++run, ++j) {
       if (!mbar_wait(acc_full, (uint32_t)j & 1, 34)) { ok = false; break; }
       tc_fence_after();
-      if (run > 0) {
-        // this run is added to what the previous run of the same tile stored: that store must be complete
-        if (lane == 0) bulk_wait0();
-        __syncwarp();
-      }
       constexpr int CH = BN / 64;
+      static_assert(CH == 4, "the epilogue holds four chunks of 32 columns per warp");
       const bool last_run = run == kseq - 1;
       const bool raw = part_rows ? true : (kseq_raw && !last_run);
       const bool pre_add = part_rows ? false : (kseq_raw && last_run && kseq > 1);
       const bool reduce = part_rows ? run > 0 : (kseq_raw ? (run > 0 && !last_run) : (ksplit > 1 || run > 0));
       const int64_t row_off = part_rows ? (int64_t)(t / tiles_mn) * part_rows : 0;
-      if (p.vec_c || part_rows)
-        tc_epilogue_warp_bulk<BN>(tmem_base, q, lane, half * CH, (half + 1) * CH, m0, n0, p.M, p.N, p.C, p.ldc,
-                                  p.epi, &maps.c, epi_base + (uint32_t)(warp - 2) * 4096u, reduce, raw, pre_add,
-                                  last_run, row_off);
-      else
+      if (p.vec_c || part_rows) {
+        // the accumulators go back to the MMA issuer as soon as they are in registers
+        uint32_t v1[32], v2[32], v3[32];
+        const uint32_t ebuf = epi_base + (uint32_t)(warp - 2) * 4096u;
+        tc_epilogue_drain<BN>(tmem_base, q, lane, half * CH, last_run, ebuf, v1, v2, v3);
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(acc_empty_leader);
+        if (run > 0) {
+          // this run is added to what the previous run of the same tile stored: that store must be complete
+          if (lane == 0) bulk_wait0();
+          __syncwarp();
+        }
+        tc_epilogue_warp_bulk(v1, v2, v3, q, lane, half * CH, m0, n0, p.M, p.N, p.C, p.ldc, p.epi, &maps.c, ebuf,
+                              reduce, raw, pre_add, row_off);
+      } else {
         tc_epilogue_warp<BN, false>(tmem_base, q, lane, half * CH, (half + 1) * CH, m0, n0, p.M, p.N, p.C, p.ldc,
                                     p.epi, p.vec_c, epi_base + (uint32_t)(warp - 2) * 4096u);
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive_cluster(acc_empty_leader);
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(acc_empty_leader);
+      }
       }
     }
     if (lane == 0) bulk_wait0();   // the stores have left shared memory and are complete
