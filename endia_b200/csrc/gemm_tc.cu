@@ -566,6 +566,49 @@ __device__ __forceinline__ void tc_epilogue_warp_bulk(const uint32_t (&v1)[32], 
       __syncwarp();
       const int64_t n = nb + c4 * 4;
       float4 cs = make_float4(0.f, 0.f, 0.f, 0.f);   // column sums of this lane's 8 rows
+      if (vec_epi && epi.beta == 0.f && m0 + q * 32 + 32 <= M && nb + 32 <= N) {
+        // a chunk inside the matrix (all of them but the ragged edges): the same steps on whole
+        // float4s, with everything that does not depend on the row taken out of the loop
+        const float alpha = epi.alpha;
+        const int act = epi.act, dact = epi.dact;
+        const float4 b4 = epi.bias ? __ldg(reinterpret_cast<const float4 *>(epi.bias + n)) : make_float4(0.f, 0.f, 0.f, 0.f);
+        const int64_t mr = m0 + q * 32 + rsub;
+        const float *cp = Cout + mr * ldc + n;
+        const float *dp = dact ? epi.dact_src + mr * epi.ld_dact + n : nullptr;
+        __nv_bfloat16 *h16 = epi.c16 ? static_cast<__nv_bfloat16 *>(epi.c16) + mr * ldc + n : nullptr;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int r = rsub + 4 * i;
+          const uint32_t a = buf + (uint32_t)r * 128u + (uint32_t)((c4 ^ (r & 7)) * 16);
+          float4 v = lds128(a);
+          if (pre_add) {
+            const float4 c = __ldcg(reinterpret_cast<const float4 *>(cp + (int64_t)(4 * i) * ldc));
+            v.x += c.x; v.y += c.y; v.z += c.z; v.w += c.w;
+          }
+          v.x = alpha * v.x + b4.x; v.y = alpha * v.y + b4.y; v.z = alpha * v.z + b4.z; v.w = alpha * v.w + b4.w;
+          if (act) { v.x = act_fwd(act, v.x); v.y = act_fwd(act, v.y); v.z = act_fwd(act, v.z); v.w = act_fwd(act, v.w); }
+          if (dact) {
+            const float4 d = __ldg(reinterpret_cast<const float4 *>(dp + (int64_t)(4 * i) * epi.ld_dact));
+            v.x *= act_bwd(dact, d.x); v.y *= act_bwd(dact, d.y); v.z *= act_bwd(dact, d.z); v.w *= act_bwd(dact, d.w);
+          }
+          cs.x += v.x; cs.y += v.y; cs.z += v.z; cs.w += v.w;
+          sts128(a, v);
+          if (h16) {
+            // the operand parts of the stored values, for the products that will read C
+            const __nv_bfloat162 h01 = __floats2bfloat162_rn(v.x, v.y), h23 = __floats2bfloat162_rn(v.z, v.w);
+            const __nv_bfloat162 l01 = __floats2bfloat162_rn(v.x - __uint_as_float(__float_as_uint(v.x) & 0xFFFFE000u),
+                                                             v.y - __uint_as_float(__float_as_uint(v.y) & 0xFFFFE000u));
+            const __nv_bfloat162 l23 = __floats2bfloat162_rn(v.z - __uint_as_float(__float_as_uint(v.z) & 0xFFFFE000u),
+                                                             v.w - __uint_as_float(__float_as_uint(v.w) & 0xFFFFE000u));
+            uint2 hv, lv;
+            hv.x = *reinterpret_cast<const uint32_t *>(&h01); hv.y = *reinterpret_cast<const uint32_t *>(&h23);
+            lv.x = *reinterpret_cast<const uint32_t *>(&l01); lv.y = *reinterpret_cast<const uint32_t *>(&l23);
+            __nv_bfloat16 *hp = h16 + (int64_t)(4 * i) * ldc;
+            *reinterpret_cast<uint2 *>(hp) = hv;
+            *reinterpret_cast<uint2 *>(hp + epi.c16_lo) = lv;
+          }
+        }
+      } else
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
         const int r = rsub + 4 * i;

@@ -118,7 +118,18 @@ def linear(x, weight, bias=None, activation=None):
             dx.name = "linear_vjp"   # a temporary of this pass, never rewritten (see _operand_parts_ptr)
             setup_shape_and_data(dx)
             epi = _mask_epilogue_for(xp, dx)
+            parts = None
+            if epi is not None and _state.cache_tf32_lo and dx.size() % 8 == 0 and dx.size() >= (1 << 20):
+                # dx is then the lower layer's dS, an operand of two more products
+                from ..functional.binary_ops import _tc_plan
+                rows, cols = xp.shape()
+                if _tc_plan(rows, cols, cols, 1, _state.gemm_algo) == "pair16":
+                    parts = alloc(dx.size())
+                    epi.c16 = parts.data_ptr()
             gemm_arrays(ds, wp.T(), dx, epi=epi)
+            if parts is not None:
+                dx._pair16 = parts
+                dx._parts_ptr = dx.buf.data_ptr()
             res.append(dx)
         else:
             res.append(zero)
