@@ -73,7 +73,7 @@ GEMM_AUTO, GEMM_FFMA, GEMM_3XTF32, GEMM_TF32_BF16X2 = 0, 1, 2, 3
  UN_ATAN) = range(21)
 (BIN_ADD, BIN_SUB, BIN_MUL, BIN_DIV, BIN_POW, BIN_GREATER, BIN_RELU_BWD, BIN_TANH_BWD,
  BIN_SIGMOID_BWD, BIN_COMPLEX, BIN_ABS_BWD, BIN_SQUARE_BWD, BIN_GREATER_EQUAL, BIN_LESS,
- BIN_LESS_EQUAL, BIN_EQUAL, BIN_NOT_EQUAL) = range(17)
+ BIN_LESS_EQUAL, BIN_EQUAL, BIN_NOT_EQUAL, BIN_TANH_OUT_BWD, BIN_TANH_OUT_BWD2) = range(19)
 
 _vp, _i64, _i32, _f32, _sz = C.c_void_p, C.c_int64, C.c_int32, C.c_float, C.c_size_t
 _TP = C.POINTER(Tensor)

@@ -82,6 +82,8 @@ __device__ __forceinline__ float bin_real(float a, float b) {
   if constexpr (OP == ENDIA_B200_BIN_SIGMOID_BWD) return a * (1.f - a) * b;  // sigmoid_op.mojo:98
   if constexpr (OP == ENDIA_B200_BIN_ABS_BWD) return (a / fabsf(a)) * b;     // abs_op.mojo:93, sign_op.mojo:78-80
   if constexpr (OP == ENDIA_B200_BIN_SQUARE_BWD) return (2.f * a) * b;       // square_op.mojo:96
+  if constexpr (OP == ENDIA_B200_BIN_TANH_OUT_BWD) return (1.f - a * a) * b;  // tanh_op.mojo:92, a = tanh output
+  if constexpr (OP == ENDIA_B200_BIN_TANH_OUT_BWD2) return (-2.f * a) * b;
   return a;
 }
 
@@ -443,6 +445,7 @@ int endia_b200_ew_binary(int op, const endia_b200_tensor *a, const endia_b200_te
     EB_CASE(ENDIA_B200_BIN_ABS_BWD) EB_CASE(ENDIA_B200_BIN_SQUARE_BWD)
     EB_CASE(ENDIA_B200_BIN_GREATER_EQUAL) EB_CASE(ENDIA_B200_BIN_LESS) EB_CASE(ENDIA_B200_BIN_LESS_EQUAL)
     EB_CASE(ENDIA_B200_BIN_EQUAL) EB_CASE(ENDIA_B200_BIN_NOT_EQUAL)
+    EB_CASE(ENDIA_B200_BIN_TANH_OUT_BWD) EB_CASE(ENDIA_B200_BIN_TANH_OUT_BWD2)
 #undef EB_CASE
   }
   return ENDIA_B200_EINVAL;

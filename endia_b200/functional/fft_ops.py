@@ -39,6 +39,11 @@ def _norm_dims(x, dims):
 
 
 def _scale(n, norm, inverse):
+    """Factor applied to a transform over n points. "backward" is the reference's scaling (nothing
+    forward, 1/n inverse). "forward" and "ortho" follow numpy.fft; the reference instead divides the
+    input by the size of the whole array, takes any other string for "ortho"
+    (fft_cooley_tukey.mojo:208-215) and still applies ifftn's 1/prod(n) (ifftn_op.mojo:67-77), which
+    is taken for a defect and not reproduced."""
     if norm == "ortho":
         return 1.0 / math.sqrt(n)
     if (norm == "backward") == bool(inverse):

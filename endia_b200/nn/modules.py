@@ -17,13 +17,38 @@ _ACTS = {None: _lib.ACT_NONE, "none": _lib.ACT_NONE, "relu": _lib.ACT_RELU, "tan
 _ACT_FNS = {_lib.ACT_RELU: relu, _lib.ACT_TANH: tanh, _lib.ACT_SIGMOID: sigmoid}
 
 
+def _tanh_out_bwd(y, g):
+    """(1 - y^2) * g for a tanh output y (tanh_op.mojo:92) as ONE differentiable op instead of the
+    square / sub / mul chain: one pass here, and in the backward pass of a gradient penalty
+    dg = (1 - y^2) * G (one pass) and dy = -2 * y * g * G (two passes) instead of the chain's
+    ten. With create_graph set again its VJP is written in differentiable ops."""
+    from ..functional.binary_ops import fused_binary, binary_op_array
+
+    def vjp(primals, grad, out):
+        yy, gg = primals
+        zero = Array(0)
+        if _state.create_graph:
+            dy = mul(mul(yy * -2.0, gg), grad) if yy.requires_grad() else zero
+            dg = _tanh_out_bwd(yy, grad) if gg.requires_grad() else zero
+        else:
+            dy = fused_binary(_lib.BIN_TANH_OUT_BWD2, yy, fused_binary(_lib.BIN_MUL, gg, grad)) \
+                if yy.requires_grad() else zero
+            dg = fused_binary(_lib.BIN_TANH_OUT_BWD, yy, grad) if gg.requires_grad() else zero
+        return [dy, dg]
+
+    def jvp(p, t):
+        # d[(1 - y^2) g] = -2 y g dy + (1 - y^2) dg
+        return add(mul(mul(p[0] * -2.0, p[1]), t[0]), _tanh_out_bwd(p[0], t[1]))
+    return binary_op_array(y, g, "tanh_out_bwd", _lib.BIN_TANH_OUT_BWD, vjp, jvp=jvp)
+
+
 def _act_bwd_graph(act, out, grad):
     """act'(.) * grad written in differentiable ops of the layer OUTPUT (relu_op.mojo:95,
     tanh_op.mojo:92, sigmoid_op.mojo:98)."""
     if act == _lib.ACT_RELU:
         return mul(greater(out, Array([out.shape()[-1]])), grad)
     if act == _lib.ACT_TANH:
-        return mul(1.0 - square(out), grad)
+        return _tanh_out_bwd(out, grad)
     if act == _lib.ACT_SIGMOID:
         return mul(mul(out, 1.0 - out), grad)
     return grad

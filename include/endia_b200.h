@@ -228,6 +228,8 @@ enum {
   /* the other comparisons of comparison_ops/: 1.0 / 0.0, real operands */
   ENDIA_B200_BIN_GREATER_EQUAL, ENDIA_B200_BIN_LESS, ENDIA_B200_BIN_LESS_EQUAL, ENDIA_B200_BIN_EQUAL,
   ENDIA_B200_BIN_NOT_EQUAL,
+  ENDIA_B200_BIN_TANH_OUT_BWD,   /* out = (1 - a^2) * b   a = tanh OUTPUT, b = grad (tanh_op.mojo:92), real only */
+  ENDIA_B200_BIN_TANH_OUT_BWD2,  /* out = -2 * a * b      the derivative of the line above w.r.t. a, real only   */
   ENDIA_B200_BIN_COUNT
 };
 

@@ -675,10 +675,33 @@ def _norm_dims(x, dims):
     return [d + nd if d < 0 else d for d in dims]
 
 
+def _norm_divisor(n, norm, inverse):
+    """Scaling of a transform over n points. "backward" (the default, the only mode the reference's
+    tests and benchmarks use) follows the reference: nothing forward, / n inverse. For "forward" and
+    "ortho" the reference divides by the size of the WHOLE array (and its `elif "ortho"` takes every
+    other string, fft_cooley_tukey.mojo:208-215), on top of ifftn's own / prod(n)
+    (ifftn_op.mojo:67-77); that is taken for a defect and NOT restated: both modes follow the usual
+    convention (numpy.fft), which the pins check."""
+    if norm == "backward":
+        return float(np.float32(n)) if inverse else 1.0
+    if norm == "forward":
+        return 1.0 if inverse else float(np.float32(n))
+    if norm == "ortho":
+        return float(np.sqrt(np.float64(n)))
+    raise ValueError("fftn: Invalid norm")
+
+
+def _points(xin, d):
+    n = 1
+    for a in d:
+        n *= xin.shape[a]
+    return n
+
+
 def fftn(x, dims=None, norm="backward"):  # fftn_op.mojo:25-79
     d = _norm_dims(x, list(dims) if dims else [])
     xin = contiguous(x) if x.is_complex() else contiguous(x).astype(np.complex64)
-    val = _fft_core(xin, d, False, False, 1.0)
+    val = _fft_core(xin, d, False, False, _norm_divisor(_points(xin, d), norm, False))
     dl = list(dims) if dims else []
     return op_array(val, [x], "fftn", lambda p, g, o: [conj(fftn(conj(g), dl, norm))])
 
@@ -686,10 +709,7 @@ def fftn(x, dims=None, norm="backward"):  # fftn_op.mojo:25-79
 def ifftn(x, dims=None, norm="backward"):  # ifftn_op.mojo:24-96: conj, forward kernel, conj, / prod(n)
     d = _norm_dims(x, list(dims) if dims else [])
     xin = contiguous(x) if x.is_complex() else contiguous(x).astype(np.complex64)
-    n = 1
-    for a in d:
-        n *= xin.shape[a]
-    val = _fft_core(xin, d, True, True, float(np.float32(n)))
+    val = _fft_core(xin, d, True, True, _norm_divisor(_points(xin, d), norm, True))
     dl = list(dims) if dims else []
     return op_array(val, [x], "ifftn", lambda p, g, o: [conj(ifftn(conj(g), dl, norm))])
 

@@ -45,6 +45,34 @@ def test_fft_real_input_and_non_contiguous_view(nd, oracle):
     assert rel_l2(yt, oracle.fft(oracle.Array(z).T()).to_numpy()) < TOL
 
 
+@pytest.mark.parametrize("norm", ["forward", "ortho"])
+@pytest.mark.parametrize("shape,dims", [((8, 1024), [-1]), ((4, 16, 64), [0, 2]), ((2, 8, 32), None),
+                                        ((2, 1 << 15), [1])])
+def test_fft_norm_modes_vs_numpy(nd, shape, dims, norm):
+    """norm = "forward" / "ortho" follow numpy.fft (the reference's scaling of these two modes is
+    taken for a defect and not reproduced): fft/ifft/fftn/ifftn values and VJPs, partial dims."""
+    r = rng(18)
+    z = (r.standard_normal(shape) + 1j * r.standard_normal(shape)).astype(np.complex64)
+    w = r.uniform(-1, 1, shape).astype(np.float32)
+    for fn, ref in ((nd.fftn, np.fft.fftn), (nd.ifftn, np.fft.ifftn)):
+        Z = nd.Array(z, requires_grad=True)
+        y = fn(Z, dims, norm)
+        assert rel_l2(y.to_numpy(), ref(z.astype(np.complex128), axes=dims, norm=norm)) < 2e-6
+        nd.sum(nd.real(y) * nd.Array(w)).backward()
+        want = np.conj(ref(w.astype(np.complex128), axes=dims, norm=norm))   # conj(F(conj(w + 0i)))
+        assert rel_l2(Z.grad().to_numpy(), want) < 2e-6
+    if dims is not None and len(dims) == 1:
+        y1 = nd.fft(nd.Array(z), dims[0], norm).to_numpy()
+        assert rel_l2(y1, np.fft.fft(z.astype(np.complex128), axis=dims[0], norm=norm)) < 2e-6
+        y2 = nd.ifft(nd.Array(z), dims[0], norm).to_numpy()
+        assert rel_l2(y2, np.fft.ifft(z.astype(np.complex128), axis=dims[0], norm=norm)) < 2e-6
+    Z = nd.Array(z, requires_grad=True)
+    nd.sum(nd.square(nd.to_abs(nd.fftn(Z, dims, norm)))).backward()      # the fused |y|^2 chain
+    s = {"forward": 1.0 / np.prod([shape[d] for d in (dims if dims is not None else range(len(shape)))]),
+         "ortho": 1.0}[norm]
+    assert rel_l2(Z.grad().to_numpy(), 2.0 * s * z.astype(np.complex128)) < 2e-6   # Parseval
+
+
 def test_fft_rejects_non_power_of_two(nd):
     with pytest.raises(nd.EndiaError) as ei:
         nd.fft(nd.Array(np.ones((4, 6), np.complex64)))

@@ -187,6 +187,31 @@ def test_c3_reduced_gradient_penalty(nd, oracle, fused):
         assert max_rel(a, b) < TOL, max_rel(a, b)
 
 
+def test_fused_tanh_layer_third_order_matches_op_composition(nd):
+    """The fused layer's create_graph VJP uses one op for (1 - y^2) * g whose own VJP is again
+    differentiable: gradient of a penalty on the second derivative (three nested grad calls),
+    fused layers against the same network written op by op."""
+    r = rng(5)
+    d = [16, 32, 1]
+    Ws = [r.uniform(-1, 1, (d[i], d[i + 1])).astype(np.float32) for i in range(2)]
+    bs = [r.uniform(-1, 1, d[i + 1]).astype(np.float32) for i in range(2)]
+    x = r.standard_normal((24, 16)).astype(np.float32)
+
+    def third(fwd):
+        W = [nd.Array(w.copy(), requires_grad=True) for w in Ws]
+        B = [nd.Array(b.copy(), requires_grad=True) for b in bs]
+        X = nd.Array(x, requires_grad=True)
+        f = fwd(nd, X, W, B)
+        g1 = nd.grad(outs=[nd.sum(f)], inputs=[X], create_graph=True)[0]
+        g2 = nd.grad(outs=[nd.sum(g1 * g1)], inputs=[X], create_graph=True)[0]
+        g3 = nd.grad(outs=[nd.sum(g2 * g2)], inputs=W + B[:1])
+        return [g1.to_numpy(), g2.to_numpy()] + [g.to_numpy() for g in g3]
+    fused, plain = third(fwd_fused("tanh")), third(fwd_unfused("tanh"))
+    for a, b in zip(fused, plain):
+        assert np.abs(b).max() > 0
+        assert max_rel(a, b) < 2e-5, max_rel(a, b)
+
+
 def test_functional_transforms_known_answers(nd):
     """README.md:62-76, 98-108 and examples/custom_ops_examples/custom_mul.mojo:64-71."""
     def foo(x):

@@ -263,6 +263,26 @@ def test_fft_forward_vs_numpy(oracle, shape, dims):
     assert rel_l2(back.v, z) < 1e-6
 
 
+@pytest.mark.parametrize("norm", ["backward", "forward", "ortho"])
+@pytest.mark.parametrize("shape,dims", [((8, 64), [-1]), ((4, 16, 32), [0, 2]), ((2, 8, 16), None)])
+def test_fft_norm_modes_vs_numpy(oracle, shape, dims, norm):
+    """Every `norm` follows numpy.fft, for partial dims too ("backward" is also the reference's
+    scaling; the other two deliberately are not, see _norm_divisor), forward values and VJPs."""
+    eo = oracle
+    r = rng(18)
+    z = (r.standard_normal(shape) + 1j * r.standard_normal(shape)).astype(np.complex64)
+    w = r.uniform(-1, 1, shape).astype(np.float32)
+    for fn, ref in ((eo.fftn, np.fft.fftn), (eo.ifftn, np.fft.ifftn)):
+        Z = eo.Array(z, requires_grad=True)
+        y = fn(Z, dims, norm)
+        assert rel_l2(y.v, ref(z.astype(np.complex128), axes=dims, norm=norm)) < 1e-6
+        eo.sum(eo.real(y) * eo.Array(w)).backward()
+        want = np.conj(ref(w.astype(np.complex128), axes=dims, norm=norm))   # conj(F(conj(w + 0i)))
+        assert rel_l2(Z.grad().v, want) < 1e-6
+    with pytest.raises(ValueError):
+        eo.fftn(eo.Array(z), dims, "bogus")
+
+
 def test_fft_vjp_vs_torch(oracle):
     eo = oracle
     r = rng(9)
