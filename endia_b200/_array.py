@@ -17,6 +17,7 @@ from . import _lib
 from ._lib import Tensor as _CTensor
 
 _device = None
+_SCALARS = {}   # (length, value) -> shared constant operand, see Array._scalar
 
 
 def device():
@@ -298,8 +299,21 @@ class Array:
 
     # ---- operator sugar (_array.mojo:957-1099): a scalar becomes full([last_dim], scalar) -------
     def _scalar(self, value):
+        """A Python scalar as an operand: an array of the last dim's length filled with it. These
+        constants are never written after their fill, so one per (length, value) is kept and
+        shared (none is created while a CUDA graph is being captured: its allocations belong to the
+        graph; the ones made by the warm-up steps are used)."""
         from .functional.init_ops import full
-        return full([self.shape()[-1]], float(value))
+        key = (self.shape()[-1] if self.ndim() else 1, float(value))
+        c = _SCALARS.get(key)
+        if c is None:
+            if torch.cuda.is_current_stream_capturing():
+                return full([key[0]], key[1])
+            if len(_SCALARS) >= 256:
+                _SCALARS.clear()
+            c = _SCALARS[key] = full([key[0]], key[1])
+            c.name = "const"
+        return c
 
     def _coerce(self, other):
         return other if isinstance(other, Array) else self._scalar(other)

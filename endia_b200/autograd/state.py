@@ -22,3 +22,6 @@ fft_timer = None
 # deferred arrays so that the loss term and its gradient are folded into the transforms
 # (functional/_deferred.py); ENDIA_B200_FFT_FUSE=0 runs every op eagerly.
 defer_fft_chains = os.environ.get("ENDIA_B200_FFT_FUSE", "1") != "0"
+# A list while utils.CapturedStep captures a step (None otherwise): the leaf arrays whose GEMM
+# operand parts were computed inside the capture and are shared by the products of that step.
+capture_parts = None

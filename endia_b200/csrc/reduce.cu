@@ -223,8 +223,18 @@ colsum_finish_kernel(const float *partial, float *out, int64_t A, int64_t C, int
   for (int64_t blk = blockIdx.x; blk < A * col_blocks; blk += gridDim.x) {
     const int64_t a = blk / col_blocks, c = (blk - a * col_blocks) * 32 + cx;
     float acc = 0.f;
-    if (c < C)
-      for (int k = sl; k < chunks; k += 8) acc += partial[(a * chunks + k) * C + c];
+    if (c < C) {
+      // eight loads in flight, added in the order of k
+      const float *src = partial + a * chunks * C + c;
+      for (int k0 = sl; k0 < chunks; k0 += 64) {
+        float t[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) t[u] = k0 + 8 * u < chunks ? __ldcs(src + (int64_t)(k0 + 8 * u) * C) : 0.f;
+#pragma unroll
+        for (int u = 0; u < 8; ++u)
+          if (k0 + 8 * u < chunks) acc += t[u];
+      }
+    }
     part[sl][cx] = acc;
     __syncthreads();
     if (sl == 0 && c < C) {

@@ -196,7 +196,10 @@ def _operand_parts_ptr(x, kind):
     or None. The parts of a whole storage buffer serve every view of it that starts at its first
     element. They are written by the optimizer for weights and computed here once for the result
     of an op (used by two products: the next layer's forward and a weight gradient). Leaves (user
-    inputs, parameters) are not cached here: their storage may be rewritten between steps."""
+    inputs, parameters) are not cached here, because their storage may be rewritten between steps;
+    except while a step is being captured as a CUDA graph (utils.CapturedStep): nothing outside
+    the step can write between its ops then, so a leaf is split once per step instead of once per
+    product, and the parts are forgotten when the capture ends."""
     base = x.base()
     if base.buf is None or x.buf is not base.buf or base.is_complex():
         return None
@@ -204,8 +207,11 @@ def _operand_parts_ptr(x, kind):
     parts = getattr(base, attr, None)
     if parts is None or base._parts_ptr != base.buf.data_ptr():
         n = base.buf.numel()
-        if base.name == "arg" or n < _LO_CACHE_MIN or n % 8 or not _state.cache_tf32_lo:
+        leaf = base.name == "arg"
+        if (leaf and _state.capture_parts is None) or n < _LO_CACHE_MIN or n % 8 or not _state.cache_tf32_lo:
             return None
+        if leaf:
+            _state.capture_parts.append(base)
         parts = alloc(n)
         if kind == "lo32":
             _lib.call("endia_b200_tf32_split", base.buf.data_ptr(), parts.data_ptr(), 1, n, n, n, stream())

@@ -115,6 +115,9 @@ class CapturedStep:
         torch.cuda.synchronize()
         before = _lib.lib.endia_b200_launch_count()
         self.graph = torch.cuda.CUDAGraph()
+        from ..autograd import state as _state
+        from .._array import drop_operand_parts
+        _state.capture_parts = []      # leaves whose GEMM operand parts are shared inside this step
         try:
             with torch.cuda.graph(self.graph):
                 self.out = fn()
@@ -122,6 +125,10 @@ class CapturedStep:
             for opt in self.optimizers:
                 opt.end_capture()
             raise
+        finally:
+            for leaf in _state.capture_parts:
+                drop_operand_parts(leaf)
+            _state.capture_parts = None
         torch.cuda.synchronize()
         # kernels of this library inside the graph (endia_b200_launch_count only sees enqueues)
         self.launches_per_replay = int(_lib.lib.endia_b200_launch_count() - before)
