@@ -197,6 +197,7 @@ class ShardedAdam:
         self.g_slice = [torch.empty(p.size() // self.world, dtype=torch.float32, device=flat_tensor(p).device)
                         if sh else None for p, sh in zip(self.params, self.sharded)]
         self._m = self._v = None  # moments: allocated (zero) at the first step or first access
+        self._early_stream, self._early_used = None, False
         self.pending = []         # reduce-scatters in flight (not pipelined)
         self.small = []           # (index, gradient) of the replicated tensors of this pass
         self.flat_small = None
@@ -238,6 +239,22 @@ class ShardedAdam:
                 work.wait()
                 out.copy_(tmp[k * r:k * (r + 1)])
         return _Done()
+
+    def _early(self, grad, launch):
+        """Start a collective on a gradient. A fused layer's VJP enqueues the weight-gradient product
+        first and records an event behind it (`_ready_event`); the collective is then ordered behind
+        that event on a stream of its own instead of behind everything enqueued so far, so it runs
+        beside the layer's dX product. step() joins the stream."""
+        ev = getattr(grad, "_ready_event", None)
+        if ev is None or not torch.cuda.is_available() or dist.get_backend(self.group) != "nccl":
+            return launch()
+        if self._early_stream is None:
+            self._early_stream = torch.cuda.Stream(device=flat_tensor(grad).device)
+        self._early_stream.wait_event(ev)
+        with torch.cuda.stream(self._early_stream):
+            work = launch()
+        self._early_used = True
+        return work
 
     def _shardable(self, p):
         return (self.world > 1 and p.size() >= self.SMALL and p.size() % self.world == 0 and p.is_contiguous()
@@ -300,7 +317,7 @@ class ShardedAdam:
             self.small.append((i, g))
             return
         self._ready[i] = True
-        rs = self._reduce_scatter(self.g_slice[i], flat_tensor(g))
+        rs = self._early(g, lambda: self._reduce_scatter(self.g_slice[i], flat_tensor(g)))
         if not self.pipelined:
             self.pending.append(rs)
             return
@@ -387,6 +404,9 @@ class ShardedAdam:
                 self.params[i].grad_(views[i])
             small = views
         capturing = torch.cuda.is_available() and torch.cuda.is_current_stream_capturing()
+        if self._early_used:
+            torch.cuda.current_stream().wait_stream(self._early_stream)
+            self._early_used = False
         if self.pipelined:
             # the replicated tensors here (and the step count), then the layers' chains join
             self._adam(sorted(small), small, stream(), advance=True)

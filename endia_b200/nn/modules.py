@@ -137,7 +137,18 @@ def linear(x, weight, bias=None, activation=None):
                 ds._parts_ptr = ds.buf.data_ptr()
         else:
             ds = g
-        res = []
+        # The weight gradient first: nothing in the backward pass waits for it, but a data-parallel
+        # hook (reduce-scatter / all-reduce) starts when it exists and then runs beside the dX product.
+        dw = zero
+        if wp.requires_grad():
+            dw = Array(ArrayShape(wp.shape()))
+            setup_shape_and_data(dw)
+            gemm_arrays(xp.T(), ds, dw)
+            if getattr(wp, "grad_hook", None) is not None and xp.requires_grad():
+                import torch
+                dw._ready_event = torch.cuda.Event()     # "dw exists", ahead of the dX product
+                dw._ready_event.record()
+        dx = zero
         if xp.requires_grad():
             dx = Array(ArrayShape(xp.shape()))
             dx.name = "linear_vjp"   # a temporary of this pass, never rewritten (see _operand_parts_ptr)
@@ -155,16 +166,7 @@ def linear(x, weight, bias=None, activation=None):
             if parts is not None:
                 dx._pair16 = parts
                 dx._parts_ptr = dx.buf.data_ptr()
-            res.append(dx)
-        else:
-            res.append(zero)
-        if wp.requires_grad():
-            dw = Array(ArrayShape(wp.shape()))
-            setup_shape_and_data(dw)
-            gemm_arrays(xp.T(), ds, dw)
-            res.append(dw)
-        else:
-            res.append(zero)
+        res = [dx, dw]
         if bias is not None:
             res.append(db if need_db else zero)
         return res
