@@ -409,7 +409,7 @@ class PenaltyStep:
         self.samples = self.batch
         self.flops = 62.32e9
         self.h2d_bytes, self.d2h_bytes = int(self.x_host.numel() * 4), 4
-        # The step is about 110 short launches: replayed as one CUDA graph (the library's
+        # The step is about 85 short launches: replayed as one CUDA graph (the library's
         # CapturedStep) it is bound by the GPU instead of the host. ENDIA_B200_BENCH_GRAPH=0 runs
         # it op by op.
         self.captured = None

@@ -96,7 +96,7 @@ class CapturedStep:
     tables) is done, then once more under capture; its return value from that run is kept and
     returned by every call, its Arrays refilled by the replay. A step whose kernels are short next
     to the ~25 us of host work per launch (the create_graph=True double-backward step has about
-    110 launches) becomes GPU-bound this way."""
+    85 launches) becomes GPU-bound this way."""
 
     def __init__(self, fn, warmup=2, optimizers=()):
         """`optimizers`: the optimizers whose step() runs inside fn. Their step count changes from

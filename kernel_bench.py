@@ -61,6 +61,7 @@ def main():
     ap.add_argument("--ta", type=int, default=0)
     ap.add_argument("--tb", type=int, default=0)
     ap.add_argument("--algo", default="auto", choices=["auto", "ffma", "3xtf32", "tf32_bf16x2"])
+    ap.add_argument("--epi", default="none", help="gemm: none, or a '+' list of bias, tanh, parts")
     ap.add_argument("--batch", type=int, default=32)
     ap.add_argument("--shape", default="256,256,256")
     ap.add_argument("--rows", type=int, default=8192)
@@ -81,12 +82,30 @@ def main():
         A = _randn((a.k, a.m) if a.ta else (a.m, a.k), 1)
         B = _randn((a.n, a.k) if a.tb else (a.k, a.n), 2)
         Cc = nd.Array([a.m, a.n])
+        epi = None
+        if a.epi != "none":
+            # the epilogue of a fused layer's forward product: bias, tanh and the operand parts of the
+            # output; the operands come with their own parts, as they do inside a training step
+            epi = _lib.Epilogue()
+            epi.alpha, epi.beta = 1.0, 0.0
+            keep = [_randn((a.n,), 12), alloc(a.m * a.n), alloc(a.m * a.k), alloc(a.k * a.n)]
+            if "bias" in a.epi:
+                epi.bias = keep[0].data_ptr()
+            if "tanh" in a.epi:
+                epi.act = _lib.ACT_TANH
+            if "parts" in a.epi:
+                epi.c16 = keep[1].data_ptr()
+            if algo != _lib.GEMM_3XTF32 and algo != _lib.GEMM_FFMA:
+                _lib.call("endia_b200_bf16_split", A.data_ptr(), keep[2].data_ptr(), a.m * a.k, stream())
+                _lib.call("endia_b200_bf16_split", B.data_ptr(), keep[3].data_ptr(), a.k * a.n, stream())
+                epi.a16, epi.b16 = keep[2].data_ptr(), keep[3].data_ptr()
+            epi = C.byref(epi)
 
         def fn():
             _lib.call("endia_b200_gemm", a.ta, a.tb, a.m, a.n, a.k, A.data_ptr(), A.shape()[1],
-                      B.data_ptr(), B.shape()[1], Cc.data_ptr(), a.n, 1, 0, 0, 0, None, algo, stream())
+                      B.data_ptr(), B.shape()[1], Cc.data_ptr(), a.n, 1, 0, 0, 0, epi, algo, stream())
         ms = _time(fn, a.warmup, a.reps, flush)
-        out.update(m=a.m, n=a.n, k=a.k, ta=a.ta, tb=a.tb, algo=a.algo, ms=ms,
+        out.update(m=a.m, n=a.n, k=a.k, ta=a.ta, tb=a.tb, algo=a.algo, epi=a.epi, ms=ms,
                    tflops=2.0 * a.m * a.n * a.k / ms / 1e9)
     elif a.case in ("fft", "fftn"):
         shape = (a.batch, a.n) if a.case == "fft" else tuple(int(s) for s in a.shape.split(","))
