@@ -168,8 +168,10 @@ torch.distributed.destroy_process_group()
 '''
 
 
-def test_sharded_adam_matches_single_gpu(nd, oracle, tmp_path):
-    """Two ranks, each on half of the batch, three steps with the sharded optimizer (reduce-scatter
+@pytest.mark.parametrize("pipeline", ["0", "1"])
+def test_sharded_adam_matches_single_gpu(nd, oracle, tmp_path, pipeline):
+    """Two ranks, each on half of the batch, three steps with the sharded optimizer, in both of its
+    schedules (gather before use; per-layer chains beside the backward pass) (reduce-scatter
     of the large gradients, 1/P Adam update, all-gather of the updated slices consumed layer by
     layer by the next forward pass): parameters and the mean of the ranks' losses must equal the
     single-process result (oracle)."""
@@ -182,7 +184,8 @@ def test_sharded_adam_matches_single_gpu(nd, oracle, tmp_path):
     s = socket.socket(); s.bind(("127.0.0.1", 0)); port = s.getsockname()[1]; s.close()
     out = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
                           "--master-addr", "127.0.0.1", "--master-port", str(port), str(script)],
-                         capture_output=True, text=True, timeout=300, env=dict(os.environ, NCCL_NVLS_ENABLE="0"))
+                         capture_output=True, text=True, timeout=300,
+                         env=dict(os.environ, NCCL_NVLS_ENABLE="0", ENDIA_B200_DP_PIPELINE=pipeline))
     assert out.returncode == 0, out.stdout + out.stderr
     Ws, bs, x, y = make_mlp_inputs([64, 512, 512, 32], 512, 0)
     oracle.config["mode"] = "fast"
