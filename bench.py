@@ -682,8 +682,8 @@ class Context:
         import torch.distributed as tdist
         self.torch, self.nd, self._lib, self.ndist, self.tdist = torch, nd, _lib, ndist, tdist
         self.args = args
-        # The launcher states the SM split between NCCL and the persistent GEMM grid (see
-        # dist.init_process_group): from 8 ranks on 16 CTAs for NCCL and 16 SMs left out of the GEMM grid.
+        # The launcher can state the SM split between NCCL and the persistent GEMM grid (see
+        # dist.init_process_group); by default neither is limited.
         self.comm_limits = {"nccl_max_ctas": args.nccl_max_ctas, "gemm_reserve_sms": args.reserve_sms}
         self.rank, self.world = ndist.init_process_group(**self.comm_limits)
         nd._array.device()
@@ -889,7 +889,12 @@ def bench_c2(ctx, steps, warmup, gemm="auto", with_cpu=True, with_parity=True):
         "implementation": {
             "gemm": ("tcgen05, one tf32 MMA + two bf16 correction MMAs per product (fp32 accumulate, "
                      "error <= 2.3e-6 of |a||b|)" if bf16c else "tcgen05 3xTF32 (fp32 accumulate)") if tc else "fp32 FFMA",
-            "data_parallel": work.dp_mode,
+            "data_parallel": work.dp_mode + (
+                "" if work.dp_mode != "sharded" else
+                (" (per-layer chains beside the backward pass: reduce-scatter, Adam on 1/P, " + (
+                    "all-gather by the copy engines into peer memory)" if getattr(work.opt, "_inbox", None) is not None
+                    else "NCCL all-gather)") if getattr(work.opt, "pipelined", False)
+                 else " (reduce-scatter, one Adam launch on 1/P, NCCL all-gather before use)")),
             "launch": ("one CUDA graph per step, collectives included (%d kernels of this library); "
                        "ENDIA_B200_BENCH_GRAPH=0 enqueues it op by op" % work.captured.launches_per_replay)
             if work.captured is not None else ("op by op" + (
@@ -1034,10 +1039,9 @@ def main():
                     help="auto = tf32_bf16x2 on the two-CTA tcgen05 kernel (one tf32 MMA + two bf16 correction "
                          "MMAs per product), 3xTF32 split-K or FFMA where that kernel does not apply")
     ap.add_argument("--nccl-max-ctas", type=int, default=-1,
-                    help="N > 1: NCCL_MAX_CTAS (0 = leave unset; default: 16 from 8 ranks on, unset below)")
+                    help="N > 1: NCCL_MAX_CTAS (0 or default: leave unset)")
     ap.add_argument("--reserve-sms", type=int, default=-1,
-                    help="N > 1: SMs left out of the persistent GEMM grid for the collectives (0 = none; "
-                         "default: 16 from 8 ranks on, none below)")
+                    help="N > 1: SMs left out of the persistent GEMM grid for the collectives (0 or default: none)")
     ap.add_argument("--workload", default="all", choices=["all", "c1", "c2", "c3", "c4", "c5"],
                     help="all (default): the c2 line with the other configurations as sub-records; c2: MLP train "
                          "step alone; c1: small MLP, single-launch step; c3: gradient-penalty (second-order) step; "
@@ -1048,14 +1052,13 @@ def main():
         return
     if args.warmup < 3:
         args.warmup = 3
-    # The SM split between NCCL and the persistent GEMM grid, measured on the c2 step: at 4 ranks no
-    # limits 2.23 ms against 2.30 ms with 16 / 16; at 8 ranks (one round of 64 tiles per product)
-    # 16 / 16 1.71 ms against 1.74 ms without.
-    world_env = int(os.environ.get("WORLD_SIZE", "1"))
+    # The SM split between NCCL and the persistent GEMM grid can be stated here; measured on the c2
+    # step with the copy-engine all-gather, no limits are best: 4 ranks 2.13 ms against 2.19 ms with
+    # 16 / 16, and 1.43 against 1.52 ms on the per-rank share of 8 ranks (1024 rows per rank).
     if args.nccl_max_ctas < 0:
-        args.nccl_max_ctas = 16 if world_env >= 8 else 0
+        args.nccl_max_ctas = 0
     if args.reserve_sms < 0:
-        args.reserve_sms = 16 if world_env >= 8 else 0
+        args.reserve_sms = 0
     args.nccl_max_ctas = args.nccl_max_ctas or None
     args.reserve_sms = args.reserve_sms or None
     ctx = Context(args)

@@ -150,6 +150,7 @@ SIGNATURES = {
     "endia_b200_adagrad_step_multi": (C.c_int, [_i32, C.POINTER(_vp), C.POINTER(_vp), C.POINTER(_vp),
                                                 C.POINTER(_i64), _f32, _f32, _f32, _vp]),
     "endia_b200_copy_strided": (C.c_int, [_TP, _TP, _vp]),
+    "endia_b200_gather_slices": (C.c_int, [_vp, _vp, _i64, _i32, _i32, _vp, _vp]),
     "endia_b200_ipc_alloc": (C.c_int, [_sz, C.POINTER(_vp), _vp]),
     "endia_b200_ipc_open": (C.c_int, [_vp, C.POINTER(_vp)]),
     "endia_b200_ipc_close": (C.c_int, [_vp]),

@@ -6,6 +6,7 @@
 // only; no bulk or multicast copy touches peer memory.
 #include "common.cuh"
 #include <string.h>
+#include <cuda_bf16.h>
 
 namespace eb {
 
@@ -105,6 +106,56 @@ extern "C" int endia_b200_copy_strided(const endia_b200_tensor *src, const endia
   if (blocks > cap) blocks = cap;
   if (vec) copy_strided_kernel<4><<<(unsigned)blocks, 256, 0, as_stream(stream)>>>(p);
   else copy_strided_kernel<1><<<(unsigned)blocks, 256, 0, as_stream(stream)>>>(p);
+  EB_LAUNCH_CHECK();
+  return ENDIA_B200_OK;
+}
+
+// The receiving side of an all-gather done with peer copies: the other ranks' slices of a
+// parameter have landed in `inbox` (laid out like the parameter); they are moved into the
+// parameter, and the bf16 operand parts of the whole parameter are written in the same pass.
+__global__ void __launch_bounds__(256)
+gather_slices_kernel(float *__restrict__ w, const float *__restrict__ inbox, int64_t n4, int64_t slice4, int rank,
+                     __nv_bfloat16 *__restrict__ hi, __nv_bfloat16 *__restrict__ lo) {
+  const int64_t step = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += step) {
+    const bool own = i / slice4 == rank;
+    float4 v;
+    if (own) {
+      v = reinterpret_cast<const float4 *>(w)[i];
+    } else {
+      v = __ldcs(reinterpret_cast<const float4 *>(inbox) + i);
+      reinterpret_cast<float4 *>(w)[i] = v;
+    }
+    if (hi) {
+      const float l0 = v.x - __uint_as_float(__float_as_uint(v.x) & 0xFFFFE000u);
+      const float l1 = v.y - __uint_as_float(__float_as_uint(v.y) & 0xFFFFE000u);
+      const float l2 = v.z - __uint_as_float(__float_as_uint(v.z) & 0xFFFFE000u);
+      const float l3 = v.w - __uint_as_float(__float_as_uint(v.w) & 0xFFFFE000u);
+      __nv_bfloat162 h01 = __floats2bfloat162_rn(v.x, v.y), h23 = __floats2bfloat162_rn(v.z, v.w);
+      __nv_bfloat162 l01 = __floats2bfloat162_rn(l0, l1), l23 = __floats2bfloat162_rn(l2, l3);
+      uint2 hv, lv;
+      hv.x = *reinterpret_cast<uint32_t *>(&h01); hv.y = *reinterpret_cast<uint32_t *>(&h23);
+      lv.x = *reinterpret_cast<uint32_t *>(&l01); lv.y = *reinterpret_cast<uint32_t *>(&l23);
+      reinterpret_cast<uint2 *>(hi)[i] = hv;
+      reinterpret_cast<uint2 *>(lo)[i] = lv;
+    }
+  }
+}
+
+extern "C" int endia_b200_gather_slices(float *w, const float *inbox, int64_t numel, int32_t rank, int32_t world,
+                                        void *pair16, void *stream) {
+  int st = eb::require_device();
+  if (st) return st;
+  EB_REQUIRE(w && inbox && numel > 0 && world >= 1 && rank >= 0 && rank < world, ENDIA_B200_EINVAL,
+             "gather_slices: bad arguments");
+  EB_REQUIRE(numel % ((int64_t)8 * world) == 0, ENDIA_B200_EINVAL,
+             "gather_slices: numel must be a multiple of 8 * world");
+  EB_REQUIRE(((reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(inbox) |
+               reinterpret_cast<uintptr_t>(pair16)) & 15) == 0, ENDIA_B200_EINVAL,
+             "gather_slices: pointers must be 16-byte aligned");
+  __nv_bfloat16 *hi = static_cast<__nv_bfloat16 *>(pair16);
+  gather_slices_kernel<<<eb::grid_for(numel / 4, 256), 256, 0, eb::as_stream(stream)>>>(
+      w, inbox, numel / 4, numel / world / 4, rank, hi, hi ? hi + numel : nullptr);
   EB_LAUNCH_CHECK();
   return ENDIA_B200_OK;
 }

@@ -164,16 +164,22 @@ class ShardedAdam:
       all-gather       the updated slices are gathered in place into every rank's parameter, and the
                        parameter's GEMM operand parts are rewritten (one pass over the weights).
 
-    pipelined=False (default): backward() only starts the reduce-scatters (each ordered behind its
-    weight-gradient product, which the layer's VJP enqueues before its dX product); step() runs ONE
-    multi-tensor update, and the gathers start when the parameters are next used (each consumer
-    waits for its own parameter: the next forward pass runs beside the later gathers).
-    pipelined=True (ENDIA_B200_DP_PIPELINE=1): the three steps of a layer run as a chain on a side
-    stream of their own as soon as the layer's gradient exists, beside the backward pass of the
-    layers below; step() updates the bias-sized tensors (one all-reduce, replicated update), joins
-    the chains and advances t. The update of a parameter then starts DURING backward(): every
-    backward() must be followed by one step(). Measured equal to the default at 2 and 4 ranks
-    (4.31 / 4.31 ms and 2.24 / 2.23 ms per c2 step), so the simpler schedule is the default.
+    pipelined=True (default): the steps of a layer run as a chain on a side stream of their own as
+    soon as the layer's gradient exists, beside the backward pass of the layers below: reduce-scatter
+    (ordered behind the weight-gradient product only, which the layer's VJP enqueues before its dX
+    product), Adam on the slice, then the all-gather. Where the ranks can map each other's memory
+    the gather is done by the COPY ENGINES: each rank copies its updated slice into an "inbox" on
+    every peer (cudaMemcpyAsync over NVLink; no SM is taken from the GEMMs and the communicator
+    stays free for the reduce-scatters of the layers below); step() updates the bias-sized tensors
+    (one all-reduce, replicated update), joins the chains, passes one barrier and moves the received
+    slices into the parameters in the pass that also writes their GEMM operand parts
+    (endia_b200_gather_slices). Without peer access the chain ends in an NCCL all-gather
+    (ENDIA_B200_DP_GATHER=nccl forces that). The update of a parameter starts DURING backward():
+    every backward() must be followed by one step(). Measured per c2 step at 2 / 4 ranks: 3.99 / 2.13
+    ms against 4.12 / 2.23 ms for the schedule below, 4.17 / 2.24 ms with the NCCL gather.
+    pipelined=False (ENDIA_B200_DP_PIPELINE=0): backward() only starts the reduce-scatters; step()
+    runs ONE multi-tensor update, and NCCL all-gathers start when the parameters are next used (each
+    consumer waits for its own parameter: the next forward pass runs beside the later gathers).
 
     Either way a step is self-contained (every collective it starts is consumed inside it or at the
     next use of the parameters), which lets it be captured as one CUDA graph. The arithmetic per
@@ -190,7 +196,7 @@ class ShardedAdam:
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
         if pipelined is None:
-            pipelined = os.environ.get("ENDIA_B200_DP_PIPELINE", "0") == "1"
+            pipelined = os.environ.get("ENDIA_B200_DP_PIPELINE", "1") != "0"
         self.pipelined = bool(pipelined) and self.world > 1 and torch.cuda.is_available() \
             and dist.get_backend(group) == "nccl"
         self.t = 1.0
@@ -208,6 +214,23 @@ class ShardedAdam:
         self._chains = {}         # index -> side stream whose chain of this pass is in flight (pipelined)
         self._streams = {}
         self._t_dev = None
+        # Pipelined with peer access: the all-gather is done by the copy engines. Every rank has an
+        # "inbox" laid out like the sharded parameters (mapped into all ranks through CUDA IPC); a
+        # rank copies its updated slice into the peers' inboxes (cudaMemcpyAsync over NVLink: no SM
+        # is taken from the GEMMs and the communicator's stream stays free for the reduce-scatters
+        # of the layers below), and after one barrier each rank moves the received slices into its
+        # parameters in the pass that also writes their GEMM operand parts.
+        self._inbox, self._inbox_off = None, {}
+        if self.pipelined and os.environ.get("ENDIA_B200_DP_GATHER", "peer") == "peer":
+            off, ok = 0, True
+            for i, p in enumerate(self.params):
+                if self.sharded[i]:
+                    self._inbox_off[i] = off
+                    off += p.size()
+                    ok = ok and p.size() % (8 * self.world) == 0
+            made = PeerBuffers._create(4 * off, group) if ok and off else None   # (collective)
+            self._inbox = made
+            self._bar = torch.zeros(1, device=flat_tensor(self.params[0]).device) if made is not None else None
         if self.pipelined:
             self._state()         # zeroed on the compute stream now: the layers' side streams start from it
         for p in self.params:
@@ -338,6 +361,15 @@ class ShardedAdam:
             self._adam([i], None, side.cuda_stream, advance=False)
             k = param.size() // self.world
             full = param.buf[:param.size()]
+            if self._inbox is not None:
+                # this rank's slice into every peer's inbox, nearest neighbour first
+                src = param.buf.data_ptr() + 4 * k * self.rank
+                for d in range(1, self.world):
+                    q = (self.rank + d) % self.world
+                    _lib.call("endia_b200_d2d", self._inbox.ptrs[q] + 4 * (self._inbox_off[i] + k * self.rank), src,
+                              4 * k, side.cuda_stream)
+                self._chains[i] = side
+                return
             ag = dist.all_gather_into_tensor(full, full[k * self.rank:k * (self.rank + 1)], group=self.group,
                                              async_op=True)
             ag.wait()
@@ -358,6 +390,12 @@ class ShardedAdam:
     def detach(self):
         for p in self.params:
             p.grad_hook = None
+
+    def close(self):
+        """Collective: release the peer-mapped inbox of the copy-engine all-gather, if there is one."""
+        if self._inbox is not None:
+            self._inbox.close()
+            self._inbox = None
 
     def reset_state(self):
         from . import _lib
@@ -418,6 +456,24 @@ class ShardedAdam:
             main = torch.cuda.current_stream()
             for side in self._chains.values():
                 main.wait_stream(side)
+            if self._inbox is not None and self._chains:
+                # every rank's copies are behind it on its stream when it joins this all-reduce, so
+                # when it completes here all slices have landed in this rank's inbox
+                dist.all_reduce(self._bar, op=dist.ReduceOp.SUM, group=self.group)
+                from . import _lib
+                for i in sorted(self._chains):
+                    p = self.params[i]
+                    p._tf32_lo = None
+                    wants = self._wants_parts(p)
+                    if wants and getattr(p, "_pair16", None) is None:
+                        p._pair16 = alloc(p.size())
+                    if not wants:
+                        p._pair16 = None
+                    _lib.call("endia_b200_gather_slices", p.buf.data_ptr(),
+                              self._inbox.ptrs[self.rank] + 4 * self._inbox_off[i], p.size(), self.rank, self.world,
+                              p._pair16.data_ptr() if wants else None, stream())
+                    if wants:
+                        p._parts_ptr = p.buf.data_ptr()
             self._chains = {}
         else:
             for w in self.pending:

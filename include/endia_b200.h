@@ -466,6 +466,15 @@ int endia_b200_alltoall_bytes(void *comm, const void *send, void *recv, int64_t 
  * receiving rank's array (the gather of fft_cooley_tukey.mojo:251-257, across GPUs). */
 int endia_b200_copy_strided(const endia_b200_tensor *src, const endia_b200_tensor *dst, void *stream);
 
+/* The receiving side of an all-gather done with peer copies (dist.ShardedAdam): `w` holds this
+ * rank's updated slice [rank * numel/world, (rank+1) * numel/world); the other ranks have copied
+ * theirs into `inbox` (numel floats, laid out like w) with endia_b200_d2d. Moves those slices
+ * into w and, when pair16 is not NULL, writes the bf16 operand parts of the whole of w
+ * ([bf16(w) | bf16(w - tf32(w))], as endia_b200_bf16_split) in the same pass.
+ * numel must be a multiple of 8 * world. No counterpart in the reference (it has no multi-GPU path). */
+int endia_b200_gather_slices(float *w, const float *inbox, int64_t numel, int32_t rank, int32_t world,
+                             void *pair16, void *stream);
+
 /* A device allocation that other processes on the same machine can map (CUDA IPC):
  *   ipc_alloc: allocates `bytes` and fills a 64-byte handle to pass to the other ranks
  *   ipc_open:  maps another process's allocation from its handle (peer access over NVLink)

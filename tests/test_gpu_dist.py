@@ -168,10 +168,11 @@ torch.distributed.destroy_process_group()
 '''
 
 
-@pytest.mark.parametrize("pipeline", ["0", "1"])
+@pytest.mark.parametrize("pipeline", ["0", "1", "1-nccl"])
 def test_sharded_adam_matches_single_gpu(nd, oracle, tmp_path, pipeline):
-    """Two ranks, each on half of the batch, three steps with the sharded optimizer, in both of its
-    schedules (gather before use; per-layer chains beside the backward pass) (reduce-scatter
+    """Two ranks, each on half of the batch, three steps with the sharded optimizer, in each of its
+    schedules (gather before use; per-layer chains beside the backward pass with the all-gather
+    done by the copy engines into peer memory, or by NCCL) (reduce-scatter
     of the large gradients, 1/P Adam update, all-gather of the updated slices consumed layer by
     layer by the next forward pass): parameters and the mean of the ranks' losses must equal the
     single-process result (oracle)."""
@@ -185,7 +186,8 @@ def test_sharded_adam_matches_single_gpu(nd, oracle, tmp_path, pipeline):
     out = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
                           "--master-addr", "127.0.0.1", "--master-port", str(port), str(script)],
                          capture_output=True, text=True, timeout=300,
-                         env=dict(os.environ, NCCL_NVLS_ENABLE="0", ENDIA_B200_DP_PIPELINE=pipeline))
+                         env=dict(os.environ, NCCL_NVLS_ENABLE="0", ENDIA_B200_DP_PIPELINE=pipeline[0],
+                                  ENDIA_B200_DP_GATHER="nccl" if pipeline.endswith("nccl") else "peer"))
     assert out.returncode == 0, out.stdout + out.stderr
     Ws, bs, x, y = make_mlp_inputs([64, 512, 512, 32], 512, 0)
     oracle.config["mode"] = "fast"
@@ -317,3 +319,29 @@ def test_sharded_adam_single_rank_equals_adam(nd):
     assert a[2] == b[2] and a[3] == b[3] == 4.0
     for u, v in zip(a[0] + a[1], b[0] + b[1]):
         assert np.array_equal(u, v)
+
+
+def test_gather_slices_moves_peer_slices_and_writes_parts(nd):
+    """endia_b200_gather_slices: the receiving side of the copy-engine all-gather. The other ranks'
+    slices come from the inbox, the own slice stays, and the bf16 operand parts of the whole
+    parameter equal endia_b200_bf16_split of the result."""
+    from endia_b200 import _lib
+    from endia_b200._array import stream, alloc
+    r = rng(3)
+    n, world, rank = 8 * 4 * 1000, 4, 1
+    w = r.standard_normal(n).astype(np.float32)
+    inbox = r.standard_normal(n).astype(np.float32)
+    W, I = nd.Array(w), nd.Array(inbox)
+    parts, want_parts = alloc(n), alloc(n)
+    _lib.call("endia_b200_gather_slices", W.data_ptr(), I.data_ptr(), n, rank, world, parts.data_ptr(), stream())
+    k = n // world
+    want = inbox.copy()
+    want[k * rank:k * (rank + 1)] = w[k * rank:k * (rank + 1)]
+    assert np.array_equal(W.to_numpy(), want)
+    _lib.call("endia_b200_bf16_split", W.data_ptr(), want_parts.data_ptr(), n, stream())
+    assert np.array_equal(parts.cpu().numpy().view(np.uint32), want_parts.cpu().numpy().view(np.uint32))
+    W2 = nd.Array(w)
+    _lib.call("endia_b200_gather_slices", W2.data_ptr(), I.data_ptr(), n, rank, world, None, stream())
+    assert np.array_equal(W2.to_numpy(), want)
+    st = _lib.lib.endia_b200_gather_slices(W2.data_ptr(), I.data_ptr(), n + 4, rank, world, None, stream())
+    assert st == _lib.EINVAL
