@@ -914,8 +914,9 @@ def bench_c2(ctx, steps, warmup, gemm="auto", with_cpu=True, with_parity=True):
                      # (8192 x 4096 x 4096, the forward and dX products of the 4096-wide layers), from
                      # the committed ncu capture; the other shapes of the step were not captured
                      "traffic": (1.37e9 if bf16c else 1.49e9) if (tc and world == 1) else None,
-                     "traffic_note": "bytes per launch of gemm_tc2p_kernel at 8192x4096x4096 from one ncu capture; "
-                                     "compulsory 0.51e9",
+                     "traffic_note": "bytes per launch of gemm_tc2p_kernel at 8192x4096x4096 from one ncu capture "
+                                     "(a product without an epilogue; 1.77e9 with bias + tanh + the bf16 operand "
+                                     "parts of the output in the epilogue, 0.78e9 compulsory); compulsory 0.51e9",
                      "kernel": "gemm (%d launches per step, %.3f ms of the %.3f ms step)" % (
                          t["n_calls"] // t.get("call_steps", steps), t["call_ms"] / t.get("call_steps", steps),
                          t["ms_step"]),
