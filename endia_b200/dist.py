@@ -175,8 +175,9 @@ class ShardedAdam:
     slices into the parameters in the pass that also writes their GEMM operand parts
     (endia_b200_gather_slices). Without peer access the chain ends in an NCCL all-gather
     (ENDIA_B200_DP_GATHER=nccl forces that). The update of a parameter starts DURING backward():
-    every backward() must be followed by one step(). Measured per c2 step at 2 / 4 ranks: 3.99 / 2.13
-    ms against 4.12 / 2.23 ms for the schedule below, 4.17 / 2.24 ms with the NCCL gather.
+    every backward() must be followed by one step(). Measured per c2 step at 2 / 4 / 8 ranks: 3.99 /
+    2.13 / 1.54 ms against 4.12 / 2.23 / 1.73 ms for the schedule below (4.17 / 2.24 ms at 2 / 4 ranks
+    with the NCCL gather).
     pipelined=False (ENDIA_B200_DP_PIPELINE=0): backward() only starts the reduce-scatters; step()
     runs ONE multi-tensor update, and NCCL all-gathers start when the parameters are next used (each
     consumer waits for its own parameter: the next forward pass runs beside the later gathers).
