@@ -247,10 +247,17 @@ class TrainStep:
             # the graph reads the batch from fixed arrays: the step's batch is copied into them first
             flat = self.ndist.flat_tensor
             if host_io:
-                flat(self.X).copy_(self.x_host.reshape(-1), non_blocking=True)
-                flat(self.Y).copy_(self.y_host.reshape(-1), non_blocking=True)
+                # the batch comes from pinned host memory on a copy stream while the previous step
+                # computes (two staging sets); a device-to-device copy then fills the graph's inputs
+                if self.feeder is None:
+                    from endia_b200.utils.general import HostBatchFeeder
+                    self.feeder = HostBatchFeeder([self.x_host, self.y_host], [self.X.shape(), self.Y.shape()])
+                Xs, Ys = self.feeder.next()
+                flat(self.X).copy_(flat(Xs), non_blocking=True)
+                flat(self.Y).copy_(flat(Ys), non_blocking=True)
             loss = self.captured()
             if host_io:
+                self.feeder.prefetch()
                 self.loss_host.copy_(flat(loss), non_blocking=True)
                 self.torch.cuda.current_stream().synchronize()
                 return float(self.loss_host[0])
@@ -413,6 +420,7 @@ class PenaltyStep:
         # CapturedStep) it is bound by the GPU instead of the host. ENDIA_B200_BENCH_GRAPH=0 runs
         # it op by op.
         self.captured = None
+        self.feeder = None
         if os.environ.get("ENDIA_B200_BENCH_GRAPH", "1") != "0":
             from endia_b200.utils.general import CapturedStep
             self.captured = CapturedStep(self._eager)
@@ -420,9 +428,15 @@ class PenaltyStep:
     def step(self, host_io=False):
         from endia_b200.dist import flat_tensor
         if host_io:
-            flat_tensor(self.X).copy_(self.x_host.reshape(-1), non_blocking=True)
+            # the batch is staged from pinned host memory on a copy stream while the previous step
+            # computes; a device-to-device copy then fills the step's (fixed) input array
+            if self.feeder is None:
+                from endia_b200.utils.general import HostBatchFeeder
+                self.feeder = HostBatchFeeder([self.x_host], [self.X.shape()])
+            flat_tensor(self.X).copy_(flat_tensor(self.feeder.next()[0]), non_blocking=True)
         loss, grads = self.captured() if self.captured is not None else self._eager()
         if host_io:
+            self.feeder.prefetch()
             self.loss_host.copy_(flat_tensor(loss), non_blocking=True)
             self.torch.cuda.current_stream().synchronize()
         return grads
