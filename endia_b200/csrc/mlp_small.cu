@@ -26,6 +26,11 @@ struct SmallMlpArgs {
   float lr, b1, b2, eps, omb1, omb2, c1, c2;
   int act_off[SM_MAX_LAYERS + 2];  // float offsets of the activations in shared memory
   int d_off[2], w_off;             // two gradient buffers and the weight staging buffer
+  // resident != 0: every layer's weights and biases have a place of their own in shared memory and
+  // are read from global memory once, at the start (one memory latency instead of one per layer
+  // and pass); otherwise each layer's weights go through the staging buffer when they are needed
+  int resident;
+  int w_offs[SM_MAX_LAYERS], b_offs[SM_MAX_LAYERS];
 };
 
 __device__ __forceinline__ float small_act(int act, float v) {
@@ -53,9 +58,19 @@ __global__ void __launch_bounds__(SM_THREADS, 1) mlp_small_step_kernel(const __g
   float *Ws = sm + a.w_off;
   // ---- forward
   for (int i = tid; i < B * a.dims[0]; i += SM_THREADS) sm[a.act_off[0] + i] = a.x[i];
+  if (a.resident) {
+    for (int l = 0; l < L; ++l) {
+      const int KN = a.dims[l] * a.dims[l + 1], N = a.dims[l + 1];
+      for (int i = tid; i < KN; i += SM_THREADS) sm[a.w_offs[l] + i] = a.W[l][i];
+      for (int i = tid; i < N; i += SM_THREADS) sm[a.b_offs[l] + i] = a.b[l][i];
+    }
+  }
   for (int l = 0; l < L; ++l) {
     const int K = a.dims[l], N = a.dims[l + 1];
-    for (int i = tid; i < K * N; i += SM_THREADS) Ws[i] = a.W[l][i];
+    const float *bias = a.resident ? sm + a.b_offs[l] : a.b[l];
+    if (a.resident) Ws = sm + a.w_offs[l];
+    else
+      for (int i = tid; i < K * N; i += SM_THREADS) Ws[i] = a.W[l][i];
     __syncthreads();
     const float *in = sm + a.act_off[l];
     float *out = sm + a.act_off[l + 1];
@@ -67,12 +82,13 @@ __global__ void __launch_bounds__(SM_THREADS, 1) mlp_small_step_kernel(const __g
       for (int i = tid; i < B * N4; i += SM_THREADS) {
         const int bi = i / N4, n = (i - bi * N4) * 4;
         float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 8
         for (int k = 0; k < K; ++k) {
           const float x = in[bi * K + k];
           const float4 w = *reinterpret_cast<const float4 *>(Ws + k * N + n);
           s.x = fmaf(x, w.x, s.x); s.y = fmaf(x, w.y, s.y); s.z = fmaf(x, w.z, s.z); s.w = fmaf(x, w.w, s.w);
         }
-        const float4 bb = *reinterpret_cast<const float4 *>(a.b[l] + n);
+        const float4 bb = *reinterpret_cast<const float4 *>(bias + n);
         float4 o;
         o.x = small_act(act, s.x + bb.x); o.y = small_act(act, s.y + bb.y);
         o.z = small_act(act, s.z + bb.z); o.w = small_act(act, s.w + bb.w);
@@ -83,7 +99,7 @@ __global__ void __launch_bounds__(SM_THREADS, 1) mlp_small_step_kernel(const __g
         const int bi = i / N, n = i - bi * N;
         float s = 0.f;
         for (int k = 0; k < K; ++k) s = fmaf(in[bi * K + k], Ws[k * N + n], s);
-        out[i] = small_act(act, s + a.b[l][n]);
+        out[i] = small_act(act, s + bias[n]);
       }
     }
     __syncthreads();
@@ -111,7 +127,9 @@ __global__ void __launch_bounds__(SM_THREADS, 1) mlp_small_step_kernel(const __g
     const int K = a.dims[l], N = a.dims[l + 1];
     const float *in = sm + a.act_off[l], *outp = sm + a.act_off[l + 1];
     const int act = l < L - 1 ? a.act : ENDIA_B200_ACT_NONE;
-    for (int i = tid; i < K * N; i += SM_THREADS) Ws[i] = a.W[l][i];
+    if (a.resident) Ws = sm + a.w_offs[l];      // (the forward pass's copy: untouched by Adam)
+    else
+      for (int i = tid; i < K * N; i += SM_THREADS) Ws[i] = a.W[l][i];
     if (act != ENDIA_B200_ACT_NONE)
       for (int i = tid; i < B * N; i += SM_THREADS) dcur[i] *= small_dact(act, outp[i]);
     __syncthreads();
@@ -121,6 +139,7 @@ __global__ void __launch_bounds__(SM_THREADS, 1) mlp_small_step_kernel(const __g
         for (int i = tid; i < B * K; i += SM_THREADS) {
           const int bi = i / K, k = i - bi * K;
           float s = 0.f;
+#pragma unroll 4
           for (int n = 0; n < N; n += 4) {
             const float4 d = *reinterpret_cast<const float4 *>(dcur + bi * N + n);
             const float4 w = *reinterpret_cast<const float4 *>(Ws + k * N + n);
@@ -142,13 +161,29 @@ __global__ void __launch_bounds__(SM_THREADS, 1) mlp_small_step_kernel(const __g
       const int N4 = N >> 2;
       for (int i = tid; i < K * N4; i += SM_THREADS) {
         const int k = i / N4, n = (i - k * N4) * 4;
-        float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (int bi = 0; bi < B; ++bi) {
+        // four partial sums over the batch rows bi = u (mod 4), so that four loads are in flight;
+        // combined in a fixed order
+        float4 p[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) p[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+        int bi = 0;
+        for (; bi + 4 <= B; bi += 4) {
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const float x = in[(bi + u) * K + k];
+            const float4 d = *reinterpret_cast<const float4 *>(dcur + (bi + u) * N + n);
+            p[u].x = fmaf(x, d.x, p[u].x); p[u].y = fmaf(x, d.y, p[u].y);
+            p[u].z = fmaf(x, d.z, p[u].z); p[u].w = fmaf(x, d.w, p[u].w);
+          }
+        }
+        for (; bi < B; ++bi) {
           const float x = in[bi * K + k];
           const float4 d = *reinterpret_cast<const float4 *>(dcur + bi * N + n);
-          s.x = fmaf(x, d.x, s.x); s.y = fmaf(x, d.y, s.y); s.z = fmaf(x, d.z, s.z); s.w = fmaf(x, d.w, s.w);
+          p[0].x = fmaf(x, d.x, p[0].x); p[0].y = fmaf(x, d.y, p[0].y);
+          p[0].z = fmaf(x, d.z, p[0].z); p[0].w = fmaf(x, d.w, p[0].w);
         }
-        const float g[4] = {s.x, s.y, s.z, s.w};
+        const float g[4] = {(p[0].x + p[1].x) + (p[2].x + p[3].x), (p[0].y + p[1].y) + (p[2].y + p[3].y),
+                            (p[0].z + p[1].z) + (p[2].z + p[3].z), (p[0].w + p[1].w) + (p[2].w + p[3].w)};
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           const int idx = k * N + n + j;
@@ -165,11 +200,17 @@ __global__ void __launch_bounds__(SM_THREADS, 1) mlp_small_step_kernel(const __g
         if (a.do_adam) small_adam(a, a.W[l][i], s, a.mW[l][i], a.vW[l][i]);
       }
     }
-    for (int n = tid; n < N; n += SM_THREADS) {
+    // bias gradient: 16 lanes per column (rows bi = j (mod 16)), added by a fixed shuffle tree
+    for (int base = 0; base < N; base += SM_THREADS / 16) {
+      const int n = base + (tid >> 4), j = tid & 15;
       float s = 0.f;
-      for (int bi = 0; bi < B; ++bi) s += dcur[bi * N + n];
-      a.gb[l][n] = s;
-      if (a.do_adam) small_adam(a, a.b[l][n], s, a.mb[l][n], a.vb[l][n]);
+      if (n < N)
+        for (int bi = j; bi < B; bi += 16) s += dcur[bi * N + n];
+      for (int o = 8; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+      if (n < N && j == 0) {
+        a.gb[l][n] = s;
+        if (a.do_adam) small_adam(a, a.b[l][n], s, a.mb[l][n], a.vb[l][n]);
+      }
     }
     __syncthreads();
     float *t = dcur; dcur = dnext; dnext = t;
@@ -210,6 +251,15 @@ extern "C" int endia_b200_mlp_small_step(int32_t n_layers, const int32_t *dims, 
   a.d_off[0] = off; off += (batch * dmax + 3) / 4 * 4;
   a.d_off[1] = off; off += (batch * dmax + 3) / 4 * 4;
   a.w_off = off; off += wmax;
+  int res = off - wmax;            // resident layout: every layer's weights and biases instead of one staging buffer
+  for (int l = 0; l < n_layers; ++l) {
+    a.w_offs[l] = res; res += (dims[l] * dims[l + 1] + 3) / 4 * 4;
+    a.b_offs[l] = res; res += (dims[l + 1] + 3) / 4 * 4;
+  }
+  if (sizeof(float) * (size_t)res <= 200 * 1024) {
+    a.resident = 1;
+    off = res > off ? res : off;
+  }
   const size_t smem = sizeof(float) * (size_t)off;
   EB_REQUIRE(smem <= 200 * 1024, ENDIA_B200_ELIMIT,
              "mlp_small_step: the network's activations need %zu bytes of shared memory (limit %d); "
