@@ -265,9 +265,11 @@ def test_c2_full_size_gemm_identities(nd):
 
 
 @pytest.mark.parametrize("act,dims,batch", [("relu", [1, 32, 32, 32, 1], 128), ("tanh", [7, 64, 33, 5], 96),
-                                            ("sigmoid", [3, 16, 2], 17)])
+                                            ("sigmoid", [3, 16, 2], 17), ("tanh", [128, 128, 128, 128, 128], 32)])
 def test_fused_small_mlp_step_matches_oracle(nd, oracle, act, dims, batch):
-    """The single-launch whole-step kernel (c1 and other small networks) over three steps."""
+    """The single-launch whole-step kernel (c1 and other small networks) over three steps. The last
+    case is too large for all its weights to stay in shared memory beside the activations: each
+    layer's weights then pass through the staging buffer."""
     Ws, bs, x, y = make_mlp_inputs(dims, batch, 0, x_dist="uniform" if dims[0] == 1 else "normal")
     if dims[0] == 1:
         y = np.sin(np.float32(15) * x).astype(np.float32)
