@@ -10,8 +10,13 @@ def backward(arg, create_graph=False):
     jacrev(arg, create_graph)
 
 
-def jacrev(arg, create_graph=False):
+def jacrev(arg, create_graph=False, only_for=None):
     """Reverse walk over the graph of `arg` (autograd/functional.mojo:26-67).
+
+    `only_for` (a list of Arrays, used by the imperative grad(outs, inputs)): VJPs are evaluated
+    only along the paths from `arg` to these arrays; gradients that cannot reach one of them (e.g.
+    the weight gradients when only the input gradient of a network is asked for) are not computed.
+    The gradients of the listed arrays are the same either way.
 
     A 1-D, one-element output is seeded with ones(1); any other output gets an identity seed of
     shape out.shape + out.shape, so the stored gradients are full Jacobians (:34-38). Gradients
@@ -22,6 +27,14 @@ def jacrev(arg, create_graph=False):
     from ..functional.binary_ops import add
     out = arg
     trace = top_order(out)
+    wanted = None
+    if only_for is not None:
+        # nodes whose value depends on one of the listed arrays (every node comes after its arguments)
+        targets = {id(a) for a in only_for}
+        wanted = set()
+        for node in trace:
+            if id(node) in targets or any(id(a) in wanted for a in node.args_):
+                wanted.add(id(node))
     last_dim = out.shape()[-1]
     if out.ndim() != 1 or last_dim != 1:
         seed = reshape(eye(out.size()), out.shape() + out.shape())
@@ -38,16 +51,19 @@ def jacrev(arg, create_graph=False):
     # (also left on the nodes for VJPs that fuse work across an edge only when it is the only one)
     for node in trace:
         node._consumers = pending.get(id(node), 0)
-    prev = _state.create_graph
+    prev, prev_wanted = _state.create_graph, _state.grad_wanted
     _state.create_graph = bool(create_graph)
+    _state.grad_wanted = wanted      # (the VJPs with expensive operands consult state.wants_grad)
     try:
         for curr in reversed(trace):
             primals = curr.args_
             if not primals:
                 continue
+            if wanted is not None and id(curr) not in wanted:
+                continue
             grads = curr.vjp_(primals, curr.grad(), curr)
             for primal, g in zip(primals, grads):
-                if not primal.requires_grad():
+                if not primal.requires_grad() or (wanted is not None and id(primal) not in wanted):
                     continue
                 if primal.has_grad():
                     g = add(g, primal.grad())
@@ -60,6 +76,7 @@ def jacrev(arg, create_graph=False):
                 pending[id(primal)] -= 1
     finally:
         _state.create_graph = prev
+        _state.grad_wanted = prev_wanted
         reset_node_id_recursive(out)
 
 
@@ -97,7 +114,7 @@ def grad(outs=None, inputs=None, retain_grads=True, create_graph=False, argnums=
     for inp in inputs:
         remove_grad_rec(inp)
     for out in outs:
-        out.backward(create_graph=create_graph)
+        jacrev(out, create_graph, only_for=inputs)
     final = []
     for inp in inputs:
         g = inp.grad()

@@ -25,3 +25,11 @@ defer_fft_chains = os.environ.get("ENDIA_B200_FFT_FUSE", "1") != "0"
 # A list while utils.CapturedStep captures a step (None otherwise): the leaf arrays whose GEMM
 # operand parts were computed inside the capture and are shared by the products of that step.
 capture_parts = None
+# While a reverse walk runs for grad(outs, inputs): the ids of the nodes whose value depends on one of
+# `inputs` (None: every gradient is computed). wants_grad() is what the VJPs whose operands' gradients
+# are expensive (matrix products) ask instead of requires_grad().
+grad_wanted = None
+
+
+def wants_grad(arr):
+    return arr.requires_grad() and (grad_wanted is None or id(arr) in grad_wanted)

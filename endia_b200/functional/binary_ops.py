@@ -282,8 +282,8 @@ def _matmul_call(curr, args):
 def _matmul_vjp(primals, grad, out):
     # dX = g @ W.T, dW = X.T @ g, each a new differentiable matmul on a transposed view
     # (matmul_op.mojo:278-284). The product with a square W is the mathematically correct one.
-    lhs = matmul(grad, primals[1].T()) if primals[0].requires_grad() else _zero()
-    rhs = matmul(primals[0].T(), grad) if primals[1].requires_grad() else _zero()
+    lhs = matmul(grad, primals[1].T()) if _state.wants_grad(primals[0]) else _zero()
+    rhs = matmul(primals[0].T(), grad) if _state.wants_grad(primals[1]) else _zero()
     return [lhs, rhs]
 
 

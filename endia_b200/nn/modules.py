@@ -97,13 +97,13 @@ def linear(x, weight, bias=None, activation=None):
         zero = Array(0)
         if _state.create_graph:
             ds = _act_bwd_graph(act, out, grad)
-            dx = matmul(ds, wp.T()) if xp.requires_grad() else zero
-            dw = matmul(xp.T(), ds) if wp.requires_grad() else zero
+            dx = matmul(ds, wp.T()) if _state.wants_grad(xp) else zero
+            dw = matmul(xp.T(), ds) if _state.wants_grad(wp) else zero
             res = [dx, dw]
             if bias is not None:
-                res.append(reduce_add(ds, [0]) if primals[2].requires_grad() else zero)
+                res.append(reduce_add(ds, [0]) if _state.wants_grad(primals[2]) else zero)
             return res
-        need_db = bias is not None and primals[2].requires_grad()
+        need_db = bias is not None and _state.wants_grad(primals[2])
         g = contiguous(grad)
         db = None
         if getattr(grad, "_masked_for", None) is out:
@@ -140,7 +140,7 @@ def linear(x, weight, bias=None, activation=None):
         # The weight gradient first: nothing in the backward pass waits for it, but a data-parallel
         # hook (reduce-scatter / all-reduce) starts when it exists and then runs beside the dX product.
         dw = zero
-        if wp.requires_grad():
+        if _state.wants_grad(wp):
             dw = Array(ArrayShape(wp.shape()))
             setup_shape_and_data(dw)
             gemm_arrays(xp.T(), ds, dw)
@@ -149,7 +149,7 @@ def linear(x, weight, bias=None, activation=None):
                 dw._ready_event = torch.cuda.Event()     # "dw exists", ahead of the dX product
                 dw._ready_event.record()
         dx = zero
-        if xp.requires_grad():
+        if _state.wants_grad(xp):
             dx = Array(ArrayShape(xp.shape()))
             dx.name = "linear_vjp"   # a temporary of this pass, never rewritten (see _operand_parts_ptr)
             setup_shape_and_data(dx)
