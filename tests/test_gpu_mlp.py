@@ -212,6 +212,35 @@ def test_fused_tanh_layer_third_order_matches_op_composition(nd):
         assert max_rel(a, b) < 2e-5, max_rel(a, b)
 
 
+def test_grad_of_inputs_skips_products_that_cannot_reach_them(nd):
+    """grad(outs, inputs) walks only the paths to `inputs`: asking for the input gradient of a
+    network runs no weight-gradient product (fewer launches, the weights get no gradient), and the
+    input gradient equals the one a full backward() leaves on the input."""
+    r = rng(11)
+    d = [32, 256, 256, 8]
+    Ws = [r.uniform(-0.3, 0.3, (d[i], d[i + 1])).astype(np.float32) for i in range(3)]
+    bs = [r.uniform(-0.3, 0.3, d[i + 1]).astype(np.float32) for i in range(3)]
+    x = r.standard_normal((128, 32)).astype(np.float32)
+
+    def run(only_input):
+        W = [nd.Array(w.copy(), requires_grad=True) for w in Ws]
+        B = [nd.Array(b.copy(), requires_grad=True) for b in bs]
+        X = nd.Array(x, requires_grad=True)
+        out = nd.sum(fwd_fused("tanh")(nd, X, W, B))
+        n0 = nd._lib.lib.endia_b200_launch_count()
+        if only_input:
+            gx = nd.grad(outs=[out], inputs=[X])[0]
+        else:
+            out.backward()
+            gx = X.grad()
+        return gx.to_numpy(), nd._lib.lib.endia_b200_launch_count() - n0, [w.has_grad() for w in W]
+    g_only, launches_only, has_only = run(True)
+    g_all, launches_all, has_all = run(False)
+    assert np.array_equal(g_only, g_all)
+    assert launches_only < launches_all
+    assert has_only == [False] * 3 and has_all == [True] * 3
+
+
 def test_functional_transforms_known_answers(nd):
     """README.md:62-76, 98-108 and examples/custom_ops_examples/custom_mul.mojo:64-71."""
     def foo(x):
