@@ -26,6 +26,7 @@ struct SmallMlpArgs {
   float lr, b1, b2, eps, omb1, omb2, c1, c2;
   int act_off[SM_MAX_LAYERS + 2];  // float offsets of the activations in shared memory
   int d_off[2], w_off;             // two gradient buffers and the weight staging buffer
+  int red_off;                     // 2048 floats: slice sums of the weight gradients
   // resident != 0: every layer's weights and biases have a place of their own in shared memory and
   // are read from global memory once, at the start (one memory latency instead of one per layer
   // and pass); otherwise each layer's weights go through the staging buffer when they are needed
@@ -76,23 +77,30 @@ __global__ void __launch_bounds__(SM_THREADS, 1) mlp_small_step_kernel(const __g
     float *out = sm + a.act_off[l + 1];
     const int act = l < L - 1 ? a.act : ENDIA_B200_ACT_NONE;
     if ((N & 3) == 0) {
-      // four adjacent outputs per thread: one broadcast read of the input and one 128-bit read
-      // of the weights feed four FMAs
-      const int N4 = N >> 2;
-      for (int i = tid; i < B * N4; i += SM_THREADS) {
-        const int bi = i / N4, n = (i - bi * N4) * 4;
-        float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+      // four adjacent outputs of two batch rows per thread: two broadcast reads of the input and
+      // one 128-bit read of the weights feed eight FMAs (the second row is masked at an odd batch)
+      const int N4 = N >> 2, B2 = (B + 1) >> 1;
+      for (int i = tid; i < B2 * N4; i += SM_THREADS) {
+        const int bp = i / N4, n = (i - bp * N4) * 4;
+        const int r0 = 2 * bp, r1 = r0 + 1 < B ? r0 + 1 : r0;
+        float4 s0 = make_float4(0.f, 0.f, 0.f, 0.f), s1 = s0;
 #pragma unroll 8
         for (int k = 0; k < K; ++k) {
-          const float x = in[bi * K + k];
+          const float x0 = in[r0 * K + k], x1 = in[r1 * K + k];
           const float4 w = *reinterpret_cast<const float4 *>(Ws + k * N + n);
-          s.x = fmaf(x, w.x, s.x); s.y = fmaf(x, w.y, s.y); s.z = fmaf(x, w.z, s.z); s.w = fmaf(x, w.w, s.w);
+          s0.x = fmaf(x0, w.x, s0.x); s0.y = fmaf(x0, w.y, s0.y); s0.z = fmaf(x0, w.z, s0.z); s0.w = fmaf(x0, w.w, s0.w);
+          s1.x = fmaf(x1, w.x, s1.x); s1.y = fmaf(x1, w.y, s1.y); s1.z = fmaf(x1, w.z, s1.z); s1.w = fmaf(x1, w.w, s1.w);
         }
         const float4 bb = *reinterpret_cast<const float4 *>(bias + n);
         float4 o;
-        o.x = small_act(act, s.x + bb.x); o.y = small_act(act, s.y + bb.y);
-        o.z = small_act(act, s.z + bb.z); o.w = small_act(act, s.w + bb.w);
-        *reinterpret_cast<float4 *>(out + bi * N + n) = o;
+        o.x = small_act(act, s0.x + bb.x); o.y = small_act(act, s0.y + bb.y);
+        o.z = small_act(act, s0.z + bb.z); o.w = small_act(act, s0.w + bb.w);
+        *reinterpret_cast<float4 *>(out + r0 * N + n) = o;
+        if (r1 != r0) {
+          o.x = small_act(act, s1.x + bb.x); o.y = small_act(act, s1.y + bb.y);
+          o.z = small_act(act, s1.z + bb.z); o.w = small_act(act, s1.w + bb.w);
+          *reinterpret_cast<float4 *>(out + r1 * N + n) = o;
+        }
       }
     } else {
       for (int i = tid; i < B * N; i += SM_THREADS) {
@@ -136,16 +144,22 @@ __global__ void __launch_bounds__(SM_THREADS, 1) mlp_small_step_kernel(const __g
     // gradient w.r.t. the layer input, with the weights as they were in the forward pass
     if (l > 0) {
       if ((N & 3) == 0) {
-        for (int i = tid; i < B * K; i += SM_THREADS) {
-          const int bi = i / K, k = i - bi * K;
-          float s = 0.f;
+        // two adjacent inputs k of one batch row per thread: one 128-bit read of the gradient and
+        // two of the weights feed eight FMAs (the second is masked at an odd K)
+        const int K2 = (K + 1) >> 1;
+        for (int i = tid; i < B * K2; i += SM_THREADS) {
+          const int bi = i / K2, k0 = (i - bi * K2) * 2, k1 = k0 + 1 < K ? k0 + 1 : k0;
+          float s0 = 0.f, s1 = 0.f;
 #pragma unroll 4
           for (int n = 0; n < N; n += 4) {
             const float4 d = *reinterpret_cast<const float4 *>(dcur + bi * N + n);
-            const float4 w = *reinterpret_cast<const float4 *>(Ws + k * N + n);
-            s = fmaf(d.x, w.x, s); s = fmaf(d.y, w.y, s); s = fmaf(d.z, w.z, s); s = fmaf(d.w, w.w, s);
+            const float4 w0 = *reinterpret_cast<const float4 *>(Ws + k0 * N + n);
+            const float4 w1 = *reinterpret_cast<const float4 *>(Ws + k1 * N + n);
+            s0 = fmaf(d.x, w0.x, s0); s0 = fmaf(d.y, w0.y, s0); s0 = fmaf(d.z, w0.z, s0); s0 = fmaf(d.w, w0.w, s0);
+            s1 = fmaf(d.x, w1.x, s1); s1 = fmaf(d.y, w1.y, s1); s1 = fmaf(d.z, w1.z, s1); s1 = fmaf(d.w, w1.w, s1);
           }
-          dnext[i] = s;
+          dnext[bi * K + k0] = s0;
+          if (k1 != k0) dnext[bi * K + k1] = s1;
         }
       } else {
         for (int i = tid; i < B * K; i += SM_THREADS) {
@@ -156,48 +170,83 @@ __global__ void __launch_bounds__(SM_THREADS, 1) mlp_small_step_kernel(const __g
         }
       }
     }
-    // weight and bias gradients, then Adam on both
-    if ((N & 3) == 0) {
-      const int N4 = N >> 2;
-      for (int i = tid; i < K * N4; i += SM_THREADS) {
-        const int k = i / N4, n = (i - k * N4) * 4;
-        // four partial sums over the batch rows bi = u (mod 4), so that four loads are in flight;
-        // combined in a fixed order
-        float4 p[4];
+    // weight gradient, then Adam. The batch rows are cut into S slices so that every thread has a
+    // share: a thread sums one slice for one group of outputs (four columns, or one), four rows
+    // in flight; with S > 1 the slice sums go through shared memory and are added in slice order.
+    {
+      const bool vec = (N & 3) == 0;
+      const int groups = vec ? K * (N >> 2) : K * N;
+      int S = SM_THREADS / groups;
+      S = S < 1 ? 1 : (S > 16 ? 16 : S);
+      if (S > B) S = B;
+      const int rows = (B + S - 1) / S;
+      float *part = sm + a.red_off;                 // [S][K * N], S * K * N <= 2048
+      for (int i = tid; i < groups * S; i += SM_THREADS) {
+        const int sl = i / groups, g = i - sl * groups;
+        const int b0 = sl * rows, b1 = b0 + rows < B ? b0 + rows : B;
+        if (vec) {
+          const int N4 = N >> 2;
+          const int k = g / N4, n = (g - k * N4) * 4;
+          float4 p[4];
 #pragma unroll
-        for (int u = 0; u < 4; ++u) p[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-        int bi = 0;
-        for (; bi + 4 <= B; bi += 4) {
+          for (int u = 0; u < 4; ++u) p[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+          int bi = b0;
+          for (; bi + 4 <= b1; bi += 4) {
 #pragma unroll
-          for (int u = 0; u < 4; ++u) {
-            const float x = in[(bi + u) * K + k];
-            const float4 d = *reinterpret_cast<const float4 *>(dcur + (bi + u) * N + n);
-            p[u].x = fmaf(x, d.x, p[u].x); p[u].y = fmaf(x, d.y, p[u].y);
-            p[u].z = fmaf(x, d.z, p[u].z); p[u].w = fmaf(x, d.w, p[u].w);
+            for (int u = 0; u < 4; ++u) {
+              const float x = in[(bi + u) * K + k];
+              const float4 d = *reinterpret_cast<const float4 *>(dcur + (bi + u) * N + n);
+              p[u].x = fmaf(x, d.x, p[u].x); p[u].y = fmaf(x, d.y, p[u].y);
+              p[u].z = fmaf(x, d.z, p[u].z); p[u].w = fmaf(x, d.w, p[u].w);
+            }
+          }
+          for (; bi < b1; ++bi) {
+            const float x = in[bi * K + k];
+            const float4 d = *reinterpret_cast<const float4 *>(dcur + bi * N + n);
+            p[0].x = fmaf(x, d.x, p[0].x); p[0].y = fmaf(x, d.y, p[0].y);
+            p[0].z = fmaf(x, d.z, p[0].z); p[0].w = fmaf(x, d.w, p[0].w);
+          }
+          const float4 gsum = make_float4((p[0].x + p[1].x) + (p[2].x + p[3].x), (p[0].y + p[1].y) + (p[2].y + p[3].y),
+                                          (p[0].z + p[1].z) + (p[2].z + p[3].z), (p[0].w + p[1].w) + (p[2].w + p[3].w));
+          if (S > 1) {
+            *reinterpret_cast<float4 *>(part + sl * K * N + k * N + n) = gsum;
+          } else {
+            const float gv[4] = {gsum.x, gsum.y, gsum.z, gsum.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const int idx = k * N + n + j;
+              a.gW[l][idx] = gv[j];
+              if (a.do_adam) small_adam(a, a.W[l][idx], gv[j], a.mW[l][idx], a.vW[l][idx]);
+            }
+          }
+        } else {
+          const int k = g / N, n = g - k * N;
+          float p0 = 0.f, p1 = 0.f, p2 = 0.f, p3 = 0.f;
+          int bi = b0;
+          for (; bi + 4 <= b1; bi += 4) {
+            p0 = fmaf(in[(bi + 0) * K + k], dcur[(bi + 0) * N + n], p0);
+            p1 = fmaf(in[(bi + 1) * K + k], dcur[(bi + 1) * N + n], p1);
+            p2 = fmaf(in[(bi + 2) * K + k], dcur[(bi + 2) * N + n], p2);
+            p3 = fmaf(in[(bi + 3) * K + k], dcur[(bi + 3) * N + n], p3);
+          }
+          for (; bi < b1; ++bi) p0 = fmaf(in[bi * K + k], dcur[bi * N + n], p0);
+          const float gv = (p0 + p1) + (p2 + p3);
+          if (S > 1) {
+            part[sl * K * N + g] = gv;
+          } else {
+            a.gW[l][g] = gv;
+            if (a.do_adam) small_adam(a, a.W[l][g], gv, a.mW[l][g], a.vW[l][g]);
           }
         }
-        for (; bi < B; ++bi) {
-          const float x = in[bi * K + k];
-          const float4 d = *reinterpret_cast<const float4 *>(dcur + bi * N + n);
-          p[0].x = fmaf(x, d.x, p[0].x); p[0].y = fmaf(x, d.y, p[0].y);
-          p[0].z = fmaf(x, d.z, p[0].z); p[0].w = fmaf(x, d.w, p[0].w);
-        }
-        const float g[4] = {(p[0].x + p[1].x) + (p[2].x + p[3].x), (p[0].y + p[1].y) + (p[2].y + p[3].y),
-                            (p[0].z + p[1].z) + (p[2].z + p[3].z), (p[0].w + p[1].w) + (p[2].w + p[3].w)};
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const int idx = k * N + n + j;
-          a.gW[l][idx] = g[j];
-          if (a.do_adam) small_adam(a, a.W[l][idx], g[j], a.mW[l][idx], a.vW[l][idx]);
-        }
       }
-    } else {
-      for (int i = tid; i < K * N; i += SM_THREADS) {
-        const int k = i / N, n = i - k * N;
-        float s = 0.f;
-        for (int bi = 0; bi < B; ++bi) s = fmaf(in[bi * K + k], dcur[bi * N + n], s);
-        a.gW[l][i] = s;
-        if (a.do_adam) small_adam(a, a.W[l][i], s, a.mW[l][i], a.vW[l][i]);
+      if (S > 1) {
+        __syncthreads();
+        for (int o = tid; o < K * N; o += SM_THREADS) {
+          float v = 0.f;
+          for (int sl = 0; sl < S; ++sl) v += part[sl * K * N + o];
+          a.gW[l][o] = v;
+          if (a.do_adam) small_adam(a, a.W[l][o], v, a.mW[l][o], a.vW[l][o]);
+        }
       }
     }
     // bias gradient: 16 lanes per column (rows bi = j (mod 16)), added by a fixed shuffle tree
@@ -250,6 +299,7 @@ extern "C" int endia_b200_mlp_small_step(int32_t n_layers, const int32_t *dims, 
   }
   a.d_off[0] = off; off += (batch * dmax + 3) / 4 * 4;
   a.d_off[1] = off; off += (batch * dmax + 3) / 4 * 4;
+  a.red_off = off; off += 2048;
   a.w_off = off; off += wmax;
   int res = off - wmax;            // resident layout: every layer's weights and biases instead of one staging buffer
   for (int l = 0; l < n_layers; ++l) {
