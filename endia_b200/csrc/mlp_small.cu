@@ -26,7 +26,8 @@ struct SmallMlpArgs {
   float lr, b1, b2, eps, omb1, omb2, c1, c2;
   int act_off[SM_MAX_LAYERS + 2];  // float offsets of the activations in shared memory
   int d_off[2], w_off;             // two gradient buffers and the weight staging buffer
-  int red_off;                     // 2048 floats: slice sums of the weight gradients
+  int red_off;                     // slice sums of the weight gradients: max over layers of slices * K * N floats
+  int slices[SM_MAX_LAYERS];       // batch slices of each layer's weight-gradient sum (1: no slice sums)
   // resident != 0: every layer's weights and biases have a place of their own in shared memory and
   // are read from global memory once, at the start (one memory latency instead of one per layer
   // and pass); otherwise each layer's weights go through the staging buffer when they are needed
@@ -84,8 +85,26 @@ __global__ void __launch_bounds__(SM_THREADS, 1) mlp_small_step_kernel(const __g
         const int bp = i / N4, n = (i - bp * N4) * 4;
         const int r0 = 2 * bp, r1 = r0 + 1 < B ? r0 + 1 : r0;
         float4 s0 = make_float4(0.f, 0.f, 0.f, 0.f), s1 = s0;
+        int k = 0;
+        if ((K & 3) == 0) {
+          // (128-bit reads of the inputs as well: six shared-memory loads per 32 FMAs)
+#pragma unroll 2
+          for (; k < K; k += 4) {
+            const float4 xa = *reinterpret_cast<const float4 *>(in + r0 * K + k);
+            const float4 xb = *reinterpret_cast<const float4 *>(in + r1 * K + k);
+            const float xs0[4] = {xa.x, xa.y, xa.z, xa.w}, xs1[4] = {xb.x, xb.y, xb.z, xb.w};
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              const float4 w = *reinterpret_cast<const float4 *>(Ws + (k + u) * N + n);
+              s0.x = fmaf(xs0[u], w.x, s0.x); s0.y = fmaf(xs0[u], w.y, s0.y);
+              s0.z = fmaf(xs0[u], w.z, s0.z); s0.w = fmaf(xs0[u], w.w, s0.w);
+              s1.x = fmaf(xs1[u], w.x, s1.x); s1.y = fmaf(xs1[u], w.y, s1.y);
+              s1.z = fmaf(xs1[u], w.z, s1.z); s1.w = fmaf(xs1[u], w.w, s1.w);
+            }
+          }
+        }
 #pragma unroll 8
-        for (int k = 0; k < K; ++k) {
+        for (; k < K; ++k) {
           const float x0 = in[r0 * K + k], x1 = in[r1 * K + k];
           const float4 w = *reinterpret_cast<const float4 *>(Ws + k * N + n);
           s0.x = fmaf(x0, w.x, s0.x); s0.y = fmaf(x0, w.y, s0.y); s0.z = fmaf(x0, w.z, s0.z); s0.w = fmaf(x0, w.w, s0.w);
@@ -171,20 +190,50 @@ __global__ void __launch_bounds__(SM_THREADS, 1) mlp_small_step_kernel(const __g
       }
     }
     // weight gradient, then Adam. The batch rows are cut into S slices so that every thread has a
-    // share: a thread sums one slice for one group of outputs (four columns, or one), four rows
-    // in flight; with S > 1 the slice sums go through shared memory and are added in slice order.
+    // share: a thread sums one slice for one group of outputs (4 inputs x 4 columns as an outer
+    // product of two 128-bit reads, or four columns, or one); with S > 1 the slice sums go through
+    // shared memory and are added in slice order.
     {
-      const bool vec = (N & 3) == 0;
-      const int groups = vec ? K * (N >> 2) : K * N;
-      int S = SM_THREADS / groups;
-      S = S < 1 ? 1 : (S > 16 ? 16 : S);
-      if (S > B) S = B;
+      const bool vec = (N & 3) == 0, quad = vec && (K & 3) == 0;
+      const int groups = quad ? (K >> 2) * (N >> 2) : (vec ? K * (N >> 2) : K * N);
+      const int S = a.slices[l];
       const int rows = (B + S - 1) / S;
-      float *part = sm + a.red_off;                 // [S][K * N], S * K * N <= 2048
+      float *part = sm + a.red_off;                 // [S][K * N]
       for (int i = tid; i < groups * S; i += SM_THREADS) {
         const int sl = i / groups, g = i - sl * groups;
         const int b0 = sl * rows, b1 = b0 + rows < B ? b0 + rows : B;
-        if (vec) {
+        if (quad) {
+          const int N4 = N >> 2;
+          const int k = (g / N4) * 4, n = (g - (g / N4) * N4) * 4;
+          float4 acc[4];
+#pragma unroll
+          for (int u = 0; u < 4; ++u) acc[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 4
+          for (int bi = b0; bi < b1; ++bi) {
+            const float4 x = *reinterpret_cast<const float4 *>(in + bi * K + k);
+            const float4 d = *reinterpret_cast<const float4 *>(dcur + bi * N + n);
+            const float xs[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              acc[u].x = fmaf(xs[u], d.x, acc[u].x); acc[u].y = fmaf(xs[u], d.y, acc[u].y);
+              acc[u].z = fmaf(xs[u], d.z, acc[u].z); acc[u].w = fmaf(xs[u], d.w, acc[u].w);
+            }
+          }
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            if (S > 1) {
+              *reinterpret_cast<float4 *>(part + sl * K * N + (k + u) * N + n) = acc[u];
+            } else {
+              const float gv[4] = {acc[u].x, acc[u].y, acc[u].z, acc[u].w};
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const int idx = (k + u) * N + n + j;
+                a.gW[l][idx] = gv[j];
+                if (a.do_adam) small_adam(a, a.W[l][idx], gv[j], a.mW[l][idx], a.vW[l][idx]);
+              }
+            }
+          }
+        } else if (vec) {
           const int N4 = N >> 2;
           const int k = g / N4, n = (g - k * N4) * 4;
           float4 p[4];
@@ -299,7 +348,23 @@ extern "C" int endia_b200_mlp_small_step(int32_t n_layers, const int32_t *dims, 
   }
   a.d_off[0] = off; off += (batch * dmax + 3) / 4 * 4;
   a.d_off[1] = off; off += (batch * dmax + 3) / 4 * 4;
-  a.red_off = off; off += 2048;
+  // batch slices of the weight-gradient sums (same grouping as the kernel), and their scratch
+  int red = 0;
+  for (int l = 0; l < n_layers; ++l) {
+    const int K = dims[l], N = dims[l + 1];
+    const bool vec = (N & 3) == 0, quad = vec && (K & 3) == 0;
+    const int groups = quad ? (K >> 2) * (N >> 2) : (vec ? K * (N >> 2) : K * N);
+    int S = SM_THREADS / groups;
+    S = S < 1 ? 1 : (S > 16 ? 16 : S);
+    if (S > batch) S = batch;
+    a.slices[l] = S;
+    if (S > 1 && S * K * N > red) red = S * K * N;
+  }
+  if (sizeof(float) * (size_t)(off + red + wmax) > 200 * 1024) {   // no room: every layer in one slice
+    for (int l = 0; l < n_layers; ++l) a.slices[l] = 1;
+    red = 0;
+  }
+  a.red_off = off; off += (red + 3) / 4 * 4;
   a.w_off = off; off += wmax;
   int res = off - wmax;            // resident layout: every layer's weights and biases instead of one staging buffer
   for (int l = 0; l < n_layers; ++l) {
